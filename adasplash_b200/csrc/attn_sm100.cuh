@@ -1,0 +1,16 @@
+// Tensor-core (tcgen05 + TMEM + TMA) kernels of the AdaSplash-2 attention path.
+#pragma once
+#include "attn_simt.cuh"
+
+namespace ads {
+namespace sm100 {
+
+// fp16 / bf16 inputs with a head dim the kernels were built for.
+bool supported(const ads_attn_shape* s);
+size_t workspace_bytes(const ads_attn_shape* s);
+int solve(const simt::Params& p, int dtype, void* ws, cudaStream_t st);
+int fwd(const simt::Params& p, int dtype, void* ws, cudaStream_t st);
+int bwd(const simt::Params& p, int dtype, void* ws, cudaStream_t st);
+
+}  // namespace sm100
+}  // namespace ads

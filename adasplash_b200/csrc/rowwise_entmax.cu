@@ -1,0 +1,534 @@
+// Row-wise entmax forward / backward for sm_100a (HBM-bound).
+//
+// One group of TPR threads owns one row and keeps it in registers, so the row
+// is read from HBM exactly once and the result written once: 8 bytes per fp32
+// element forward, 12 backward.  Reductions are warp shuffles, plus one shared
+// memory hop when a row spans several warps.  Rows too long for registers use a
+// streaming variant that re-reads the row from L2/HBM.
+//
+// The threshold search follows adasplash/triton_entmax_v2.py:361-536 (4-bin
+// histogram lower bound, quadratic start on the bin-centre model, Halley /
+// Newton / secant / bisection refinement); the backward follows :539-617.
+#include "common.cuh"
+
+namespace ads {
+namespace {
+
+constexpr int kBins = 4;  // triton_entmax_v2.py:386
+
+struct Sum3 { float a, b, c; };
+
+template <int TPR>
+struct GroupReduce {
+  // smem: [2][CTA_WARPS][4] floats, double buffered by `phase`
+  float* smem;
+  int phase;
+  int group_warp0;  // first warp index of this group inside the CTA
+  __device__ GroupReduce(float* s) : smem(s), phase(0) {
+    group_warp0 = (threadIdx.x / TPR) * (TPR / 32);
+  }
+  template <typename Op>
+  __device__ __forceinline__ void reduce4(float v[4], Op op) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) v[i] = op(v[i], __shfl_xor_sync(0xffffffffu, v[i], o));
+    }
+    if constexpr (TPR > 32) {
+      const int warps_cta = blockDim.x / 32;
+      float* buf = smem + phase * warps_cta * 4;
+      int w = threadIdx.x / 32;
+      if ((threadIdx.x & 31) == 0) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) buf[w * 4 + i] = v[i];
+      }
+      __syncthreads();
+#pragma unroll
+      for (int i = 0; i < 4; ++i) v[i] = buf[group_warp0 * 4 + i];
+      for (int g = 1; g < TPR / 32; ++g) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) v[i] = op(v[i], buf[(group_warp0 + g) * 4 + i]);
+      }
+      phase ^= 1;
+    }
+  }
+};
+
+struct OpAdd { __device__ __forceinline__ float operator()(float a, float b) const { return a + b; } };
+struct OpMax { __device__ __forceinline__ float operator()(float a, float b) const { return fmaxf(a, b); } };
+
+__device__ __forceinline__ float masked_pow(float x, bool m, float c, int fast_math) {
+  // triton_entmax_v2.py:22-39
+  float r = fast_math ? __powf(x, c) : exp2f(log2f(fmaxf(x, 1e-6f)) * c);
+  return m ? r : 0.f;
+}
+
+__device__ __forceinline__ float f_hist(float tau, float t_shift, const float* raw) {
+  // bin-centre model sum_b c_b [centre_b - tau]_+^2 - 1 (triton_entmax_v2.py:164-204)
+  float acc = 0.f;
+#pragma unroll
+  for (int b = 0; b < kBins; ++b) {
+    float d = (t_shift + (b + 0.5f) / kBins) - tau;
+    float dp = d > 0.f ? d : 0.f;
+    acc += raw[b] * dp * dp;
+  }
+  return acc - 1.0f;
+}
+
+__device__ __forceinline__ float muller_init(float a, float c, float t_shift, const float* raw) {
+  // triton_entmax_v2.py:207-322
+  const float eps = 1e-10f;
+  float b = 0.5f * (a + c);
+  float fa = f_hist(a, t_shift, raw), fb = f_hist(b, t_shift, raw), fc = f_hist(c, t_shift, raw);
+  float denom = (a - b) * (a - c) * (b - c);
+  float mid = 0.5f * (a + c);
+  float A = (fa * (b - c) + fb * (c - a) + fc * (a - b)) / denom;
+  float B = (fa * (c * c - b * b) + fb * (a * a - c * c) + fc * (b * b - a * a)) / denom;
+  float C = (fa * b * c * (b - c) + fb * a * c * (c - a) + fc * a * b * (a - b)) / denom;
+  float x_lin = fabsf(B) > eps ? -C / B : mid;
+  float disc = B * B - 4.f * A * C;
+  float sq = sqrtf(fmaxf(disc, 0.f));
+  float r1 = (-B + sq) / (2.f * A), r2 = (-B - sq) / (2.f * A);
+  bool v1 = (r1 >= a) && (r1 <= c), v2 = (r2 >= a) && (r2 <= c);
+  float d1 = fabsf(c - r1), d2 = fabsf(c - r2);
+  float xq = (v1 && v2) ? (d1 <= d2 ? r1 : r2) : (v1 ? r1 : (v2 ? r2 : mid));
+  float sden = fc - fa;
+  float xs = fabsf(sden) > eps ? c - fc * (c - a) / sden : mid;
+  if (!(disc >= 0.f)) xq = xs;
+  float x = (fabsf(A) < eps) ? x_lin : xq;
+  if (fabsf(denom) < eps) x = mid;
+  return fminf(fmaxf(x, a), c);
+}
+
+struct Hybrid {
+  float t, lo, hi, t_prev, f_prev;
+};
+
+__device__ __forceinline__ void hybrid_update(Hybrid& s, float a0, float a1, float a2, float c0,
+                                              float c1, float alpha, bool allow_secant) {
+  // triton_entmax_v2.py:42-110
+  const float eps = 1e-6f, eps_den = 1e-12f;
+  float t = s.t;
+  float ff = a0 - 1.0f, df = -c0 * a1, ddf = c0 * c1 * a2;
+  if (ff > 0.f) s.lo = t;
+  if (ff < 0.f) s.hi = t;
+  bool has = false;
+  float cand = 0.f;
+  {
+    float den = 2.f * df * df - ff * ddf;
+    float th = t - (2.f * ff * df) / den;
+    bool ok = (th > s.lo - eps) && (th < s.hi + eps) && !isinf(th) && (fabsf(den) > eps_den) &&
+              (alpha <= 1.5f);
+    if (ok) { cand = th; has = true; }
+  }
+  if (!has) {
+    float tn = t - ff / df;
+    bool ok = (tn > s.lo - eps) && (tn < s.hi + eps) && !isinf(tn) && (fabsf(df) > eps_den) &&
+              (alpha <= 2.0f);
+    if (ok) { cand = tn; has = true; }
+  }
+  if (!has && allow_secant) {
+    float den = ff - s.f_prev;
+    float ts = t - ff * (t - s.t_prev) / den;
+    bool ok = (ts > s.lo - eps) && (ts < s.hi + eps) && !isinf(ts) && (fabsf(den) > eps_den);
+    if (ok) { cand = ts; has = true; }
+  }
+  s.t_prev = t;
+  s.f_prev = ff;
+  s.t = has ? cand : 0.5f * (s.lo + s.hi);
+}
+
+// ---------------------------------------------------------------------------
+// Row sources: where the (alpha-1)-scaled row elements come from.
+// ---------------------------------------------------------------------------
+template <typename T, int TPR, int NV, bool VEC>
+struct RegRow {
+  float v[NV * 4];
+  int cols, tl;
+  __device__ __forceinline__ int col_of(int c, int e) const {
+    return VEC ? (c * TPR + tl) * 4 + e : (c * 4 + e) * TPR + tl;
+  }
+  __device__ __forceinline__ void load(const T* row, int cols_, float sc) {
+    cols = cols_;
+    tl = threadIdx.x % TPR;
+#pragma unroll
+    for (int c = 0; c < NV; ++c) {
+      if constexpr (VEC) {
+        int c0 = (c * TPR + tl) * 4;
+        if (c0 < cols) {  // cols % 4 == 0 on this path
+          if constexpr (sizeof(T) == 4) {
+            float4 q = *reinterpret_cast<const float4*>(row + c0);
+            v[c * 4 + 0] = q.x * sc; v[c * 4 + 1] = q.y * sc;
+            v[c * 4 + 2] = q.z * sc; v[c * 4 + 3] = q.w * sc;
+          } else {
+            uint2 q = *reinterpret_cast<const uint2*>(row + c0);
+            const T* h = reinterpret_cast<const T*>(&q);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) v[c * 4 + e] = DT<T>::to_f(h[e]) * sc;
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) v[c * 4 + e] = -INFINITY;
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          int col = col_of(c, e);
+          v[c * 4 + e] = col < cols ? DT<T>::to_f(row[col]) * sc : -INFINITY;
+        }
+      }
+    }
+  }
+  template <typename F> __device__ __forceinline__ void for_each(F f) const {
+#pragma unroll
+    for (int i = 0; i < NV * 4; ++i) f(v[i]);
+  }
+  template <typename F> __device__ __forceinline__ void store(T* row, F f) const {
+#pragma unroll
+    for (int c = 0; c < NV; ++c) {
+      if constexpr (VEC) {
+        int c0 = (c * TPR + tl) * 4;
+        if (c0 < cols) {
+          if constexpr (sizeof(T) == 4) {
+            float4 q = make_float4(f(v[c * 4]), f(v[c * 4 + 1]), f(v[c * 4 + 2]), f(v[c * 4 + 3]));
+            *reinterpret_cast<float4*>(row + c0) = q;
+          } else {
+            uint2 q;
+            T* h = reinterpret_cast<T*>(&q);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) h[e] = DT<T>::from_f(f(v[c * 4 + e]));
+            *reinterpret_cast<uint2*>(row + c0) = q;
+          }
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          int col = col_of(c, e);
+          if (col < cols) row[col] = DT<T>::from_f(f(v[c * 4 + e]));
+        }
+      }
+    }
+  }
+};
+
+template <typename T, int TPR>
+struct StreamRow {  // re-reads the row from global memory on every pass
+  const T* row;
+  int cols, tl;
+  float sc;
+  __device__ __forceinline__ void load(const T* r, int cols_, float sc_) {
+    row = r; cols = cols_; sc = sc_; tl = threadIdx.x % TPR;
+  }
+  template <typename F> __device__ __forceinline__ void for_each(F f) const {
+    for (int c = tl; c < cols; c += TPR) f(DT<T>::to_f(row[c]) * sc);
+  }
+  template <typename F> __device__ __forceinline__ void store(T* out, F f) const {
+    for (int c = tl; c < cols; c += TPR) out[c] = DT<T>::from_f(f(DT<T>::to_f(row[c]) * sc));
+  }
+};
+
+template <typename T, int TPR, typename Row>
+__device__ __forceinline__ void entmax_fwd_row(Row& r, T* yrow, float* tau_out, long long row_idx,
+                                               bool row_ok, float alpha, int n_iter, int use_hist,
+                                               int fast_math, float* smem) {
+  GroupReduce<TPR> red(smem);
+  const int mode = (alpha == 1.5f) ? 0 : (alpha == 2.0f ? 1 : 2);
+  const float c0 = 1.0f / (alpha - 1.0f), c1 = c0 - 1.0f, c2 = c1 - 1.0f;
+  float red4[4];
+  // stage 1: maximum of the scaled row
+  float mx = -INFINITY;
+  r.for_each([&](float x) { mx = fmaxf(mx, x); });
+  red4[0] = mx; red4[1] = red4[2] = red4[3] = -INFINITY;
+  red.reduce4(red4, OpMax());
+  mx = red4[0];
+  Hybrid s;
+  if (use_hist && alpha <= 2.0f) {
+    // stage 2: 4-bin histogram of x - (max-1) on [0,1]; cumulative counts
+    // N_b = #{proj*4 >= b} give the same bins as floor(proj*4) clamped to 3.
+    float t_init = mx - 1.0f;
+    float n0 = 0.f, n1 = 0.f, n2 = 0.f, n3 = 0.f;
+    r.for_each([&](float x) {
+      float p4 = (x - t_init) * (float)kBins;
+      n0 += (p4 >= 0.f) ? 1.f : 0.f;
+      n1 += (p4 >= 1.f) ? 1.f : 0.f;
+      n2 += (p4 >= 2.f) ? 1.f : 0.f;
+      n3 += (p4 >= 3.f) ? 1.f : 0.f;
+    });
+    red4[0] = n0; red4[1] = n1; red4[2] = n2; red4[3] = n3;
+    red.reduce4(red4, OpAdd());
+    float raw[kBins] = {red4[0] - red4[1], red4[1] - red4[2], red4[2] - red4[3], red4[3]};
+    float t0;
+    if (mode == 0) {
+      int cnt[kBins] = {(int)raw[0], (int)raw[1], (int)raw[2], (int)raw[3]};
+      t0 = hist_tau_alpha15<kBins>(cnt, kBins, t_init);
+    } else {  // alpha == 2 (triton_entmax_v2.py:113-131)
+      float sz = 1.f, sk = 1.f;
+      for (int sj = kBins - 1; sj >= 0; --sj) {
+        float c = raw[sj] - (sj == kBins - 1 ? 1.f : 0.f);
+        float e = (float)sj / kBins;
+        float nz = sz + c * e, nk = sk + c;
+        if ((nz - nk * e) < 1.0f) { sz = nz; sk = nk; }
+      }
+      t0 = t_init + (sz - 1.0f) / sk;
+    }
+    s.lo = t0;
+    s.hi = t0 + 1.0f / kBins;
+    s.t = muller_init(s.lo, s.hi, t_init, raw);
+  } else {
+    s.hi = mx;
+    s.lo = mx - 1.0f;
+    s.t = 0.5f * (s.lo + s.hi);
+  }
+  s.t_prev = s.t;
+  s.f_prev = 0.f;
+  // stage 3: refinement
+  for (int it = 0; it < n_iter; ++it) {
+    float a0 = 0.f, a1 = 0.f, a2 = 0.f;
+    const float t = s.t;
+    if (mode == 1) {
+      r.for_each([&](float x) { bool m = x > t; a0 += m ? (x - t) : 0.f; a1 += m ? 1.f : 0.f; });
+    } else if (mode == 0) {
+      r.for_each([&](float x) {
+        bool m = x > t;
+        float u = m ? (x - t) : 0.f;
+        a0 = fmaf(u, u, a0); a1 += u; a2 += m ? 1.f : 0.f;
+      });
+    } else {
+      r.for_each([&](float x) {
+        bool m = x > t;
+        float u = fmaxf(x - t, 0.f);
+        a0 += masked_pow(u, m, c0, fast_math);
+        a1 += masked_pow(u, m, c1, fast_math);
+        a2 += masked_pow(u, m, c2, fast_math);
+      });
+    }
+    red4[0] = a0; red4[1] = a1; red4[2] = a2; red4[3] = 0.f;
+    red.reduce4(red4, OpAdd());
+    hybrid_update(s, red4[0], red4[1], red4[2], c0, c1, alpha, it > 0);
+  }
+  // stage 4: output
+  const float t = s.t;
+  if (row_ok) {
+    if (mode == 1) {
+      r.store(yrow, [&](float x) { return x > t ? x - t : 0.f; });
+    } else if (mode == 0) {
+      r.store(yrow, [&](float x) { float u = x > t ? x - t : 0.f; return u * u; });
+    } else {
+      r.store(yrow, [&](float x) { return masked_pow(fmaxf(x - t, 0.f), x > t, c0, fast_math); });
+    }
+    if (tau_out != nullptr && (threadIdx.x % TPR) == 0) tau_out[row_idx] = t;
+  }
+}
+
+template <typename T, int TPR, int NV, bool VEC>
+__global__ void __launch_bounds__((TPR > 128 ? TPR : 128))
+entmax_fwd_reg_kernel(const T* __restrict__ x, T* __restrict__ y, float* __restrict__ tau_out,
+                      long long rows, int cols, float alpha, int n_iter, int use_hist,
+                      int fast_math) {
+  __shared__ float smem[2 * 32 * 4];
+  const int rows_per_cta = blockDim.x / TPR;
+  long long row = (long long)blockIdx.x * rows_per_cta + threadIdx.x / TPR;
+  bool ok = row < rows;
+  long long rr = ok ? row : rows - 1;
+  RegRow<T, TPR, NV, VEC> r;
+  r.load(x + rr * cols, cols, alpha - 1.0f);
+  entmax_fwd_row<T, TPR>(r, y + rr * cols, tau_out, rr, ok, alpha, n_iter, use_hist, fast_math, smem);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(1024)
+entmax_fwd_stream_kernel(const T* __restrict__ x, T* __restrict__ y, float* __restrict__ tau_out,
+                         long long rows, int cols, float alpha, int n_iter, int use_hist,
+                         int fast_math) {
+  __shared__ float smem[2 * 32 * 4];
+  long long row = blockIdx.x;
+  StreamRow<T, 1024> r;
+  r.load(x + row * cols, cols, alpha - 1.0f);
+  entmax_fwd_row<T, 1024>(r, y + row * cols, tau_out, row, true, alpha, n_iter, use_hist, fast_math, smem);
+}
+
+// ---------------------------------------------------------------------------
+// backward
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ float bwd_u(float y, float alpha, int mode, int fast_math) {
+  bool m = y > 0.f;
+  if (mode == 1) return m ? 1.f : 0.f;
+  if (mode == 0) return m ? sqrtf(y) : 0.f;
+  return masked_pow(y, m, 2.0f - alpha, fast_math);
+}
+
+template <typename T, int TPR, int NV, bool VEC>
+__global__ void __launch_bounds__((TPR > 128 ? TPR : 128))
+entmax_bwd_reg_kernel(const T* __restrict__ y, const T* __restrict__ dy, T* __restrict__ dx,
+                      long long rows, int cols, float alpha, int fast_math) {
+  __shared__ float smem[2 * 32 * 4];
+  const int rows_per_cta = blockDim.x / TPR;
+  long long row = (long long)blockIdx.x * rows_per_cta + threadIdx.x / TPR;
+  bool ok = row < rows;
+  long long rr = ok ? row : rows - 1;
+  const int mode = (alpha == 1.5f) ? 0 : (alpha == 2.0f ? 1 : 2);
+  RegRow<T, TPR, NV, VEC> ry, rdy;
+  ry.load(y + rr * cols, cols, 1.0f);
+  rdy.load(dy + rr * cols, cols, 1.0f);
+  float su = 0.f, sud = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV * 4; ++i) {
+    // out-of-range slots hold -inf in both rows: y > 0 is false there, u = 0
+    float u = bwd_u(ry.v[i], alpha, mode, fast_math);
+    ry.v[i] = u;
+    float d = (u != 0.f) ? rdy.v[i] : 0.f;
+    rdy.v[i] = d;
+    su += u;
+    sud = fmaf(u, d, sud);
+  }
+  GroupReduce<TPR> red(smem);
+  float red4[4] = {su, sud, 0.f, 0.f};
+  red.reduce4(red4, OpAdd());
+  float scalar = red4[1] / red4[0];
+  if (ok) {
+    // grad = u*dy - scalar*u (triton_entmax_v2.py:616)
+#pragma unroll
+    for (int i = 0; i < NV * 4; ++i) rdy.v[i] = ry.v[i] * rdy.v[i] - scalar * ry.v[i];
+    rdy.store(dx + rr * cols, [](float g) { return g; });
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(1024)
+entmax_bwd_stream_kernel(const T* __restrict__ y, const T* __restrict__ dy, T* __restrict__ dx,
+                         long long rows, int cols, float alpha, int fast_math) {
+  __shared__ float smem[2 * 32 * 4];
+  long long row = blockIdx.x;
+  const int mode = (alpha == 1.5f) ? 0 : (alpha == 2.0f ? 1 : 2);
+  const T* yr = y + row * cols;
+  const T* dr = dy + row * cols;
+  float su = 0.f, sud = 0.f;
+  for (int c = threadIdx.x; c < cols; c += 1024) {
+    float u = bwd_u(DT<T>::to_f(yr[c]), alpha, mode, fast_math);
+    su += u;
+    sud = fmaf(u, DT<T>::to_f(dr[c]), sud);
+  }
+  GroupReduce<1024> red(smem);
+  float red4[4] = {su, sud, 0.f, 0.f};
+  red.reduce4(red4, OpAdd());
+  float scalar = red4[1] / red4[0];
+  T* xr = dx + row * cols;
+  for (int c = threadIdx.x; c < cols; c += 1024) {
+    float u = bwd_u(DT<T>::to_f(yr[c]), alpha, mode, fast_math);
+    xr[c] = DT<T>::from_f(u * DT<T>::to_f(dr[c]) - scalar * u);
+  }
+}
+
+template <typename T, int TPR, int NV>
+int launch_fwd_cfg(const T* x, T* y, float* tau, long long rows, int cols, float alpha, int n_iter,
+                   int use_hist, int fast_math, bool vec, cudaStream_t st) {
+  const int threads = TPR > 128 ? TPR : 128;
+  const int rpc = threads / TPR;
+  unsigned grid = (unsigned)((rows + rpc - 1) / rpc);
+  if (vec)
+    entmax_fwd_reg_kernel<T, TPR, NV, true><<<grid, threads, 0, st>>>(x, y, tau, rows, cols, alpha, n_iter, use_hist, fast_math);
+  else
+    entmax_fwd_reg_kernel<T, TPR, NV, false><<<grid, threads, 0, st>>>(x, y, tau, rows, cols, alpha, n_iter, use_hist, fast_math);
+  return check_launch("entmax_fwd");
+}
+
+template <typename T>
+int launch_fwd(const void* xv, void* yv, float* tau, long long rows, long long cols, float alpha,
+               int n_iter, int use_hist, int fast_math, cudaStream_t st) {
+  const T* x = (const T*)xv;
+  T* y = (T*)yv;
+  const size_t vec_bytes = 4 * sizeof(T);
+  bool vec = (cols % 4 == 0) && ((uintptr_t)x % vec_bytes == 0) && ((uintptr_t)y % vec_bytes == 0);
+  int c = (int)cols;
+#define ADS_FWD(TPR, NV) return launch_fwd_cfg<T, TPR, NV>(x, y, tau, rows, c, alpha, n_iter, use_hist, fast_math, vec, st)
+  if (cols <= 128) ADS_FWD(32, 1);
+  if (cols <= 512) ADS_FWD(32, 4);
+  if (cols <= 1024) ADS_FWD(32, 8);
+  if (cols <= 2048) ADS_FWD(64, 8);
+  if (cols <= 4096) ADS_FWD(128, 8);
+  if (cols <= 8192) ADS_FWD(256, 8);
+  if (cols <= 16384) ADS_FWD(512, 8);
+  if (cols <= 32768) ADS_FWD(1024, 8);
+#undef ADS_FWD
+  entmax_fwd_stream_kernel<T><<<(unsigned)rows, 1024, 0, st>>>(x, y, tau, rows, c, alpha, n_iter, use_hist, fast_math);
+  return check_launch("entmax_fwd_stream");
+}
+
+template <typename T, int TPR, int NV>
+int launch_bwd_cfg(const T* y, const T* dy, T* dx, long long rows, int cols, float alpha,
+                   int fast_math, bool vec, cudaStream_t st) {
+  const int threads = TPR > 128 ? TPR : 128;
+  const int rpc = threads / TPR;
+  unsigned grid = (unsigned)((rows + rpc - 1) / rpc);
+  if (vec)
+    entmax_bwd_reg_kernel<T, TPR, NV, true><<<grid, threads, 0, st>>>(y, dy, dx, rows, cols, alpha, fast_math);
+  else
+    entmax_bwd_reg_kernel<T, TPR, NV, false><<<grid, threads, 0, st>>>(y, dy, dx, rows, cols, alpha, fast_math);
+  return check_launch("entmax_bwd");
+}
+
+template <typename T>
+int launch_bwd(const void* yv, const void* dyv, void* dxv, long long rows, long long cols,
+               float alpha, int fast_math, cudaStream_t st) {
+  const T* y = (const T*)yv;
+  const T* dy = (const T*)dyv;
+  T* dx = (T*)dxv;
+  const size_t vb = 4 * sizeof(T);
+  bool vec = (cols % 4 == 0) && ((uintptr_t)y % vb == 0) && ((uintptr_t)dy % vb == 0) && ((uintptr_t)dx % vb == 0);
+  int c = (int)cols;
+#define ADS_BWD(TPR, NV) return launch_bwd_cfg<T, TPR, NV>(y, dy, dx, rows, c, alpha, fast_math, vec, st)
+  if (cols <= 128) ADS_BWD(32, 1);
+  if (cols <= 512) ADS_BWD(32, 4);
+  if (cols <= 1024) ADS_BWD(64, 4);
+  if (cols <= 2048) ADS_BWD(128, 4);
+  if (cols <= 4096) ADS_BWD(256, 4);
+  if (cols <= 8192) ADS_BWD(512, 4);
+  if (cols <= 16384) ADS_BWD(1024, 4);
+#undef ADS_BWD
+  entmax_bwd_stream_kernel<T><<<(unsigned)rows, 1024, 0, st>>>(y, dy, dx, rows, c, alpha, fast_math);
+  return check_launch("entmax_bwd_stream");
+}
+
+}  // namespace
+}  // namespace ads
+
+extern "C" int adasplash_entmax_fwd(const void* x, void* y, float* tau_out, int64_t rows,
+                                    int64_t cols, float alpha, int32_t n_iter,
+                                    int32_t use_histogram, int32_t fast_math, int32_t dtype,
+                                    void* stream) {
+  using namespace ads;
+  if (rows < 0 || cols < 0 || !(alpha > 1.0f) || n_iter < 0) {
+    set_error("entmax_fwd: bad argument (rows=%lld cols=%lld alpha=%f n_iter=%d)", (long long)rows,
+              (long long)cols, alpha, n_iter);
+    return ADS_ERR_BAD_ARG;
+  }
+  if (rows == 0 || cols == 0) return ADS_OK;
+  if (x == nullptr || y == nullptr) { set_error("entmax_fwd: null pointer"); return ADS_ERR_BAD_ARG; }
+  if (cols > 0x7fffffffLL || rows > 0x7fffffffLL) { set_error("entmax_fwd: size too large"); return ADS_ERR_UNSUPPORTED; }
+  cudaStream_t st = (cudaStream_t)stream;
+  switch (dtype) {
+    case ADS_F32: return launch_fwd<float>(x, y, tau_out, rows, cols, alpha, n_iter, use_histogram, fast_math, st);
+    case ADS_F16: return launch_fwd<__half>(x, y, tau_out, rows, cols, alpha, n_iter, use_histogram, fast_math, st);
+    case ADS_BF16: return launch_fwd<__nv_bfloat16>(x, y, tau_out, rows, cols, alpha, n_iter, use_histogram, fast_math, st);
+  }
+  set_error("entmax_fwd: unknown dtype %d", dtype);
+  return ADS_ERR_BAD_ARG;
+}
+
+extern "C" int adasplash_entmax_bwd(const void* y, const void* dy, void* dx, int64_t rows,
+                                    int64_t cols, float alpha, int32_t fast_math, int32_t dtype,
+                                    void* stream) {
+  using namespace ads;
+  if (rows < 0 || cols < 0 || !(alpha > 1.0f)) { set_error("entmax_bwd: bad argument"); return ADS_ERR_BAD_ARG; }
+  if (rows == 0 || cols == 0) return ADS_OK;
+  if (y == nullptr || dy == nullptr || dx == nullptr) { set_error("entmax_bwd: null pointer"); return ADS_ERR_BAD_ARG; }
+  if (cols > 0x7fffffffLL || rows > 0x7fffffffLL) { set_error("entmax_bwd: size too large"); return ADS_ERR_UNSUPPORTED; }
+  cudaStream_t st = (cudaStream_t)stream;
+  switch (dtype) {
+    case ADS_F32: return launch_bwd<float>(y, dy, dx, rows, cols, alpha, fast_math, st);
+    case ADS_F16: return launch_bwd<__half>(y, dy, dx, rows, cols, alpha, fast_math, st);
+    case ADS_BF16: return launch_bwd<__nv_bfloat16>(y, dy, dx, rows, cols, alpha, fast_math, st);
+  }
+  set_error("entmax_bwd: unknown dtype %d", dtype);
+  return ADS_ERR_BAD_ARG;
+}

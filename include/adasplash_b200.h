@@ -1,0 +1,128 @@
+/*
+ * C ABI of the B200 (sm_100a) sparse entmax attention library.
+ *
+ * Every entry point takes raw device pointers, sizes and a CUDA stream
+ * (`void* stream` is a `cudaStream_t`), launches asynchronously on that stream,
+ * never synchronises the host, and -- unless its comment says otherwise --
+ * never allocates or frees memory: the caller owns every buffer, including
+ * scratch.  Return value: 0 on success, otherwise an `ads_status` code; the
+ * message of the last failure on the calling thread is returned by
+ * `adasplash_last_error_string()`.
+ *
+ * The comments cite the interface of deep-spin/adasplash that each entry point
+ * replaces (file:line inside that project).
+ */
+#ifndef ADASPLASH_B200_H_
+#define ADASPLASH_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum { ADS_F32 = 0, ADS_F16 = 1, ADS_BF16 = 2 } ads_dtype;
+
+typedef enum {
+  ADS_OK = 0,
+  ADS_ERR_BAD_ARG = 1,      /* null pointer, negative size, bad enum            */
+  ADS_ERR_UNSUPPORTED = 2,  /* head dim / dtype / size outside the built range  */
+  ADS_ERR_WORKSPACE = 3,    /* scratch buffer missing or too small              */
+  ADS_ERR_CUDA = 4,         /* a CUDA runtime / driver call failed              */
+  ADS_ERR_TIMEOUT = 5       /* a bounded device-side wait gave up (status word) */
+} ads_status;
+
+/* Kernel family selection for the attention entry points. */
+enum {
+  ADS_PATH_AUTO = 0,   /* tcgen05/TMA kernels when dtype/head-dim allow, else SIMT */
+  ADS_PATH_SIMT = 1,   /* fp32-accumulating CUDA-core kernels (any dtype, any D)   */
+  ADS_PATH_TCGEN05 = 2 /* tensor-core kernels only; error if not applicable        */
+};
+
+/* Shape of one attention problem.  q is (B,Hq,N,D) contiguous, k and v are
+ * (B,Hkv,N,D) contiguous, Hq % Hkv == 0, D in {16,32,64,128,256}, N >= 64
+ * (adasplash/adasplash_v2.py:1245-1276).  `varlen` is NULL or B lengths
+ * (int32, or int64 when varlen_is_i64 != 0) on the device. */
+typedef struct {
+  int32_t B, Hq, Hkv, N, D;
+  int32_t dtype;          /* ads_dtype of q,k,v,out,dout,dq,dk,dv            */
+  int32_t niter;          /* Halley refinements after the histogram start     */
+  int32_t varlen_is_i64;
+  int32_t path;           /* ADS_PATH_*                                       */
+} ads_attn_shape;
+
+/* Row-wise entmax forward over the last dimension of a contiguous
+ * (rows, cols) matrix.  Replaces `_entmax_triton.forward` / `_fwd_entmax`
+ * (adasplash/triton_entmax_v2.py:361-536, :623-664).  alpha > 1; the caller
+ * applies the wrapper rule of triton_entmax_v2.py:713-715 (alpha not in
+ * {1.5, 2} => no histogram, n_iter >= 10).  `tau_out` may be NULL; if not, it
+ * receives the final threshold of each row (fp32, rows entries). */
+int adasplash_entmax_fwd(const void* x, void* y, float* tau_out, int64_t rows, int64_t cols,
+                         float alpha, int32_t n_iter, int32_t use_histogram, int32_t fast_math,
+                         int32_t dtype, void* stream);
+
+/* Row-wise entmax backward: dx = u*(dy - sum(u dy)/sum(u)), u = y^(2-alpha) on
+ * the support.  Replaces `_bwd_entmax` (adasplash/triton_entmax_v2.py:539-617). */
+int adasplash_entmax_bwd(const void* y, const void* dy, void* dx, int64_t rows, int64_t cols,
+                         float alpha, int32_t fast_math, int32_t dtype, void* stream);
+
+/* Bytes of scratch the attention entry points need for `shape` (forward and
+ * backward use the same buffer; 256-byte aligned base expected). */
+size_t adasplash2_workspace_bytes(const ads_attn_shape* shape);
+
+/* Number of int32 words of one bitmap tensor (B,Hq,rows_padded,n_words) and its
+ * two inner extents, in the layout of adasplash/adasplash_v2.py:1345-1350:
+ * rows_padded = max(32, ceil32(ceil(N/64))), n_words = ceil(ceil(N/64)/32);
+ * bit j of word w of row m <=> the 64x64 tile (q-tile m, k-tile 32w+j). */
+int64_t adasplash2_bitmap_words(const ads_attn_shape* shape, int32_t* rows_padded,
+                                int32_t* n_words);
+
+/* Threshold solver + block-mask builder.  Replaces the launches of `_get_tau`,
+ * `_get_tau_v2` and `_get_tau_v3` (adasplash/adasplash_v2.py:1287-1379).
+ * Writes taus (B,Hq,N) fp32 and bmask (int32, zero-filled by this call).  The
+ * bitmap is taken at the tau entering the last refinement sweep, as the
+ * reference does (adasplash_v2.py:618-681). */
+int adasplash2_solve(const void* q, const void* k, const void* varlen, float* taus,
+                     int32_t* bmask, const ads_attn_shape* shape, void* workspace,
+                     size_t workspace_bytes, void* stream);
+
+/* Block-mask builder alone: bit(m,n) = any(z > taus) on each valid 64x64 tile,
+ * for thresholds supplied by the caller.  No reference entry point does only
+ * this (it is the bitmap half of `_get_tau_v3`, adasplash_v2.py:618-674); it
+ * exists so that bitmaps can be compared for identical fp32 taus. */
+int adasplash2_mask_from_tau(const void* q, const void* k, const void* varlen,
+                             const float* taus, int32_t* bmask, const ads_attn_shape* shape,
+                             void* workspace, size_t workspace_bytes, void* stream);
+
+/* Sparse forward.  Replaces `_get_output` (adasplash/adasplash_v2.py:696-835,
+ * launch at :1391-1419).  out and out2 have q's shape and dtype; rows at or
+ * beyond varlen[b] are written as zero by this call. */
+int adasplash2_fwd(const void* q, const void* k, const void* v, const void* varlen,
+                   const float* taus, const int32_t* bmask, void* out, void* out2,
+                   const ads_attn_shape* shape, void* workspace, size_t workspace_bytes,
+                   void* stream);
+
+/* Backward.  Replaces `_bwd_preprocess`, `_bwd_q_kernel`, `transpose_bmask` and
+ * `_bwd_kv_kernel` (adasplash/adasplash_v2.py:1441-1564).  `delta` (B,Hq,N fp32)
+ * and `bmask_t` (same extent as bmask) are caller-owned scratch outputs.
+ * dq (B,Hq,N,D), dk, dv (B,Hkv,N,D) in the input dtype; padded rows are zero. */
+int adasplash2_bwd(const void* q, const void* k, const void* v, const void* dout,
+                   const void* out2, const void* varlen, const float* taus,
+                   const int32_t* bmask, int32_t* bmask_t, float* delta, void* dq, void* dk,
+                   void* dv, const ads_attn_shape* shape, void* workspace,
+                   size_t workspace_bytes, void* stream);
+
+/* Which kernel family `ADS_PATH_AUTO` resolves to for `shape`
+ * (ADS_PATH_SIMT or ADS_PATH_TCGEN05). */
+int adasplash2_resolved_path(const ads_attn_shape* shape);
+
+/* Number of kernels launched by this library since it was loaded (all threads). */
+int64_t adasplash_launch_count(void);
+
+const char* adasplash_last_error_string(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ADASPLASH_B200_H_ */

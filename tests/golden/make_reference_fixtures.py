@@ -1,0 +1,204 @@
+"""Generate the golden fixtures in this folder by running the reference itself.
+
+The reference (deep-spin/adasplash) is Triton code and needs a GPU, so this
+script is run once on a B200 box with the unmodified reference installed under
+baseline/_ref (``python -m pip install --no-index --no-build-isolation --no-deps
+--target baseline/_ref <reference checkout>``; that folder is git-ignored):
+
+    python tests/golden/make_reference_fixtures.py --out tests/golden [--time]
+
+Inputs are drawn from seeded CPU generators and stored with the outputs, so the
+tests never need the reference.  ``--time`` additionally times the reference's
+kernels (CUDA events, median of 20 after warm-up) and writes
+``reference_timings.json``.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def _gen(shape, seed, scale=1.0, dtype=torch.float32):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * scale).to(dtype)
+
+
+ATTN_CASES = {
+    # name: (B, Hq, Hkv, N, D, dtype, input scale, niter, varlen)
+    "v2_fp32_smoke": (1, 2, 2, 256, 32, torch.float32, 1.0, 10, None),
+    "v2_fp32_gqa_varlen": (1, 2, 1, 256, 64, torch.float32, 1.0, 10, [160]),
+    "v2_fp32_niter1": (1, 2, 2, 512, 64, torch.float32, 1.0, 1, None),
+    "v2_bf16_d128": (1, 2, 1, 512, 128, torch.bfloat16, 1.5, 1, None),
+    "v2_bf16_varlen": (2, 2, 2, 256, 64, torch.bfloat16, 1.0, 1, [200, 256]),
+    "v2_fp16_d64": (1, 1, 1, 256, 64, torch.float16, 1.0, 1, None),
+    "v2_bf16_d128_n2048": (1, 1, 1, 2048, 128, torch.bfloat16, 1.5, 1, None),
+}
+
+V1_CASES = {
+    # name: (alpha, is_causal)
+    "v1_a1333_causal": (1.333, True), "v1_a1333_full": (1.333, False),
+    "v1_a15_full": (1.5, False), "v1_a2_causal": (2.0, True), "v1_a2_full": (2.0, False),
+}
+
+
+def make_attention(adasplash, out_dir):
+    for idx, (name, (B, Hq, Hkv, N, D, dt, sc, niter, vl)) in enumerate(ATTN_CASES.items()):
+        seed = 1000 + idx
+        q = _gen((B, Hq, N, D), seed, sc, dt)
+        k = _gen((B, Hkv, N, D), seed + 100, sc, dt)
+        v = _gen((B, Hkv, N, D), seed + 200, sc, dt)
+        do = _gen((B, Hq, N, D), seed + 300, 1.0, dt)
+        varlen = None if vl is None else torch.tensor(vl, dtype=torch.int32)
+        if varlen is not None:
+            rows = torch.arange(N)[None, None, :, None] < varlen[:, None, None, None]
+            do = do * rows
+        qc, kc, vc = (t.cuda().requires_grad_(True) for t in (q, k, v))
+        out = adasplash.adasplash_v2(qc, kc, vc, niter=niter,
+                                     varlen=None if varlen is None else varlen.cuda())
+        saved = out.grad_fn.saved_tensors
+        out2, taus, bmask = saved[3], saved[4], saved[5]
+        dq, dk, dv = torch.autograd.grad(out, (qc, kc, vc), do.cuda())
+        fx = {"q": q, "k": k, "v": v, "dout": do, "varlen": varlen, "niter": niter,
+              "out": out.detach().cpu(), "out2": out2.cpu(), "taus": taus.cpu(),
+              "bmask": bmask.cpu(), "dq": dq.cpu(), "dk": dk.cpu(), "dv": dv.cpu()}
+        if name.endswith("n2048"):  # keep the file small: inputs are regenerated from the seed
+            for key in ("q", "k", "v", "dout"):
+                fx[key] = None
+            fx["seed"] = seed
+            fx["scale"] = sc
+            for key in ("out", "out2", "dq", "dk", "dv"):
+                fx[key] = fx[key][:, :, ::8].contiguous()
+            fx["row_stride"] = 8
+        torch.save(fx, os.path.join(out_dir, name + ".pt"))
+        print("wrote", name, flush=True)
+
+
+def make_v1(adasplash, out_dir):
+    B, H, N, D = 1, 2, 128, 32
+    for idx, (name, (alpha, causal)) in enumerate(V1_CASES.items()):
+        seed = 2000 + idx
+        q, k, v = (_gen((B, H, N, D), seed + 100 * i) for i in range(3))
+        do = _gen((B, H, N, D), seed + 300)
+        qc, kc, vc = (t.cuda().requires_grad_(True) for t in (q, k, v))
+        out = adasplash.adasplash(qc, kc, vc, alpha=alpha, is_causal=causal, niter=10)
+        dq, dk, dv = torch.autograd.grad(out, (qc, kc, vc), do.cuda())
+        torch.save({"q": q, "k": k, "v": v, "dout": do, "alpha": alpha, "is_causal": causal,
+                    "out": out.detach().cpu(), "dq": dq.cpu(), "dk": dk.cpu(), "dv": dv.cpu()},
+                   os.path.join(out_dir, name + ".pt"))
+        print("wrote", name, flush=True)
+
+
+def make_rowwise(adasplash, out_dir):
+    fx = {}
+    x = _gen((16, 4096), 3000, 4.0)
+    dy = _gen((16, 4096), 3001)
+    fx["x"], fx["dy"] = x, dy
+    for tag, kw in (("a15_hist", dict(alpha=1.5, n_iter=2, use_histogram=True)),
+                    ("a2_default", dict(alpha=2.0)),
+                    ("a1333", dict(alpha=1.333, use_histogram=False)),
+                    ("a15_nohist_it10", dict(alpha=1.5, n_iter=10, use_histogram=False))):
+        xc = x.cuda().requires_grad_(True)
+        y = adasplash.triton_entmax(xc, **kw)
+        (dx,) = torch.autograd.grad(y, xc, dy.cuda())
+        fx[tag] = {"kwargs": kw, "y": y.detach().cpu(), "dx": dx.cpu()}
+    xs = _gen((4, 8, 100), 3002, 2.0, torch.float16)
+    dys = _gen((4, 8, 100), 3003, 1.0, torch.float16)
+    fx["x_small_f16"], fx["dy_small_f16"] = xs, dys
+    for tag, kw in (("small_a15", dict(alpha=1.5)), ("small_a2", dict(alpha=2.0)),
+                    ("small_a1333", dict(alpha=1.333))):
+        xc = xs.cuda().requires_grad_(True)
+        y = adasplash.triton_entmax(xc, **kw)
+        (dx,) = torch.autograd.grad(y, xc, dys.cuda())
+        fx[tag] = {"kwargs": kw, "y": y.detach().cpu(), "dx": dx.cpu()}
+    torch.save(fx, os.path.join(out_dir, "rowwise.pt"))
+    print("wrote rowwise", flush=True)
+
+
+def _time(fn, reps=20, warm=3):
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(reps):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        ts.append(a.elapsed_time(b))
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def time_reference(adasplash, out_dir, big):
+    res = {"device": torch.cuda.get_device_name(0), "torch": torch.__version__}
+    import triton
+    res["triton"] = triton.__version__
+    # row-wise, 16384 x 4096 fp32
+    x = (torch.randn(16384, 4096, device="cuda") * 4).requires_grad_(True)
+    dy = torch.randn(16384, 4096, device="cuda")
+    for tag, kw in (("a15_hist", dict(alpha=1.5, n_iter=2, use_histogram=True)),
+                    ("a2_default", dict(alpha=2.0)), ("a1333", dict(alpha=1.333, use_histogram=False))):
+        y = adasplash.triton_entmax(x, **kw)
+        res["rowwise_fwd_ms_" + tag] = _time(lambda: adasplash.triton_entmax(x, **kw))
+        res["rowwise_bwd_ms_" + tag] = _time(lambda: torch.autograd.grad(y, x, dy, retain_graph=True))
+        print(tag, res["rowwise_fwd_ms_" + tag], res["rowwise_bwd_ms_" + tag], flush=True)
+    del x, dy, y
+    cfgs = {"B1_H8_N4096_D128": (1, 8, 8, 4096, 128, 1.5, 10)}
+    if big:
+        cfgs["C3_B4_H32_N8192_D128"] = (4, 32, 32, 8192, 128, 1.5, 5)
+    for tag, (B, Hq, Hkv, N, D, sc, reps) in cfgs.items():
+        q = (torch.randn(B, Hq, N, D, device="cuda") * sc).bfloat16().requires_grad_(True)
+        k = (torch.randn(B, Hkv, N, D, device="cuda") * sc).bfloat16().requires_grad_(True)
+        v = (torch.randn(B, Hkv, N, D, device="cuda") * sc).bfloat16().requires_grad_(True)
+        do = torch.randn(B, Hq, N, D, device="cuda").bfloat16()
+        t0 = time.time()
+        out = adasplash.adasplash_v2(q, k, v, niter=1)
+        torch.autograd.grad(out, (q, k, v), do)
+        torch.cuda.synchronize()
+        res[tag + "_first_call_s"] = time.time() - t0
+        res[tag + "_fwd_ms"] = _time(lambda: adasplash.adasplash_v2(q, k, v, niter=1), reps)
+
+        def fb():
+            o = adasplash.adasplash_v2(q, k, v, niter=1)
+            torch.autograd.grad(o, (q, k, v), do)
+        res[tag + "_fwdbwd_ms"] = _time(fb, reps)
+        bm = out.grad_fn.saved_tensors[5]
+        nb = N // 64
+        active = sum(bin(int(w) & 0xFFFFFFFF).count("1") for w in bm[0, 0].flatten().tolist())
+        res[tag + "_block_sparsity_head0"] = 1.0 - active / (nb * (nb + 1) / 2)
+        print(tag, res[tag + "_fwd_ms"], res[tag + "_fwdbwd_ms"], flush=True)
+        del q, k, v, do, out
+    with open(os.path.join(out_dir, "reference_timings.json"), "w") as f:
+        json.dump(res, f, indent=1)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--out", default=os.path.join(ROOT, "tests", "golden"))
+    ap.add_argument("--ref", default=os.path.join(ROOT, "baseline", "_ref"))
+    ap.add_argument("--time", action="store_true")
+    ap.add_argument("--big", action="store_true", help="also time the B=4,H=32,N=8192 config")
+    ap.add_argument("--skip-fixtures", action="store_true")
+    a = ap.parse_args()
+    sys.path.insert(0, a.ref)
+    import adasplash
+    assert os.path.abspath(adasplash.__file__).startswith(os.path.abspath(a.ref)), adasplash.__file__
+    os.makedirs(a.out, exist_ok=True)
+    if not a.skip_fixtures:
+        make_rowwise(adasplash, a.out)
+        make_attention(adasplash, a.out)
+        make_v1(adasplash, a.out)
+    if a.time:
+        time_reference(adasplash, a.out, a.big)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,205 @@
+"""GPU parity of the AdaSplash-2 attention path (through the C ABI) against
+the CPU oracle, the exact dense definition and the reference's golden outputs.
+
+Tolerances: fp32 1e-4 on out/dq/dk/dv and tau (the reference's own test
+tolerance, tests/test_adasplash_v2.py:94-97); bf16/fp16 max-abs 2e-2 on outputs
+and gradients against the reference; bitmaps bit-exact for identical fp32 tau.
+"""
+import os
+
+import pytest
+import torch
+
+import adasplash_b200 as adasplash
+from adasplash_b200 import _lib, attention as att
+from oracle import entmax_oracle as O
+
+pytestmark = pytest.mark.gpu
+GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+PATHS = ["simt", "tcgen05"]
+
+
+def _randn(shape, seed, scale=1.0, dtype=torch.float32):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * scale).to(dtype)
+
+
+@pytest.fixture(autouse=True)
+def _reset_path():
+    yield
+    _lib.set_kernel_path(None)
+
+
+def _use(path, q):
+    """Select a kernel family; skip if it does not cover this dtype / head dim."""
+    _lib.set_kernel_path(path)
+    if path == "tcgen05":
+        import ctypes
+        sh = att.make_shape(q, q, 1, None)
+        if _lib.load().adasplash2_resolved_path(ctypes.byref(sh)) != _lib.PATH_TCGEN05:
+            pytest.skip("tensor-core kernels do not cover this dtype/head dim")
+
+
+def _run(q, k, v, do, niter, varlen):
+    qc, kc, vc = (t.cuda().requires_grad_(True) for t in (q, k, v))
+    vl = None if varlen is None else varlen.cuda()
+    out = adasplash.adasplash_v2(qc, kc, vc, niter=niter, varlen=vl)
+    saved = out.grad_fn.saved_tensors
+    dq, dk, dv = torch.autograd.grad(out, (qc, kc, vc), do.cuda())
+    return {"out": out.detach().float().cpu(), "out2": saved[3].float().cpu(), "tau": saved[4].cpu(),
+            "bmask": saved[5].cpu(), "dq": dq.float().cpu(), "dk": dk.float().cpu(),
+            "dv": dv.float().cpu()}
+
+
+def _mask_rows(do, varlen):
+    if varlen is None:
+        return do
+    N = do.shape[2]
+    return do * (torch.arange(N)[None, None, :, None] < varlen[:, None, None, None])
+
+
+CASES_FP32 = [
+    # B, Hq, Hkv, N, D, varlen
+    (1, 1, 1, 256, 32, None), (2, 2, 2, 128, 64, None), (1, 2, 1, 256, 32, [160]),
+    (2, 4, 2, 192, 16, [65, 130]), (1, 2, 2, 64, 128, None), (1, 1, 1, 128, 256, None),
+    (2, 2, 1, 200, 64, [200, 64]), (1, 8, 2, 1024, 64, None),
+]
+
+
+@pytest.mark.parametrize("path", ["simt"])
+@pytest.mark.parametrize("case", CASES_FP32)
+def test_fp32_matches_exact_definition(path, case):
+    B, Hq, Hkv, N, D, vl = case
+    q, k, v = _randn((B, Hq, N, D), 1), _randn((B, Hkv, N, D), 2), _randn((B, Hkv, N, D), 3)
+    varlen = None if vl is None else torch.tensor(vl, dtype=torch.int32)
+    do = _mask_rows(_randn((B, Hq, N, D), 4), varlen)
+    _use(path, q)
+    got = _run(q, k, v, do, 10, varlen)
+    ex = O.dense_entmax_attention(q, k, v, 1.5, True, varlen, do)
+    for b in range(B):
+        L = N if vl is None else vl[b]
+        assert (got["tau"][b, :, :L].double() - ex["tau"][b, :, :L]).abs().max() < 1e-4
+    for key in ("out", "dq", "dk", "dv"):
+        assert (got[key].double() - ex[key]).abs().max() < 1e-4, key
+    if vl is not None:
+        for b in range(B):
+            assert got["out"][b, :, vl[b]:].abs().max() == 0
+            assert got["dq"][b, :, vl[b]:].abs().max() == 0
+            assert got["dk"][b, :, vl[b]:].abs().max() == 0
+
+
+@pytest.mark.parametrize("path", PATHS)
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("case", [(1, 2, 1, 256, 64, None, 1.0), (1, 2, 2, 512, 128, None, 1.5),
+                                  (2, 4, 1, 320, 128, [300, 129], 1.0), (1, 1, 1, 192, 64, [191], 1.0),
+                                  (1, 2, 2, 128, 32, None, 1.0)])
+def test_16bit_matches_trajectory_oracle(path, dtype, case):
+    B, Hq, Hkv, N, D, vl, sc = case
+    q, k, v = (_randn(s, i, sc, dtype) for i, s in
+               enumerate([(B, Hq, N, D), (B, Hkv, N, D), (B, Hkv, N, D)], 10))
+    varlen = None if vl is None else torch.tensor(vl, dtype=torch.int64)
+    do = _mask_rows(_randn((B, Hq, N, D), 14, 1.0, dtype), varlen)
+    _use(path, q)
+    got = _run(q, k, v, do, 1, varlen)
+    tr = O.v2_attention(q, k, v, 1, varlen, do)
+    for b in range(B):
+        L = N if vl is None else vl[b]
+        assert (got["tau"][b, :, :L] - tr["tau"][b, :, :L]).abs().max() < 1e-4
+    assert (got["bmask"] == tr["bmask"]).all()
+    tol = 2e-2
+    for key in ("out", "out2", "dq", "dk", "dv"):
+        assert (got[key] - tr[key]).abs().max() < tol, key
+
+
+@pytest.mark.parametrize("path", PATHS)
+def test_bitmap_bit_exact_for_given_tau(path):
+    # thresholds chosen so that many tiles are empty; identical fp32 tau in, bitmap out
+    B, Hq, Hkv, N, D = 1, 2, 1, 512, 128
+    q, k = _randn((B, Hq, N, D), 20, 1.5, torch.bfloat16), _randn((B, Hkv, N, D), 21, 1.5, torch.bfloat16)
+    _use(path, q)
+    for shift in (0.0, 0.8, 2.5):
+        taus = torch.full((B, Hq, N), 1.0 + shift) + _randn((B, Hq, N), 22) * 0.3
+        bm = att.mask_from_tau(q.cuda(), k.cuda(), taus.cuda())
+        ref = torch.zeros_like(bm.cpu())
+        for h in range(Hq):
+            z = O.v2_scaled_scores(q[0, h], k[0, 0], N, torch.bfloat16)
+            hit = (z > taus[0, h][:, None]).view(N // 64, 64, N // 64, 64).any(3).any(1)
+            ref[0, h] = O.pack_bitmap(hit)
+        assert (bm.cpu() == ref).all(), shift
+
+
+@pytest.mark.parametrize("path", PATHS)
+def test_zero_scores_give_running_mean_of_v(path):
+    # all-zero q/k: uniform attention over the causal prefix (tests/test_adasplash.py:173-184)
+    B, H, N, D = 1, 2, 128, 64
+    q = torch.zeros(B, H, N, D, dtype=torch.bfloat16)
+    v = _randn((B, H, N, D), 30, 1.0, torch.bfloat16)
+    _use(path, q)
+    out = adasplash.adasplash_v2(q.cuda(), q.cuda(), v.cuda(), niter=4)
+    ref = v.float().cumsum(2) / torch.arange(1, N + 1)[None, None, :, None]
+    assert (out.float().cpu() - ref).abs().max() < 2e-2
+
+
+@pytest.mark.parametrize("path", PATHS)
+def test_deterministic(path):
+    q, k, v, do = (_randn((1, 2, 256, 64), 40 + i, 1.0, torch.bfloat16) for i in range(4))
+    _use(path, q)
+    a = _run(q, k, v, do, 1, None)
+    b = _run(q, k, v, do, 1, None)
+    for key in a:
+        assert torch.equal(a[key], b[key]), key
+
+
+@pytest.mark.parametrize("path", PATHS)
+@pytest.mark.parametrize("name,tol", [
+    ("v2_fp32_smoke", 1e-4), ("v2_fp32_gqa_varlen", 1e-4), ("v2_fp32_niter1", 1e-4),
+    ("v2_bf16_d128", 2e-2), ("v2_bf16_varlen", 2e-2), ("v2_fp16_d64", 2e-2),
+])
+def test_reference_golden(path, name, tol):
+    fpath = os.path.join(GOLD, name + ".pt")
+    if not os.path.exists(fpath):
+        pytest.fail(f"tests/golden/{name}.pt missing")
+    fx = torch.load(fpath, weights_only=False)
+    _use(path, fx["q"])
+    got = _run(fx["q"], fx["k"], fx["v"], fx["dout"], fx["niter"], fx["varlen"])
+    N = fx["q"].shape[2]
+    for b in range(fx["q"].shape[0]):
+        L = N if fx["varlen"] is None else int(fx["varlen"][b])
+        assert (got["tau"][b, :, :L] - fx["taus"][b, :, :L]).abs().max() < 1e-4
+    assert (got["bmask"] == fx["bmask"]).all()
+    for key in ("out", "dq", "dk", "dv"):
+        assert (got[key] - fx[key].float()).abs().max() < tol, key
+
+
+@pytest.mark.parametrize("path", ["tcgen05"])
+def test_tensor_core_path_matches_cuda_core_path(path):
+    # larger case than the CPU oracle handles comfortably: the two kernel
+    # families must agree (same rounding points, different summation order)
+    B, Hq, Hkv, N, D = 2, 4, 2, 2048, 128
+    q, k, v, do = (_randn(s, 50 + i, 1.5 if i < 3 else 1.0, torch.bfloat16) for i, s in
+                   enumerate([(B, Hq, N, D), (B, Hkv, N, D), (B, Hkv, N, D), (B, Hq, N, D)]))
+    varlen = torch.tensor([2048, 1500], dtype=torch.int32)
+    do = _mask_rows(do, varlen)
+    _use(path, q)
+    a = _run(q, k, v, do, 1, varlen)
+    _lib.set_kernel_path("simt")
+    b = _run(q, k, v, do, 1, varlen)
+    assert (a["tau"][0] - b["tau"][0]).abs().max() < 1e-5
+    assert (a["tau"][1, :, :1500] - b["tau"][1, :, :1500]).abs().max() < 1e-5
+    diff_words = (a["bmask"] != b["bmask"]).sum().item()
+    assert diff_words == 0
+    for key in ("out", "out2", "dq", "dk", "dv"):
+        assert (a[key] - b[key]).abs().max() < 2e-2, key
+
+
+def test_c_abi_error_codes_on_device():
+    import ctypes
+    lib = _lib.load()
+    q = torch.zeros(1, 2, 64, 64, device="cuda", dtype=torch.bfloat16)
+    sh = _lib.AttnShape(B=1, Hq=2, Hkv=2, N=64, D=64, dtype=_lib.BF16, niter=1, varlen_is_i64=0,
+                        path=_lib.PATH_SIMT)
+    rc = lib.adasplash2_solve(q.data_ptr(), None, None, None, None, ctypes.byref(sh), None, 0, None)
+    assert rc == 1 and b"null pointer" in lib.adasplash_last_error_string()
+    sh.path = 9
+    rc = lib.adasplash2_fwd(*([q.data_ptr()] * 8), ctypes.byref(sh), None, 0, None)
+    assert rc == 1 and b"unknown path" in lib.adasplash_last_error_string()

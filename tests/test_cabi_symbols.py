@@ -1,0 +1,52 @@
+"""The shared library loads without a GPU and exports every symbol that
+include/adasplash_b200.h declares (no compute calls here)."""
+import ctypes
+import os
+import re
+
+from adasplash_b200 import _lib
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared():
+    text = open(os.path.join(ROOT, "include", "adasplash_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(adasplash2?_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_matches_binding_table():
+    assert _declared() == sorted(_lib.SIGNATURES)
+
+
+def test_library_exports_every_declared_symbol():
+    lib = _lib.load()
+    for name in _declared():
+        assert hasattr(lib, name), name
+
+
+def test_error_reporting_without_gpu():
+    lib = _lib.load()
+    before = lib.adasplash_launch_count()
+    # negative sizes are rejected before any CUDA call
+    rc = lib.adasplash_entmax_fwd(None, None, None, -1, 4, 1.5, 2, 1, 0, 0, None)
+    assert rc == 1
+    assert b"bad argument" in lib.adasplash_last_error_string()
+    sh = _lib.AttnShape(B=1, Hq=3, Hkv=2, N=64, D=64, dtype=0, niter=1, varlen_is_i64=0, path=0)
+    assert lib.adasplash2_resolved_path(ctypes.byref(sh)) == -1
+    assert b"not a multiple" in lib.adasplash_last_error_string()
+    sh = _lib.AttnShape(B=1, Hq=2, Hkv=2, N=64, D=48, dtype=0, niter=1, varlen_is_i64=0, path=0)
+    assert lib.adasplash2_workspace_bytes(ctypes.byref(sh)) == 0
+    sh = _lib.AttnShape(B=1, Hq=2, Hkv=2, N=32, D=64, dtype=0, niter=1, varlen_is_i64=0, path=0)
+    assert lib.adasplash2_resolved_path(ctypes.byref(sh)) == -1
+    assert lib.adasplash_launch_count() == before
+
+
+def test_bitmap_extent_matches_reference_layout():
+    # rows_padded = max(32, ceil32(nb)), n_words = ceil(nb/32) (adasplash_v2.py:1345-1350)
+    lib = _lib.load()
+    for n, rows, words in ((64, 32, 1), (2048, 32, 1), (2112, 64, 2), (8192, 128, 4), (65536, 1024, 32)):
+        sh = _lib.AttnShape(B=2, Hq=3, Hkv=3, N=n, D=64, dtype=2, niter=1, varlen_is_i64=0, path=0)
+        r, w = ctypes.c_int32(), ctypes.c_int32()
+        total = lib.adasplash2_bitmap_words(ctypes.byref(sh), ctypes.byref(r), ctypes.byref(w))
+        assert (r.value, w.value, total) == (rows, words, 6 * rows * words)
