@@ -70,6 +70,14 @@ def _workspace(shape, device):
     return torch.empty(max(nbytes, 256), device=device, dtype=torch.uint8), nbytes
 
 
+DEBUG_STATUS = False  # tests set this: check the device status word after every call (synchronises)
+
+
+def _maybe_check(ws, st):
+    if DEBUG_STATUS:
+        _lib.check(_lib.load().adasplash2_check_status(_ptr(ws), st))
+
+
 def solve(q, k, niter=1, varlen=None, path=None):
     """Thresholds and block mask only: (taus (B,Hq,N) fp32, bmask int32)."""
     lib = _lib.load()
@@ -83,6 +91,7 @@ def solve(q, k, niter=1, varlen=None, path=None):
         st = torch.cuda.current_stream().cuda_stream
         _lib.check(lib.adasplash2_solve(_ptr(q), _ptr(k), _ptr(varlen), _ptr(taus), _ptr(bmask),
                                         ctypes.byref(shape), _ptr(ws), nbytes, st))
+        _maybe_check(ws, st)
     return taus, bmask
 
 
@@ -100,6 +109,7 @@ def mask_from_tau(q, k, taus, varlen=None, path=None):
         _lib.check(lib.adasplash2_mask_from_tau(_ptr(q), _ptr(k), _ptr(varlen), _ptr(taus),
                                                 _ptr(bmask), ctypes.byref(shape), _ptr(ws),
                                                 nbytes, st))
+        _maybe_check(ws, st)
     return bmask
 
 
@@ -122,9 +132,11 @@ class _SparseAttention(torch.autograd.Function):
             sp = ctypes.byref(shape)
             _lib.check(lib.adasplash2_solve(_ptr(q), _ptr(k), _ptr(varlen), _ptr(taus),
                                             _ptr(bmask), sp, _ptr(ws), nbytes, st))
+            _maybe_check(ws, st)
             _lib.check(lib.adasplash2_fwd(_ptr(q), _ptr(k), _ptr(v), _ptr(varlen), _ptr(taus),
                                           _ptr(bmask), _ptr(out), _ptr(out2), sp, _ptr(ws),
                                           nbytes, st))
+            _maybe_check(ws, st)
         ctx.save_for_backward(q, k, v, out2, taus, bmask)
         ctx.varlen = varlen
         ctx.niter = niter
@@ -152,6 +164,7 @@ class _SparseAttention(torch.autograd.Function):
                                           _ptr(varlen), _ptr(taus), _ptr(bmask), _ptr(bmask_t),
                                           _ptr(delta), _ptr(dq), _ptr(dk), _ptr(dv),
                                           ctypes.byref(shape), _ptr(ws), nbytes, st))
+            _maybe_check(ws, st)
         return dq, dk, dv, None, None
 
 

@@ -220,3 +220,17 @@ extern "C" int adasplash2_bwd(const void* q, const void* k, const void* v, const
       [&] { return simt::launch_bwd<__half>(p, st); },
       [&] { return simt::launch_bwd<__nv_bfloat16>(p, st); });
 }
+
+extern "C" int adasplash2_check_status(const void* workspace, void* stream) {
+  if (workspace == nullptr) { set_error("check_status: null workspace"); return ADS_ERR_BAD_ARG; }
+  int host = 0;
+  cudaStream_t st = (cudaStream_t)stream;
+  cudaError_t e = cudaMemcpyAsync(&host, workspace, sizeof(int), cudaMemcpyDeviceToHost, st);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+  if (e != cudaSuccess) { set_error("check_status: %s", cudaGetErrorString(e)); return ADS_ERR_CUDA; }
+  if (host != 0) {
+    set_error("a device-side wait timed out (code %d: 101 = TMA producer, 102 = MMA issuer, 103 = row warps)", host);
+    return ADS_ERR_TIMEOUT;
+  }
+  return ADS_OK;
+}

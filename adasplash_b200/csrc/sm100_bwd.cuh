@@ -1,0 +1,730 @@
+// Backward on the tensor cores (adasplash_v2.py:943-1234).
+//
+// dQ kernel: one CTA per 128-row query tile, walking the active 128-key tiles.
+//   S = Q~ K^T, dP = dO V^T (operands in shared memory), u = max(S - tau, 0),
+//   dS = rn(u (dP - delta)) written over S in TMEM, dQ += dS K (A operand in TMEM,
+//   K read MN-major from the same shared-memory tile).  S is double buffered.
+//
+// dK/dV kernel: one CTA per 128-key tile of one kv head, walking the q heads of
+//   the group and, per head, the 64-row query blocks whose bit is set in the
+//   transposed block mask.  S^T = K~ Q^T, dP^T = V dO^T (128 keys x 64 queries),
+//   P^T = rn(u^2) and dS^T = rn(u (dP - delta)) written over them in TMEM,
+//   dV += P^T dO, dK += dS^T Q.  K is the scaled + rounded operand here and Q is
+//   raw, as in the reference.  S^T / dP^T are double buffered.
+#pragma once
+#include <type_traits>
+
+#include "sm100_fwd.cuh"
+
+namespace ads {
+namespace sm100 {
+
+// ---------------------------------------------------------------------------
+// dQ
+// ---------------------------------------------------------------------------
+constexpr int kDqThreads = 192;
+constexpr int kDqKStages = 3;
+constexpr int kDqVStages = 2;
+constexpr int kDqTmemCols = 512;
+
+template <int D>
+struct DqSmem {
+  static constexpr int tile_bytes = (D / 64) * kPanelBytes;
+  static constexpr int q_off = 0;
+  static constexpr int do_off = tile_bytes;
+  static constexpr int k_off = 2 * tile_bytes;
+  static constexpr int v_off = k_off + kDqKStages * tile_bytes;
+  static constexpr int bar_off = v_off + kDqVStages * tile_bytes;
+  static constexpr int n_bars = 2 + 2 * kDqKStages + 2 * kDqVStages + 2 + 1 + 2 + 2 + 1;
+  static constexpr int misc_off = bar_off + n_bars * 8;
+  static constexpr size_t bytes = 1024 + misc_off + 64;
+};
+
+template <typename T, int D>
+__global__ void __launch_bounds__(kDqThreads, 1)
+bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDO,
+              const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+              TcParams p) {
+  using L = DqSmem<D>;
+  constexpr int PANELS = D / 64;
+  constexpr int KSTEPS = D / 16;
+  constexpr int FMT = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
+  constexpr uint32_t DP_COL = 256, DQ_COL = 384;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* sQ = smem + L::q_off;
+  uint8_t* sDO = smem + L::do_off;
+  uint8_t* sK = smem + L::k_off;
+  uint8_t* sV = smem + L::v_off;
+  uint64_t* bars = (uint64_t*)(smem + L::bar_off);
+  uint64_t* q_full = bars + 0;
+  uint64_t* q_ready = bars + 1;
+  uint64_t* k_full = bars + 2;
+  uint64_t* k_empty = k_full + kDqKStages;
+  uint64_t* v_full = k_empty + kDqKStages;
+  uint64_t* v_empty = v_full + kDqVStages;
+  uint64_t* s_full = v_empty + kDqVStages;   // [2]
+  uint64_t* dp_full = s_full + 2;            // [1]
+  uint64_t* p_full = dp_full + 1;            // [2] dS written, dP consumed
+  uint64_t* s_free = p_full + 2;             // [2]
+  uint64_t* dq_full = s_free + 2;
+  uint32_t* tmem_holder = (uint32_t*)(smem + L::misc_off);
+  volatile int* cta_abort = (volatile int*)(smem + L::misc_off + 4);
+  int* start_status = (int*)(smem + L::misc_off + 8);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int heads = p.B * p.Hq;
+  const int qt = p.nq - 1 - (int)(blockIdx.x / heads);
+  const int bh = blockIdx.x % heads;
+  const int b = bh / p.Hq, h = bh % p.Hq;
+  const int kvh = h / (p.Hq / p.Hkv);
+  const int len = load_len(p.varlen, p.varlen_is_i64, b, p.N);
+  const int m0 = qt * kBlockM;
+  T* dqg = (T*)p.dq + (size_t)bh * p.N * D;
+  if (m0 >= len) {
+    for (int v = threadIdx.x; v < kBlockM * (D / 8); v += kDqThreads) {
+      const int rr = m0 + v / (D / 8);
+      if (rr < p.N) reinterpret_cast<uint4*>(dqg + (size_t)rr * D)[v % (D / 8)] = make_uint4(0, 0, 0, 0);
+    }
+    return;
+  }
+  const int T_tiles = qt + 1;
+  const int32_t* bm_head = p.bmask + (size_t)bh * p.rows_padded * p.n_words;
+
+  if (threadIdx.x == 0) {
+    *start_status = *(volatile int*)p.status;
+    *cta_abort = 0;
+  }
+  if (warp == 5) {
+    if (lane == 0) {
+      ptx::mbar_init(q_full, 1);
+      ptx::mbar_init(q_ready, 128);
+      for (int s = 0; s < kDqKStages; ++s) { ptx::mbar_init(k_full + s, 1); ptx::mbar_init(k_empty + s, 1); }
+      for (int s = 0; s < kDqVStages; ++s) { ptx::mbar_init(v_full + s, 1); ptx::mbar_init(v_empty + s, 1); }
+      for (int s = 0; s < 2; ++s) {
+        ptx::mbar_init(s_full + s, 1);
+        ptx::mbar_init(p_full + s, 128);
+        ptx::mbar_init(s_free + s, 1);
+      }
+      ptx::mbar_init(dp_full, 1);
+      ptx::mbar_init(dq_full, 1);
+      ptx::fence_mbar_init();
+    }
+    __syncwarp();
+    ptx::tmem_alloc(tmem_holder, kDqTmemCols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::tc_fence_after_sync();
+  if (*start_status != 0) {
+    if (warp == 5) ptx::tmem_dealloc(*tmem_holder, kDqTmemCols);
+    return;
+  }
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 4) {
+    if (lane == 0) {
+      ptx::prefetch_tmap(&tmQ); ptx::prefetch_tmap(&tmDO); ptx::prefetch_tmap(&tmK); ptx::prefetch_tmap(&tmV);
+      ptx::mbar_arrive_expect_tx(q_full, 2 * L::tile_bytes);
+      for (int pn = 0; pn < PANELS; ++pn) {
+        ptx::tma_load_3d(sQ + pn * kPanelBytes, &tmQ, q_full, pn * 64, m0, bh);
+        ptx::tma_load_3d(sDO + pn * kPanelBytes, &tmDO, q_full, pn * 64, m0, bh);
+      }
+      const int kv_head = b * p.Hkv + kvh;
+      TileScan scan(bm_head, qt, T_tiles, p.rows_padded, p.n_words);
+      int kt;
+      uint32_t flags;
+      for (int j = 0; scan.next(kt, flags); ++j) {
+        const int ks = j % kDqKStages, vs = j % kDqVStages;
+        if (*cta_abort) break;
+        if (!ptx::mbar_wait(k_empty + ks, ((j / kDqKStages) & 1) ^ 1)) { raise_abort(cta_abort, p.status, kStTimeoutProducer); break; }
+        ptx::mbar_arrive_expect_tx(k_full + ks, L::tile_bytes);
+        for (int pn = 0; pn < PANELS; ++pn)
+          ptx::tma_load_3d(sK + ks * L::tile_bytes + pn * kPanelBytes, &tmK, k_full + ks, pn * 64, kt * kBlockN, kv_head);
+        if (!ptx::mbar_wait(v_empty + vs, ((j / kDqVStages) & 1) ^ 1)) { raise_abort(cta_abort, p.status, kStTimeoutProducer); break; }
+        ptx::mbar_arrive_expect_tx(v_full + vs, L::tile_bytes);
+        for (int pn = 0; pn < PANELS; ++pn)
+          ptx::tma_load_3d(sV + vs * L::tile_bytes + pn * kPanelBytes, &tmV, v_full + vs, pn * 64, kt * kBlockN, kv_head);
+      }
+    }
+  } else if (warp == 5) {
+    constexpr uint32_t idesc_s = ptx::make_idesc(FMT, kBlockM, kBlockN, 0, 0);
+    constexpr uint32_t idesc_dq = ptx::make_idesc(FMT, kBlockM, D, 0, 1);
+    bool ok = true;
+    if (lane == 0) ok = ptx::mbar_wait(q_ready, 0);
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    if (!ok && lane == 0) raise_abort(cta_abort, p.status, kStTimeoutMma);
+
+    // S_j = Q~ K_j^T into S buffer j&1 (lane 0)
+    auto issue_s = [&](int j) -> bool {
+      const int ks = j % kDqKStages, buf = j & 1;
+      if (!ptx::mbar_wait(k_full + ks, (j / kDqKStages) & 1) ||
+          !ptx::mbar_wait(s_free + buf, ((j >> 1) & 1) ^ 1))
+        return false;
+      ptx::tc_fence_after_sync();
+      const uint32_t a0 = ptx::smem_u32(sQ), b0 = ptx::smem_u32(sK + ks * L::tile_bytes);
+#pragma unroll
+      for (int kk = 0; kk < KSTEPS; ++kk) {
+        const uint32_t off = (kk >> 2) * kPanelBytes + (kk & 3) * 32;
+        ptx::mma_ss(tmem_base + buf * kBlockN, ptx::make_smem_desc(a0 + off, 16, 1024),
+                    ptx::make_smem_desc(b0 + off, 16, 1024), idesc_s, kk > 0);
+      }
+      ptx::mma_commit(s_full + buf);
+      return true;
+    };
+    // dP_j = dO V_j^T into the single dP buffer (lane 0); the caller guarantees
+    // that the row warps have finished reading dP_{j-1}
+    auto issue_dp = [&](int j) -> bool {
+      const int vs = j % kDqVStages;
+      if (!ptx::mbar_wait(v_full + vs, (j / kDqVStages) & 1)) return false;
+      ptx::tc_fence_after_sync();
+      const uint32_t a0 = ptx::smem_u32(sDO), b0 = ptx::smem_u32(sV + vs * L::tile_bytes);
+#pragma unroll
+      for (int kk = 0; kk < KSTEPS; ++kk) {
+        const uint32_t off = (kk >> 2) * kPanelBytes + (kk & 3) * 32;
+        ptx::mma_ss(tmem_base + DP_COL, ptx::make_smem_desc(a0 + off, 16, 1024),
+                    ptx::make_smem_desc(b0 + off, 16, 1024), idesc_s, kk > 0);
+      }
+      ptx::mma_commit(v_empty + vs);
+      ptx::mma_commit(dp_full);
+      return true;
+    };
+
+    TileScan scan(bm_head, qt, T_tiles, p.rows_padded, p.n_words);
+    int kt, kt_next = 0;
+    uint32_t flags;
+    bool have = scan.next(kt, flags);
+    if (ok && have) {
+      if (lane == 0) ok = issue_s(0) && issue_dp(0);
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+    }
+    int j = 0;
+    for (; ok && have; ++j) {
+      const int ks = j % kDqKStages, buf = j & 1;
+      const bool have_next = scan.next(kt_next, flags);
+      if (*cta_abort) { ok = false; break; }
+      if (lane == 0 && have_next) ok = issue_s(j + 1);
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) break;
+      uint8_t* ktile = sK + ks * L::tile_bytes;
+      // padded keys: K rows = 0 for the dS K product (S_j, the other reader of this
+      // tile, has completed: its commit precedes p_full in program order of the row warps)
+      const bool fix_k = (kt + 1) * kBlockN > len;
+      if (lane == 0) ok = ptx::mbar_wait(p_full + buf, (j >> 1) & 1);
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) break;
+      if (fix_k) zero_tile_rows(ktile, PANELS, len - kt * kBlockN, lane);
+      if (lane == 0) {
+        ptx::tc_fence_after_sync();
+        const uint32_t k0 = ptx::smem_u32(ktile);
+        const uint32_t pbase = tmem_base + buf * kBlockN;
+#pragma unroll
+        for (int kk = 0; kk < kBlockN / 16; ++kk) {
+          const uint64_t bd = ptx::make_smem_desc(k0 + kk * 2048, kPanelBytes, 1024);
+          ptx::mma_ts(tmem_base + DQ_COL, pbase + (kk >> 1) * 32 + (kk & 1) * 8, bd, idesc_dq, (j > 0 || kk > 0));
+        }
+        ptx::mma_commit(k_empty + ks);
+        ptx::mma_commit(s_free + buf);
+        if (!have_next) ptx::mma_commit(dq_full);
+        else ok = issue_dp(j + 1);
+      }
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      kt = kt_next;
+      have = have_next;
+    }
+    if (!ok && lane == 0 && !*cta_abort) raise_abort(cta_abort, p.status, kStTimeoutMma);
+  } else {
+    const int wq = warp;
+    const int r = wq * 32 + lane;
+    const int row = m0 + r;
+    const bool row_ok = row < len;
+    const int rb = wq >> 1;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(wq * 32) << 16);
+    bool dead = false;
+    if (!ptx::mbar_wait(q_full, 0)) { raise_abort(cta_abort, p.status, kStTimeoutEpilogue); dead = true; }
+    if (!dead) {
+      const float sc = 0.5f * p.sm_scale;
+      for (int v = threadIdx.x; v < L::tile_bytes / 16; v += 128) {
+        uint4* ptr = reinterpret_cast<uint4*>(sQ) + v;
+        const int vrow = ((v * 16) % kPanelBytes) / 128;
+        uint4 val = *ptr;
+        T* e = reinterpret_cast<T*>(&val);
+        const bool keep = (m0 + vrow) < len;
+#pragma unroll
+        for (int jj = 0; jj < 8; ++jj) e[jj] = DT<T>::from_f(keep ? DT<T>::to_f(e[jj]) * sc : 0.f);
+        *ptr = val;
+      }
+      ptx::fence_proxy_async_smem();
+    }
+    ptx::mbar_arrive(q_ready);
+    const float tau = row_ok ? p.taus[(size_t)bh * p.N + row] : 0.f;
+    const float dl = row_ok ? p.delta[(size_t)bh * p.N + row] : 0.f;
+    TileScan scan(bm_head, qt, T_tiles, p.rows_padded, p.n_words);
+    int kt, n_active = 0;
+    uint32_t flags;
+    for (int j = 0; !dead && scan.next(kt, flags); ++j) {
+      const int buf = j & 1;
+      n_active = j + 1;
+      const uint32_t my_flags = (flags >> (2 * rb)) & 3u;
+      if (*cta_abort) { dead = true; break; }
+      if (!ptx::mbar_wait(s_full + buf, (j >> 1) & 1) || !ptx::mbar_wait(dp_full, j & 1)) {
+        raise_abort(cta_abort, p.status, kStTimeoutEpilogue);
+        dead = true;
+        break;
+      }
+      ptx::tc_fence_after_sync();
+      const int n0 = kt * kBlockN;
+      const bool need_mask = (kt == qt) || (n0 + kBlockN > len);
+#pragma unroll 1
+      for (int ch = 0; ch < 4; ++ch) {
+        uint32_t rs[32], rp[32];
+        const uint32_t caddr = lane_addr + buf * kBlockN + ch * 32;
+        ptx::tmem_ld32(caddr, rs);
+        ptx::tmem_ld32(lane_addr + DP_COL + ch * 32, rp);
+        ptx::tmem_ld_wait();
+        const float* s = reinterpret_cast<const float*>(rs);
+        const float* dp = reinterpret_cast<const float*>(rp);
+        const bool sub_on = (my_flags >> (ch >> 1)) & 1u;
+        uint32_t dk[16];
+#pragma unroll
+        for (int c = 0; c < 32; c += 2) {
+          float d0 = 0.f, d1 = 0.f;
+          const int col = n0 + ch * 32 + c;
+          const bool ok0 = sub_on && (!need_mask || (col <= row && col < len));
+          const bool ok1 = sub_on && (!need_mask || (col + 1 <= row && col + 1 < len));
+          const float u0 = s[c] - tau, u1 = s[c + 1] - tau;
+          if (ok0 && u0 > 0.f) d0 = u0 * (dp[c] - dl);
+          if (ok1 && u1 > 0.f) d1 = u1 * (dp[c + 1] - dl);
+          dk[c >> 1] = pack2<T>(d0, d1);
+        }
+        ptx::tmem_st16(caddr, dk);
+      }
+      ptx::tmem_st_wait();
+      ptx::tc_fence_before_sync();
+      ptx::mbar_arrive(p_full + buf);
+    }
+    if (!dead && n_active > 0) {
+      if (!ptx::mbar_wait(dq_full, 0)) { raise_abort(cta_abort, p.status, kStTimeoutEpilogue); dead = true; }
+    }
+    if (!dead && row < p.N) {
+      ptx::tc_fence_after_sync();
+#pragma unroll 1
+      for (int ch = 0; ch < D / 32; ++ch) {
+        uint32_t ro[32];
+        if (n_active > 0) {
+          ptx::tmem_ld32(lane_addr + DQ_COL + ch * 32, ro);
+          ptx::tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int c = 0; c < 32; ++c) ro[c] = 0u;
+        }
+        const float* fo = reinterpret_cast<const float*>(ro);
+        uint32_t po[16];
+#pragma unroll
+        for (int c = 0; c < 32; c += 2)
+          po[c >> 1] = row_ok ? pack2<T>(fo[c] * p.sm_scale, fo[c + 1] * p.sm_scale) : 0u;
+        uint4* dst = reinterpret_cast<uint4*>(dqg + (size_t)row * D + ch * 32);
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) dst[q4] = make_uint4(po[q4 * 4], po[q4 * 4 + 1], po[q4 * 4 + 2], po[q4 * 4 + 3]);
+      }
+    }
+  }
+
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if (*cta_abort && threadIdx.x == 0) {
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);
+  }
+  __syncthreads();
+  if (warp == 5) {
+    ptx::tc_fence_after_sync();
+    ptx::tmem_dealloc(tmem_base, kDqTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// dK, dV
+// ---------------------------------------------------------------------------
+constexpr int kDkvThreads = 192;
+constexpr int kDkvStages = 3;       // (Q block, dO block) pairs in flight
+constexpr int kDkvTmemCols = 512;
+constexpr int kQBlock = 64;         // query rows per step (one block-mask row block)
+constexpr int kQPanelBytes = kQBlock * 128;
+
+template <int D>
+struct DkvSmem {
+  static constexpr int tile_bytes = (D / 64) * kPanelBytes;     // 128-key K / V tile
+  static constexpr int qblk_bytes = (D / 64) * kQPanelBytes;    // 64-row Q / dO block
+  static constexpr int k_off = 0;
+  static constexpr int v_off = tile_bytes;
+  static constexpr int q_off = 2 * tile_bytes;
+  static constexpr int do_off = q_off + kDkvStages * qblk_bytes;
+  static constexpr int bar_off = do_off + kDkvStages * qblk_bytes;
+  static constexpr int n_bars = 2 + 2 * kDkvStages + 2 + 2 + 2 + 1;
+  static constexpr int misc_off = bar_off + n_bars * 8;
+  static constexpr int td_off = misc_off + 64;                  // [2][2][64] floats: tau, delta
+  static constexpr size_t bytes = 1024 + td_off + 2 * 2 * 64 * 4;
+};
+
+// Walks (q head of the group, 64-row query block) pairs whose bit is set in rows
+// 2nt / 2nt+1 of the transposed block mask.  flags: bit0 = keys 0..63 of the
+// tile, bit1 = keys 64..127.
+struct QBlockScan {
+  const int32_t* bmt;
+  int G, h0, rows_padded, n_words, nt, n_qblocks;
+  int g, m;
+  const uint32_t* r0;
+  const uint32_t* r1;
+  uint32_t w0, w1;
+  __device__ QBlockScan(const int32_t* bmask_t, int b, int Hq, int G_, int kvh, int nt_, int n_qblocks_,
+                        int rows_padded_, int n_words_)
+      : bmt(bmask_t), G(G_), rows_padded(rows_padded_), n_words(n_words_), nt(nt_), n_qblocks(n_qblocks_),
+        g(-1), m(0), r0(nullptr), r1(nullptr), w0(0), w1(0) {
+    h0 = b * Hq + kvh * G_;
+    m = n_qblocks;  // forces a head switch on the first call
+  }
+  __device__ __forceinline__ bool next(int& g_out, int& m_out, uint32_t& flags) {
+    for (;;) {
+      if (m >= n_qblocks) {
+        if (++g >= G) return false;
+        r0 = reinterpret_cast<const uint32_t*>(bmt) + ((size_t)(h0 + g) * rows_padded + 2 * nt) * n_words;
+        r1 = (2 * nt + 1) < rows_padded ? r0 + n_words : nullptr;
+        m = 2 * nt;  // causal: query blocks before the key tile never see it
+        w0 = r0[m >> 5];
+        w1 = r1 ? r1[m >> 5] : 0u;
+      }
+      while (m < n_qblocks) {
+        if ((m & 31) == 0) { w0 = r0[m >> 5]; w1 = r1 ? r1[m >> 5] : 0u; }
+        const uint32_t f = ((w0 >> (m & 31)) & 1u) | (((w1 >> (m & 31)) & 1u) << 1);
+        const int cur = m++;
+        if (f) { g_out = g; m_out = cur; flags = f; return true; }
+      }
+    }
+  }
+};
+
+template <typename T, int D>
+__global__ void __launch_bounds__(kDkvThreads, 1)
+bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+               const __grid_constant__ CUtensorMap tmQ64, const __grid_constant__ CUtensorMap tmDO64,
+               TcParams p) {
+  using L = DkvSmem<D>;
+  constexpr int PANELS = D / 64;
+  constexpr int KSTEPS = D / 16;
+  constexpr int FMT = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
+  constexpr uint32_t DP_COL0 = 128, DK_COL = 256, DV_COL = 256 + D;  // S^T[2] at 0/64, dP^T[2] at 128/192
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* sK = smem + L::k_off;
+  uint8_t* sV = smem + L::v_off;
+  uint8_t* sQ = smem + L::q_off;
+  uint8_t* sDO = smem + L::do_off;
+  uint64_t* bars = (uint64_t*)(smem + L::bar_off);
+  uint64_t* kv_full = bars + 0;
+  uint64_t* k_ready = bars + 1;
+  uint64_t* x_full = bars + 2;               // [stages] Q block + dO block landed
+  uint64_t* x_empty = x_full + kDkvStages;
+  uint64_t* s_full = x_empty + kDkvStages;   // [2] S^T and dP^T of a step computed
+  uint64_t* p_full = s_full + 2;             // [2] P^T and dS^T written
+  uint64_t* s_free = p_full + 2;             // [2]
+  uint64_t* acc_full = s_free + 2;
+  uint32_t* tmem_holder = (uint32_t*)(smem + L::misc_off);
+  volatile int* cta_abort = (volatile int*)(smem + L::misc_off + 4);
+  int* start_status = (int*)(smem + L::misc_off + 8);
+  float* s_td = (float*)(smem + L::td_off);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kvheads = p.B * p.Hkv;
+  const int nt = (int)(blockIdx.x / kvheads);  // low key tiles (most work) first
+  const int bkv = blockIdx.x % kvheads;
+  const int b = bkv / p.Hkv, kvh = bkv % p.Hkv;
+  const int G = p.Hq / p.Hkv;
+  const int len = load_len(p.varlen, p.varlen_is_i64, b, p.N);
+  const int n0 = nt * kBlockN;
+  T* dkg = (T*)p.dk + (size_t)bkv * p.N * D;
+  T* dvg = (T*)p.dv + (size_t)bkv * p.N * D;
+  if (n0 >= len) {
+    for (int v = threadIdx.x; v < kBlockN * (D / 8); v += kDkvThreads) {
+      const int rr = n0 + v / (D / 8);
+      if (rr < p.N) {
+        reinterpret_cast<uint4*>(dkg + (size_t)rr * D)[v % (D / 8)] = make_uint4(0, 0, 0, 0);
+        reinterpret_cast<uint4*>(dvg + (size_t)rr * D)[v % (D / 8)] = make_uint4(0, 0, 0, 0);
+      }
+    }
+    return;
+  }
+  const int n_qblocks = (len + kQBlock - 1) / kQBlock;  // query blocks with at least one valid row
+
+  if (threadIdx.x == 0) {
+    *start_status = *(volatile int*)p.status;
+    *cta_abort = 0;
+  }
+  if (warp == 5) {
+    if (lane == 0) {
+      ptx::mbar_init(kv_full, 1);
+      ptx::mbar_init(k_ready, 128);
+      for (int s = 0; s < kDkvStages; ++s) { ptx::mbar_init(x_full + s, 1); ptx::mbar_init(x_empty + s, 1); }
+      for (int s = 0; s < 2; ++s) {
+        ptx::mbar_init(s_full + s, 1);
+        ptx::mbar_init(p_full + s, 128);
+        ptx::mbar_init(s_free + s, 1);
+      }
+      ptx::mbar_init(acc_full, 1);
+      ptx::fence_mbar_init();
+    }
+    __syncwarp();
+    ptx::tmem_alloc(tmem_holder, kDkvTmemCols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::tc_fence_after_sync();
+  if (*start_status != 0) {
+    if (warp == 5) ptx::tmem_dealloc(*tmem_holder, kDkvTmemCols);
+    return;
+  }
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 4) {
+    if (lane == 0) {
+      ptx::prefetch_tmap(&tmK); ptx::prefetch_tmap(&tmV); ptx::prefetch_tmap(&tmQ64); ptx::prefetch_tmap(&tmDO64);
+      ptx::mbar_arrive_expect_tx(kv_full, 2 * L::tile_bytes);
+      for (int pn = 0; pn < PANELS; ++pn) {
+        ptx::tma_load_3d(sK + pn * kPanelBytes, &tmK, kv_full, pn * 64, n0, bkv);
+        ptx::tma_load_3d(sV + pn * kPanelBytes, &tmV, kv_full, pn * 64, n0, bkv);
+      }
+      QBlockScan scan(p.bmask_t, b, p.Hq, G, kvh, nt, n_qblocks, p.rows_padded, p.n_words);
+      int g, m;
+      uint32_t flags;
+      for (int j = 0; scan.next(g, m, flags); ++j) {
+        const int st = j % kDkvStages;
+        const int qh = b * p.Hq + kvh * G + g;
+        if (*cta_abort) break;
+        if (!ptx::mbar_wait(x_empty + st, ((j / kDkvStages) & 1) ^ 1)) { raise_abort(cta_abort, p.status, kStTimeoutProducer); break; }
+        ptx::mbar_arrive_expect_tx(x_full + st, 2 * L::qblk_bytes);
+        for (int pn = 0; pn < PANELS; ++pn) {
+          ptx::tma_load_3d(sQ + st * L::qblk_bytes + pn * kQPanelBytes, &tmQ64, x_full + st, pn * 64, m * kQBlock, qh);
+          ptx::tma_load_3d(sDO + st * L::qblk_bytes + pn * kQPanelBytes, &tmDO64, x_full + st, pn * 64, m * kQBlock, qh);
+        }
+      }
+    }
+  } else if (warp == 5) {
+    constexpr uint32_t idesc_s = ptx::make_idesc(FMT, kBlockN, kQBlock, 0, 0);   // 128 keys x 64 queries
+    constexpr uint32_t idesc_acc = ptx::make_idesc(FMT, kBlockN, D, 0, 1);        // 128 keys x D
+    bool ok = true;
+    if (lane == 0) ok = ptx::mbar_wait(k_ready, 0);
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    if (!ok && lane == 0) raise_abort(cta_abort, p.status, kStTimeoutMma);
+
+    // S^T_j = K~ Q_j^T and dP^T_j = V dO_j^T into buffer j&1 (lane 0)
+    auto issue_s = [&](int j) -> bool {
+      const int st = j % kDkvStages, buf = j & 1;
+      if (!ptx::mbar_wait(x_full + st, (j / kDkvStages) & 1) ||
+          !ptx::mbar_wait(s_free + buf, ((j >> 1) & 1) ^ 1))
+        return false;
+      ptx::tc_fence_after_sync();
+      const uint32_t k0 = ptx::smem_u32(sK), v0 = ptx::smem_u32(sV);
+      const uint32_t q0 = ptx::smem_u32(sQ + st * L::qblk_bytes), d0 = ptx::smem_u32(sDO + st * L::qblk_bytes);
+#pragma unroll
+      for (int kk = 0; kk < KSTEPS; ++kk) {
+        const uint32_t offa = (kk >> 2) * kPanelBytes + (kk & 3) * 32;
+        const uint32_t offb = (kk >> 2) * kQPanelBytes + (kk & 3) * 32;
+        ptx::mma_ss(tmem_base + buf * kQBlock, ptx::make_smem_desc(k0 + offa, 16, 1024),
+                    ptx::make_smem_desc(q0 + offb, 16, 1024), idesc_s, kk > 0);
+      }
+#pragma unroll
+      for (int kk = 0; kk < KSTEPS; ++kk) {
+        const uint32_t offa = (kk >> 2) * kPanelBytes + (kk & 3) * 32;
+        const uint32_t offb = (kk >> 2) * kQPanelBytes + (kk & 3) * 32;
+        ptx::mma_ss(tmem_base + DP_COL0 + buf * kQBlock, ptx::make_smem_desc(v0 + offa, 16, 1024),
+                    ptx::make_smem_desc(d0 + offb, 16, 1024), idesc_s, kk > 0);
+      }
+      ptx::mma_commit(s_full + buf);
+      return true;
+    };
+
+    QBlockScan scan(p.bmask_t, b, p.Hq, G, kvh, nt, n_qblocks, p.rows_padded, p.n_words);
+    int g, m, g_next = 0, m_next = 0;
+    uint32_t flags;
+    bool have = scan.next(g, m, flags);
+    if (ok && have) {
+      if (lane == 0) ok = issue_s(0);
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+    }
+    int j = 0;
+    for (; ok && have; ++j) {
+      const int st = j % kDkvStages, buf = j & 1;
+      const bool have_next = scan.next(g_next, m_next, flags);
+      if (*cta_abort) { ok = false; break; }
+      if (lane == 0 && have_next) ok = issue_s(j + 1);
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) break;
+      if (lane == 0) ok = ptx::mbar_wait(p_full + buf, (j >> 1) & 1);
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) break;
+      uint8_t* qt_ = sQ + st * L::qblk_bytes;
+      uint8_t* dot_ = sDO + st * L::qblk_bytes;
+      if ((m + 1) * kQBlock > len) {
+        // padded query rows: Q and dO rows = 0 for the transposed products
+        const int first = len - m * kQBlock;
+        for (int pn = 0; pn < PANELS; ++pn) {
+          uint4* bq = reinterpret_cast<uint4*>(qt_ + pn * kQPanelBytes + first * 128);
+          uint4* bd = reinterpret_cast<uint4*>(dot_ + pn * kQPanelBytes + first * 128);
+          for (int v = lane; v < (kQBlock - first) * 8; v += 32) { bq[v] = make_uint4(0, 0, 0, 0); bd[v] = make_uint4(0, 0, 0, 0); }
+        }
+        ptx::fence_proxy_async_smem();
+        __syncwarp();
+      }
+      if (lane == 0) {
+        ptx::tc_fence_after_sync();
+        const uint32_t q0 = ptx::smem_u32(qt_), d0 = ptx::smem_u32(dot_);
+        const uint32_t pa = tmem_base + buf * kQBlock;            // P^T: 32 packed columns
+        const uint32_t da = tmem_base + DP_COL0 + buf * kQBlock;  // dS^T
+#pragma unroll
+        for (int kk = 0; kk < kQBlock / 16; ++kk) {
+          ptx::mma_ts(tmem_base + DV_COL, pa + kk * 8, ptx::make_smem_desc(d0 + kk * 2048, kQPanelBytes, 1024),
+                      idesc_acc, (j > 0 || kk > 0));
+        }
+#pragma unroll
+        for (int kk = 0; kk < kQBlock / 16; ++kk) {
+          ptx::mma_ts(tmem_base + DK_COL, da + kk * 8, ptx::make_smem_desc(q0 + kk * 2048, kQPanelBytes, 1024),
+                      idesc_acc, (j > 0 || kk > 0));
+        }
+        ptx::mma_commit(x_empty + st);
+        ptx::mma_commit(s_free + buf);
+        if (!have_next) ptx::mma_commit(acc_full);
+      }
+      g = g_next; m = m_next;
+      have = have_next;
+    }
+    if (!ok && lane == 0 && !*cta_abort) raise_abort(cta_abort, p.status, kStTimeoutMma);
+  } else {
+    const int wq = warp;
+    const int r = wq * 32 + lane;        // key row inside the tile
+    const int key = n0 + r;
+    const bool key_ok = key < len;
+    const int kh = wq >> 1;              // which 64-key half
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(wq * 32) << 16);
+    bool dead = false;
+    if (!ptx::mbar_wait(kv_full, 0)) { raise_abort(cta_abort, p.status, kStTimeoutEpilogue); dead = true; }
+    if (!dead) {
+      // K~ = rn(k * fp32(0.5/sqrt(D))) in place; rows >= len -> 0 in K and V
+      const float sc = 0.5f * p.sm_scale;
+      for (int v = threadIdx.x; v < L::tile_bytes / 16; v += 128) {
+        const int vrow = ((v * 16) % kPanelBytes) / 128;
+        const bool keep = (n0 + vrow) < len;
+        uint4* pk = reinterpret_cast<uint4*>(sK) + v;
+        uint4 val = *pk;
+        T* e = reinterpret_cast<T*>(&val);
+#pragma unroll
+        for (int jj = 0; jj < 8; ++jj) e[jj] = DT<T>::from_f(keep ? DT<T>::to_f(e[jj]) * sc : 0.f);
+        *pk = val;
+        if (!keep) reinterpret_cast<uint4*>(sV)[v] = make_uint4(0, 0, 0, 0);
+      }
+      ptx::fence_proxy_async_smem();
+    }
+    ptx::mbar_arrive(k_ready);
+    QBlockScan scan(p.bmask_t, b, p.Hq, G, kvh, nt, n_qblocks, p.rows_padded, p.n_words);
+    int g, m, n_active = 0;
+    uint32_t flags;
+    for (int j = 0; scan.next(g, m, flags); ++j) {
+      const int buf = j & 1;
+      n_active = j + 1;
+      const size_t toff = (size_t)(b * p.Hq + kvh * G + g) * p.N;
+      // stage tau and delta of the 64 query rows of this block (double buffered)
+      float* td = s_td + buf * 128;
+      {
+        const int qrow = m * kQBlock + (threadIdx.x & 63);
+        const float* src = (threadIdx.x < 64) ? p.taus : p.delta;
+        td[threadIdx.x] = (qrow < len) ? src[toff + qrow] : 0.f;
+      }
+      ptx::bar_sync(1, 128);
+      if (dead || *cta_abort) { dead = true; continue; }
+      if (!ptx::mbar_wait(s_full + buf, (j >> 1) & 1)) { raise_abort(cta_abort, p.status, kStTimeoutEpilogue); dead = true; continue; }
+      ptx::tc_fence_after_sync();
+      const bool sub_on = (flags >> kh) & 1u;
+      const int q0 = m * kQBlock;
+      const bool need_mask = (q0 < n0 + kBlockN) || (q0 + kQBlock > len);  // diagonal or padded queries
+#pragma unroll 1
+      for (int ch = 0; ch < 2; ++ch) {
+        uint32_t rs[32], rp[32];
+        const uint32_t saddr = lane_addr + buf * kQBlock + ch * 32;
+        const uint32_t daddr = lane_addr + DP_COL0 + buf * kQBlock + ch * 32;
+        ptx::tmem_ld32(saddr, rs);
+        ptx::tmem_ld32(daddr, rp);
+        ptx::tmem_ld_wait();
+        const float* s = reinterpret_cast<const float*>(rs);
+        const float* dp = reinterpret_cast<const float*>(rp);
+        uint32_t pk[16], dk[16];
+#pragma unroll
+        for (int c = 0; c < 32; c += 2) {
+          const int qc = ch * 32 + c;
+          const float t0 = td[qc], t1 = td[qc + 1];
+          const float dl0 = td[64 + qc], dl1 = td[64 + qc + 1];
+          const int qrow = q0 + qc;
+          const bool ok0 = sub_on && key_ok && (!need_mask || (key <= qrow && qrow < len));
+          const bool ok1 = sub_on && key_ok && (!need_mask || (key <= qrow + 1 && qrow + 1 < len));
+          const float u0 = s[c] - t0, u1 = s[c + 1] - t1;
+          float p0 = 0.f, p1 = 0.f, d0 = 0.f, d1 = 0.f;
+          if (ok0 && u0 > 0.f) { p0 = u0 * u0; d0 = u0 * (dp[c] - dl0); }
+          if (ok1 && u1 > 0.f) { p1 = u1 * u1; d1 = u1 * (dp[c + 1] - dl1); }
+          pk[c >> 1] = pack2<T>(p0, p1);
+          dk[c >> 1] = pack2<T>(d0, d1);
+        }
+        ptx::tmem_st16(lane_addr + buf * kQBlock + ch * 16, pk);
+        ptx::tmem_st16(lane_addr + DP_COL0 + buf * kQBlock + ch * 16, dk);
+      }
+      ptx::tmem_st_wait();
+      ptx::tc_fence_before_sync();
+      ptx::mbar_arrive(p_full + buf);
+    }
+    if (!dead && n_active > 0) {
+      if (!ptx::mbar_wait(acc_full, 0)) { raise_abort(cta_abort, p.status, kStTimeoutEpilogue); dead = true; }
+    }
+    if (!dead && key < p.N) {
+      ptx::tc_fence_after_sync();
+#pragma unroll 1
+      for (int ch = 0; ch < D / 32; ++ch) {
+        uint32_t rk[32], rv[32];
+        if (n_active > 0) {
+          ptx::tmem_ld32(lane_addr + DK_COL + ch * 32, rk);
+          ptx::tmem_ld32(lane_addr + DV_COL + ch * 32, rv);
+          ptx::tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int c = 0; c < 32; ++c) { rk[c] = 0u; rv[c] = 0u; }
+        }
+        const float* fk = reinterpret_cast<const float*>(rk);
+        const float* fv = reinterpret_cast<const float*>(rv);
+        uint32_t pk[16], pv[16];
+#pragma unroll
+        for (int c = 0; c < 32; c += 2) {
+          pk[c >> 1] = key_ok ? pack2<T>(fk[c] * p.sm_scale, fk[c + 1] * p.sm_scale) : 0u;
+          pv[c >> 1] = key_ok ? pack2<T>(fv[c], fv[c + 1]) : 0u;
+        }
+        uint4* dst = reinterpret_cast<uint4*>(dkg + (size_t)key * D + ch * 32);
+        uint4* dst2 = reinterpret_cast<uint4*>(dvg + (size_t)key * D + ch * 32);
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          dst[q4] = make_uint4(pk[q4 * 4], pk[q4 * 4 + 1], pk[q4 * 4 + 2], pk[q4 * 4 + 3]);
+          dst2[q4] = make_uint4(pv[q4 * 4], pv[q4 * 4 + 1], pv[q4 * 4 + 2], pv[q4 * 4 + 3]);
+        }
+      }
+    }
+  }
+
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if (*cta_abort && threadIdx.x == 0) {
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);
+  }
+  __syncthreads();
+  if (warp == 5) {
+    ptx::tc_fence_after_sync();
+    ptx::tmem_dealloc(tmem_base, kDkvTmemCols);
+  }
+}
+
+}  // namespace sm100
+}  // namespace ads

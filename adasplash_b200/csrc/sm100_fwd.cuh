@@ -1,0 +1,360 @@
+// Sparse forward on the tensor cores (adasplash_v2.py:696-835).
+//
+// One CTA owns a 128-row query tile of one head and walks the 128-key tiles in
+// which the block mask has at least one of its four 64x64 bits set.  Per tile:
+//   S  = Q~ K^T            tcgen05.mma, operands in shared memory (TMA), fp32 in TMEM
+//   u  = max(S - tau, 0)   one thread per row reads its TMEM lane
+//   P  = rn(u*u), U = rn(u) written back over S in TMEM as 16-bit pairs
+//   O += P V, O2 += U V    tcgen05.mma with the A operand in TMEM, V in shared memory
+// S is double buffered so that the S product of tile j+1 overlaps the row work
+// of tile j.  Sub-tiles whose bit is clear contribute exactly zero, as in the
+// reference, which never visits them.
+#pragma once
+#include <type_traits>
+
+#include "sm100_common.cuh"
+
+namespace ads {
+namespace sm100 {
+
+constexpr int kFwdThreads = 192;  // 4 row warps + TMA warp + MMA warp
+constexpr int kFwdKStages = 2;
+constexpr int kFwdVStages = 3;
+constexpr int kFwdTmemCols = 512;
+
+template <int D>
+struct FwdSmem {
+  static constexpr int tile_bytes = (D / 64) * kPanelBytes;
+  static constexpr int q_off = 0;
+  static constexpr int k_off = tile_bytes;
+  static constexpr int v_off = k_off + kFwdKStages * tile_bytes;
+  static constexpr int bar_off = v_off + kFwdVStages * tile_bytes;
+  static constexpr int n_bars = 2 + 2 * kFwdKStages + 2 * kFwdVStages + 6 + 1;
+  static constexpr int misc_off = bar_off + n_bars * 8;
+  static constexpr size_t bytes = 1024 + misc_off + 64;
+};
+
+// Pack two fp32 values as 16-bit pairs (first value in the low half).
+template <typename T> __device__ __forceinline__ uint32_t pack2(float lo, float hi);
+template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+template <> __device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi) {
+  __half2 v = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Zero the rows [first_row, 128) of a swizzled 128-row tile (whole 128-byte rows,
+// so the swizzle does not matter).  Called by one full warp.
+__device__ __forceinline__ void zero_tile_rows(uint8_t* tile, int panels, int first_row, int lane) {
+  if (first_row < 0) first_row = 0;
+  const int nrows = 128 - first_row;
+  for (int pn = 0; pn < panels; ++pn) {
+    uint4* base = reinterpret_cast<uint4*>(tile + pn * kPanelBytes + first_row * 128);
+    for (int v = lane; v < nrows * 8; v += 32) base[v] = make_uint4(0, 0, 0, 0);
+  }
+  ptx::fence_proxy_async_smem();
+  __syncwarp();
+}
+
+template <typename T, int D>
+__global__ void __launch_bounds__(kFwdThreads, 1)
+fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+           const __grid_constant__ CUtensorMap tmV, TcParams p) {
+  using L = FwdSmem<D>;
+  constexpr int PANELS = D / 64;
+  constexpr int KSTEPS = D / 16;
+  constexpr int FMT = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
+  constexpr uint32_t O_COL = 256, O2_COL = 256 + D;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* sQ = smem + L::q_off;
+  uint8_t* sK = smem + L::k_off;
+  uint8_t* sV = smem + L::v_off;
+  uint64_t* bars = (uint64_t*)(smem + L::bar_off);
+  uint64_t* q_full = bars + 0;
+  uint64_t* q_ready = bars + 1;
+  uint64_t* k_full = bars + 2;
+  uint64_t* k_empty = k_full + kFwdKStages;
+  uint64_t* v_full = k_empty + kFwdKStages;
+  uint64_t* v_empty = v_full + kFwdVStages;
+  uint64_t* s_full = v_empty + kFwdVStages;
+  uint64_t* p_full = s_full + 2;
+  uint64_t* s_free = p_full + 2;
+  uint64_t* o_full = s_free + 2;
+  uint32_t* tmem_holder = (uint32_t*)(smem + L::misc_off);
+  volatile int* cta_abort = (volatile int*)(smem + L::misc_off + 4);
+  int* start_status = (int*)(smem + L::misc_off + 8);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int heads = p.B * p.Hq;
+  const int qt = p.nq - 1 - (int)(blockIdx.x / heads);
+  const int bh = blockIdx.x % heads;
+  const int b = bh / p.Hq, h = bh % p.Hq;
+  const int kvh = h / (p.Hq / p.Hkv);
+  const int len = load_len(p.varlen, p.varlen_is_i64, b, p.N);
+  const int m0 = qt * kBlockM;
+  T* og = (T*)p.out + (size_t)bh * p.N * D;
+  T* o2g = (T*)p.out2 + (size_t)bh * p.N * D;
+  if (m0 >= len) {
+    // fully padded query tile: its output rows are zero
+    for (int v = threadIdx.x; v < kBlockM * (D / 8); v += kFwdThreads) {
+      const int rr = m0 + v / (D / 8);
+      if (rr < p.N) {
+        reinterpret_cast<uint4*>(og + (size_t)rr * D)[v % (D / 8)] = make_uint4(0, 0, 0, 0);
+        reinterpret_cast<uint4*>(o2g + (size_t)rr * D)[v % (D / 8)] = make_uint4(0, 0, 0, 0);
+      }
+    }
+    return;
+  }
+  const int T_tiles = qt + 1;
+
+  if (threadIdx.x == 0) {
+    *start_status = *(volatile int*)p.status;
+    *cta_abort = 0;
+  }
+  const int32_t* bm_head = p.bmask + (size_t)bh * p.rows_padded * p.n_words;
+  if (warp == 5) {
+    if (lane == 0) {
+      ptx::mbar_init(q_full, 1);
+      ptx::mbar_init(q_ready, 128);
+      for (int s = 0; s < kFwdKStages; ++s) { ptx::mbar_init(k_full + s, 1); ptx::mbar_init(k_empty + s, 1); }
+      for (int s = 0; s < kFwdVStages; ++s) { ptx::mbar_init(v_full + s, 1); ptx::mbar_init(v_empty + s, 1); }
+      for (int s = 0; s < 2; ++s) {
+        ptx::mbar_init(s_full + s, 1);
+        ptx::mbar_init(p_full + s, 128);
+        ptx::mbar_init(s_free + s, 1);
+      }
+      ptx::mbar_init(o_full, 1);
+      ptx::fence_mbar_init();
+    }
+    __syncwarp();
+    ptx::tmem_alloc(tmem_holder, kFwdTmemCols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::tc_fence_after_sync();
+  if (*start_status != 0) {
+    if (warp == 5) ptx::tmem_dealloc(*tmem_holder, kFwdTmemCols);
+    return;
+  }
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 4) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      ptx::prefetch_tmap(&tmQ);
+      ptx::prefetch_tmap(&tmK);
+      ptx::prefetch_tmap(&tmV);
+      ptx::mbar_arrive_expect_tx(q_full, L::tile_bytes);
+      for (int pn = 0; pn < PANELS; ++pn) ptx::tma_load_3d(sQ + pn * kPanelBytes, &tmQ, q_full, pn * 64, m0, bh);
+      const int kv_head = b * p.Hkv + kvh;
+      TileScan scan(bm_head, qt, T_tiles, p.rows_padded, p.n_words);
+      int kt;
+      uint32_t flags;
+      for (int j = 0; scan.next(kt, flags); ++j) {
+        const int ks = j % kFwdKStages, vs = j % kFwdVStages;
+        if (*cta_abort) break;
+        if (!ptx::mbar_wait(k_empty + ks, ((j / kFwdKStages) & 1) ^ 1)) { raise_abort(cta_abort, p.status, kStTimeoutProducer); break; }
+        ptx::mbar_arrive_expect_tx(k_full + ks, L::tile_bytes);
+        for (int pn = 0; pn < PANELS; ++pn)
+          ptx::tma_load_3d(sK + ks * L::tile_bytes + pn * kPanelBytes, &tmK, k_full + ks, pn * 64, kt * kBlockN, kv_head);
+        if (!ptx::mbar_wait(v_empty + vs, ((j / kFwdVStages) & 1) ^ 1)) { raise_abort(cta_abort, p.status, kStTimeoutProducer); break; }
+        ptx::mbar_arrive_expect_tx(v_full + vs, L::tile_bytes);
+        for (int pn = 0; pn < PANELS; ++pn)
+          ptx::tma_load_3d(sV + vs * L::tile_bytes + pn * kPanelBytes, &tmV, v_full + vs, pn * 64, kt * kBlockN, kv_head);
+      }
+    }
+  } else if (warp == 5) {
+    // ---------------- MMA issuer (whole warp stays converged; lane 0 issues) ----------------
+    constexpr uint32_t idesc_s = ptx::make_idesc(FMT, kBlockM, kBlockN, 0, 0);
+    constexpr uint32_t idesc_pv = ptx::make_idesc(FMT, kBlockM, D, 0, 1);
+    bool ok = true;
+    if (lane == 0) ok = ptx::mbar_wait(q_ready, 0);
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    if (!ok && lane == 0) raise_abort(cta_abort, p.status, kStTimeoutMma);
+
+    auto issue_s = [&](int j) -> bool {  // lane 0 only
+      const int ks = j % kFwdKStages, buf = j & 1;
+      if (!ptx::mbar_wait(k_full + ks, (j / kFwdKStages) & 1) ||
+          !ptx::mbar_wait(s_free + buf, ((j >> 1) & 1) ^ 1))
+        return false;
+      ptx::tc_fence_after_sync();
+      const uint32_t a0 = ptx::smem_u32(sQ), b0 = ptx::smem_u32(sK + ks * L::tile_bytes);
+      const uint32_t d = tmem_base + buf * kBlockN;
+#pragma unroll
+      for (int kk = 0; kk < KSTEPS; ++kk) {
+        const uint32_t off = (kk >> 2) * kPanelBytes + (kk & 3) * 32;
+        ptx::mma_ss(d, ptx::make_smem_desc(a0 + off, 16, 1024), ptx::make_smem_desc(b0 + off, 16, 1024),
+                    idesc_s, kk > 0);
+      }
+      ptx::mma_commit(k_empty + ks);
+      ptx::mma_commit(s_full + buf);
+      return true;
+    };
+
+    TileScan scan(bm_head, qt, T_tiles, p.rows_padded, p.n_words);
+    int kt, kt_next = 0;
+    uint32_t flags;
+    bool have = scan.next(kt, flags);
+    if (ok && have) {
+      if (lane == 0) ok = issue_s(0);
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+    }
+    int j = 0;
+    for (; ok && have; ++j) {
+      const int vs = j % kFwdVStages, buf = j & 1;
+      const bool have_next = scan.next(kt_next, flags);
+      if (*cta_abort) { ok = false; break; }
+      if (lane == 0) {
+        if (have_next) ok = issue_s(j + 1);
+        if (ok) ok = ptx::mbar_wait(v_full + vs, (j / kFwdVStages) & 1);
+      }
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) break;
+      uint8_t* vt = sV + vs * L::tile_bytes;
+      if ((kt + 1) * kBlockN > len) zero_tile_rows(vt, PANELS, len - kt * kBlockN, lane);  // padded keys: V = 0
+      if (lane == 0) {
+        ok = ptx::mbar_wait(p_full + buf, (j >> 1) & 1);
+        if (ok) {
+          ptx::tc_fence_after_sync();
+          const uint32_t v0 = ptx::smem_u32(vt);
+          const uint32_t pbase = tmem_base + buf * kBlockN;
+#pragma unroll
+          for (int kk = 0; kk < kBlockN / 16; ++kk) {
+            const uint64_t bd = ptx::make_smem_desc(v0 + kk * 2048, kPanelBytes, 1024);
+            const uint32_t pa = pbase + (kk >> 1) * 32 + (kk & 1) * 8;
+            ptx::mma_ts(tmem_base + O_COL, pa, bd, idesc_pv, (j > 0 || kk > 0));
+            ptx::mma_ts(tmem_base + O2_COL, pa + 16, bd, idesc_pv, (j > 0 || kk > 0));
+          }
+          ptx::mma_commit(v_empty + vs);
+          ptx::mma_commit(s_free + buf);
+          if (!have_next) ptx::mma_commit(o_full);
+        }
+      }
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      kt = kt_next;
+      have = have_next;
+    }
+    if (!ok && lane == 0 && !*cta_abort) raise_abort(cta_abort, p.status, kStTimeoutMma);
+  } else {
+    // ---------------- row warps: one score row per thread ----------------
+    const int wq = warp;  // TMEM lanes 32*wq .. 32*wq+31
+    const int r = wq * 32 + lane;
+    const int row = m0 + r;
+    const bool row_ok = row < len;
+    const int rb = wq >> 1;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(wq * 32) << 16);
+    bool dead = false;
+    if (!ptx::mbar_wait(q_full, 0)) { raise_abort(cta_abort, p.status, kStTimeoutEpilogue); dead = true; }
+    if (!dead) {
+      const float sc = 0.5f * p.sm_scale;
+      for (int v = threadIdx.x; v < L::tile_bytes / 16; v += 128) {
+        uint4* ptr = reinterpret_cast<uint4*>(sQ) + v;
+        const int vrow = ((v * 16) % kPanelBytes) / 128;
+        uint4 val = *ptr;
+        T* e = reinterpret_cast<T*>(&val);
+        const bool keep = (m0 + vrow) < len;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) e[j] = DT<T>::from_f(keep ? DT<T>::to_f(e[j]) * sc : 0.f);
+        *ptr = val;
+      }
+      ptx::fence_proxy_async_smem();
+    }
+    ptx::mbar_arrive(q_ready);
+    const float tau = row_ok ? p.taus[(size_t)bh * p.N + row] : 0.f;
+    float supp = 0.f;
+    TileScan scan(bm_head, qt, T_tiles, p.rows_padded, p.n_words);
+    int kt, n_active = 0;
+    uint32_t flags;
+    for (int j = 0; !dead && scan.next(kt, flags); ++j) {
+      const int buf = j & 1;
+      n_active = j + 1;
+      const uint32_t my_flags = (flags >> (2 * rb)) & 3u;  // bit0: keys 0..63, bit1: keys 64..127
+      if (*cta_abort) { dead = true; break; }
+      if (!ptx::mbar_wait(s_full + buf, (j >> 1) & 1)) { raise_abort(cta_abort, p.status, kStTimeoutEpilogue); dead = true; break; }
+      ptx::tc_fence_after_sync();
+      const int n0 = kt * kBlockN;
+      const bool need_mask = (kt == qt) || (n0 + kBlockN > len);
+#pragma unroll 1
+      for (int ch = 0; ch < 4; ++ch) {
+        uint32_t raw[32];
+        const uint32_t caddr = lane_addr + buf * kBlockN + ch * 32;
+        ptx::tmem_ld32(caddr, raw);
+        ptx::tmem_ld_wait();
+        const float* v = reinterpret_cast<const float*>(raw);
+        const bool sub_on = (my_flags >> (ch >> 1)) & 1u;
+        uint32_t pk[16], uk[16];
+#pragma unroll
+        for (int c = 0; c < 32; c += 2) {
+          float u0 = fmaxf(v[c] - tau, 0.f), u1 = fmaxf(v[c + 1] - tau, 0.f);
+          if (need_mask) {
+            const int col = n0 + ch * 32 + c;
+            if (!(col <= row && col < len)) u0 = 0.f;
+            if (!(col + 1 <= row && col + 1 < len)) u1 = 0.f;
+          }
+          if (!sub_on) { u0 = 0.f; u1 = 0.f; }
+          supp += u0 + u1;
+          pk[c >> 1] = pack2<T>(u0 * u0, u1 * u1);
+          uk[c >> 1] = pack2<T>(u0, u1);
+        }
+        ptx::tmem_st16(caddr, pk);
+        ptx::tmem_st16(caddr + 16, uk);
+      }
+      ptx::tmem_st_wait();
+      ptx::tc_fence_before_sync();
+      ptx::mbar_arrive(p_full + buf);
+    }
+    // epilogue: O, O2 -> global
+    if (!dead && n_active > 0) {
+      if (!ptx::mbar_wait(o_full, 0)) { raise_abort(cta_abort, p.status, kStTimeoutEpilogue); dead = true; }
+    }
+    if (!dead && row < p.N) {
+      ptx::tc_fence_after_sync();
+      const float inv = (row_ok && supp > 0.f) ? 1.0f / supp : 0.f;
+#pragma unroll 1
+      for (int ch = 0; ch < D / 32; ++ch) {
+        uint32_t ro[32], ro2[32];
+        if (n_active > 0) {
+          ptx::tmem_ld32(lane_addr + O_COL + ch * 32, ro);
+          ptx::tmem_ld32(lane_addr + O2_COL + ch * 32, ro2);
+          ptx::tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int c = 0; c < 32; ++c) { ro[c] = 0u; ro2[c] = 0u; }
+        }
+        const float* fo = reinterpret_cast<const float*>(ro);
+        const float* fo2 = reinterpret_cast<const float*>(ro2);
+        uint32_t po[16], po2[16];
+#pragma unroll
+        for (int c = 0; c < 32; c += 2) {
+          po[c >> 1] = row_ok ? pack2<T>(fo[c], fo[c + 1]) : 0u;
+          po2[c >> 1] = row_ok ? pack2<T>(fo2[c] * inv, fo2[c + 1] * inv) : 0u;
+        }
+        uint4* dst = reinterpret_cast<uint4*>(og + (size_t)row * D + ch * 32);
+        uint4* dst2 = reinterpret_cast<uint4*>(o2g + (size_t)row * D + ch * 32);
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          dst[q4] = make_uint4(po[q4 * 4], po[q4 * 4 + 1], po[q4 * 4 + 2], po[q4 * 4 + 3]);
+          dst2[q4] = make_uint4(po2[q4 * 4], po2[q4 * 4 + 1], po2[q4 * 4 + 2], po2[q4 * 4 + 3]);
+        }
+      }
+    }
+  }
+
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if (*cta_abort && threadIdx.x == 0) {
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);
+  }
+  __syncthreads();
+  if (warp == 5) {
+    ptx::tc_fence_after_sync();
+    ptx::tmem_dealloc(tmem_base, kFwdTmemCols);
+  }
+}
+
+}  // namespace sm100
+}  // namespace ads

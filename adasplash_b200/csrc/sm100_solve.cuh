@@ -1,0 +1,320 @@
+// Threshold solver + block-mask builder on the tensor cores.
+//
+// One CTA owns a 128-row query tile of one head and sweeps the causal key range
+// (niter + 3) times without leaving the SM: the scaled Q tile stays in shared
+// memory, K tiles arrive by TMA through a 4-stage ring, S = Q~ K^T is produced by
+// tcgen05.mma into two 128x128 fp32 TMEM buffers, and two 128-thread epilogue
+// groups (one TMEM lane = one score row = one thread) alternate on the buffers,
+// so the row statistics of tile i overlap the MMA of tile i+1.
+//
+// Sweeps (adasplash_v2.py:151-681): row max -> tau0; BINS-bin histogram -> tau1;
+// niter Halley/bisection steps; a last sweep that records, per 64x64 sub-tile,
+// whether any score exceeds the tau entering the sweep, then one more step.
+#pragma once
+#include <type_traits>
+
+#include "sm100_common.cuh"
+
+namespace ads {
+namespace sm100 {
+
+constexpr int kSolveStages = 4;
+constexpr int kSolveThreads = 320;  // 8 epilogue warps + TMA warp + MMA warp
+constexpr int kSolveTmemCols = 256;
+
+enum SweepMode : int { kModeMax = 0, kModeHist = 1, kModeHalley = 2, kModeFinal = 3 };
+
+template <int D>
+struct SolveSmem {
+  static constexpr int tile_bytes = (D / 64) * kPanelBytes;
+  static constexpr int q_off = 0;
+  static constexpr int k_off = tile_bytes;
+  static constexpr int bar_off = k_off + kSolveStages * tile_bytes;
+  static constexpr int n_bars = 2 + 2 * kSolveStages + 4;
+  static constexpr int misc_off = bar_off + n_bars * 8;           // tmem base, abort flag, status
+  static constexpr int xchg_off = misc_off + 64;                  // [2][2][8][128] floats
+  static constexpr int bits_off = xchg_off + 2 * 2 * 8 * 128 * 4; // [2][n_words] words
+  static size_t bytes(int n_words) { return 1024 + bits_off + 2 * (size_t)n_words * 4; }
+};
+
+template <typename T, int D>
+__global__ void __launch_bounds__(kSolveThreads, 1)
+solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+             TcParams p) {
+  using L = SolveSmem<D>;
+  constexpr int PANELS = D / 64;
+  constexpr int KSTEPS = D / 16;
+  constexpr int FMT = sizeof(T) == 2 && std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* sQ = smem + L::q_off;
+  uint8_t* sK = smem + L::k_off;
+  uint64_t* bars = (uint64_t*)(smem + L::bar_off);
+  uint64_t* q_full = bars + 0;
+  uint64_t* q_ready = bars + 1;
+  uint64_t* k_full = bars + 2;
+  uint64_t* k_empty = k_full + kSolveStages;
+  uint64_t* s_full = k_empty + kSolveStages;
+  uint64_t* s_free = s_full + 2;
+  uint32_t* tmem_holder = (uint32_t*)(smem + L::misc_off);
+  volatile int* cta_abort = (volatile int*)(smem + L::misc_off + 4);
+  int* start_status = (int*)(smem + L::misc_off + 8);
+  float* xchg = (float*)(smem + L::xchg_off);
+  uint32_t* s_bits = (uint32_t*)(smem + L::bits_off);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int heads = p.B * p.Hq;
+  const int qt = p.nq - 1 - (int)(blockIdx.x / heads);  // heaviest tiles first
+  const int bh = blockIdx.x % heads;
+  const int b = bh / p.Hq, h = bh % p.Hq;
+  const int kvh = h / (p.Hq / p.Hkv);
+  const int len = load_len(p.varlen, p.varlen_is_i64, b, p.N);
+  const int m0 = qt * kBlockM;
+  if (m0 >= len) return;
+  const int T_tiles = qt + 1;  // 128-key tiles up to the diagonal (= up to len for the last valid tile)
+  const int nsweeps = p.tau_given ? 1 : p.niter + 3;
+  const int total = nsweeps * T_tiles;
+
+  if (threadIdx.x == 0) {
+    *start_status = *(volatile int*)p.status;
+    *cta_abort = 0;
+  }
+  if (warp == 9) {
+    if (lane == 0) {
+      ptx::mbar_init(q_full, 1);
+      ptx::mbar_init(q_ready, 256);
+      for (int s = 0; s < kSolveStages; ++s) { ptx::mbar_init(k_full + s, 1); ptx::mbar_init(k_empty + s, 1); }
+      for (int s = 0; s < 2; ++s) { ptx::mbar_init(s_full + s, 1); ptx::mbar_init(s_free + s, 128); }
+      ptx::fence_mbar_init();
+    }
+    __syncwarp();
+    ptx::tmem_alloc(tmem_holder, kSolveTmemCols);
+    ptx::tmem_relinquish();
+  }
+  for (int w = threadIdx.x; w < 2 * p.n_words; w += kSolveThreads) s_bits[w] = 0u;
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::tc_fence_after_sync();
+  if (*start_status != 0) {  // an earlier CTA of this launch already failed: do nothing
+    if (warp == 9) ptx::tmem_dealloc(*tmem_holder, kSolveTmemCols);
+    return;
+  }
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 8) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      ptx::prefetch_tmap(&tmQ);
+      ptx::prefetch_tmap(&tmK);
+      ptx::mbar_arrive_expect_tx(q_full, L::tile_bytes);
+      for (int pn = 0; pn < PANELS; ++pn) ptx::tma_load_3d(sQ + pn * kPanelBytes, &tmQ, q_full, pn * 64, m0, bh);
+      const int kv_head = b * p.Hkv + kvh;
+      for (int i = 0; i < total; ++i) {
+        const int st = i % kSolveStages, kt = i % T_tiles;
+        if (*cta_abort) break;
+        if (!ptx::mbar_wait(k_empty + st, ((i / kSolveStages) & 1) ^ 1)) {
+          raise_abort(cta_abort, p.status, kStTimeoutProducer);
+          break;
+        }
+        ptx::mbar_arrive_expect_tx(k_full + st, L::tile_bytes);
+        for (int pn = 0; pn < PANELS; ++pn)
+          ptx::tma_load_3d(sK + st * L::tile_bytes + pn * kPanelBytes, &tmK, k_full + st, pn * 64,
+                           kt * kBlockN, kv_head);
+      }
+    }
+  } else if (warp == 9) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = ptx::make_idesc(FMT, kBlockM, kBlockN, 0, 0);
+      bool ok = ptx::mbar_wait(q_ready, 0);
+      if (!ok) raise_abort(cta_abort, p.status, kStTimeoutMma);
+      for (int i = 0; ok && i < total; ++i) {
+        const int st = i % kSolveStages, buf = i & 1;
+        if (*cta_abort) break;
+        if (!ptx::mbar_wait(k_full + st, (i / kSolveStages) & 1) ||
+            !ptx::mbar_wait(s_free + buf, ((i >> 1) & 1) ^ 1)) {
+          raise_abort(cta_abort, p.status, kStTimeoutMma);
+          break;
+        }
+        ptx::tc_fence_after_sync();
+        const uint32_t a0 = ptx::smem_u32(sQ), b0 = ptx::smem_u32(sK + st * L::tile_bytes);
+        const uint32_t d = tmem_base + buf * kBlockN;
+#pragma unroll
+        for (int kk = 0; kk < KSTEPS; ++kk) {
+          const uint32_t off = (kk >> 2) * kPanelBytes + (kk & 3) * 32;
+          ptx::mma_ss(d, ptx::make_smem_desc(a0 + off, 16, 1024), ptx::make_smem_desc(b0 + off, 16, 1024),
+                      idesc, kk > 0);
+        }
+        ptx::mma_commit(k_empty + st);
+        ptx::mma_commit(s_full + buf);
+      }
+    }
+  } else {
+    // ---------------- epilogue: 2 groups x 128 threads, one score row per thread ----------------
+    const int wg = warp >> 2, wq = warp & 3;
+    const int r = wq * 32 + lane;
+    const int row = m0 + r;
+    const bool row_ok = row < len;
+    const int rb = wq >> 1;
+    bool dead = false;
+    // scale Q by fp32(0.5/sqrt(D)) and round to the input dtype, in place; rows >= len -> 0
+    if (!ptx::mbar_wait(q_full, 0)) { raise_abort(cta_abort, p.status, kStTimeoutEpilogue); dead = true; }
+    if (!dead) {
+      const float sc = 0.5f * p.sm_scale;
+      for (int v = threadIdx.x; v < L::tile_bytes / 16; v += 256) {
+        uint4* ptr = reinterpret_cast<uint4*>(sQ) + v;
+        const int vrow = ((v * 16) % kPanelBytes) / 128;
+        uint4 val = *ptr;
+        T* e = reinterpret_cast<T*>(&val);
+        const bool keep = (m0 + vrow) < len;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) e[j] = DT<T>::from_f(keep ? DT<T>::to_f(e[j]) * sc : 0.f);
+        *ptr = val;
+      }
+      ptx::fence_proxy_async_smem();
+    }
+    ptx::mbar_arrive(q_ready);
+
+    float mx = -1.0e3f, tau0 = 0.f;
+    int cnt[8];
+    HalleyState hs;
+    hs.t = hs.lo = hs.hi = 0.f;
+    if (p.tau_given) {
+      hs.t = row_ok ? p.taus[((size_t)bh) * p.N + row] : 0.f;
+    }
+    const float fbins = (float)p.bins;
+    for (int s = 0; s < nsweeps; ++s) {
+      const int mode = p.tau_given ? kModeFinal : (s == 0 ? kModeMax : (s == 1 ? kModeHist : (s == nsweeps - 1 ? kModeFinal : kModeHalley)));
+      float a0 = 0.f, a1 = 0.f, a2 = 0.f;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) cnt[c] = 0;
+      for (int kt = 0; kt < T_tiles; ++kt) {
+        const int i = s * T_tiles + kt;
+        if ((i & 1) != wg) continue;
+        if (dead || *cta_abort) { dead = true; continue; }
+        if (!ptx::mbar_wait(s_full + wg, (i >> 1) & 1)) {
+          raise_abort(cta_abort, p.status, kStTimeoutEpilogue);
+          dead = true;
+          continue;
+        }
+        ptx::tc_fence_after_sync();
+        const int n0 = kt * kBlockN;
+        const bool need_mask = (kt == qt) || (n0 + kBlockN > len);
+        float a2_mark = a2;  // support count at the start of the current 64-key half
+        bool hit0 = false, hit1 = false;
+#pragma unroll 1
+        for (int ch = 0; ch < 4; ++ch) {
+          uint32_t raw[32];
+          ptx::tmem_ld32(tmem_base + ((uint32_t)(wq * 32) << 16) + wg * kBlockN + ch * 32, raw);
+          ptx::tmem_ld_wait();
+          float* v = reinterpret_cast<float*>(raw);
+          if (need_mask) {
+#pragma unroll
+            for (int c = 0; c < 32; ++c) {
+              const int col = n0 + ch * 32 + c;
+              v[c] = (col <= row && col < len) ? v[c] : kMaskedScore;
+            }
+          }
+          if (mode == kModeMax) {
+#pragma unroll
+            for (int c = 0; c < 32; c += 2) mx = ptx::fmax3(mx, v[c], v[c + 1]);
+          } else if (mode == kModeHist) {
+#pragma unroll
+            for (int g8 = 0; g8 < 4; ++g8) {
+              float cm = ptx::fmax3(v[g8 * 8], v[g8 * 8 + 1], v[g8 * 8 + 2]);
+              cm = ptx::fmax3(cm, v[g8 * 8 + 3], v[g8 * 8 + 4]);
+              cm = ptx::fmax3(cm, v[g8 * 8 + 5], v[g8 * 8 + 6]);
+              cm = fmaxf(cm, v[g8 * 8 + 7]);
+              if (cm >= tau0) {
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                  const float pr = (v[g8 * 8 + c] - tau0) * fbins;
+#pragma unroll
+                  for (int bb = 0; bb < 8; ++bb) cnt[bb] += (pr >= (float)bb) ? 1 : 0;
+                }
+              }
+            }
+          } else {
+            if (ch == 2) { hit0 = a2 > a2_mark; a2_mark = a2; }
+#pragma unroll
+            for (int c = 0; c < 32; ++c) {
+              const float u = __saturatef(v[c] - hs.t);
+              a0 = fmaf(u, u, a0);
+              a1 += u;
+              a2 += (u > 0.f) ? 1.f : 0.f;
+            }
+          }
+        }
+        ptx::tc_fence_before_sync();
+        ptx::mbar_arrive(s_free + wg);
+        if (mode == kModeFinal) {
+          hit1 = a2 > a2_mark;
+          const bool any0 = __any_sync(0xffffffffu, hit0 && row_ok);
+          const bool any1 = __any_sync(0xffffffffu, hit1 && row_ok);
+          if (lane == 0) {
+            const int kb = 2 * kt;
+            if (any0) atomicOr(&s_bits[rb * p.n_words + (kb >> 5)], 1u << (kb & 31));
+            if (any1) atomicOr(&s_bits[rb * p.n_words + ((kb + 1) >> 5)], 1u << ((kb + 1) & 31));
+          }
+        }
+      }
+      // combine the two groups' partial statistics of this sweep
+      float* xb = xchg + (s & 1) * (2 * 8 * 128);
+      float* mine = xb + wg * (8 * 128);
+      if (mode == kModeMax) {
+        mine[r] = mx;
+      } else if (mode == kModeHist) {
+#pragma unroll
+        for (int c = 0; c < 8; ++c) mine[c * 128 + r] = __int_as_float(cnt[c]);
+      } else {
+        mine[r] = a0; mine[128 + r] = a1; mine[256 + r] = a2;
+      }
+      ptx::bar_sync(1, 256);
+      const float* o0 = xb;
+      const float* o1 = xb + 8 * 128;
+      if (mode == kModeMax) {
+        mx = fmaxf(o0[r], o1[r]);
+        tau0 = mx - 1.0f;
+      } else if (mode == kModeHist) {
+        int bins_cnt[8];
+        int cum[9];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) cum[c] = __float_as_int(o0[c * 128 + r]) + __float_as_int(o1[c * 128 + r]);
+        cum[8] = 0;
+        for (int c = 0; c < p.bins; ++c) bins_cnt[c] = cum[c] - (c + 1 < p.bins ? cum[c + 1] : 0);
+        const float t1 = hist_tau_alpha15<8>(bins_cnt, p.bins, tau0);
+        hs.lo = t1;
+        hs.hi = t1 + 1.0f / fbins;
+        hs.t = 0.5f * (hs.lo + hs.hi);
+      } else if (!p.tau_given) {
+        halley_bisect_update(hs, o0[r] + o1[r], o0[128 + r] + o1[128 + r], o0[256 + r] + o1[256 + r]);
+      }
+    }
+    ptx::bar_sync(1, 256);  // every atomicOr on s_bits is done
+    if (!*cta_abort) {
+      for (int t = threadIdx.x; t < 2 * p.n_words; t += 256) {
+        const int rbi = t / p.n_words, w = t % p.n_words;
+        const int mrow = 2 * qt + rbi;
+        if (mrow < p.rows_padded) p.bmask[((size_t)bh * p.rows_padded + mrow) * p.n_words + w] = (int32_t)s_bits[t];
+      }
+      if (!p.tau_given && wg == 0 && row_ok) p.taus[(size_t)bh * p.N + row] = hs.t;
+    }
+  }
+
+  // ---------------- teardown ----------------
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if (*cta_abort && threadIdx.x == 0) {
+    // give copies that may still be in flight a bounded time to land before the
+    // shared memory of this CTA is handed to the next one
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);
+  }
+  __syncthreads();
+  if (warp == 9) {
+    ptx::tc_fence_after_sync();
+    ptx::tmem_dealloc(tmem_base, kSolveTmemCols);
+  }
+}
+
+}  // namespace sm100
+}  // namespace ads

@@ -113,6 +113,12 @@ int adasplash2_bwd(const void* q, const void* k, const void* v, const void* dout
                    void* dv, const ads_attn_shape* shape, void* workspace,
                    size_t workspace_bytes, void* stream);
 
+/* Debug aid, the one entry point that synchronises: waits for `stream`, reads
+ * the status word that the tensor-core kernels keep at the start of `workspace`
+ * and returns ADS_ERR_TIMEOUT if a bounded device-side wait gave up (the code is
+ * in the error string), ADS_OK otherwise.  No counterpart in the reference. */
+int adasplash2_check_status(const void* workspace, void* stream);
+
 /* Which kernel family `ADS_PATH_AUTO` resolves to for `shape`
  * (ADS_PATH_SIMT or ADS_PATH_TCGEN05). */
 int adasplash2_resolved_path(const ads_attn_shape* shape);

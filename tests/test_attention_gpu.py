@@ -26,7 +26,9 @@ def _randn(shape, seed, scale=1.0, dtype=torch.float32):
 
 @pytest.fixture(autouse=True)
 def _reset_path():
+    att.DEBUG_STATUS = True   # every call also checks the kernels' bounded-wait status word
     yield
+    att.DEBUG_STATUS = False
     _lib.set_kernel_path(None)
 
 
@@ -83,9 +85,10 @@ def test_fp32_matches_exact_definition(path, case):
         assert (got[key].double() - ex[key]).abs().max() < 1e-4, key
     if vl is not None:
         for b in range(B):
-            assert got["out"][b, :, vl[b]:].abs().max() == 0
-            assert got["dq"][b, :, vl[b]:].abs().max() == 0
-            assert got["dk"][b, :, vl[b]:].abs().max() == 0
+            if vl[b] < N:
+                assert got["out"][b, :, vl[b]:].abs().max() == 0
+                assert got["dq"][b, :, vl[b]:].abs().max() == 0
+                assert got["dk"][b, :, vl[b]:].abs().max() == 0
 
 
 @pytest.mark.parametrize("path", PATHS)
@@ -106,9 +109,9 @@ def test_16bit_matches_trajectory_oracle(path, dtype, case):
         L = N if vl is None else vl[b]
         assert (got["tau"][b, :, :L] - tr["tau"][b, :, :L]).abs().max() < 1e-4
     assert (got["bmask"] == tr["bmask"]).all()
-    tol = 2e-2
     for key in ("out", "out2", "dq", "dk", "dv"):
-        assert (got[key] - tr[key]).abs().max() < tol, key
+        scale = max(1.0, tr[key].abs().max().item())
+        assert (got[key] - tr[key]).abs().max() < 2e-2 * scale, key
 
 
 @pytest.mark.parametrize("path", PATHS)
@@ -163,12 +166,33 @@ def test_reference_golden(path, name, tol):
     _use(path, fx["q"])
     got = _run(fx["q"], fx["k"], fx["v"], fx["dout"], fx["niter"], fx["varlen"])
     N = fx["q"].shape[2]
+    keys = ("out", "dq", "dk", "dv") if fx["dq"] is not None else ("out",)
     for b in range(fx["q"].shape[0]):
         L = N if fx["varlen"] is None else int(fx["varlen"][b])
         assert (got["tau"][b, :, :L] - fx["taus"][b, :, :L]).abs().max() < 1e-4
     assert (got["bmask"] == fx["bmask"]).all()
-    for key in ("out", "dq", "dk", "dv"):
-        assert (got[key] - fx[key].float()).abs().max() < tol, key
+    assert (got["out"] - fx["out"].float()).abs().max() < tol
+    if len(keys) > 1:
+        _check_grads_vs_reference(got, fx, tol)
+
+
+def _check_grads_vs_reference(got, fx, tol):
+    """Gradients against the reference's own.  In 16-bit the reference forms
+    delta = rowsum(out2*dO) in the input dtype (adasplash_v2.py:891), which costs it
+    about two digits; this library accumulates delta in fp32.  So the 16-bit check is
+    (i) agreement within `tol` relative to the gradient's scale and (ii) being at
+    least as close to the exact fp64 gradients as the reference is."""
+    exact = None
+    if fx["q"].dtype != torch.float32:
+        exact = O.dense_entmax_attention(fx["q"], fx["k"], fx["v"], 1.5, True, fx["varlen"], fx["dout"])
+    for key in ("dq", "dk", "dv"):
+        ref = fx[key].float()
+        scale = max(1.0, ref.abs().max().item()) if exact is not None else 1.0
+        assert (got[key] - ref).abs().max() < tol * scale, key
+        if exact is not None:
+            mine = (got[key].double() - exact[key]).abs().max().item()
+            theirs = (ref.double() - exact[key]).abs().max().item()
+            assert mine <= 1.25 * theirs + 1e-3, (key, mine, theirs)
 
 
 @pytest.mark.parametrize("path", ["tcgen05"])
@@ -189,7 +213,8 @@ def test_tensor_core_path_matches_cuda_core_path(path):
     diff_words = (a["bmask"] != b["bmask"]).sum().item()
     assert diff_words == 0
     for key in ("out", "out2", "dq", "dk", "dv"):
-        assert (a[key] - b[key]).abs().max() < 2e-2, key
+        scale = max(1.0, b[key].abs().max().item())
+        assert (a[key] - b[key]).abs().max() < 2e-2 * scale, key
 
 
 def test_c_abi_error_codes_on_device():

@@ -95,8 +95,11 @@ def test_v2_oracle_vs_reference_golden(name, tol_out, tol_grad):
         assert (tr["tau"][b, :, :L] - fx["taus"][b, :, :L]).abs().max() < 1e-5, "tau"
     assert (tr["bmask"] == fx["bmask"]).all(), "bitmap"
     assert (tr["out"] - fx["out"].float()).abs().max() < tol_out
-    for key in ("dq", "dk", "dv"):
-        assert (tr[key] - fx[key].float()).abs().max() < tol_grad, key
+    for key in (("dq", "dk", "dv") if fx["dq"] is not None else ()):
+        # 16-bit: the reference forms delta in the input dtype (adasplash_v2.py:891),
+        # the oracle in fp32, so gradients agree to the tolerance times their scale
+        scale = 1.0 if fx["q"].dtype == torch.float32 else max(1.0, fx[key].float().abs().max().item())
+        assert (tr[key] - fx[key].float()).abs().max() < tol_grad * scale, key
     # and the exact definition, at the reference's own test tolerance for fp32
     if fx["q"].dtype == torch.float32 and fx["niter"] == 10:
         ex = O.dense_entmax_attention(fx["q"], fx["k"], fx["v"], 1.5, True, vl, fx["dout"])
