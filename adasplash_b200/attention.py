@@ -145,27 +145,51 @@ class _SparseAttention(torch.autograd.Function):
     @staticmethod
     def backward(ctx, do):
         q, k, v, out2, taus, bmask = ctx.saved_tensors
-        varlen = ctx.varlen
-        lib = _lib.load()
         do = do.contiguous()
         if do.dtype != q.dtype:
             do = do.to(q.dtype)
-        shape = make_shape(q, k, ctx.niter, varlen)
-        dev = q.device
-        delta = torch.empty(taus.shape, device=dev, dtype=torch.float32)
-        bmask_t = torch.empty_like(bmask)
-        dq = torch.empty_like(q)
-        dk = torch.empty_like(k)
-        dv = torch.empty_like(v)
-        with torch.cuda.device(dev):
-            ws, nbytes = _workspace(shape, dev)
-            st = torch.cuda.current_stream().cuda_stream
-            _lib.check(lib.adasplash2_bwd(_ptr(q), _ptr(k), _ptr(v), _ptr(do), _ptr(out2),
-                                          _ptr(varlen), _ptr(taus), _ptr(bmask), _ptr(bmask_t),
-                                          _ptr(delta), _ptr(dq), _ptr(dk), _ptr(dv),
-                                          ctypes.byref(shape), _ptr(ws), nbytes, st))
-            _maybe_check(ws, st)
+        dq, dk, dv, _, _ = backward_raw(q, k, v, do, out2, taus, bmask, ctx.varlen, ctx.niter)
         return dq, dk, dv, None, None
+
+
+def forward_raw(q, k, v, taus, bmask, varlen=None, path=None):
+    """`adasplash2_fwd` alone for given thresholds and block mask: (out, out2)."""
+    lib = _lib.load()
+    shape = make_shape(q, k, 0, varlen, path)
+    out = torch.empty_like(q)
+    out2 = torch.empty_like(q)
+    with torch.cuda.device(q.device):
+        ws, nbytes = _workspace(shape, q.device)
+        st = torch.cuda.current_stream().cuda_stream
+        _lib.check(lib.adasplash2_fwd(_ptr(q), _ptr(k), _ptr(v), _ptr(varlen), _ptr(taus),
+                                      _ptr(bmask), _ptr(out), _ptr(out2), ctypes.byref(shape),
+                                      _ptr(ws), nbytes, st))
+        _maybe_check(ws, st)
+    return out, out2
+
+
+def backward_raw(q, k, v, do, out2, taus, bmask, varlen=None, niter=1, stages=0, buffers=None,
+                 path=None):
+    """`adasplash2_bwd`: returns (dq, dk, dv, delta, bmask_t).  `stages` != 0 runs only
+    the named kernels (ADS_BWD_* mask; a measurement aid), reusing `buffers` =
+    (dq, dk, dv, delta, bmask_t) from an earlier full call."""
+    lib = _lib.load()
+    shape = make_shape(q, k, niter, varlen, path)
+    shape.bwd_stages = int(stages)
+    dev = q.device
+    if buffers is None:
+        buffers = (torch.empty_like(q), torch.empty_like(k), torch.empty_like(v),
+                   torch.empty(taus.shape, device=dev, dtype=torch.float32), torch.empty_like(bmask))
+    dq, dk, dv, delta, bmask_t = buffers
+    with torch.cuda.device(dev):
+        ws, nbytes = _workspace(shape, dev)
+        st = torch.cuda.current_stream().cuda_stream
+        _lib.check(lib.adasplash2_bwd(_ptr(q), _ptr(k), _ptr(v), _ptr(do), _ptr(out2),
+                                      _ptr(varlen), _ptr(taus), _ptr(bmask), _ptr(bmask_t),
+                                      _ptr(delta), _ptr(dq), _ptr(dk), _ptr(dv),
+                                      ctypes.byref(shape), _ptr(ws), nbytes, st))
+        _maybe_check(ws, st)
+    return dq, dk, dv, delta, bmask_t
 
 
 def sparse_attn(q, k, v, niter=1, varlen=None):

@@ -79,7 +79,18 @@ simt::Params make_params(const ads_attn_shape* s) {
   p.nb = g.nb; p.n_words = g.n_words; p.rows_padded = g.rows_padded;
   p.sm_scale = (float)(1.0 / std::sqrt((double)s->D));
   p.varlen_is_i64 = s->varlen_is_i64;
+  p.bwd_stages = s->bwd_stages;
   return p;
+}
+
+// The first word of the workspace is the status word of the tensor-core kernels'
+// bounded waits.  Every entry point clears it, whichever kernel family runs, so
+// that adasplash2_check_status never reads an uninitialised value.
+int clear_status(void* ws, size_t ws_bytes, cudaStream_t st, const char* who) {
+  if (ws == nullptr || ws_bytes < sizeof(int)) return ADS_OK;
+  cudaError_t e = cudaMemsetAsync(ws, 0, sizeof(int), st);
+  if (e != cudaSuccess) { set_error("%s: memset status: %s", who, cudaGetErrorString(e)); return ADS_ERR_CUDA; }
+  return ADS_OK;
 }
 
 template <typename F32, typename F16, typename BF16>
@@ -136,6 +147,7 @@ static int solve_common(const void* q, const void* k, const void* varlen, float*
   size_t bm_bytes = (size_t)s->B * s->Hq * p.rows_padded * p.n_words * sizeof(int32_t);
   cudaError_t e = cudaMemsetAsync(bmask, 0, bm_bytes, st);
   if (e != cudaSuccess) { set_error("%s: memset bitmap: %s", who, cudaGetErrorString(e)); return ADS_ERR_CUDA; }
+  if (int rc = clear_status(ws, ws_bytes, st, who)) return rc;
   if (path == ADS_PATH_TCGEN05) {
     if (ws == nullptr || ws_bytes < sm100::workspace_bytes(s)) {
       set_error("%s: workspace too small (%zu < %zu)", who, ws_bytes, sm100::workspace_bytes(s));
@@ -177,6 +189,7 @@ extern "C" int adasplash2_fwd(const void* q, const void* k, const void* v, const
   p.q = q; p.k = k; p.v = v; p.varlen = varlen;
   p.taus = const_cast<float*>(taus); p.bmask = const_cast<int32_t*>(bmask);
   p.out = out; p.out2 = out2;
+  if (int rc = clear_status(ws, ws_bytes, st, who)) return rc;
   if (path == ADS_PATH_TCGEN05) {
     if (ws == nullptr || ws_bytes < sm100::workspace_bytes(s)) {
       set_error("%s: workspace too small (%zu < %zu)", who, ws_bytes, sm100::workspace_bytes(s));
@@ -208,6 +221,7 @@ extern "C" int adasplash2_bwd(const void* q, const void* k, const void* v, const
   p.q = q; p.k = k; p.v = v; p.varlen = varlen; p.dout = dout; p.out2_in = out2;
   p.taus = const_cast<float*>(taus); p.bmask = const_cast<int32_t*>(bmask);
   p.bmask_t = bmask_t; p.delta = delta; p.dq = dq; p.dk = dk; p.dv = dv;
+  if (int rc = clear_status(ws, ws_bytes, st, who)) return rc;
   if (path == ADS_PATH_TCGEN05) {
     if (ws == nullptr || ws_bytes < sm100::workspace_bytes(s)) {
       set_error("%s: workspace too small (%zu < %zu)", who, ws_bytes, sm100::workspace_bytes(s));

@@ -170,6 +170,7 @@ struct Params {
   int nb, n_words, rows_padded;
   float sm_scale;   // fp32(1/sqrt(D))
   int tau_given;    // solve kernel: 1 = only build the bitmap from taus
+  int bwd_stages;   // 0 = all kernels of the backward, else a mask of ADS_BWD_*
 };
 
 // ---------------------------------------------------------------------------

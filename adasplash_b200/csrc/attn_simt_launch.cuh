@@ -46,14 +46,15 @@ template <typename T> int launch_fwd(const Params& p, cudaStream_t st) {
 }
 
 template <typename T> int launch_bwd(const Params& p, cudaStream_t st) {
-  {
+  const int stages = p.bwd_stages ? p.bwd_stages : 0xF;
+  if (stages & ADS_BWD_DELTA) {
     long long rows = (long long)p.B * p.Hq * p.N;
     unsigned grid = (unsigned)((rows + 7) / 8);
     bwd_delta_kernel<T><<<grid, 256, 0, st>>>((const T*)p.out2_in, (const T*)p.dout, p.delta,
                                               p.varlen, p.varlen_is_i64, p.B, p.Hq, p.N, p.D);
     if (int rc = check_launch("simt::bwd_delta")) return rc;
   }
-  {
+  if (stages & ADS_BWD_TRANSPOSE) {
     long long words = (long long)p.B * p.Hq * p.rows_padded * p.n_words;
     unsigned grid = (unsigned)((words + 255) / 256);
     transpose_bitmap_kernel<<<grid, 256, 0, st>>>(p.bmask, p.bmask_t, p.B * p.Hq, p.rows_padded, p.n_words);
@@ -61,13 +62,18 @@ template <typename T> int launch_bwd(const Params& p, cudaStream_t st) {
   }
   ADS_DISPATCH_D(p.D, {
     size_t sm = (3 * Cfg<DD>::tile_floats + 64 * kPPitch) * sizeof(float);
-    if (int rc = set_smem(bwd_dq_kernel<T, DD>, sm, "bwd_dq")) return rc;
-    bwd_dq_kernel<T, DD><<<dim3(p.nb, p.Hq, p.B), kThreads, sm, st>>>(p);
-    if (int rc = check_launch("simt::bwd_dq")) return rc;
-    if (int rc = set_smem(bwd_dkv_kernel<T, DD>, sm, "bwd_dkv")) return rc;
-    bwd_dkv_kernel<T, DD><<<dim3(p.nb, p.Hkv, p.B), kThreads, sm, st>>>(p);
+    if (stages & ADS_BWD_DQ) {
+      if (int rc = set_smem(bwd_dq_kernel<T, DD>, sm, "bwd_dq")) return rc;
+      bwd_dq_kernel<T, DD><<<dim3(p.nb, p.Hq, p.B), kThreads, sm, st>>>(p);
+      if (int rc = check_launch("simt::bwd_dq")) return rc;
+    }
+    if (stages & ADS_BWD_DKV) {
+      if (int rc = set_smem(bwd_dkv_kernel<T, DD>, sm, "bwd_dkv")) return rc;
+      bwd_dkv_kernel<T, DD><<<dim3(p.nb, p.Hkv, p.B), kThreads, sm, st>>>(p);
+      if (int rc = check_launch("simt::bwd_dkv")) return rc;
+    }
   })
-  return check_launch("simt::bwd_dkv");
+  return ADS_OK;
 }
 
 }  // namespace simt

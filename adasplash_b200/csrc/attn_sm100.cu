@@ -98,14 +98,15 @@ int fwd_d(const simt::Params& p, void* ws, cudaStream_t st) {
 
 template <typename T, int D>
 int bwd_t(const simt::Params& p, void* ws, cudaStream_t st) {
-  {
+  const int stages = p.bwd_stages ? p.bwd_stages : 0xF;
+  if (stages & ADS_BWD_DELTA) {
     long long rows = (long long)p.B * p.Hq * p.N;
     unsigned grid = (unsigned)((rows + 7) / 8);
     simt::bwd_delta_kernel<T><<<grid, 256, 0, st>>>((const T*)p.out2_in, (const T*)p.dout, p.delta,
                                                     p.varlen, p.varlen_is_i64, p.B, p.Hq, p.N, D);
     if (int rc = check_launch("sm100::bwd_delta")) return rc;
   }
-  {
+  if (stages & ADS_BWD_TRANSPOSE) {
     long long words = (long long)p.B * p.Hq * p.rows_padded * p.n_words;
     unsigned grid = (unsigned)((words + 255) / 256);
     simt::transpose_bitmap_kernel<<<grid, 256, 0, st>>>(p.bmask, p.bmask_t, p.B * p.Hq, p.rows_padded, p.n_words);
@@ -119,20 +120,21 @@ int bwd_t(const simt::Params& p, void* ws, cudaStream_t st) {
   if (int rc = make_tmap(&tmQ64, p.q, p.B * p.Hq, p.N, D, kQBlock)) return rc;
   if (int rc = make_tmap(&tmDO64, p.dout, p.B * p.Hq, p.N, D, kQBlock)) return rc;
   TcParams t = to_tc(p, ws);
-  {
+  if (stages & ADS_BWD_DQ) {
     size_t sm = DqSmem<D>::bytes;
     if (int rc = set_smem(bwd_dq_kernel<T, D>, sm, "sm100::bwd_dq")) return rc;
     long long ctas = (long long)t.nq * p.B * p.Hq;
     bwd_dq_kernel<T, D><<<(unsigned)ctas, kDqThreads, sm, st>>>(tmQ, tmDO, tmK, tmV, t);
     if (int rc = check_launch("sm100::bwd_dq")) return rc;
   }
-  {
+  if (stages & ADS_BWD_DKV) {
     size_t sm = DkvSmem<D>::bytes;
     if (int rc = set_smem(bwd_dkv_kernel<T, D>, sm, "sm100::bwd_dkv")) return rc;
     long long ctas = (long long)t.nq * p.B * p.Hkv;
     bwd_dkv_kernel<T, D><<<(unsigned)ctas, kDkvThreads, sm, st>>>(tmK, tmV, tmQ64, tmDO64, t);
+    return check_launch("sm100::bwd_dkv");
   }
-  return check_launch("sm100::bwd_dkv");
+  return ADS_OK;
 }
 
 template <typename T>
@@ -181,28 +183,17 @@ bool supported(const ads_attn_shape* s) {
 
 size_t workspace_bytes(const ads_attn_shape*) { return kStatusBytes; }
 
-// Every entry point starts from a clean status word, so a kernel never skips its
-// work because of what an earlier call (or an uninitialised buffer) left there.
-static int clear_status(void* ws, cudaStream_t st) {
-  cudaError_t e = cudaMemsetAsync(ws, 0, kStatusBytes, st);
-  if (e != cudaSuccess) { set_error("sm100: memset status: %s", cudaGetErrorString(e)); return ADS_ERR_CUDA; }
-  return ADS_OK;
-}
-
 int solve(const simt::Params& p, int dtype, void* ws, cudaStream_t st) {
-  if (int rc = clear_status(ws, st)) return rc;
   if (dtype == ADS_F16) return solve_d<__half>(p, ws, st);
   return solve_d<__nv_bfloat16>(p, ws, st);
 }
 
 int fwd(const simt::Params& p, int dtype, void* ws, cudaStream_t st) {
-  if (int rc = clear_status(ws, st)) return rc;
   if (dtype == ADS_F16) return fwd_d<__half>(p, ws, st);
   return fwd_d<__nv_bfloat16>(p, ws, st);
 }
 
 int bwd(const simt::Params& p, int dtype, void* ws, cudaStream_t st) {
-  if (int rc = clear_status(ws, st)) return rc;
   if (dtype == ADS_F16) return bwd_d<__half>(p, ws, st);
   return bwd_d<__nv_bfloat16>(p, ws, st);
 }

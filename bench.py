@@ -48,6 +48,10 @@ WORKLOADS = {
 }
 SEED_BASE = 20260
 
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of a kernel, from the
+# ncu captures summarised under profiles/ (None = not captured for that workload)
+NCU_DRAM_BYTES_PER_LAUNCH = {}
+
 
 def dense_equiv_flops(w, lens):
     """FlashAttention convention, causal: 7 * Hq * D * sum_b L_b^2 for fwd+bwd."""
@@ -243,45 +247,60 @@ def run_ours(args):
     h2d = sum(t.numel() * t.element_size() for t in (hq, hk, hv, hdo))
     d2h = sum(t.numel() * t.element_size() for t in host_out)
 
-    # per-stage kernel timing through the C ABI (rank 0, N=1 semantics) for the roofline
+    # per-kernel timing through the C ABI (rank 0) for the roofline: CUDA events on the
+    # launching stream around `reps` back-to-back launches of one kernel
     roof = None
     extra = {}
     if rank == 0:
         pk = peaks()
         out = adasplash.adasplash_v2(q.requires_grad_(True), k, v, niter=niter, varlen=vl_dev)
-        bmask = out.grad_fn.saved_tensors[5]
+        saved = out.grad_fn.saved_tensors
+        out2, taus, bmask = saved[3], saved[4], saved[5]
         del out
-        reps = 3
-        stage_ms = {}
+        qd, kd, vd = q.detach(), k.detach(), v.detach()
+        reps = 5
+        stream = torch.cuda.current_stream()
 
         def ev(fn):
             fn()
             torch.cuda.synchronize()
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a.record()
+            a.record(stream)
             for _ in range(reps):
                 fn()
-            b.record()
+            b.record(stream)
             torch.cuda.synchronize()
             return a.elapsed_time(b) / reps
-        stage_ms["solve"] = ev(lambda: att.solve(q.detach(), k.detach(), niter, vl_dev))
-        with torch.no_grad():
-            stage_ms["solve+fwd"] = ev(lambda: adasplash.adasplash_v2(q.detach(), k.detach(), v.detach(),
-                                                                      niter=niter, varlen=vl_dev))
-        stage_ms["fwd"] = stage_ms["solve+fwd"] - stage_ms["solve"]
-        stage_ms["bwd"] = ms_step - stage_ms["solve+fwd"]
+        kernel_ms = {"solve": ev(lambda: att.solve(qd, kd, niter, vl_dev)),
+                     "fwd": ev(lambda: att.forward_raw(qd, kd, vd, taus, bmask, vl_dev))}
+        bufs = att.backward_raw(qd, kd, vd, do, out2, taus, bmask, vl_dev, niter)
+        for name, mask in (("bwd_delta", 1), ("bwd_transpose", 2), ("bwd_dq", 4), ("bwd_dkv", 8)):
+            kernel_ms[name] = ev(lambda: att.backward_raw(qd, kd, vd, do, out2, taus, bmask, vl_dev,
+                                                          niter, stages=mask, buffers=bufs))
         sweeps = 3 + niter
         total_f, solver_f, active, causal_tiles = executed_tile_flops(bmask, w, lens, niter, sweeps)
         g = 2.0 * 64 * 64 * w["D"]
-        stage_flops = {"solve": solver_f, "fwd": 3.0 * active * g, "bwd": 7.0 * active * g}
-        dom = max(("solve", "fwd", "bwd"), key=lambda s: stage_ms[s])
-        achieved = stage_flops[dom] / (stage_ms[dom] * 1e-3) / 1e12
+        kernel_flops = {"solve": solver_f, "fwd": 3.0 * active * g, "bwd_dq": 3.0 * active * g,
+                        "bwd_dkv": 4.0 * active * g}
+        dom = max(kernel_flops, key=lambda s: kernel_ms[s])
+        achieved = kernel_flops[dom] / (kernel_ms[dom] * 1e-3) / 1e12
         peak = pk["bf16_tflops_sustained"]
         roof = {"bound": "tensor", "kernel": dom, "achieved": round(achieved, 2), "peak": peak,
-                "unit": "TFLOP/s", "frac": round(achieved / peak, 4), "traffic": None,
-                "peak_source": pk["source"] + " (sustained cuBLAS bf16)"}
+                "unit": "TFLOP/s", "frac": round(achieved / peak, 4),
+                "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get((args.workload, dom)),
+                "peak_source": pk["source"] + " (sustained cuBLAS bf16; the kernel runs inside a long step)",
+                "algorithmic_flops_per_launch": kernel_flops[dom],
+                "ms_per_launch": round(kernel_ms[dom], 3)}
+        rows_total = float(w["B"] * w["Hq"] * w["N"])
+        delta_bytes = rows_total * (2 * w["D"] * 2 + 4)
         extra = {
-            "stage_ms": {k2: round(v2, 3) for k2, v2 in stage_ms.items()},
+            "kernel_ms": {k2: round(v2, 3) for k2, v2 in kernel_ms.items()},
+            "kernel_tflops": {k2: round(kernel_flops[k2] / (kernel_ms[k2] * 1e-3) / 1e12, 1)
+                              for k2 in kernel_flops},
+            "kernel_frac_of_peak": {k2: round(kernel_flops[k2] / (kernel_ms[k2] * 1e-3) / 1e12 / peak, 3)
+                                    for k2 in kernel_flops},
+            "bwd_delta_hbm_gbs": round(delta_bytes / (kernel_ms["bwd_delta"] * 1e-3) / 1e9, 1),
+            "bwd_delta_frac_of_hbm_peak": round(delta_bytes / (kernel_ms["bwd_delta"] * 1e-3) / 1e9 / pk["hbm_gbs"], 3),
             "executed_tile_tflops": round(total_f / (ms_step * 1e-3) / 1e12, 2),
             "executed_tile_frac_of_peak": round(total_f / (ms_step * 1e-3) / 1e12 / peak, 4),
             "block_sparsity": round(1.0 - active / max(1, causal_tiles), 4),
@@ -310,6 +329,101 @@ def run_ours(args):
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+ROWWISE_METRIC = "triton_entmax fwd+bwd algorithmic GB/s (x 16384x4096 fp32, alpha=1.5, n_iter=2, histogram)"
+
+
+def run_rowwise(args):
+    """Secondary workload: row-wise entmax on a 16384 x 4096 fp32 matrix = N(0,1)*4
+    (HBM-bound).  One step = forward + backward for alpha = 1.5; alpha = 2.0 and
+    1.333 are timed beside it.  Algorithmic bytes: 8 per element forward (read x,
+    write y), 12 backward (read y, dy, write dx)."""
+    import adasplash_b200 as adasplash
+    from adasplash_b200 import _lib
+    from oracle import entmax_oracle as O
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    rows, cols = 16384, 4096
+    g = torch.Generator().manual_seed(SEED_BASE + 1)
+    hx = torch.empty(rows, cols, pin_memory=True)
+    hdy = torch.empty(rows, cols, pin_memory=True)
+    for r0 in range(0, rows, 2048):
+        hx[r0:r0 + 2048] = torch.randn(2048, cols, generator=g) * 4
+        hdy[r0:r0 + 2048] = torch.randn(2048, cols, generator=g)
+    x = hx.to(dev).requires_grad_(True)
+    dy = hdy.to(dev)
+    hdx = torch.empty(rows, cols, pin_memory=True)
+    stream = torch.cuda.current_stream()
+
+    def ev(fn, reps):
+        for _ in range(max(3, args.warmup)):
+            fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        l0 = _lib.launch_count()
+        a.record(stream)
+        for _ in range(reps):
+            fn()
+        b.record(stream)
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / reps, _lib.launch_count() - l0
+    fb = 8.0 * rows * cols
+    bb = 12.0 * rows * cols
+    per_alpha = {}
+    for tag, kw in (("alpha1.5", dict(alpha=1.5, n_iter=2, use_histogram=True)), ("alpha2.0", dict(alpha=2.0)),
+                    ("alpha1.333", dict(alpha=1.333, use_histogram=False))):
+        y = adasplash.triton_entmax(x, **kw)
+        f_ms, _ = ev(lambda: adasplash.triton_entmax(x.detach(), **kw), args.steps)
+        b_ms, _ = ev(lambda: torch.autograd.grad(y, x, dy, retain_graph=True), args.steps)
+        per_alpha[tag] = {"fwd_ms": round(f_ms, 4), "bwd_ms": round(b_ms, 4),
+                          "fwd_gbs": round(fb / f_ms / 1e6, 1), "bwd_gbs": round(bb / b_ms / 1e6, 1)}
+        del y
+    sampler = ClockSampler(dev.index)
+    sampler.start()
+
+    def step():
+        yy = adasplash.triton_entmax(x, alpha=1.5, n_iter=2, use_histogram=True)
+        torch.autograd.grad(yy, x, dy)
+    ms, launches = ev(step, max(args.steps, 20))
+    clocks = sampler.stop()
+
+    def step_e2e():
+        xx = hx.to(dev, non_blocking=True).requires_grad_(True)
+        dd = hdy.to(dev, non_blocking=True)
+        yy = adasplash.triton_entmax(xx, alpha=1.5, n_iter=2, use_histogram=True)
+        (dx,) = torch.autograd.grad(yy, xx, dd)
+        hdx.copy_(dx, non_blocking=True)
+    ms_e2e, _ = ev(step_e2e, 5)
+    pk = peaks()
+    f = per_alpha["alpha1.5"]
+    # CPU baseline: the oracle's restatement of the reference kernel on a 1024-row slice
+    torch.set_num_threads(os.cpu_count() or 1)
+    xs, dys = hx[:1024].clone(), hdy[:1024].clone()
+    t0 = time.perf_counter()
+    ys = O.rowwise_entmax_v2(xs, 1.5, 2, True)
+    O.rowwise_entmax_backward(ys, dys, 1.5)
+    tc = time.perf_counter() - t0
+    line = {
+        "metric": ROWWISE_METRIC, "value": round((fb + bb) / ms / 1e6, 1), "unit": "GB/s", "n_gpus": 1,
+        "steps": max(args.steps, 20), "warmup": max(3, args.warmup), "ms_per_step": round(ms, 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "row-wise entmax, x 16384x4096 fp32 = N(0,1)*4, dY N(0,1); forward + backward",
+                   "l2": "x, y, dy, dx are 256 MiB each (> 126 MB L2)"},
+        "e2e": {"value": round((fb + bb) / ms_e2e / 1e6, 1), "unit": "GB/s", "ms_per_step": round(ms_e2e, 3),
+                "h2d_bytes_per_step": 2 * rows * cols * 4, "d2h_bytes_per_step": rows * cols * 4},
+        "gpu_launches": int(launches), "clocks": clocks,
+        "roofline": {"bound": "hbm", "kernel": "entmax_fwd_reg_kernel<float,128,8>", "achieved": f["fwd_gbs"],
+                     "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": round(f["fwd_gbs"] / pk["hbm_gbs"], 4),
+                     "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get(("c2", "entmax_fwd")),
+                     "peak_source": pk["source"] + " (STREAM-style copy)",
+                     "algorithmic_bytes_per_launch": fb, "ms_per_launch": f["fwd_ms"]},
+        "cpu_baseline": {"value": round(20.0 * 1024 * cols / tc / 1e9, 3), "unit": "GB/s", "cores": os.cpu_count(),
+                         "kind": "port", "sample": "oracle restatement of the reference kernel, fwd+bwd, 1024x4096 slice",
+                         "seconds": round(tc, 2)},
+        "per_alpha": per_alpha,
+    }
+    print(json.dumps(line), flush=True)
 
 
 def _cpu_sample(steps=1):
@@ -353,7 +467,7 @@ def run_reference(args):
         "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": len(ts), "warmup": min(args.warmup, 1),
         "ms_per_step": round(t * 1e3, 1), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOADS[args.workload]["label"], "sample": what},
+        "config": {"workload": WORKLOADS.get(args.workload, WORKLOADS["c3"])["label"], "sample": what},
         "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": os.cpu_count(), "kind": "port",
                          "sample": what},
         "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -368,12 +482,14 @@ def main():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS) + ["c2"])
     ap.add_argument("--path", default=None, choices=["auto", "simt", "tcgen05"])
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "c2":
+        run_rowwise(args)
     else:
         run_ours(args)
 

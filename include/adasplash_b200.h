@@ -50,7 +50,12 @@ typedef struct {
   int32_t niter;          /* Halley refinements after the histogram start     */
   int32_t varlen_is_i64;
   int32_t path;           /* ADS_PATH_*                                       */
+  int32_t bwd_stages;     /* 0 = whole backward; else a mask of ADS_BWD_* (timing aid) */
 } ads_attn_shape;
+
+/* Kernels of adasplash2_bwd, for `bwd_stages` (measurement only: a partial
+ * backward leaves the skipped outputs untouched). */
+enum { ADS_BWD_DELTA = 1, ADS_BWD_TRANSPOSE = 2, ADS_BWD_DQ = 4, ADS_BWD_DKV = 8 };
 
 /* Row-wise entmax forward over the last dimension of a contiguous
  * (rows, cols) matrix.  Replaces `_entmax_triton.forward` / `_fwd_entmax`
