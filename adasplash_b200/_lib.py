@@ -38,6 +38,7 @@ SIGNATURES = {
                                            POINTER(AttnShape), c_void_p, c_size_t, c_void_p]),
     "adasplash2_fwd": (c_int32, [c_void_p] * 8 + [POINTER(AttnShape), c_void_p, c_size_t, c_void_p]),
     "adasplash2_bwd": (c_int32, [c_void_p] * 13 + [POINTER(AttnShape), c_void_p, c_size_t, c_void_p]),
+    "adasplash2_bwd_static": (c_int32, [c_void_p] * 11 + [POINTER(AttnShape), c_void_p]),
     "adasplash2_check_status": (c_int32, [c_void_p, c_void_p]),
     "adasplash2_resolved_path": (c_int32, [POINTER(AttnShape)]),
     "adasplash_launch_count": (c_int64, []),

@@ -118,6 +118,32 @@ int adasplash2_bwd(const void* q, const void* k, const void* v, const void* dout
                    void* dv, const ads_attn_shape* shape, void* workspace,
                    size_t workspace_bytes, void* stream);
 
+/* Backward for callers that cannot allocate.  It has no counterpart in the
+ * reference (whose host code allocates freely through torch).  It exists for
+ * hosts that are handed their device pointers and may not call an allocator on
+ * the way: framework plugins with a fixed tensor list, code that runs inside a
+ * region where allocation is forbidden, processes with a pre-set memory budget.
+ * Same result as adasplash2_bwd, but the three scratch buffers (status word,
+ * delta, transposed block mask) are carved out of an array of
+ * ADS_STATIC_SCRATCH_BYTES that is part of the library image on every GPU that
+ * loads it.  The call makes no cudaMalloc / cudaFree and uses no allocating
+ * library routine.  Limits and rules:
+ *  - 256 + 4*B*Hq*N + 4*bitmap_words bytes (each rounded up to 256) must fit in
+ *    ADS_STATIC_SCRATCH_BYTES, otherwise ADS_ERR_WORKSPACE is returned and
+ *    nothing is launched;
+ *  - the first call on each device looks up the array's device address (with
+ *    that device current) and caches it; make that first call outside any
+ *    stream capture;
+ *  - all calls on one device share the array and it keeps the previous call's
+ *    contents (the backward rewrites every word before reading it); two calls
+ *    that overlap on the GPU -- different streams, or graphs replayed
+ *    concurrently -- race on it.  Serialise them. */
+#define ADS_STATIC_SCRATCH_BYTES (8u << 20)
+int adasplash2_bwd_static(const void* q, const void* k, const void* v, const void* dout,
+                          const void* out2, const void* varlen, const float* taus,
+                          const int32_t* bmask, void* dq, void* dk, void* dv,
+                          const ads_attn_shape* shape, void* stream);
+
 /* Debug aid, the one entry point that synchronises: waits for `stream`, reads
  * the status word that the tensor-core kernels keep at the start of `workspace`
  * and returns ADS_ERR_TIMEOUT if a bounded device-side wait gave up (the code is
