@@ -9,6 +9,8 @@
 // The threshold search follows adasplash/triton_entmax_v2.py:361-536 (4-bin
 // histogram lower bound, quadratic start on the bin-centre model, Halley /
 // Newton / secant / bisection refinement); the backward follows :539-617.
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace ads {
@@ -58,9 +60,20 @@ struct OpAdd { __device__ __forceinline__ float operator()(float a, float b) con
 struct OpMax { __device__ __forceinline__ float operator()(float a, float b) const { return fmaxf(a, b); } };
 
 __device__ __forceinline__ float masked_pow(float x, bool m, float c, int fast_math) {
-  // triton_entmax_v2.py:22-39
-  float r = fast_math ? __powf(x, c) : exp2f(log2f(fmaxf(x, 1e-6f)) * c);
-  return m ? r : 0.f;
+  // triton_entmax_v2.py:22-39: fast_powf(x, c), or exp2(log2(max(x, 1e-6)) * c) -- both are
+  // the approximate ex2 / lg2 units in the reference's build.  Evaluated on the support only.
+  if (!m) return 0.f;
+  const float base = fast_math ? x : fmaxf(x, 1e-6f);
+  return exp2f(__log2f(base) * c);
+}
+
+// base^c0, base^(c0-1), base^(c0-2) for one support element: one lg2, one ex2 and two
+// fast divisions instead of three lg2/ex2 pairs.
+__device__ __forceinline__ void pow3(float u, float c0, int fast_math, float& p0, float& p1, float& p2) {
+  const float base = fast_math ? u : fmaxf(u, 1e-6f);
+  p0 = exp2f(__log2f(base) * c0);
+  p1 = __fdividef(p0, base);
+  p2 = __fdividef(p1, base);
 }
 
 __device__ __forceinline__ float f_hist(float tau, float t_shift, const float* raw) {
@@ -248,11 +261,14 @@ __device__ __forceinline__ void entmax_fwd_row(Row& r, T* yrow, float* tau_out, 
     float t_init = mx - 1.0f;
     float n0 = 0.f, n1 = 0.f, n2 = 0.f, n3 = 0.f;
     r.for_each([&](float x) {
-      float p4 = (x - t_init) * (float)kBins;
-      n0 += (p4 >= 0.f) ? 1.f : 0.f;
-      n1 += (p4 >= 1.f) ? 1.f : 0.f;
-      n2 += (p4 >= 2.f) ? 1.f : 0.f;
-      n3 += (p4 >= 3.f) ? 1.f : 0.f;
+      const float d = x - t_init;
+      if (d >= 0.f) {  // only the few elements within 1 of the row maximum land in a bin
+        const float p4 = d * (float)kBins;
+        n0 += 1.f;
+        n1 += (p4 >= 1.f) ? 1.f : 0.f;
+        n2 += (p4 >= 2.f) ? 1.f : 0.f;
+        n3 += (p4 >= 3.f) ? 1.f : 0.f;
+      }
     });
     red4[0] = n0; red4[1] = n1; red4[2] = n2; red4[3] = n3;
     red.reduce4(red4, OpAdd());
@@ -286,20 +302,21 @@ __device__ __forceinline__ void entmax_fwd_row(Row& r, T* yrow, float* tau_out, 
     float a0 = 0.f, a1 = 0.f, a2 = 0.f;
     const float t = s.t;
     if (mode == 1) {
-      r.for_each([&](float x) { bool m = x > t; a0 += m ? (x - t) : 0.f; a1 += m ? 1.f : 0.f; });
+      r.for_each([&](float x) { if (x > t) { a0 += x - t; a1 += 1.f; } });
     } else if (mode == 0) {
       r.for_each([&](float x) {
-        bool m = x > t;
-        float u = m ? (x - t) : 0.f;
-        a0 = fmaf(u, u, a0); a1 += u; a2 += m ? 1.f : 0.f;
+        if (x > t) {  // the support is a small part of the row
+          const float u = x - t;
+          a0 = fmaf(u, u, a0); a1 += u; a2 += 1.f;
+        }
       });
     } else {
       r.for_each([&](float x) {
-        bool m = x > t;
-        float u = fmaxf(x - t, 0.f);
-        a0 += masked_pow(u, m, c0, fast_math);
-        a1 += masked_pow(u, m, c1, fast_math);
-        a2 += masked_pow(u, m, c2, fast_math);
+        if (x > t) {  // the support is a small part of the row: skip the transcendental work elsewhere
+          float p0, p1, p2;
+          pow3(x - t, c0, fast_math, p0, p1, p2);
+          a0 += p0; a1 += p1; a2 += p2;
+        }
       });
     }
     red4[0] = a0; red4[1] = a1; red4[2] = a2; red4[3] = 0.f;
@@ -445,7 +462,13 @@ int launch_fwd(const void* xv, void* yv, float* tau, long long rows, long long c
   if (cols <= 512) ADS_FWD(32, 4);
   if (cols <= 1024) ADS_FWD(32, 8);
   if (cols <= 2048) ADS_FWD(64, 8);
-  if (cols <= 4096) ADS_FWD(128, 8);
+  if (cols <= 4096) {
+    static const int knob = getenv("ADS_ROWWISE_TPR") ? atoi(getenv("ADS_ROWWISE_TPR")) : 0;
+    if (knob == 32) ADS_FWD(32, 32);
+    if (knob == 64) ADS_FWD(64, 16);
+    if (knob == 256) ADS_FWD(256, 4);
+    ADS_FWD(128, 8);
+  }
   if (cols <= 8192) ADS_FWD(256, 8);
   if (cols <= 16384) ADS_FWD(512, 8);
   if (cols <= 32768) ADS_FWD(1024, 8);

@@ -57,6 +57,8 @@ def test_trajectory_matches_oracle(alpha, n_iter, hist):
     # with no refinement the result is the raw quadratic start, whose Lagrange
     # coefficients cancel catastrophically in fp32: only loosely comparable
     tol = 2e-6 if n_iter > 0 else 2e-3
+    if alpha not in (1.5, 2.0):
+        tol = 1e-5  # generic alpha goes through the approximate lg2 / ex2 units
     assert (tau.cpu() - to).abs().max() < tol
     assert (y.cpu() - yo).abs().max() < tol
 
@@ -109,7 +111,7 @@ def test_reference_golden():
     for tag in ("a15_hist", "a2_default", "a1333", "a15_nohist_it10"):
         y = adasplash.triton_entmax(x, **fx[tag]["kwargs"])
         (dx,) = torch.autograd.grad(y, x, fx["dy"].cuda())
-        assert (y.detach().cpu() - fx[tag]["y"]).abs().max() < 2e-6, tag
+        assert (y.detach().cpu() - fx[tag]["y"]).abs().max() < (1e-5 if tag == "a1333" else 2e-6), tag
         assert (dx.cpu() - fx[tag]["dx"]).abs().max() < 1e-4, tag
     xs = fx["x_small_f16"].cuda().requires_grad_(True)
     for tag in ("small_a15", "small_a2", "small_a1333"):
