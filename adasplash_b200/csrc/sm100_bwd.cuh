@@ -22,7 +22,8 @@ namespace sm100 {
 // ---------------------------------------------------------------------------
 // dQ
 // ---------------------------------------------------------------------------
-constexpr int kDqThreads = 192;
+constexpr int kDqThreads = 320;   // 8 row warps + TMA warp + MMA warp
+constexpr int kDqRowThreads = 256;
 constexpr int kDqKStages = 3;
 constexpr int kDqVStages = 2;
 constexpr int kDqTmemCols = 512;
@@ -95,15 +96,15 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     *start_status = *(volatile int*)p.status;
     *cta_abort = 0;
   }
-  if (warp == 5) {
+  if (warp == 9) {
     if (lane == 0) {
       ptx::mbar_init(q_full, 1);
-      ptx::mbar_init(q_ready, 128);
+      ptx::mbar_init(q_ready, kDqRowThreads);
       for (int s = 0; s < kDqKStages; ++s) { ptx::mbar_init(k_full + s, 1); ptx::mbar_init(k_empty + s, 1); }
       for (int s = 0; s < kDqVStages; ++s) { ptx::mbar_init(v_full + s, 1); ptx::mbar_init(v_empty + s, 1); }
       for (int s = 0; s < 2; ++s) {
         ptx::mbar_init(s_full + s, 1);
-        ptx::mbar_init(p_full + s, 128);
+        ptx::mbar_init(p_full + s, kDqRowThreads);
         ptx::mbar_init(s_free + s, 1);
       }
       ptx::mbar_init(dp_full, 1);
@@ -118,12 +119,12 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   __syncthreads();
   ptx::tc_fence_after_sync();
   if (*start_status != 0) {
-    if (warp == 5) ptx::tmem_dealloc(*tmem_holder, kDqTmemCols);
+    if (warp == 9) ptx::tmem_dealloc(*tmem_holder, kDqTmemCols);
     return;
   }
   const uint32_t tmem_base = *tmem_holder;
 
-  if (warp == 4) {
+  if (warp == 8) {
     if (lane == 0) {
       ptx::prefetch_tmap(&tmQ); ptx::prefetch_tmap(&tmDO); ptx::prefetch_tmap(&tmK); ptx::prefetch_tmap(&tmV);
       ptx::mbar_arrive_expect_tx(q_full, 2 * L::tile_bytes);
@@ -148,7 +149,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
           ptx::tma_load_3d(sV + vs * L::tile_bytes + pn * kPanelBytes, &tmV, v_full + vs, pn * 64, kt * kBlockN, kv_head);
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     constexpr uint32_t idesc_s = ptx::make_idesc(FMT, kBlockM, kBlockN, 0, 0);
     constexpr uint32_t idesc_dq = ptx::make_idesc(FMT, kBlockM, D, 0, 1);
     bool ok = true;
@@ -235,7 +236,8 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     }
     if (!ok && lane == 0 && !*cta_abort) raise_abort(cta_abort, p.status, kStTimeoutMma);
   } else {
-    const int wq = warp;
+    const int wq = warp & 3;     // TMEM lanes 32*wq .. 32*wq+31
+    const int half = warp >> 2;  // keys 64*half .. 64*half+63 of each tile
     const int r = wq * 32 + lane;
     const int row = m0 + r;
     const bool row_ok = row < len;
@@ -245,7 +247,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     if (!ptx::mbar_wait(q_full, 0)) { raise_abort(cta_abort, p.status, kStTimeoutEpilogue); dead = true; }
     if (!dead) {
       const float sc = 0.5f * p.sm_scale;
-      for (int v = threadIdx.x; v < L::tile_bytes / 16; v += 128) {
+      for (int v = threadIdx.x; v < L::tile_bytes / 16; v += kDqRowThreads) {
         uint4* ptr = reinterpret_cast<uint4*>(sQ) + v;
         const int vrow = ((v * 16) % kPanelBytes) / 128;
         uint4 val = *ptr;
@@ -266,7 +268,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     for (int j = 0; !dead && scan.next(kt, flags); ++j) {
       const int buf = j & 1;
       n_active = j + 1;
-      const uint32_t my_flags = (flags >> (2 * rb)) & 3u;
+      const bool sub_on = (flags >> (2 * rb + half)) & 1u;
       if (*cta_abort) { dead = true; break; }
       if (!ptx::mbar_wait(s_full + buf, (j >> 1) & 1) || !ptx::mbar_wait(dp_full, j & 1)) {
         raise_abort(cta_abort, p.status, kStTimeoutEpilogue);
@@ -276,27 +278,30 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       ptx::tc_fence_after_sync();
       const int n0 = kt * kBlockN;
       const bool need_mask = (kt == qt) || (n0 + kBlockN > len);
-#pragma unroll 1
-      for (int ch = 0; ch < 4; ++ch) {
-        uint32_t rs[32], rp[32];
-        const uint32_t caddr = lane_addr + buf * kBlockN + ch * 32;
-        ptx::tmem_ld32(caddr, rs);
-        ptx::tmem_ld32(lane_addr + DP_COL + ch * 32, rp);
-        ptx::tmem_ld_wait();
-        const float* s = reinterpret_cast<const float*>(rs);
-        const float* dp = reinterpret_cast<const float*>(rp);
-        const bool sub_on = (my_flags >> (ch >> 1)) & 1u;
-        uint32_t dk[16];
 #pragma unroll
-        for (int c = 0; c < 32; c += 2) {
-          float d0 = 0.f, d1 = 0.f;
-          const int col = n0 + ch * 32 + c;
-          const bool ok0 = sub_on && (!need_mask || (col <= row && col < len));
-          const bool ok1 = sub_on && (!need_mask || (col + 1 <= row && col + 1 < len));
-          const float u0 = s[c] - tau, u1 = s[c + 1] - tau;
-          if (ok0 && u0 > 0.f) d0 = u0 * (dp[c] - dl);
-          if (ok1 && u1 > 0.f) d1 = u1 * (dp[c + 1] - dl);
-          dk[c >> 1] = pack2<T>(d0, d1);
+      for (int cc = 0; cc < 2; ++cc) {
+        const int ch = 2 * half + cc;
+        const uint32_t caddr = lane_addr + buf * kBlockN + ch * 32;
+        uint32_t dk[16];
+        if (!sub_on) {
+#pragma unroll
+          for (int c = 0; c < 16; ++c) dk[c] = 0u;
+        } else {
+          uint32_t rs[32], rp[32];
+          ptx::tmem_ld32(caddr, rs);
+          ptx::tmem_ld32(lane_addr + DP_COL + ch * 32, rp);
+          ptx::tmem_ld_wait();
+          const float* s = reinterpret_cast<const float*>(rs);
+          const float* dp = reinterpret_cast<const float*>(rp);
+          const int lim = need_mask ? (min(row, len - 1) - (n0 + ch * 32)) : 64;  // columns c <= lim survive
+#pragma unroll
+          for (int c = 0; c < 32; c += 2) {
+            const float u0 = s[c] - tau, u1 = s[c + 1] - tau;
+            // select, not multiply: dP of a padded key may be anything
+            const float d0 = (u0 > 0.f && c <= lim) ? u0 * (dp[c] - dl) : 0.f;
+            const float d1 = (u1 > 0.f && c + 1 <= lim) ? u1 * (dp[c + 1] - dl) : 0.f;
+            dk[c >> 1] = pack2<T>(d0, d1);
+          }
         }
         ptx::tmem_st16(caddr, dk);
       }
@@ -307,10 +312,11 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     if (!dead && n_active > 0) {
       if (!ptx::mbar_wait(dq_full, 0)) { raise_abort(cta_abort, p.status, kStTimeoutEpilogue); dead = true; }
     }
-    if (!dead && row < p.N) {
+    if (!dead) {  // TMEM loads are warp-collective: only the global stores are per-row
       ptx::tc_fence_after_sync();
 #pragma unroll 1
-      for (int ch = 0; ch < D / 32; ++ch) {
+      for (int cc = 0; cc < D / 64; ++cc) {
+        const int ch = half * (D / 64) + cc;
         uint32_t ro[32];
         if (n_active > 0) {
           ptx::tmem_ld32(lane_addr + DQ_COL + ch * 32, ro);
@@ -325,8 +331,10 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         for (int c = 0; c < 32; c += 2)
           po[c >> 1] = row_ok ? pack2<T>(fo[c] * p.sm_scale, fo[c + 1] * p.sm_scale) : 0u;
         uint4* dst = reinterpret_cast<uint4*>(dqg + (size_t)row * D + ch * 32);
+        if (row < p.N) {
 #pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) dst[q4] = make_uint4(po[q4 * 4], po[q4 * 4 + 1], po[q4 * 4 + 2], po[q4 * 4 + 3]);
+          for (int q4 = 0; q4 < 4; ++q4) dst[q4] = make_uint4(po[q4 * 4], po[q4 * 4 + 1], po[q4 * 4 + 2], po[q4 * 4 + 3]);
+        }
       }
     }
   }
@@ -337,7 +345,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     for (int i = 0; i < 64; ++i) __nanosleep(1000);
   }
   __syncthreads();
-  if (warp == 5) {
+  if (warp == 9) {
     ptx::tc_fence_after_sync();
     ptx::tmem_dealloc(tmem_base, kDqTmemCols);
   }
@@ -346,7 +354,8 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
 // ---------------------------------------------------------------------------
 // dK, dV
 // ---------------------------------------------------------------------------
-constexpr int kDkvThreads = 192;
+constexpr int kDkvThreads = 320;    // 8 row warps + TMA warp + MMA warp
+constexpr int kDkvRowThreads = 256;
 constexpr int kDkvStages = 3;       // (Q block, dO block) pairs in flight
 constexpr int kDkvTmemCols = 512;
 constexpr int kQBlock = 64;         // query rows per step (one block-mask row block)
@@ -460,14 +469,14 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
     *start_status = *(volatile int*)p.status;
     *cta_abort = 0;
   }
-  if (warp == 5) {
+  if (warp == 9) {
     if (lane == 0) {
       ptx::mbar_init(kv_full, 1);
-      ptx::mbar_init(k_ready, 128);
+      ptx::mbar_init(k_ready, kDkvRowThreads);
       for (int s = 0; s < kDkvStages; ++s) { ptx::mbar_init(x_full + s, 1); ptx::mbar_init(x_empty + s, 1); }
       for (int s = 0; s < 2; ++s) {
         ptx::mbar_init(s_full + s, 1);
-        ptx::mbar_init(p_full + s, 128);
+        ptx::mbar_init(p_full + s, kDkvRowThreads);
         ptx::mbar_init(s_free + s, 1);
       }
       ptx::mbar_init(acc_full, 1);
@@ -481,12 +490,12 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
   __syncthreads();
   ptx::tc_fence_after_sync();
   if (*start_status != 0) {
-    if (warp == 5) ptx::tmem_dealloc(*tmem_holder, kDkvTmemCols);
+    if (warp == 9) ptx::tmem_dealloc(*tmem_holder, kDkvTmemCols);
     return;
   }
   const uint32_t tmem_base = *tmem_holder;
 
-  if (warp == 4) {
+  if (warp == 8) {
     if (lane == 0) {
       ptx::prefetch_tmap(&tmK); ptx::prefetch_tmap(&tmV); ptx::prefetch_tmap(&tmQ64); ptx::prefetch_tmap(&tmDO64);
       ptx::mbar_arrive_expect_tx(kv_full, 2 * L::tile_bytes);
@@ -509,7 +518,7 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
         }
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     constexpr uint32_t idesc_s = ptx::make_idesc(FMT, kBlockN, kQBlock, 0, 0);   // 128 keys x 64 queries
     constexpr uint32_t idesc_acc = ptx::make_idesc(FMT, kBlockN, D, 0, 1);        // 128 keys x D
     bool ok = true;
@@ -579,16 +588,17 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
       if (lane == 0) {
         ptx::tc_fence_after_sync();
         const uint32_t q0 = ptx::smem_u32(qt_), d0 = ptx::smem_u32(dot_);
-        const uint32_t pa = tmem_base + buf * kQBlock;            // P^T: 32 packed columns
-        const uint32_t da = tmem_base + DP_COL0 + buf * kQBlock;  // dS^T
+        // P^T / dS^T: 16 queries = 8 packed columns per k-step, at the start of each 32-column half
+        const uint32_t pa = tmem_base + buf * kQBlock;
+        const uint32_t da = tmem_base + DP_COL0 + buf * kQBlock;
 #pragma unroll
         for (int kk = 0; kk < kQBlock / 16; ++kk) {
-          ptx::mma_ts(tmem_base + DV_COL, pa + kk * 8, ptx::make_smem_desc(d0 + kk * 2048, kQPanelBytes, 1024),
+          ptx::mma_ts(tmem_base + DV_COL, pa + (kk >> 1) * 32 + (kk & 1) * 8, ptx::make_smem_desc(d0 + kk * 2048, kQPanelBytes, 1024),
                       idesc_acc, (j > 0 || kk > 0));
         }
 #pragma unroll
         for (int kk = 0; kk < kQBlock / 16; ++kk) {
-          ptx::mma_ts(tmem_base + DK_COL, da + kk * 8, ptx::make_smem_desc(q0 + kk * 2048, kQPanelBytes, 1024),
+          ptx::mma_ts(tmem_base + DK_COL, da + (kk >> 1) * 32 + (kk & 1) * 8, ptx::make_smem_desc(q0 + kk * 2048, kQPanelBytes, 1024),
                       idesc_acc, (j > 0 || kk > 0));
         }
         ptx::mma_commit(x_empty + st);
@@ -600,7 +610,8 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
     }
     if (!ok && lane == 0 && !*cta_abort) raise_abort(cta_abort, p.status, kStTimeoutMma);
   } else {
-    const int wq = warp;
+    const int wq = warp & 3;             // TMEM lanes 32*wq .. 32*wq+31
+    const int half = warp >> 2;          // query columns 32*half .. 32*half+31 of each block
     const int r = wq * 32 + lane;        // key row inside the tile
     const int key = n0 + r;
     const bool key_ok = key < len;
@@ -611,7 +622,7 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
     if (!dead) {
       // K~ = rn(k * fp32(0.5/sqrt(D))) in place; rows >= len -> 0 in K and V
       const float sc = 0.5f * p.sm_scale;
-      for (int v = threadIdx.x; v < L::tile_bytes / 16; v += 128) {
+      for (int v = threadIdx.x; v < L::tile_bytes / 16; v += kDkvRowThreads) {
         const int vrow = ((v * 16) % kPanelBytes) / 128;
         const bool keep = (n0 + vrow) < len;
         uint4* pk = reinterpret_cast<uint4*>(sK) + v;
@@ -634,47 +645,50 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
       const size_t toff = (size_t)(b * p.Hq + kvh * G + g) * p.N;
       // stage tau and delta of the 64 query rows of this block (double buffered)
       float* td = s_td + buf * 128;
-      {
+      if (threadIdx.x < 128) {
         const int qrow = m * kQBlock + (threadIdx.x & 63);
         const float* src = (threadIdx.x < 64) ? p.taus : p.delta;
         td[threadIdx.x] = (qrow < len) ? src[toff + qrow] : 0.f;
       }
-      ptx::bar_sync(1, 128);
+      ptx::bar_sync(1, kDkvRowThreads);
       if (dead || *cta_abort) { dead = true; continue; }
       if (!ptx::mbar_wait(s_full + buf, (j >> 1) & 1)) { raise_abort(cta_abort, p.status, kStTimeoutEpilogue); dead = true; continue; }
       ptx::tc_fence_after_sync();
-      const bool sub_on = (flags >> kh) & 1u;
-      const int q0 = m * kQBlock;
-      const bool need_mask = (q0 < n0 + kBlockN) || (q0 + kQBlock > len);  // diagonal or padded queries
-#pragma unroll 1
-      for (int ch = 0; ch < 2; ++ch) {
+      const bool sub_on = (flags >> kh) & 1u;  // warp-uniform: the TMEM loads below are warp-collective
+      const int q0 = m * kQBlock + half * 32;  // first query row of this thread's columns
+      const uint32_t saddr = lane_addr + buf * kQBlock + half * 32;
+      const uint32_t daddr = lane_addr + DP_COL0 + buf * kQBlock + half * 32;
+      uint32_t pk[16], dk[16];
+      if (!sub_on) {
+#pragma unroll
+        for (int c = 0; c < 16; ++c) { pk[c] = 0u; dk[c] = 0u; }
+      } else {
         uint32_t rs[32], rp[32];
-        const uint32_t saddr = lane_addr + buf * kQBlock + ch * 32;
-        const uint32_t daddr = lane_addr + DP_COL0 + buf * kQBlock + ch * 32;
         ptx::tmem_ld32(saddr, rs);
         ptx::tmem_ld32(daddr, rp);
         ptx::tmem_ld_wait();
         const float* s = reinterpret_cast<const float*>(rs);
         const float* dp = reinterpret_cast<const float*>(rp);
-        uint32_t pk[16], dk[16];
+        const float* tq = td + half * 32;
+        const float* dq_ = td + 64 + half * 32;
+        // query column c is valid iff key <= q0 + c < len  <=>  lo <= c < hi
+        const int lo = key - q0, hi = key_ok ? len - q0 : 0;  // a padded key keeps nothing
 #pragma unroll
         for (int c = 0; c < 32; c += 2) {
-          const int qc = ch * 32 + c;
-          const float t0 = td[qc], t1 = td[qc + 1];
-          const float dl0 = td[64 + qc], dl1 = td[64 + qc + 1];
-          const int qrow = q0 + qc;
-          const bool ok0 = sub_on && key_ok && (!need_mask || (key <= qrow && qrow < len));
-          const bool ok1 = sub_on && key_ok && (!need_mask || (key <= qrow + 1 && qrow + 1 < len));
-          const float u0 = s[c] - t0, u1 = s[c + 1] - t1;
-          float p0 = 0.f, p1 = 0.f, d0 = 0.f, d1 = 0.f;
-          if (ok0 && u0 > 0.f) { p0 = u0 * u0; d0 = u0 * (dp[c] - dl0); }
-          if (ok1 && u1 > 0.f) { p1 = u1 * u1; d1 = u1 * (dp[c + 1] - dl1); }
-          pk[c >> 1] = pack2<T>(p0, p1);
-          dk[c >> 1] = pack2<T>(d0, d1);
+          const float2 t2 = *reinterpret_cast<const float2*>(tq + c);
+          const float2 l2 = *reinterpret_cast<const float2*>(dq_ + c);
+          const float u0 = s[c] - t2.x, u1 = s[c + 1] - t2.y;
+          const bool ok0 = (u0 > 0.f) && (c >= lo) && (c < hi);
+          const bool ok1 = (u1 > 0.f) && (c + 1 >= lo) && (c + 1 < hi);
+          // select, not multiply: S / dP entries of padded rows may be anything
+          pk[c >> 1] = pack2<T>(ok0 ? u0 * u0 : 0.f, ok1 ? u1 * u1 : 0.f);
+          dk[c >> 1] = pack2<T>(ok0 ? u0 * (dp[c] - l2.x) : 0.f, ok1 ? u1 * (dp[c + 1] - l2.y) : 0.f);
         }
-        ptx::tmem_st16(lane_addr + buf * kQBlock + ch * 16, pk);
-        ptx::tmem_st16(lane_addr + DP_COL0 + buf * kQBlock + ch * 16, dk);
       }
+      // written inside this thread's own 32 columns: the other half of the row is
+      // read by another warp at its own pace
+      ptx::tmem_st16(saddr, pk);
+      ptx::tmem_st16(daddr, dk);
       ptx::tmem_st_wait();
       ptx::tc_fence_before_sync();
       ptx::mbar_arrive(p_full + buf);
@@ -682,10 +696,11 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
     if (!dead && n_active > 0) {
       if (!ptx::mbar_wait(acc_full, 0)) { raise_abort(cta_abort, p.status, kStTimeoutEpilogue); dead = true; }
     }
-    if (!dead && key < p.N) {
+    if (!dead) {  // TMEM loads are warp-collective: only the global stores are per-row
       ptx::tc_fence_after_sync();
 #pragma unroll 1
-      for (int ch = 0; ch < D / 32; ++ch) {
+      for (int cc = 0; cc < D / 64; ++cc) {
+        const int ch = half * (D / 64) + cc;
         uint32_t rk[32], rv[32];
         if (n_active > 0) {
           ptx::tmem_ld32(lane_addr + DK_COL + ch * 32, rk);
@@ -697,18 +712,20 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
         }
         const float* fk = reinterpret_cast<const float*>(rk);
         const float* fv = reinterpret_cast<const float*>(rv);
-        uint32_t pk[16], pv[16];
+        uint32_t ok_[16], ov_[16];
 #pragma unroll
         for (int c = 0; c < 32; c += 2) {
-          pk[c >> 1] = key_ok ? pack2<T>(fk[c] * p.sm_scale, fk[c + 1] * p.sm_scale) : 0u;
-          pv[c >> 1] = key_ok ? pack2<T>(fv[c], fv[c + 1]) : 0u;
+          ok_[c >> 1] = key_ok ? pack2<T>(fk[c] * p.sm_scale, fk[c + 1] * p.sm_scale) : 0u;
+          ov_[c >> 1] = key_ok ? pack2<T>(fv[c], fv[c + 1]) : 0u;
         }
         uint4* dst = reinterpret_cast<uint4*>(dkg + (size_t)key * D + ch * 32);
         uint4* dst2 = reinterpret_cast<uint4*>(dvg + (size_t)key * D + ch * 32);
+        if (key < p.N) {
 #pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          dst[q4] = make_uint4(pk[q4 * 4], pk[q4 * 4 + 1], pk[q4 * 4 + 2], pk[q4 * 4 + 3]);
-          dst2[q4] = make_uint4(pv[q4 * 4], pv[q4 * 4 + 1], pv[q4 * 4 + 2], pv[q4 * 4 + 3]);
+          for (int q4 = 0; q4 < 4; ++q4) {
+          dst[q4] = make_uint4(ok_[q4 * 4], ok_[q4 * 4 + 1], ok_[q4 * 4 + 2], ok_[q4 * 4 + 3]);
+          dst2[q4] = make_uint4(ov_[q4 * 4], ov_[q4 * 4 + 1], ov_[q4 * 4 + 2], ov_[q4 * 4 + 3]);
+        }
         }
       }
     }
@@ -720,7 +737,7 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
     for (int i = 0; i < 64; ++i) __nanosleep(1000);
   }
   __syncthreads();
-  if (warp == 5) {
+  if (warp == 9) {
     ptx::tc_fence_after_sync();
     ptx::tmem_dealloc(tmem_base, kDkvTmemCols);
   }

@@ -7,8 +7,11 @@
 //   P  = rn(u*u), U = rn(u) written back over S in TMEM as 16-bit pairs
 //   O += P V, O2 += U V    tcgen05.mma with the A operand in TMEM, V in shared memory
 // S is double buffered so that the S product of tile j+1 overlaps the row work
-// of tile j.  Sub-tiles whose bit is clear contribute exactly zero, as in the
-// reference, which never visits them.
+// of tile j.  Eight row warps share the work: warps w and w+4 own the same 32
+// TMEM lanes (rows) and split the 128 keys of a tile in halves, which doubles the
+// warps per scheduler that hide the TMEM and ALU latency of the row work.
+// Sub-tiles whose bit is clear contribute exactly zero, as in the reference,
+// which never visits them.
 #pragma once
 #include <type_traits>
 
@@ -17,7 +20,8 @@
 namespace ads {
 namespace sm100 {
 
-constexpr int kFwdThreads = 192;  // 4 row warps + TMA warp + MMA warp
+constexpr int kFwdThreads = 320;  // 8 row warps (two per TMEM lane quarter) + TMA warp + MMA warp
+constexpr int kFwdRowThreads = 256;
 constexpr int kFwdKStages = 2;
 constexpr int kFwdVStages = 3;
 constexpr int kFwdTmemCols = 512;
@@ -31,7 +35,8 @@ struct FwdSmem {
   static constexpr int bar_off = v_off + kFwdVStages * tile_bytes;
   static constexpr int n_bars = 2 + 2 * kFwdKStages + 2 * kFwdVStages + 6 + 1;
   static constexpr int misc_off = bar_off + n_bars * 8;
-  static constexpr size_t bytes = 1024 + misc_off + 64;
+  static constexpr int supp_off = misc_off + 64;  // [2][128] floats: per-half partial sums of u
+  static constexpr size_t bytes = 1024 + supp_off + 2 * 128 * 4;
 };
 
 // Pack two fp32 values as 16-bit pairs (first value in the low half).
@@ -115,15 +120,15 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     *cta_abort = 0;
   }
   const int32_t* bm_head = p.bmask + (size_t)bh * p.rows_padded * p.n_words;
-  if (warp == 5) {
+  if (warp == 9) {
     if (lane == 0) {
       ptx::mbar_init(q_full, 1);
-      ptx::mbar_init(q_ready, 128);
+      ptx::mbar_init(q_ready, kFwdRowThreads);
       for (int s = 0; s < kFwdKStages; ++s) { ptx::mbar_init(k_full + s, 1); ptx::mbar_init(k_empty + s, 1); }
       for (int s = 0; s < kFwdVStages; ++s) { ptx::mbar_init(v_full + s, 1); ptx::mbar_init(v_empty + s, 1); }
       for (int s = 0; s < 2; ++s) {
         ptx::mbar_init(s_full + s, 1);
-        ptx::mbar_init(p_full + s, 128);
+        ptx::mbar_init(p_full + s, kFwdRowThreads);
         ptx::mbar_init(s_free + s, 1);
       }
       ptx::mbar_init(o_full, 1);
@@ -137,12 +142,12 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
   __syncthreads();
   ptx::tc_fence_after_sync();
   if (*start_status != 0) {
-    if (warp == 5) ptx::tmem_dealloc(*tmem_holder, kFwdTmemCols);
+    if (warp == 9) ptx::tmem_dealloc(*tmem_holder, kFwdTmemCols);
     return;
   }
   const uint32_t tmem_base = *tmem_holder;
 
-  if (warp == 4) {
+  if (warp == 8) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
       ptx::prefetch_tmap(&tmQ);
@@ -167,7 +172,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
           ptx::tma_load_3d(sV + vs * L::tile_bytes + pn * kPanelBytes, &tmV, v_full + vs, pn * 64, kt * kBlockN, kv_head);
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     // ---------------- MMA issuer (whole warp stays converged; lane 0 issues) ----------------
     constexpr uint32_t idesc_s = ptx::make_idesc(FMT, kBlockM, kBlockN, 0, 0);
     constexpr uint32_t idesc_pv = ptx::make_idesc(FMT, kBlockM, D, 0, 1);
@@ -240,18 +245,20 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     }
     if (!ok && lane == 0 && !*cta_abort) raise_abort(cta_abort, p.status, kStTimeoutMma);
   } else {
-    // ---------------- row warps: one score row per thread ----------------
-    const int wq = warp;  // TMEM lanes 32*wq .. 32*wq+31
+    // ---------------- row warps: thread = (score row, key half) ----------------
+    const int wq = warp & 3;     // TMEM lanes 32*wq .. 32*wq+31
+    const int half = warp >> 2;  // keys 64*half .. 64*half+63 of each tile
     const int r = wq * 32 + lane;
     const int row = m0 + r;
     const bool row_ok = row < len;
     const int rb = wq >> 1;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(wq * 32) << 16);
+    float* s_supp = (float*)(smem + L::supp_off);
     bool dead = false;
     if (!ptx::mbar_wait(q_full, 0)) { raise_abort(cta_abort, p.status, kStTimeoutEpilogue); dead = true; }
     if (!dead) {
       const float sc = 0.5f * p.sm_scale;
-      for (int v = threadIdx.x; v < L::tile_bytes / 16; v += 128) {
+      for (int v = threadIdx.x; v < L::tile_bytes / 16; v += kFwdRowThreads) {
         uint4* ptr = reinterpret_cast<uint4*>(sQ) + v;
         const int vrow = ((v * 16) % kPanelBytes) / 128;
         uint4 val = *ptr;
@@ -272,33 +279,46 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     for (int j = 0; !dead && scan.next(kt, flags); ++j) {
       const int buf = j & 1;
       n_active = j + 1;
-      const uint32_t my_flags = (flags >> (2 * rb)) & 3u;  // bit0: keys 0..63, bit1: keys 64..127
+      const bool sub_on = (flags >> (2 * rb + half)) & 1u;  // this thread's 64x64 sub-tile
       if (*cta_abort) { dead = true; break; }
       if (!ptx::mbar_wait(s_full + buf, (j >> 1) & 1)) { raise_abort(cta_abort, p.status, kStTimeoutEpilogue); dead = true; break; }
       ptx::tc_fence_after_sync();
       const int n0 = kt * kBlockN;
       const bool need_mask = (kt == qt) || (n0 + kBlockN > len);
-#pragma unroll 1
-      for (int ch = 0; ch < 4; ++ch) {
-        uint32_t raw[32];
-        const uint32_t caddr = lane_addr + buf * kBlockN + ch * 32;
-        ptx::tmem_ld32(caddr, raw);
-        ptx::tmem_ld_wait();
-        const float* v = reinterpret_cast<const float*>(raw);
-        const bool sub_on = (my_flags >> (ch >> 1)) & 1u;
-        uint32_t pk[16], uk[16];
 #pragma unroll
-        for (int c = 0; c < 32; c += 2) {
-          float u0 = fmaxf(v[c] - tau, 0.f), u1 = fmaxf(v[c + 1] - tau, 0.f);
+      for (int cc = 0; cc < 2; ++cc) {
+        const int ch = 2 * half + cc;
+        const uint32_t caddr = lane_addr + buf * kBlockN + ch * 32;
+        uint32_t pk[16], uk[16];
+        if (!sub_on) {
+#pragma unroll
+          for (int c = 0; c < 16; ++c) { pk[c] = 0u; uk[c] = 0u; }
+        } else {
+          uint32_t raw[32];
+          ptx::tmem_ld32(caddr, raw);
+          ptx::tmem_ld_wait();
+          const float* v = reinterpret_cast<const float*>(raw);
           if (need_mask) {
-            const int col = n0 + ch * 32 + c;
-            if (!(col <= row && col < len)) u0 = 0.f;
-            if (!(col + 1 <= row && col + 1 < len)) u1 = 0.f;
+            const int col0 = n0 + ch * 32;
+            const int lim = min(row, len - 1) - col0;  // columns c <= lim survive
+#pragma unroll
+            for (int c = 0; c < 32; c += 2) {
+              float u0 = fmaxf(v[c] - tau, 0.f), u1 = fmaxf(v[c + 1] - tau, 0.f);
+              if (c > lim) u0 = 0.f;
+              if (c + 1 > lim) u1 = 0.f;
+              supp += u0 + u1;
+              pk[c >> 1] = pack2<T>(u0 * u0, u1 * u1);
+              uk[c >> 1] = pack2<T>(u0, u1);
+            }
+          } else {
+#pragma unroll
+            for (int c = 0; c < 32; c += 2) {
+              const float u0 = fmaxf(v[c] - tau, 0.f), u1 = fmaxf(v[c + 1] - tau, 0.f);
+              supp += u0 + u1;
+              pk[c >> 1] = pack2<T>(u0 * u0, u1 * u1);
+              uk[c >> 1] = pack2<T>(u0, u1);
+            }
           }
-          if (!sub_on) { u0 = 0.f; u1 = 0.f; }
-          supp += u0 + u1;
-          pk[c >> 1] = pack2<T>(u0 * u0, u1 * u1);
-          uk[c >> 1] = pack2<T>(u0, u1);
         }
         ptx::tmem_st16(caddr, pk);
         ptx::tmem_st16(caddr + 16, uk);
@@ -307,15 +327,20 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       ptx::tc_fence_before_sync();
       ptx::mbar_arrive(p_full + buf);
     }
-    // epilogue: O, O2 -> global
+    // the two halves of a row add up their partial sums of u
+    s_supp[half * 128 + r] = supp;
+    ptx::bar_sync(1, kFwdRowThreads);
+    supp = s_supp[r] + s_supp[128 + r];
+    // epilogue: O, O2 -> global; each half stores D/2 of the row
     if (!dead && n_active > 0) {
       if (!ptx::mbar_wait(o_full, 0)) { raise_abort(cta_abort, p.status, kStTimeoutEpilogue); dead = true; }
     }
-    if (!dead && row < p.N) {
+    if (!dead) {  // TMEM loads are warp-collective: only the global stores are per-row
       ptx::tc_fence_after_sync();
       const float inv = (row_ok && supp > 0.f) ? 1.0f / supp : 0.f;
 #pragma unroll 1
-      for (int ch = 0; ch < D / 32; ++ch) {
+      for (int cc = 0; cc < D / 64; ++cc) {
+        const int ch = half * (D / 64) + cc;
         uint32_t ro[32], ro2[32];
         if (n_active > 0) {
           ptx::tmem_ld32(lane_addr + O_COL + ch * 32, ro);
@@ -335,10 +360,12 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
         }
         uint4* dst = reinterpret_cast<uint4*>(og + (size_t)row * D + ch * 32);
         uint4* dst2 = reinterpret_cast<uint4*>(o2g + (size_t)row * D + ch * 32);
+        if (row < p.N) {
 #pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
+          for (int q4 = 0; q4 < 4; ++q4) {
           dst[q4] = make_uint4(po[q4 * 4], po[q4 * 4 + 1], po[q4 * 4 + 2], po[q4 * 4 + 3]);
           dst2[q4] = make_uint4(po2[q4 * 4], po2[q4 * 4 + 1], po2[q4 * 4 + 2], po2[q4 * 4 + 3]);
+        }
         }
       }
     }
@@ -350,7 +377,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     for (int i = 0; i < 64; ++i) __nanosleep(1000);
   }
   __syncthreads();
-  if (warp == 5) {
+  if (warp == 9) {
     ptx::tc_fence_after_sync();
     ptx::tmem_dealloc(tmem_base, kFwdTmemCols);
   }

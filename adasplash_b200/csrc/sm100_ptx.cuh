@@ -49,14 +49,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait.  Each try_wait already blocks for a hardware-defined slice, so
-// kMaxPolls polls is on the order of seconds; a healthy kernel needs a handful.
-constexpr uint32_t kMaxPolls = 1u << 22;
+// Bounded wait: gives up after kMaxWaitCycles SM clocks (about 0.1 s; a healthy
+// kernel waits microseconds) and returns false, so a protocol bug surfaces as an
+// error status instead of a hung GPU.
+constexpr long long kMaxWaitCycles = 1ll << 28;
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-  for (uint32_t i = 0; i < kMaxPolls; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (!mbar_try_wait(bar, parity)) {
+    if (clock64() - t0 > kMaxWaitCycles) return false;
   }
-  return false;
+  return true;
 }
 
 // ---- fences -------------------------------------------------------------------

@@ -1,9 +1,11 @@
 // Threshold solver + block-mask builder on the tensor cores.
 //
 // One CTA owns a 128-row query tile of one head and sweeps the causal key range
-// (niter + 3) times without leaving the SM: the scaled Q tile stays in shared
-// memory, K tiles arrive by TMA through a 4-stage ring, S = Q~ K^T is produced by
-// tcgen05.mma into two 128x128 fp32 TMEM buffers, and two 128-thread epilogue
+// (niter + 3) times without leaving the SM: the Q tile is scaled, rounded and
+// parked in TMEM as the A operand (so the MMA reads only K from shared memory,
+// half the operand traffic of a shared-memory A), K tiles arrive by TMA through
+// a 4-stage ring, S = Q~ K^T is produced by tcgen05.mma into two 128x128 fp32
+// TMEM buffers, and two 128-thread epilogue
 // groups (one TMEM lane = one score row = one thread) alternate on the buffers,
 // so the row statistics of tile i overlap the MMA of tile i+1.
 //
@@ -13,14 +15,16 @@
 #pragma once
 #include <type_traits>
 
-#include "sm100_common.cuh"
+#include "sm100_fwd.cuh"
 
 namespace ads {
 namespace sm100 {
 
 constexpr int kSolveStages = 4;
 constexpr int kSolveThreads = 320;  // 8 epilogue warps + TMA warp + MMA warp
-constexpr int kSolveTmemCols = 256;
+constexpr int kSolveTmemCols = 512;  // S[2] at columns 0..255, the scaled Q tile (A operand) at 256..
+
+constexpr uint32_t kSolveQCol = 256;
 
 enum SweepMode : int { kModeMax = 0, kModeHist = 1, kModeHalley = 2, kModeFinal = 3 };
 
@@ -137,13 +141,12 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
           break;
         }
         ptx::tc_fence_after_sync();
-        const uint32_t a0 = ptx::smem_u32(sQ), b0 = ptx::smem_u32(sK + st * L::tile_bytes);
+        const uint32_t b0 = ptx::smem_u32(sK + st * L::tile_bytes);
         const uint32_t d = tmem_base + buf * kBlockN;
 #pragma unroll
         for (int kk = 0; kk < KSTEPS; ++kk) {
           const uint32_t off = (kk >> 2) * kPanelBytes + (kk & 3) * 32;
-          ptx::mma_ss(d, ptx::make_smem_desc(a0 + off, 16, 1024), ptx::make_smem_desc(b0 + off, 16, 1024),
-                      idesc, kk > 0);
+          ptx::mma_ts(d, tmem_base + kSolveQCol + kk * 8, ptx::make_smem_desc(b0 + off, 16, 1024), idesc, kk > 0);
         }
         ptx::mma_commit(k_empty + st);
         ptx::mma_commit(s_full + buf);
@@ -157,21 +160,30 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
     const bool row_ok = row < len;
     const int rb = wq >> 1;
     bool dead = false;
-    // scale Q by fp32(0.5/sqrt(D)) and round to the input dtype, in place; rows >= len -> 0
+    // Q~ = rn(q * fp32(0.5/sqrt(D))) (rows >= len -> 0), moved from the TMA tile in
+    // shared memory into TMEM: thread (row r, group wg) converts D/2 elements of
+    // its row and stores them as 16-bit pairs in lane r.
     if (!ptx::mbar_wait(q_full, 0)) { raise_abort(cta_abort, p.status, kStTimeoutEpilogue); dead = true; }
     if (!dead) {
-      const float sc = 0.5f * p.sm_scale;
-      for (int v = threadIdx.x; v < L::tile_bytes / 16; v += 256) {
-        uint4* ptr = reinterpret_cast<uint4*>(sQ) + v;
-        const int vrow = ((v * 16) % kPanelBytes) / 128;
-        uint4 val = *ptr;
-        T* e = reinterpret_cast<T*>(&val);
-        const bool keep = (m0 + vrow) < len;
+      const float sc = row_ok ? 0.5f * p.sm_scale : 0.f;
+      constexpr int CHUNKS = D / 16;  // 16-byte chunks (8 elements) per thread
 #pragma unroll
-        for (int j = 0; j < 8; ++j) e[j] = DT<T>::from_f(keep ? DT<T>::to_f(e[j]) * sc : 0.f);
-        *ptr = val;
+      for (int h16 = 0; h16 < CHUNKS / 4; ++h16) {
+        uint32_t pk[16];
+#pragma unroll
+        for (int cc = 0; cc < 4; ++cc) {
+          const int e0 = wg * (D / 2) + (h16 * 4 + cc) * 8;  // first element of the chunk
+          const int pn = e0 >> 6, c = (e0 & 63) >> 3;        // panel, chunk inside the 128-byte row
+          const uint4 val = *reinterpret_cast<const uint4*>(sQ + pn * kPanelBytes + r * 128 + ((c ^ (r & 7)) << 4));
+          const T* e = reinterpret_cast<const T*>(&val);
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            pk[cc * 4 + j] = pack2<T>(DT<T>::to_f(e[2 * j]) * sc, DT<T>::to_f(e[2 * j + 1]) * sc);
+        }
+        ptx::tmem_st16(tmem_base + ((uint32_t)(wq * 32) << 16) + kSolveQCol + wg * (D / 4) + h16 * 16, pk);
       }
-      ptx::fence_proxy_async_smem();
+      ptx::tmem_st_wait();
+      ptx::tc_fence_before_sync();
     }
     ptx::mbar_arrive(q_ready);
 
@@ -202,48 +214,48 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
         const bool need_mask = (kt == qt) || (n0 + kBlockN > len);
         float a2_mark = a2;  // support count at the start of the current 64-key half
         bool hit0 = false, hit1 = false;
+        const float thr = (mode == kModeHist) ? tau0 : hs.t;
 #pragma unroll 1
-        for (int ch = 0; ch < 4; ++ch) {
-          uint32_t raw[32];
-          ptx::tmem_ld32(tmem_base + ((uint32_t)(wq * 32) << 16) + wg * kBlockN + ch * 32, raw);
+        for (int hf = 0; hf < 2; ++hf) {  // 64 keys at a time: two TMEM loads in flight
+          uint32_t raw[64];
+          const uint32_t caddr = tmem_base + ((uint32_t)(wq * 32) << 16) + wg * kBlockN + hf * 64;
+          ptx::tmem_ld32(caddr, raw);
+          ptx::tmem_ld32(caddr + 32, raw + 32);
           ptx::tmem_ld_wait();
           float* v = reinterpret_cast<float*>(raw);
           if (need_mask) {
+            const int lim = min(row, len - 1) - (n0 + hf * 64);  // columns c <= lim survive
 #pragma unroll
-            for (int c = 0; c < 32; ++c) {
-              const int col = n0 + ch * 32 + c;
-              v[c] = (col <= row && col < len) ? v[c] : kMaskedScore;
-            }
+            for (int c = 0; c < 64; ++c) v[c] = (c <= lim) ? v[c] : kMaskedScore;
           }
           if (mode == kModeMax) {
 #pragma unroll
-            for (int c = 0; c < 32; c += 2) mx = ptx::fmax3(mx, v[c], v[c + 1]);
-          } else if (mode == kModeHist) {
+            for (int c = 0; c < 64; c += 2) mx = ptx::fmax3(mx, v[c], v[c + 1]);
+          } else {
+            // the scores above the threshold are a tiny part of a row: look at
+            // four at a time and only open a group that contains one
 #pragma unroll
-            for (int g8 = 0; g8 < 4; ++g8) {
-              float cm = ptx::fmax3(v[g8 * 8], v[g8 * 8 + 1], v[g8 * 8 + 2]);
-              cm = ptx::fmax3(cm, v[g8 * 8 + 3], v[g8 * 8 + 4]);
-              cm = ptx::fmax3(cm, v[g8 * 8 + 5], v[g8 * 8 + 6]);
-              cm = fmaxf(cm, v[g8 * 8 + 7]);
-              if (cm >= tau0) {
+            for (int g4 = 0; g4 < 16; ++g4) {
+              const float cm = fmaxf(ptx::fmax3(v[g4 * 4], v[g4 * 4 + 1], v[g4 * 4 + 2]), v[g4 * 4 + 3]);
+              if (mode == kModeHist) {
+                if (cm >= thr) {
 #pragma unroll
-                for (int c = 0; c < 8; ++c) {
-                  const float pr = (v[g8 * 8 + c] - tau0) * fbins;
+                  for (int c = 0; c < 4; ++c) {
+                    const float pr = (v[g4 * 4 + c] - tau0) * fbins;
 #pragma unroll
-                  for (int bb = 0; bb < 8; ++bb) cnt[bb] += (pr >= (float)bb) ? 1 : 0;
+                    for (int bb = 0; bb < 8; ++bb) cnt[bb] += (pr >= (float)bb) ? 1 : 0;
+                  }
+                }
+              } else if (cm > thr) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                  const float d = v[g4 * 4 + c] - thr;
+                  if (d > 0.f) { a0 = fmaf(d, d, a0); a1 += d; a2 += 1.f; }
                 }
               }
             }
-          } else {
-            if (ch == 2) { hit0 = a2 > a2_mark; a2_mark = a2; }
-#pragma unroll
-            for (int c = 0; c < 32; ++c) {
-              const float u = __saturatef(v[c] - hs.t);
-              a0 = fmaf(u, u, a0);
-              a1 += u;
-              a2 += (u > 0.f) ? 1.f : 0.f;
-            }
           }
+          if (hf == 0) { hit0 = a2 > a2_mark; a2_mark = a2; }
         }
         ptx::tc_fence_before_sync();
         ptx::mbar_arrive(s_free + wg);
