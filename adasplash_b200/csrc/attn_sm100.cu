@@ -67,7 +67,7 @@ int solve_t(const simt::Params& p, void* ws, cudaStream_t st) {
   size_t sm = SolveSmem<D>::bytes(p.n_words);
   if (sm > 227 * 1024) { set_error("sm100::solve: sequence too long for the bitmap staging (%zu B smem)", sm); return ADS_ERR_UNSUPPORTED; }
   if (int rc = set_smem(solve_kernel<T, D>, sm, "sm100::solve")) return rc;
-  long long ctas = (long long)t.nq * p.B * p.Hq;
+  long long ctas = (long long)((t.nq + 1) / 2) * p.B * p.Hq;  // one CTA per 256 query rows
   solve_kernel<T, D><<<(unsigned)ctas, kSolveThreads, sm, st>>>(tmQ, tmK, t);
   return check_launch("sm100::solve");
 }

@@ -354,8 +354,9 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
 // ---------------------------------------------------------------------------
 // dK, dV
 // ---------------------------------------------------------------------------
-constexpr int kDkvThreads = 320;    // 8 row warps + TMA warp + MMA warp
-constexpr int kDkvRowThreads = 256;
+constexpr int kDkvThreads = 576;    // 16 row warps (2 step groups x 2 column halves) + TMA warp + MMA warp
+constexpr int kDkvRowThreads = 512;
+constexpr int kDkvGroupThreads = 256;
 constexpr int kDkvStages = 3;       // (Q block, dO block) pairs in flight
 constexpr int kDkvTmemCols = 512;
 constexpr int kQBlock = 64;         // query rows per step (one block-mask row block)
@@ -469,14 +470,14 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
     *start_status = *(volatile int*)p.status;
     *cta_abort = 0;
   }
-  if (warp == 9) {
+  if (warp == 17) {
     if (lane == 0) {
       ptx::mbar_init(kv_full, 1);
       ptx::mbar_init(k_ready, kDkvRowThreads);
       for (int s = 0; s < kDkvStages; ++s) { ptx::mbar_init(x_full + s, 1); ptx::mbar_init(x_empty + s, 1); }
       for (int s = 0; s < 2; ++s) {
         ptx::mbar_init(s_full + s, 1);
-        ptx::mbar_init(p_full + s, kDkvRowThreads);
+        ptx::mbar_init(p_full + s, kDkvGroupThreads);
         ptx::mbar_init(s_free + s, 1);
       }
       ptx::mbar_init(acc_full, 1);
@@ -490,12 +491,12 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
   __syncthreads();
   ptx::tc_fence_after_sync();
   if (*start_status != 0) {
-    if (warp == 9) ptx::tmem_dealloc(*tmem_holder, kDkvTmemCols);
+    if (warp == 17) ptx::tmem_dealloc(*tmem_holder, kDkvTmemCols);
     return;
   }
   const uint32_t tmem_base = *tmem_holder;
 
-  if (warp == 8) {
+  if (warp == 16) {
     if (lane == 0) {
       ptx::prefetch_tmap(&tmK); ptx::prefetch_tmap(&tmV); ptx::prefetch_tmap(&tmQ64); ptx::prefetch_tmap(&tmDO64);
       ptx::mbar_arrive_expect_tx(kv_full, 2 * L::tile_bytes);
@@ -518,7 +519,7 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
         }
       }
     }
-  } else if (warp == 9) {
+  } else if (warp == 17) {
     constexpr uint32_t idesc_s = ptx::make_idesc(FMT, kBlockN, kQBlock, 0, 0);   // 128 keys x 64 queries
     constexpr uint32_t idesc_acc = ptx::make_idesc(FMT, kBlockN, D, 0, 1);        // 128 keys x D
     bool ok = true;
@@ -588,17 +589,17 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
       if (lane == 0) {
         ptx::tc_fence_after_sync();
         const uint32_t q0 = ptx::smem_u32(qt_), d0 = ptx::smem_u32(dot_);
-        // P^T / dS^T: 16 queries = 8 packed columns per k-step, at the start of each 32-column half
+        // P^T / dS^T: 16 queries = 8 packed columns per k-step, at the start of each 16-column group
         const uint32_t pa = tmem_base + buf * kQBlock;
         const uint32_t da = tmem_base + DP_COL0 + buf * kQBlock;
 #pragma unroll
         for (int kk = 0; kk < kQBlock / 16; ++kk) {
-          ptx::mma_ts(tmem_base + DV_COL, pa + (kk >> 1) * 32 + (kk & 1) * 8, ptx::make_smem_desc(d0 + kk * 2048, kQPanelBytes, 1024),
+          ptx::mma_ts(tmem_base + DV_COL, pa + kk * 16, ptx::make_smem_desc(d0 + kk * 2048, kQPanelBytes, 1024),
                       idesc_acc, (j > 0 || kk > 0));
         }
 #pragma unroll
         for (int kk = 0; kk < kQBlock / 16; ++kk) {
-          ptx::mma_ts(tmem_base + DK_COL, da + (kk >> 1) * 32 + (kk & 1) * 8, ptx::make_smem_desc(q0 + kk * 2048, kQPanelBytes, 1024),
+          ptx::mma_ts(tmem_base + DK_COL, da + kk * 16, ptx::make_smem_desc(q0 + kk * 2048, kQPanelBytes, 1024),
                       idesc_acc, (j > 0 || kk > 0));
         }
         ptx::mma_commit(x_empty + st);
@@ -611,7 +612,9 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
     if (!ok && lane == 0 && !*cta_abort) raise_abort(cta_abort, p.status, kStTimeoutMma);
   } else {
     const int wq = warp & 3;             // TMEM lanes 32*wq .. 32*wq+31
-    const int half = warp >> 2;          // query columns 32*half .. 32*half+31 of each block
+    const int half = (warp >> 2) & 1;    // query columns 32*half .. 32*half+31 of a block
+    const int group = warp >> 3;         // steps j with (j & 1) == group, buffer `group`
+    const int gtid = threadIdx.x & (kDkvGroupThreads - 1);
     const int r = wq * 32 + lane;        // key row inside the tile
     const int key = n0 + r;
     const bool key_ok = key < len;
@@ -636,71 +639,93 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
       ptx::fence_proxy_async_smem();
     }
     ptx::mbar_arrive(k_ready);
+    // tau / delta of a block's 64 query rows: fetched one own-step ahead into a register
+    // by the first 128 threads of the group, parked in shared memory at the step itself
+    auto fetch_td = [&](int g_, int m_) -> float {
+      if (gtid >= 128) return 0.f;
+      const int qrow = m_ * kQBlock + (gtid & 63);
+      const float* src = (gtid < 64) ? p.taus : p.delta;
+      return (qrow < len) ? src[(size_t)(b * p.Hq + kvh * G + g_) * p.N + qrow] : 0.f;
+    };
+    float* td = s_td + group * 128;
     QBlockScan scan(p.bmask_t, b, p.Hq, G, kvh, nt, n_qblocks, p.rows_padded, p.n_words);
     int g, m, n_active = 0;
     uint32_t flags;
-    for (int j = 0; scan.next(g, m, flags); ++j) {
-      const int buf = j & 1;
-      n_active = j + 1;
-      const size_t toff = (size_t)(b * p.Hq + kvh * G + g) * p.N;
-      // stage tau and delta of the 64 query rows of this block (double buffered)
-      float* td = s_td + buf * 128;
-      if (threadIdx.x < 128) {
-        const int qrow = m * kQBlock + (threadIdx.x & 63);
-        const float* src = (threadIdx.x < 64) ? p.taus : p.delta;
-        td[threadIdx.x] = (qrow < len) ? src[toff + qrow] : 0.f;
-      }
-      ptx::bar_sync(1, kDkvRowThreads);
-      if (dead || *cta_abort) { dead = true; continue; }
-      if (!ptx::mbar_wait(s_full + buf, (j >> 1) & 1)) { raise_abort(cta_abort, p.status, kStTimeoutEpilogue); dead = true; continue; }
-      ptx::tc_fence_after_sync();
-      const bool sub_on = (flags >> kh) & 1u;  // warp-uniform: the TMEM loads below are warp-collective
-      const int q0 = m * kQBlock + half * 32;  // first query row of this thread's columns
-      const uint32_t saddr = lane_addr + buf * kQBlock + half * 32;
-      const uint32_t daddr = lane_addr + DP_COL0 + buf * kQBlock + half * 32;
-      uint32_t pk[16], dk[16];
-      if (!sub_on) {
-#pragma unroll
-        for (int c = 0; c < 16; ++c) { pk[c] = 0u; dk[c] = 0u; }
+    // advance to this group's first step
+    bool have = scan.next(g, m, flags);
+    if (have) n_active = 1;
+    if (have && group == 1) { have = scan.next(g, m, flags); if (have) n_active = 2; }
+    float td_reg = have ? fetch_td(g, m) : 0.f;
+    for (int j = group; have; j += 2) {
+      // look ahead to this group's next step (skipping the other group's step)
+      int g2 = 0, m2 = 0;
+      uint32_t f2 = 0;
+      bool have2 = scan.next(g2, m2, f2);
+      if (have2) { n_active = j + 2; have2 = scan.next(g2, m2, f2); if (have2) n_active = j + 3; }
+      ptx::bar_sync(1 + group, kDkvGroupThreads);  // everyone is done reading the previous td
+      if (gtid < 128) td[gtid] = td_reg;
+      ptx::bar_sync(1 + group, kDkvGroupThreads);
+      td_reg = have2 ? fetch_td(g2, m2) : 0.f;
+      if (!(dead || *cta_abort)) {
+        if (!ptx::mbar_wait(s_full + group, (j >> 1) & 1)) { raise_abort(cta_abort, p.status, kStTimeoutEpilogue); dead = true; }
       } else {
-        uint32_t rs[32], rp[32];
-        ptx::tmem_ld32(saddr, rs);
-        ptx::tmem_ld32(daddr, rp);
-        ptx::tmem_ld_wait();
-        const float* s = reinterpret_cast<const float*>(rs);
-        const float* dp = reinterpret_cast<const float*>(rp);
-        const float* tq = td + half * 32;
-        const float* dq_ = td + 64 + half * 32;
-        // query column c is valid iff key <= q0 + c < len  <=>  lo <= c < hi
-        const int lo = key - q0, hi = key_ok ? len - q0 : 0;  // a padded key keeps nothing
-#pragma unroll
-        for (int c = 0; c < 32; c += 2) {
-          const float2 t2 = *reinterpret_cast<const float2*>(tq + c);
-          const float2 l2 = *reinterpret_cast<const float2*>(dq_ + c);
-          const float u0 = s[c] - t2.x, u1 = s[c + 1] - t2.y;
-          const bool ok0 = (u0 > 0.f) && (c >= lo) && (c < hi);
-          const bool ok1 = (u1 > 0.f) && (c + 1 >= lo) && (c + 1 < hi);
-          // select, not multiply: S / dP entries of padded rows may be anything
-          pk[c >> 1] = pack2<T>(ok0 ? u0 * u0 : 0.f, ok1 ? u1 * u1 : 0.f);
-          dk[c >> 1] = pack2<T>(ok0 ? u0 * (dp[c] - l2.x) : 0.f, ok1 ? u1 * (dp[c + 1] - l2.y) : 0.f);
-        }
+        dead = true;
       }
-      // written inside this thread's own 32 columns: the other half of the row is
-      // read by another warp at its own pace
-      ptx::tmem_st16(saddr, pk);
-      ptx::tmem_st16(daddr, dk);
-      ptx::tmem_st_wait();
-      ptx::tc_fence_before_sync();
-      ptx::mbar_arrive(p_full + buf);
+      if (!dead) {
+        ptx::tc_fence_after_sync();
+        const bool sub_on = (flags >> kh) & 1u;  // warp-uniform: the TMEM loads below are warp-collective
+#pragma unroll
+        for (int sc16 = 0; sc16 < 2; ++sc16) {
+          const int c0 = half * 32 + sc16 * 16;     // first query column of this sub-chunk
+          const int q0 = m * kQBlock + c0;
+          const uint32_t saddr = lane_addr + group * kQBlock + c0;
+          const uint32_t daddr = lane_addr + DP_COL0 + group * kQBlock + c0;
+          uint32_t pk[8], dk[8];
+          if (!sub_on) {
+#pragma unroll
+            for (int c = 0; c < 8; ++c) { pk[c] = 0u; dk[c] = 0u; }
+          } else {
+            uint32_t rs[16], rp[16];
+            ptx::tmem_ld16(saddr, rs);
+            ptx::tmem_ld16(daddr, rp);
+            ptx::tmem_ld_wait();
+            const float* s = reinterpret_cast<const float*>(rs);
+            const float* dp = reinterpret_cast<const float*>(rp);
+            const float* tq = td + c0;
+            const float* dq_ = td + 64 + c0;
+            // query column c is valid iff key <= q0 + c < len  <=>  lo <= c < hi
+            const int lo = key - q0, hi = key_ok ? len - q0 : 0;
+#pragma unroll
+            for (int c = 0; c < 16; c += 2) {
+              const float2 t2 = *reinterpret_cast<const float2*>(tq + c);
+              const float2 l2 = *reinterpret_cast<const float2*>(dq_ + c);
+              const float u0 = s[c] - t2.x, u1 = s[c + 1] - t2.y;
+              const bool ok0 = (u0 > 0.f) && (c >= lo) && (c < hi);
+              const bool ok1 = (u1 > 0.f) && (c + 1 >= lo) && (c + 1 < hi);
+              // select, not multiply: S / dP entries of padded rows may be anything
+              pk[c >> 1] = pack2<T>(ok0 ? u0 * u0 : 0.f, ok1 ? u1 * u1 : 0.f);
+              dk[c >> 1] = pack2<T>(ok0 ? u0 * (dp[c] - l2.x) : 0.f, ok1 ? u1 * (dp[c + 1] - l2.y) : 0.f);
+            }
+          }
+          // 16 queries = 8 packed columns, written at the start of this thread's own
+          // 16 columns: nobody else reads or writes those
+          ptx::tmem_st8(saddr, pk);
+          ptx::tmem_st8(daddr, dk);
+        }
+        ptx::tmem_st_wait();
+        ptx::tc_fence_before_sync();
+        ptx::mbar_arrive(p_full + group);
+      }
+      g = g2; m = m2; flags = f2;
+      have = have2;
     }
     if (!dead && n_active > 0) {
       if (!ptx::mbar_wait(acc_full, 0)) { raise_abort(cta_abort, p.status, kStTimeoutEpilogue); dead = true; }
     }
     if (!dead) {  // TMEM loads are warp-collective: only the global stores are per-row
       ptx::tc_fence_after_sync();
-#pragma unroll 1
-      for (int cc = 0; cc < D / 64; ++cc) {
-        const int ch = half * (D / 64) + cc;
+      const int ch = group * 2 + half;  // the four threads of a key row share the D/32 column chunks
+      if (ch < D / 32) {
         uint32_t rk[32], rv[32];
         if (n_active > 0) {
           ptx::tmem_ld32(lane_addr + DK_COL + ch * 32, rk);
@@ -737,7 +762,7 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
     for (int i = 0; i < 64; ++i) __nanosleep(1000);
   }
   __syncthreads();
-  if (warp == 9) {
+  if (warp == 17) {
     ptx::tc_fence_after_sync();
     ptx::tmem_dealloc(tmem_base, kDkvTmemCols);
   }

@@ -7,9 +7,11 @@
 //   P  = rn(u*u), U = rn(u) written back over S in TMEM as 16-bit pairs
 //   O += P V, O2 += U V    tcgen05.mma with the A operand in TMEM, V in shared memory
 // S is double buffered so that the S product of tile j+1 overlaps the row work
-// of tile j.  Eight row warps share the work: warps w and w+4 own the same 32
-// TMEM lanes (rows) and split the 128 keys of a tile in halves, which doubles the
-// warps per scheduler that hide the TMEM and ALU latency of the row work.
+// of tile j.  The row work of a tile is a chain of TMEM round trips, so sixteen
+// row warps share it: two groups alternate on the tiles (group g owns S buffer g),
+// and inside a group the warps w and w+4 own the same 32 TMEM lanes (rows) and
+// split the 128 keys in halves.  That puts four warps on every scheduler to hide
+// the TMEM and ALU latency.
 // Sub-tiles whose bit is clear contribute exactly zero, as in the reference,
 // which never visits them.
 #pragma once
@@ -20,8 +22,9 @@
 namespace ads {
 namespace sm100 {
 
-constexpr int kFwdThreads = 320;  // 8 row warps (two per TMEM lane quarter) + TMA warp + MMA warp
-constexpr int kFwdRowThreads = 256;
+constexpr int kFwdThreads = 576;  // 16 row warps (four per TMEM lane quarter) + TMA warp + MMA warp
+constexpr int kFwdRowThreads = 512;
+constexpr int kFwdGroupThreads = 256;  // row threads that work on one tile
 constexpr int kFwdKStages = 2;
 constexpr int kFwdVStages = 3;
 constexpr int kFwdTmemCols = 512;
@@ -35,8 +38,8 @@ struct FwdSmem {
   static constexpr int bar_off = v_off + kFwdVStages * tile_bytes;
   static constexpr int n_bars = 2 + 2 * kFwdKStages + 2 * kFwdVStages + 6 + 1;
   static constexpr int misc_off = bar_off + n_bars * 8;
-  static constexpr int supp_off = misc_off + 64;  // [2][128] floats: per-half partial sums of u
-  static constexpr size_t bytes = 1024 + supp_off + 2 * 128 * 4;
+  static constexpr int supp_off = misc_off + 64;  // [4][128] floats: partial sums of u per (group, half)
+  static constexpr size_t bytes = 1024 + supp_off + 4 * 128 * 4;
 };
 
 // Pack two fp32 values as 16-bit pairs (first value in the low half).
@@ -120,7 +123,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     *cta_abort = 0;
   }
   const int32_t* bm_head = p.bmask + (size_t)bh * p.rows_padded * p.n_words;
-  if (warp == 9) {
+  if (warp == 17) {
     if (lane == 0) {
       ptx::mbar_init(q_full, 1);
       ptx::mbar_init(q_ready, kFwdRowThreads);
@@ -128,7 +131,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       for (int s = 0; s < kFwdVStages; ++s) { ptx::mbar_init(v_full + s, 1); ptx::mbar_init(v_empty + s, 1); }
       for (int s = 0; s < 2; ++s) {
         ptx::mbar_init(s_full + s, 1);
-        ptx::mbar_init(p_full + s, kFwdRowThreads);
+        ptx::mbar_init(p_full + s, kFwdGroupThreads);
         ptx::mbar_init(s_free + s, 1);
       }
       ptx::mbar_init(o_full, 1);
@@ -142,12 +145,12 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
   __syncthreads();
   ptx::tc_fence_after_sync();
   if (*start_status != 0) {
-    if (warp == 9) ptx::tmem_dealloc(*tmem_holder, kFwdTmemCols);
+    if (warp == 17) ptx::tmem_dealloc(*tmem_holder, kFwdTmemCols);
     return;
   }
   const uint32_t tmem_base = *tmem_holder;
 
-  if (warp == 8) {
+  if (warp == 16) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
       ptx::prefetch_tmap(&tmQ);
@@ -172,7 +175,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
           ptx::tma_load_3d(sV + vs * L::tile_bytes + pn * kPanelBytes, &tmV, v_full + vs, pn * 64, kt * kBlockN, kv_head);
       }
     }
-  } else if (warp == 9) {
+  } else if (warp == 17) {
     // ---------------- MMA issuer (whole warp stays converged; lane 0 issues) ----------------
     constexpr uint32_t idesc_s = ptx::make_idesc(FMT, kBlockM, kBlockN, 0, 0);
     constexpr uint32_t idesc_pv = ptx::make_idesc(FMT, kBlockM, D, 0, 1);
@@ -246,8 +249,9 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     if (!ok && lane == 0 && !*cta_abort) raise_abort(cta_abort, p.status, kStTimeoutMma);
   } else {
     // ---------------- row warps: thread = (score row, key half) ----------------
-    const int wq = warp & 3;     // TMEM lanes 32*wq .. 32*wq+31
-    const int half = warp >> 2;  // keys 64*half .. 64*half+63 of each tile
+    const int wq = warp & 3;            // TMEM lanes 32*wq .. 32*wq+31
+    const int half = (warp >> 2) & 1;   // keys 64*half .. 64*half+63 of a tile
+    const int group = warp >> 3;        // tiles j with (j & 1) == group, S buffer `group`
     const int r = wq * 32 + lane;
     const int row = m0 + r;
     const bool row_ok = row < len;
@@ -279,6 +283,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     for (int j = 0; !dead && scan.next(kt, flags); ++j) {
       const int buf = j & 1;
       n_active = j + 1;
+      if (buf != group) continue;
       const bool sub_on = (flags >> (2 * rb + half)) & 1u;  // this thread's 64x64 sub-tile
       if (*cta_abort) { dead = true; break; }
       if (!ptx::mbar_wait(s_full + buf, (j >> 1) & 1)) { raise_abort(cta_abort, p.status, kStTimeoutEpilogue); dead = true; break; }
@@ -327,20 +332,19 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       ptx::tc_fence_before_sync();
       ptx::mbar_arrive(p_full + buf);
     }
-    // the two halves of a row add up their partial sums of u
-    s_supp[half * 128 + r] = supp;
+    // the four threads of a row add up their partial sums of u
+    s_supp[(group * 2 + half) * 128 + r] = supp;
     ptx::bar_sync(1, kFwdRowThreads);
-    supp = s_supp[r] + s_supp[128 + r];
-    // epilogue: O, O2 -> global; each half stores D/2 of the row
+    supp = (s_supp[r] + s_supp[128 + r]) + (s_supp[256 + r] + s_supp[384 + r]);
+    // epilogue: O, O2 -> global; the four threads of a row share the D/32 column chunks
     if (!dead && n_active > 0) {
       if (!ptx::mbar_wait(o_full, 0)) { raise_abort(cta_abort, p.status, kStTimeoutEpilogue); dead = true; }
     }
     if (!dead) {  // TMEM loads are warp-collective: only the global stores are per-row
       ptx::tc_fence_after_sync();
       const float inv = (row_ok && supp > 0.f) ? 1.0f / supp : 0.f;
-#pragma unroll 1
-      for (int cc = 0; cc < D / 64; ++cc) {
-        const int ch = half * (D / 64) + cc;
+      const int ch = group * 2 + half;
+      if (ch < D / 32) {
         uint32_t ro[32], ro2[32];
         if (n_active > 0) {
           ptx::tmem_ld32(lane_addr + O_COL + ch * 32, ro);
@@ -377,7 +381,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     for (int i = 0; i < 64; ++i) __nanosleep(1000);
   }
   __syncthreads();
-  if (warp == 9) {
+  if (warp == 17) {
     ptx::tc_fence_after_sync();
     ptx::tmem_dealloc(tmem_base, kFwdTmemCols);
   }

@@ -1,13 +1,19 @@
 // Threshold solver + block-mask builder on the tensor cores.
 //
-// One CTA owns a 128-row query tile of one head and sweeps the causal key range
-// (niter + 3) times without leaving the SM: the Q tile is scaled, rounded and
-// parked in TMEM as the A operand (so the MMA reads only K from shared memory,
-// half the operand traffic of a shared-memory A), K tiles arrive by TMA through
-// a 4-stage ring, S = Q~ K^T is produced by tcgen05.mma into two 128x128 fp32
-// TMEM buffers, and two 128-thread epilogue
-// groups (one TMEM lane = one score row = one thread) alternate on the buffers,
-// so the row statistics of tile i overlap the MMA of tile i+1.
+// One CTA owns 256 query rows of one head -- two 128-row MMA tiles A and B --
+// and sweeps the causal key range (niter + 3) times without leaving the SM.
+// Both row tiles use every K tile that TMA brings in, which halves the L2 -> SM
+// traffic per FLOP (a solver sweep has no other operand to amortise it: one
+// 32 KB K tile per 128x128x128 product made it L2-bandwidth-bound).
+//
+//   * the two Q tiles are scaled by fp32(0.5/sqrt(D)), rounded to the input
+//     dtype and parked in TMEM as A operands, so the MMA reads only K from
+//     shared memory;
+//   * S_A = Q~_A K^T and S_B = Q~_B K^T go to two 128-column fp32 TMEM buffers;
+//     row group A (4 warps, TMEM lane = score row = thread) reduces S_A while
+//     the tensor pipe produces S_B, and vice versa;
+//   * each thread owns its row for the whole solve, so no cross-thread exchange
+//     of row statistics is needed.
 //
 // Sweeps (adasplash_v2.py:151-681): row max -> tau0; BINS-bin histogram -> tau1;
 // niter Halley/bisection steps; a last sweep that records, per 64x64 sub-tile,
@@ -21,24 +27,23 @@ namespace ads {
 namespace sm100 {
 
 constexpr int kSolveStages = 4;
-constexpr int kSolveThreads = 320;  // 8 epilogue warps + TMA warp + MMA warp
-constexpr int kSolveTmemCols = 512;  // S[2] at columns 0..255, the scaled Q tile (A operand) at 256..
-
+constexpr int kSolveThreads = 320;   // 2 row groups x 4 warps + TMA warp + MMA warp
+constexpr int kSolveTmemCols = 512;  // S_A, S_B at columns 0 / 128, Q~_A, Q~_B from column 256
 constexpr uint32_t kSolveQCol = 256;
+constexpr int kSolveRows = 2 * kBlockM;  // query rows per CTA
 
 enum SweepMode : int { kModeMax = 0, kModeHist = 1, kModeHalley = 2, kModeFinal = 3 };
 
 template <int D>
 struct SolveSmem {
   static constexpr int tile_bytes = (D / 64) * kPanelBytes;
-  static constexpr int q_off = 0;
-  static constexpr int k_off = tile_bytes;
+  static constexpr int q_off = 0;                                  // two Q tiles
+  static constexpr int k_off = 2 * tile_bytes;
   static constexpr int bar_off = k_off + kSolveStages * tile_bytes;
   static constexpr int n_bars = 2 + 2 * kSolveStages + 4;
-  static constexpr int misc_off = bar_off + n_bars * 8;           // tmem base, abort flag, status
-  static constexpr int xchg_off = misc_off + 64;                  // [2][2][8][128] floats
-  static constexpr int bits_off = xchg_off + 2 * 2 * 8 * 128 * 4; // [2][n_words] words
-  static size_t bytes(int n_words) { return 1024 + bits_off + 2 * (size_t)n_words * 4; }
+  static constexpr int misc_off = bar_off + n_bars * 8;            // tmem base, abort flag, status
+  static constexpr int bits_off = misc_off + 64;                   // [4][n_words] words
+  static size_t bytes(int n_words) { return 1024 + bits_off + 4 * (size_t)n_words * 4; }
 };
 
 template <typename T, int D>
@@ -48,7 +53,7 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
   using L = SolveSmem<D>;
   constexpr int PANELS = D / 64;
   constexpr int KSTEPS = D / 16;
-  constexpr int FMT = sizeof(T) == 2 && std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
+  constexpr int FMT = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* sQ = smem + L::q_off;
@@ -58,26 +63,29 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
   uint64_t* q_ready = bars + 1;
   uint64_t* k_full = bars + 2;
   uint64_t* k_empty = k_full + kSolveStages;
-  uint64_t* s_full = k_empty + kSolveStages;
+  uint64_t* s_full = k_empty + kSolveStages;  // [2]: row tile A, B
   uint64_t* s_free = s_full + 2;
   uint32_t* tmem_holder = (uint32_t*)(smem + L::misc_off);
   volatile int* cta_abort = (volatile int*)(smem + L::misc_off + 4);
   int* start_status = (int*)(smem + L::misc_off + 8);
-  float* xchg = (float*)(smem + L::xchg_off);
   uint32_t* s_bits = (uint32_t*)(smem + L::bits_off);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int heads = p.B * p.Hq;
-  const int qt = p.nq - 1 - (int)(blockIdx.x / heads);  // heaviest tiles first
+  const int npair = (p.nq + 1) / 2;
+  const int pr_idx = npair - 1 - (int)(blockIdx.x / heads);  // heaviest row pairs first
   const int bh = blockIdx.x % heads;
   const int b = bh / p.Hq, h = bh % p.Hq;
   const int kvh = h / (p.Hq / p.Hkv);
   const int len = load_len(p.varlen, p.varlen_is_i64, b, p.N);
-  const int m0 = qt * kBlockM;
+  const int m0 = pr_idx * kSolveRows;  // first row of tile A; tile B starts at m0 + 128
   if (m0 >= len) return;
-  const int T_tiles = qt + 1;  // 128-key tiles up to the diagonal (= up to len for the last valid tile)
+  const bool b_on = (m0 + kBlockM) < len;           // row tile B has at least one valid row
+  const int qtA = 2 * pr_idx, qtB = qtA + 1;        // their 128-row tile indices
+  const int T_a = qtA + 1;                          // key tiles of A: 0 .. qtA
+  const int T_k = b_on ? qtB + 1 : T_a;             // key tiles streamed per sweep
   const int nsweeps = p.tau_given ? 1 : p.niter + 3;
-  const int total = nsweeps * T_tiles;
+  const int total = nsweeps * T_k;
 
   if (threadIdx.x == 0) {
     *start_status = *(volatile int*)p.status;
@@ -95,7 +103,7 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
     ptx::tmem_alloc(tmem_holder, kSolveTmemCols);
     ptx::tmem_relinquish();
   }
-  for (int w = threadIdx.x; w < 2 * p.n_words; w += kSolveThreads) s_bits[w] = 0u;
+  for (int w = threadIdx.x; w < 4 * p.n_words; w += kSolveThreads) s_bits[w] = 0u;
   ptx::tc_fence_before_sync();
   __syncthreads();
   ptx::tc_fence_after_sync();
@@ -110,11 +118,13 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
     if (lane == 0) {
       ptx::prefetch_tmap(&tmQ);
       ptx::prefetch_tmap(&tmK);
-      ptx::mbar_arrive_expect_tx(q_full, L::tile_bytes);
-      for (int pn = 0; pn < PANELS; ++pn) ptx::tma_load_3d(sQ + pn * kPanelBytes, &tmQ, q_full, pn * 64, m0, bh);
+      ptx::mbar_arrive_expect_tx(q_full, 2 * L::tile_bytes);
+      for (int t = 0; t < 2; ++t)
+        for (int pn = 0; pn < PANELS; ++pn)
+          ptx::tma_load_3d(sQ + t * L::tile_bytes + pn * kPanelBytes, &tmQ, q_full, pn * 64, m0 + t * kBlockM, bh);
       const int kv_head = b * p.Hkv + kvh;
       for (int i = 0; i < total; ++i) {
-        const int st = i % kSolveStages, kt = i % T_tiles;
+        const int st = i % kSolveStages, kt = i % T_k;
         if (*cta_abort) break;
         if (!ptx::mbar_wait(k_empty + st, ((i / kSolveStages) & 1) ^ 1)) {
           raise_abort(cta_abort, p.status, kStTimeoutProducer);
@@ -132,55 +142,70 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
       constexpr uint32_t idesc = ptx::make_idesc(FMT, kBlockM, kBlockN, 0, 0);
       bool ok = ptx::mbar_wait(q_ready, 0);
       if (!ok) raise_abort(cta_abort, p.status, kStTimeoutMma);
+      int use_a = 0, use_b = 0;  // how often each S buffer has been filled
       for (int i = 0; ok && i < total; ++i) {
-        const int st = i % kSolveStages, buf = i & 1;
+        const int st = i % kSolveStages, kt = i % T_k;
         if (*cta_abort) break;
-        if (!ptx::mbar_wait(k_full + st, (i / kSolveStages) & 1) ||
-            !ptx::mbar_wait(s_free + buf, ((i >> 1) & 1) ^ 1)) {
-          raise_abort(cta_abort, p.status, kStTimeoutMma);
-          break;
-        }
-        ptx::tc_fence_after_sync();
+        if (!ptx::mbar_wait(k_full + st, (i / kSolveStages) & 1)) { raise_abort(cta_abort, p.status, kStTimeoutMma); break; }
         const uint32_t b0 = ptx::smem_u32(sK + st * L::tile_bytes);
-        const uint32_t d = tmem_base + buf * kBlockN;
+        if (kt < T_a) {
+          if (!ptx::mbar_wait(s_free + 0, (use_a & 1) ^ 1)) { raise_abort(cta_abort, p.status, kStTimeoutMma); break; }
+          ptx::tc_fence_after_sync();
 #pragma unroll
-        for (int kk = 0; kk < KSTEPS; ++kk) {
-          const uint32_t off = (kk >> 2) * kPanelBytes + (kk & 3) * 32;
-          ptx::mma_ts(d, tmem_base + kSolveQCol + kk * 8, ptx::make_smem_desc(b0 + off, 16, 1024), idesc, kk > 0);
+          for (int kk = 0; kk < KSTEPS; ++kk) {
+            const uint32_t off = (kk >> 2) * kPanelBytes + (kk & 3) * 32;
+            ptx::mma_ts(tmem_base, tmem_base + kSolveQCol + kk * 8, ptx::make_smem_desc(b0 + off, 16, 1024), idesc, kk > 0);
+          }
+          ptx::mma_commit(s_full + 0);
+          ++use_a;
+        }
+        if (b_on) {
+          if (!ptx::mbar_wait(s_free + 1, (use_b & 1) ^ 1)) { raise_abort(cta_abort, p.status, kStTimeoutMma); break; }
+          ptx::tc_fence_after_sync();
+#pragma unroll
+          for (int kk = 0; kk < KSTEPS; ++kk) {
+            const uint32_t off = (kk >> 2) * kPanelBytes + (kk & 3) * 32;
+            ptx::mma_ts(tmem_base + kBlockN, tmem_base + kSolveQCol + D / 2 + kk * 8,
+                        ptx::make_smem_desc(b0 + off, 16, 1024), idesc, kk > 0);
+          }
+          ptx::mma_commit(s_full + 1);
+          ++use_b;
         }
         ptx::mma_commit(k_empty + st);
-        ptx::mma_commit(s_full + buf);
       }
     }
   } else {
-    // ---------------- epilogue: 2 groups x 128 threads, one score row per thread ----------------
-    const int wg = warp >> 2, wq = warp & 3;
+    // ---------------- row groups: group t owns row tile t, one score row per thread ----------------
+    const int grp = warp >> 2, wq = warp & 3;
     const int r = wq * 32 + lane;
-    const int row = m0 + r;
+    const int row = m0 + grp * kBlockM + r;
     const bool row_ok = row < len;
     const int rb = wq >> 1;
+    const int qt = grp == 0 ? qtA : qtB;            // this group's 128-row tile index
+    const bool grp_on = grp == 0 || b_on;
+    const int T_g = qt + 1;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(wq * 32) << 16);
     bool dead = false;
-    // Q~ = rn(q * fp32(0.5/sqrt(D))) (rows >= len -> 0), moved from the TMA tile in
-    // shared memory into TMEM: thread (row r, group wg) converts D/2 elements of
-    // its row and stores them as 16-bit pairs in lane r.
+    // Q~ = rn(q * fp32(0.5/sqrt(D))) (rows >= len -> 0), from the TMA tile in shared
+    // memory into TMEM: thread r converts the D elements of its row (16-bit pairs, lane r)
     if (!ptx::mbar_wait(q_full, 0)) { raise_abort(cta_abort, p.status, kStTimeoutEpilogue); dead = true; }
     if (!dead) {
       const float sc = row_ok ? 0.5f * p.sm_scale : 0.f;
-      constexpr int CHUNKS = D / 16;  // 16-byte chunks (8 elements) per thread
+      const uint8_t* qtile = sQ + grp * L::tile_bytes;
 #pragma unroll
-      for (int h16 = 0; h16 < CHUNKS / 4; ++h16) {
+      for (int h16 = 0; h16 < D / 32; ++h16) {  // 32 elements -> 16 packed columns per store
         uint32_t pk[16];
 #pragma unroll
         for (int cc = 0; cc < 4; ++cc) {
-          const int e0 = wg * (D / 2) + (h16 * 4 + cc) * 8;  // first element of the chunk
-          const int pn = e0 >> 6, c = (e0 & 63) >> 3;        // panel, chunk inside the 128-byte row
-          const uint4 val = *reinterpret_cast<const uint4*>(sQ + pn * kPanelBytes + r * 128 + ((c ^ (r & 7)) << 4));
+          const int e0 = (h16 * 4 + cc) * 8;               // first element of the 16-byte chunk
+          const int pn = e0 >> 6, c = (e0 & 63) >> 3;      // panel, chunk inside the 128-byte row
+          const uint4 val = *reinterpret_cast<const uint4*>(qtile + pn * kPanelBytes + r * 128 + ((c ^ (r & 7)) << 4));
           const T* e = reinterpret_cast<const T*>(&val);
 #pragma unroll
           for (int j = 0; j < 4; ++j)
             pk[cc * 4 + j] = pack2<T>(DT<T>::to_f(e[2 * j]) * sc, DT<T>::to_f(e[2 * j + 1]) * sc);
         }
-        ptx::tmem_st16(tmem_base + ((uint32_t)(wq * 32) << 16) + kSolveQCol + wg * (D / 4) + h16 * 16, pk);
+        ptx::tmem_st16(lane_addr + kSolveQCol + grp * (D / 2) + h16 * 16, pk);
       }
       ptx::tmem_st_wait();
       ptx::tc_fence_before_sync();
@@ -191,20 +216,17 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
     int cnt[8];
     HalleyState hs;
     hs.t = hs.lo = hs.hi = 0.f;
-    if (p.tau_given) {
-      hs.t = row_ok ? p.taus[((size_t)bh) * p.N + row] : 0.f;
-    }
+    if (p.tau_given) hs.t = row_ok ? p.taus[((size_t)bh) * p.N + row] : 0.f;
     const float fbins = (float)p.bins;
-    for (int s = 0; s < nsweeps; ++s) {
+    int use = 0;  // tiles of this group consumed so far
+    for (int s = 0; grp_on && s < nsweeps; ++s) {
       const int mode = p.tau_given ? kModeFinal : (s == 0 ? kModeMax : (s == 1 ? kModeHist : (s == nsweeps - 1 ? kModeFinal : kModeHalley)));
       float a0 = 0.f, a1 = 0.f, a2 = 0.f;
 #pragma unroll
       for (int c = 0; c < 8; ++c) cnt[c] = 0;
-      for (int kt = 0; kt < T_tiles; ++kt) {
-        const int i = s * T_tiles + kt;
-        if ((i & 1) != wg) continue;
+      for (int kt = 0; kt < T_g; ++kt, ++use) {
         if (dead || *cta_abort) { dead = true; continue; }
-        if (!ptx::mbar_wait(s_full + wg, (i >> 1) & 1)) {
+        if (!ptx::mbar_wait(s_full + grp, use & 1)) {
           raise_abort(cta_abort, p.status, kStTimeoutEpilogue);
           dead = true;
           continue;
@@ -214,11 +236,12 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
         const bool need_mask = (kt == qt) || (n0 + kBlockN > len);
         float a2_mark = a2;  // support count at the start of the current 64-key half
         bool hit0 = false, hit1 = false;
+        unsigned long long packed = 0ull;  // eight 8-bit cumulative bin counters of this tile
         const float thr = (mode == kModeHist) ? tau0 : hs.t;
 #pragma unroll 1
         for (int hf = 0; hf < 2; ++hf) {  // 64 keys at a time: two TMEM loads in flight
           uint32_t raw[64];
-          const uint32_t caddr = tmem_base + ((uint32_t)(wq * 32) << 16) + wg * kBlockN + hf * 64;
+          const uint32_t caddr = lane_addr + grp * kBlockN + hf * 64;
           ptx::tmem_ld32(caddr, raw);
           ptx::tmem_ld32(caddr + 32, raw + 32);
           ptx::tmem_ld_wait();
@@ -229,8 +252,16 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
             for (int c = 0; c < 64; ++c) v[c] = (c <= lim) ? v[c] : kMaskedScore;
           }
           if (mode == kModeMax) {
+            // four independent chains: a single running max would serialise 32 dependent ops
+            float m0_ = mx, m1_ = mx, m2_ = mx, m3_ = mx;
 #pragma unroll
-            for (int c = 0; c < 64; c += 2) mx = ptx::fmax3(mx, v[c], v[c + 1]);
+            for (int c = 0; c < 64; c += 8) {
+              m0_ = ptx::fmax3(m0_, v[c], v[c + 1]);
+              m1_ = ptx::fmax3(m1_, v[c + 2], v[c + 3]);
+              m2_ = ptx::fmax3(m2_, v[c + 4], v[c + 5]);
+              m3_ = ptx::fmax3(m3_, v[c + 6], v[c + 7]);
+            }
+            mx = fmaxf(fmaxf(m0_, m1_), fmaxf(m2_, m3_));
           } else {
             // the scores above the threshold are a tiny part of a row: look at
             // four at a time and only open a group that contains one
@@ -241,9 +272,13 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
                 if (cm >= thr) {
 #pragma unroll
                   for (int c = 0; c < 4; ++c) {
-                    const float pr = (v[g4 * 4 + c] - tau0) * fbins;
-#pragma unroll
-                    for (int bb = 0; bb < 8; ++bb) cnt[bb] += (pr >= (float)bb) ? 1 : 0;
+                    // bin = floor((z - tau0) * BINS) clamped to 7; one add of a byte pattern
+                    // bumps the cumulative counters N_0..N_bin (<= 128 hits per tile: no overflow)
+                    const float prj = (v[g4 * 4 + c] - tau0) * fbins;
+                    if (prj >= 0.f) {
+                      const int bsel = min(__float2int_rd(prj), 7);
+                      packed += 0x0101010101010101ull >> ((7 - bsel) * 8);
+                    }
                   }
                 }
               } else if (cm > thr) {
@@ -258,58 +293,46 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
           if (hf == 0) { hit0 = a2 > a2_mark; a2_mark = a2; }
         }
         ptx::tc_fence_before_sync();
-        ptx::mbar_arrive(s_free + wg);
+        ptx::mbar_arrive(s_free + grp);
+        if (packed != 0ull) {
+#pragma unroll
+          for (int bb = 0; bb < 8; ++bb) cnt[bb] += (int)((packed >> (8 * bb)) & 0xffull);
+        }
         if (mode == kModeFinal) {
           hit1 = a2 > a2_mark;
           const bool any0 = __any_sync(0xffffffffu, hit0 && row_ok);
           const bool any1 = __any_sync(0xffffffffu, hit1 && row_ok);
           if (lane == 0) {
             const int kb = 2 * kt;
-            if (any0) atomicOr(&s_bits[rb * p.n_words + (kb >> 5)], 1u << (kb & 31));
-            if (any1) atomicOr(&s_bits[rb * p.n_words + ((kb + 1) >> 5)], 1u << ((kb + 1) & 31));
+            uint32_t* bits = s_bits + (grp * 2 + rb) * p.n_words;
+            if (any0) atomicOr(&bits[kb >> 5], 1u << (kb & 31));
+            if (any1) atomicOr(&bits[(kb + 1) >> 5], 1u << ((kb + 1) & 31));
           }
         }
       }
-      // combine the two groups' partial statistics of this sweep
-      float* xb = xchg + (s & 1) * (2 * 8 * 128);
-      float* mine = xb + wg * (8 * 128);
+      // end of sweep: this thread has seen its whole row
       if (mode == kModeMax) {
-        mine[r] = mx;
-      } else if (mode == kModeHist) {
-#pragma unroll
-        for (int c = 0; c < 8; ++c) mine[c * 128 + r] = __int_as_float(cnt[c]);
-      } else {
-        mine[r] = a0; mine[128 + r] = a1; mine[256 + r] = a2;
-      }
-      ptx::bar_sync(1, 256);
-      const float* o0 = xb;
-      const float* o1 = xb + 8 * 128;
-      if (mode == kModeMax) {
-        mx = fmaxf(o0[r], o1[r]);
         tau0 = mx - 1.0f;
       } else if (mode == kModeHist) {
         int bins_cnt[8];
-        int cum[9];
-#pragma unroll
-        for (int c = 0; c < 8; ++c) cum[c] = __float_as_int(o0[c * 128 + r]) + __float_as_int(o1[c * 128 + r]);
-        cum[8] = 0;
-        for (int c = 0; c < p.bins; ++c) bins_cnt[c] = cum[c] - (c + 1 < p.bins ? cum[c + 1] : 0);
+        for (int c = 0; c < p.bins; ++c) bins_cnt[c] = cnt[c] - (c + 1 < p.bins ? cnt[c + 1] : 0);
         const float t1 = hist_tau_alpha15<8>(bins_cnt, p.bins, tau0);
         hs.lo = t1;
         hs.hi = t1 + 1.0f / fbins;
         hs.t = 0.5f * (hs.lo + hs.hi);
       } else if (!p.tau_given) {
-        halley_bisect_update(hs, o0[r] + o1[r], o0[128 + r] + o1[128 + r], o0[256 + r] + o1[256 + r]);
+        halley_bisect_update(hs, a0, a1, a2);
       }
     }
     ptx::bar_sync(1, 256);  // every atomicOr on s_bits is done
     if (!*cta_abort) {
-      for (int t = threadIdx.x; t < 2 * p.n_words; t += 256) {
+      for (int t = threadIdx.x; t < 4 * p.n_words; t += 256) {
         const int rbi = t / p.n_words, w = t % p.n_words;
-        const int mrow = 2 * qt + rbi;
-        if (mrow < p.rows_padded) p.bmask[((size_t)bh * p.rows_padded + mrow) * p.n_words + w] = (int32_t)s_bits[t];
+        const int mrow = 4 * pr_idx + rbi;  // 64-row block index
+        if (mrow < p.rows_padded && (rbi < 2 || b_on))
+          p.bmask[((size_t)bh * p.rows_padded + mrow) * p.n_words + w] = (int32_t)s_bits[t];
       }
-      if (!p.tau_given && wg == 0 && row_ok) p.taus[(size_t)bh * p.N + row] = hs.t;
+      if (!p.tau_given && grp_on && row_ok) p.taus[(size_t)bh * p.N + row] = hs.t;
     }
   }
 

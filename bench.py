@@ -43,6 +43,8 @@ WORKLOADS = {
                label="adasplash_v2 GQA+varlen bf16 B=8 Hq=32 Hkv=8 N=16384 D=128 niter=1"),
     "c5": dict(B=2, Hq=64, Hkv=8, N=65536, D=128, scale=1.5, varlen=False,
                label="adasplash_v2 long context bf16 B=2 Hq=64 Hkv=8 N=65536 D=128 niter=1"),
+    "mid": dict(B=2, Hq=16, Hkv=16, N=8192, D=128, scale=1.5, varlen=False,
+                label="adasplash_v2 bf16 B=2 Hq=Hkv=16 N=8192 D=128 niter=1 (ncu capture case, 268 MB of inputs)"),
     "small": dict(B=1, Hq=8, Hkv=8, N=2048, D=128, scale=1.5, varlen=False,
                   label="adasplash_v2 bf16 B=1 Hq=Hkv=8 N=2048 D=128 niter=1 (profiling case)"),
 }
@@ -56,6 +58,23 @@ NCU_DRAM_BYTES_PER_LAUNCH = {}
 def dense_equiv_flops(w, lens):
     """FlashAttention convention, causal: 7 * Hq * D * sum_b L_b^2 for fwd+bwd."""
     return 7.0 * w["Hq"] * w["D"] * float(sum(l * l for l in lens))
+
+
+def max_over_ranks(ms, world, device):
+    """Slowest rank's elapsed time (the only communication of a multi-GPU run, outside
+    the timed region; works on the nccl and the gloo backend alike)."""
+    if world <= 1:
+        return float(ms)
+    import torch.distributed as dist
+    t = torch.tensor([float(ms)], device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def aggregate_tflops(world, flops_per_rank, ms_step):
+    """Whole-job throughput: every rank processed `flops_per_rank` per step in the
+    slowest rank's time."""
+    return world * flops_per_rank / (ms_step * 1e-3) / 1e12
 
 
 def make_inputs(w, rank, pinned=True):
@@ -228,10 +247,7 @@ def run_ours(args):
         barrier()
         ms = a.elapsed_time(b)
         launches = _lib.launch_count() - l0
-        if world > 1:
-            t = torch.tensor([ms], device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
+        ms = max_over_ranks(ms, world, dev)
         return ms / steps, launches
 
     sampler = ClockSampler(local)
@@ -242,8 +258,8 @@ def run_ours(args):
     ms_e2e, _ = timed(step_e2e, max(2, min(args.steps, 5)), 1)
 
     flops = dense_equiv_flops(w, lens)
-    value = world * flops / (ms_step * 1e-3) / 1e12
-    e2e_value = world * flops / (ms_e2e * 1e-3) / 1e12
+    value = aggregate_tflops(world, flops, ms_step)
+    e2e_value = aggregate_tflops(world, flops, ms_e2e)
     h2d = sum(t.numel() * t.element_size() for t in (hq, hk, hv, hdo))
     d2h = sum(t.numel() * t.element_size() for t in host_out)
 
