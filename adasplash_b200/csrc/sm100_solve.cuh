@@ -10,10 +10,13 @@
 //     dtype and parked in TMEM as A operands, so the MMA reads only K from
 //     shared memory;
 //   * S_A = Q~_A K^T and S_B = Q~_B K^T go to two 128-column fp32 TMEM buffers;
-//     row group A (4 warps, TMEM lane = score row = thread) reduces S_A while
-//     the tensor pipe produces S_B, and vice versa;
-//   * each thread owns its row for the whole solve, so no cross-thread exchange
-//     of row statistics is needed.
+//     row group A (8 warps) reduces S_A while the tensor pipe produces S_B, and
+//     vice versa;
+//   * inside a group, TMEM lane = score row, and the two warps that own the same
+//     32 lanes split the 128 keys of a tile in halves (the row work of a tile is
+//     a chain of TMEM round trips; two threads per row halve it).  The two
+//     partial statistics of a row are combined once per sweep through shared
+//     memory.
 //
 // Sweeps (adasplash_v2.py:151-681): row max -> tau0; BINS-bin histogram -> tau1;
 // niter Halley/bisection steps; a last sweep that records, per 64x64 sub-tile,
@@ -26,8 +29,10 @@
 namespace ads {
 namespace sm100 {
 
-constexpr int kSolveStages = 4;
-constexpr int kSolveThreads = 320;   // 2 row groups x 4 warps + TMA warp + MMA warp
+constexpr int kSolveStages = 3;  // each K tile feeds two products, three tiles in flight cover the TMA latency
+constexpr int kSolveThreads = 576;   // 2 row groups x 8 warps + TMA warp + MMA warp
+constexpr int kSolveRowThreads = 512;
+constexpr int kSolveGroupThreads = 256;
 constexpr int kSolveTmemCols = 512;  // S_A, S_B at columns 0 / 128, Q~_A, Q~_B from column 256
 constexpr uint32_t kSolveQCol = 256;
 constexpr int kSolveRows = 2 * kBlockM;  // query rows per CTA
@@ -42,7 +47,8 @@ struct SolveSmem {
   static constexpr int bar_off = k_off + kSolveStages * tile_bytes;
   static constexpr int n_bars = 2 + 2 * kSolveStages + 4;
   static constexpr int misc_off = bar_off + n_bars * 8;            // tmem base, abort flag, status
-  static constexpr int bits_off = misc_off + 64;                   // [4][n_words] words
+  static constexpr int xchg_off = misc_off + 64;                   // [2 sweep parities][2 groups][2 halves][8][128] floats
+  static constexpr int bits_off = xchg_off + 2 * 2 * 2 * 8 * 128 * 4;  // [4][n_words] words
   static size_t bytes(int n_words) { return 1024 + bits_off + 4 * (size_t)n_words * 4; }
 };
 
@@ -68,6 +74,7 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
   uint32_t* tmem_holder = (uint32_t*)(smem + L::misc_off);
   volatile int* cta_abort = (volatile int*)(smem + L::misc_off + 4);
   int* start_status = (int*)(smem + L::misc_off + 8);
+  float* xchg = (float*)(smem + L::xchg_off);
   uint32_t* s_bits = (uint32_t*)(smem + L::bits_off);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -91,12 +98,12 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
     *start_status = *(volatile int*)p.status;
     *cta_abort = 0;
   }
-  if (warp == 9) {
+  if (warp == 17) {
     if (lane == 0) {
       ptx::mbar_init(q_full, 1);
-      ptx::mbar_init(q_ready, 256);
+      ptx::mbar_init(q_ready, kSolveRowThreads);
       for (int s = 0; s < kSolveStages; ++s) { ptx::mbar_init(k_full + s, 1); ptx::mbar_init(k_empty + s, 1); }
-      for (int s = 0; s < 2; ++s) { ptx::mbar_init(s_full + s, 1); ptx::mbar_init(s_free + s, 128); }
+      for (int s = 0; s < 2; ++s) { ptx::mbar_init(s_full + s, 1); ptx::mbar_init(s_free + s, kSolveGroupThreads); }
       ptx::fence_mbar_init();
     }
     __syncwarp();
@@ -108,12 +115,12 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
   __syncthreads();
   ptx::tc_fence_after_sync();
   if (*start_status != 0) {  // an earlier CTA of this launch already failed: do nothing
-    if (warp == 9) ptx::tmem_dealloc(*tmem_holder, kSolveTmemCols);
+    if (warp == 17) ptx::tmem_dealloc(*tmem_holder, kSolveTmemCols);
     return;
   }
   const uint32_t tmem_base = *tmem_holder;
 
-  if (warp == 8) {
+  if (warp == 16) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
       ptx::prefetch_tmap(&tmQ);
@@ -136,7 +143,7 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
                            kt * kBlockN, kv_head);
       }
     }
-  } else if (warp == 9) {
+  } else if (warp == 17) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
       constexpr uint32_t idesc = ptx::make_idesc(FMT, kBlockM, kBlockN, 0, 0);
@@ -176,7 +183,7 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
     }
   } else {
     // ---------------- row groups: group t owns row tile t, one score row per thread ----------------
-    const int grp = warp >> 2, wq = warp & 3;
+    const int grp = warp >> 3, half = (warp >> 2) & 1, wq = warp & 3;
     const int r = wq * 32 + lane;
     const int row = m0 + grp * kBlockM + r;
     const bool row_ok = row < len;
@@ -187,13 +194,14 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
     const uint32_t lane_addr = tmem_base + ((uint32_t)(wq * 32) << 16);
     bool dead = false;
     // Q~ = rn(q * fp32(0.5/sqrt(D))) (rows >= len -> 0), from the TMA tile in shared
-    // memory into TMEM: thread r converts the D elements of its row (16-bit pairs, lane r)
+    // memory into TMEM: the two threads of row r convert D/2 elements each (16-bit pairs, lane r)
     if (!ptx::mbar_wait(q_full, 0)) { raise_abort(cta_abort, p.status, kStTimeoutEpilogue); dead = true; }
     if (!dead) {
       const float sc = row_ok ? 0.5f * p.sm_scale : 0.f;
       const uint8_t* qtile = sQ + grp * L::tile_bytes;
 #pragma unroll
-      for (int h16 = 0; h16 < D / 32; ++h16) {  // 32 elements -> 16 packed columns per store
+      for (int hh = 0; hh < D / 64; ++hh) {  // 32 elements -> 16 packed columns per store; D/2 elements per thread
+        const int h16 = half * (D / 64) + hh;
         uint32_t pk[16];
 #pragma unroll
         for (int cc = 0; cc < 4; ++cc) {
@@ -234,28 +242,26 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
         ptx::tc_fence_after_sync();
         const int n0 = kt * kBlockN;
         const bool need_mask = (kt == qt) || (n0 + kBlockN > len);
-        float a2_mark = a2;  // support count at the start of the current 64-key half
-        bool hit0 = false, hit1 = false;
+        const float a2_mark = a2;  // support count before this thread's 64 keys of the tile
         unsigned long long packed = 0ull;  // eight 8-bit cumulative bin counters of this tile
         const float thr = (mode == kModeHist) ? tau0 : hs.t;
 #pragma unroll 1
-        for (int hf = 0; hf < 2; ++hf) {  // 64 keys at a time: two TMEM loads in flight
-          uint32_t raw[64];
-          const uint32_t caddr = lane_addr + grp * kBlockN + hf * 64;
-          ptx::tmem_ld32(caddr, raw);
-          ptx::tmem_ld32(caddr + 32, raw + 32);
+        for (int q32 = 0; q32 < 2; ++q32) {  // this thread's 64 keys, 32 at a time
+          uint32_t raw[32];
+          const int c0 = half * 64 + q32 * 32;
+          ptx::tmem_ld32(lane_addr + grp * kBlockN + c0, raw);
           ptx::tmem_ld_wait();
           float* v = reinterpret_cast<float*>(raw);
           if (need_mask) {
-            const int lim = min(row, len - 1) - (n0 + hf * 64);  // columns c <= lim survive
+            const int lim = min(row, len - 1) - (n0 + c0);  // columns c <= lim survive
 #pragma unroll
-            for (int c = 0; c < 64; ++c) v[c] = (c <= lim) ? v[c] : kMaskedScore;
+            for (int c = 0; c < 32; ++c) v[c] = (c <= lim) ? v[c] : kMaskedScore;
           }
           if (mode == kModeMax) {
-            // four independent chains: a single running max would serialise 32 dependent ops
+            // four independent chains: a single running max would serialise the dependent ops
             float m0_ = mx, m1_ = mx, m2_ = mx, m3_ = mx;
 #pragma unroll
-            for (int c = 0; c < 64; c += 8) {
+            for (int c = 0; c < 32; c += 8) {
               m0_ = ptx::fmax3(m0_, v[c], v[c + 1]);
               m1_ = ptx::fmax3(m1_, v[c + 2], v[c + 3]);
               m2_ = ptx::fmax3(m2_, v[c + 4], v[c + 5]);
@@ -266,14 +272,14 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
             // the scores above the threshold are a tiny part of a row: look at
             // four at a time and only open a group that contains one
 #pragma unroll
-            for (int g4 = 0; g4 < 16; ++g4) {
+            for (int g4 = 0; g4 < 8; ++g4) {
               const float cm = fmaxf(ptx::fmax3(v[g4 * 4], v[g4 * 4 + 1], v[g4 * 4 + 2]), v[g4 * 4 + 3]);
               if (mode == kModeHist) {
                 if (cm >= thr) {
 #pragma unroll
                   for (int c = 0; c < 4; ++c) {
                     // bin = floor((z - tau0) * BINS) clamped to 7; one add of a byte pattern
-                    // bumps the cumulative counters N_0..N_bin (<= 128 hits per tile: no overflow)
+                    // bumps the cumulative counters N_0..N_bin (<= 64 hits per tile: no overflow)
                     const float prj = (v[g4 * 4 + c] - tau0) * fbins;
                     if (prj >= 0.f) {
                       const int bsel = min(__float2int_rd(prj), 7);
@@ -290,7 +296,6 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
               }
             }
           }
-          if (hf == 0) { hit0 = a2 > a2_mark; a2_mark = a2; }
         }
         ptx::tc_fence_before_sync();
         ptx::mbar_arrive(s_free + grp);
@@ -299,40 +304,57 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
           for (int bb = 0; bb < 8; ++bb) cnt[bb] += (int)((packed >> (8 * bb)) & 0xffull);
         }
         if (mode == kModeFinal) {
-          hit1 = a2 > a2_mark;
-          const bool any0 = __any_sync(0xffffffffu, hit0 && row_ok);
-          const bool any1 = __any_sync(0xffffffffu, hit1 && row_ok);
-          if (lane == 0) {
-            const int kb = 2 * kt;
-            uint32_t* bits = s_bits + (grp * 2 + rb) * p.n_words;
-            if (any0) atomicOr(&bits[kb >> 5], 1u << (kb & 31));
-            if (any1) atomicOr(&bits[(kb + 1) >> 5], 1u << ((kb + 1) & 31));
+          // this warp covers 32 rows x 64 keys of the 64x64 sub-tile (row block rb, key block 2kt+half)
+          const bool any = __any_sync(0xffffffffu, (a2 > a2_mark) && row_ok);
+          if (lane == 0 && any) {
+            const int kb = 2 * kt + half;
+            atomicOr(&s_bits[(grp * 2 + rb) * p.n_words + (kb >> 5)], 1u << (kb & 31));
           }
         }
       }
-      // end of sweep: this thread has seen its whole row
+      // end of sweep: the two threads of a row exchange their partial statistics
+      // (double buffered by sweep parity; both compute the same new state)
+      float* xb = xchg + ((s & 1) * 2 + grp) * (2 * 8 * 128);
+      float* mine = xb + half * (8 * 128);
+      const float* other = xb + (half ^ 1) * (8 * 128);
       if (mode == kModeMax) {
+        mine[r] = mx;
+      } else if (mode == kModeHist) {
+#pragma unroll
+        for (int c = 0; c < 8; ++c) mine[c * 128 + r] = __int_as_float(cnt[c]);
+      } else {
+        mine[r] = a0; mine[128 + r] = a1; mine[256 + r] = a2;
+      }
+      ptx::bar_sync(1 + grp, kSolveGroupThreads);
+      if (mode == kModeMax) {
+        mx = fmaxf(mx, other[r]);
         tau0 = mx - 1.0f;
       } else if (mode == kModeHist) {
-        int bins_cnt[8];
-        for (int c = 0; c < p.bins; ++c) bins_cnt[c] = cnt[c] - (c + 1 < p.bins ? cnt[c + 1] : 0);
+        int bins_cnt[8], cum[8];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) cum[c] = cnt[c] + __float_as_int(other[c * 128 + r]);
+        for (int c = 0; c < p.bins; ++c) bins_cnt[c] = cum[c] - (c + 1 < p.bins ? cum[c + 1] : 0);
         const float t1 = hist_tau_alpha15<8>(bins_cnt, p.bins, tau0);
         hs.lo = t1;
         hs.hi = t1 + 1.0f / fbins;
         hs.t = 0.5f * (hs.lo + hs.hi);
       } else if (!p.tau_given) {
-        halley_bisect_update(hs, a0, a1, a2);
+        // fixed operand order so that both threads of a row get bit-identical sums
+        const float s0 = half == 0 ? a0 + other[r] : other[r] + a0;
+        const float s1 = half == 0 ? a1 + other[128 + r] : other[128 + r] + a1;
+        const float s2 = half == 0 ? a2 + other[256 + r] : other[256 + r] + a2;
+        halley_bisect_update(hs, s0, s1, s2);
       }
     }
-    ptx::bar_sync(1, 256);  // every atomicOr on s_bits is done
+    ptx::bar_sync(3, kSolveRowThreads);  // every atomicOr on s_bits is done
     if (!*cta_abort) {
-      for (int t = threadIdx.x; t < 4 * p.n_words; t += 256) {
+      for (int t = threadIdx.x; t < 4 * p.n_words; t += kSolveRowThreads) {
         const int rbi = t / p.n_words, w = t % p.n_words;
         const int mrow = 4 * pr_idx + rbi;  // 64-row block index
         if (mrow < p.rows_padded && (rbi < 2 || b_on))
           p.bmask[((size_t)bh * p.rows_padded + mrow) * p.n_words + w] = (int32_t)s_bits[t];
       }
-      if (!p.tau_given && grp_on && row_ok) p.taus[(size_t)bh * p.N + row] = hs.t;
+      if (!p.tau_given && grp_on && half == 0 && row_ok) p.taus[(size_t)bh * p.N + row] = hs.t;
     }
   }
 
@@ -345,7 +367,7 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
     for (int i = 0; i < 64; ++i) __nanosleep(1000);
   }
   __syncthreads();
-  if (warp == 9) {
+  if (warp == 17) {
     ptx::tc_fence_after_sync();
     ptx::tmem_dealloc(tmem_base, kSolveTmemCols);
   }
