@@ -9,8 +9,6 @@
 // The threshold search follows adasplash/triton_entmax_v2.py:361-536 (4-bin
 // histogram lower bound, quadratic start on the bin-centre model, Halley /
 // Newton / secant / bisection refinement); the backward follows :539-617.
-#include <cstdlib>
-
 #include "common.cuh"
 
 namespace ads {
@@ -462,13 +460,7 @@ int launch_fwd(const void* xv, void* yv, float* tau, long long rows, long long c
   if (cols <= 512) ADS_FWD(32, 4);
   if (cols <= 1024) ADS_FWD(32, 8);
   if (cols <= 2048) ADS_FWD(64, 8);
-  if (cols <= 4096) {
-    static const int knob = getenv("ADS_ROWWISE_TPR") ? atoi(getenv("ADS_ROWWISE_TPR")) : 0;
-    if (knob == 32) ADS_FWD(32, 32);
-    if (knob == 64) ADS_FWD(64, 16);
-    if (knob == 256) ADS_FWD(256, 4);
-    ADS_FWD(128, 8);
-  }
+  if (cols <= 4096) ADS_FWD(128, 8);  // measured best of (32,32), (64,16), (128,8), (256,4) on 16384 x 4096
   if (cols <= 8192) ADS_FWD(256, 8);
   if (cols <= 16384) ADS_FWD(512, 8);
   if (cols <= 32768) ADS_FWD(1024, 8);

@@ -75,8 +75,9 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int heads = p.B * p.Hq;
-  const int qt = p.nq - 1 - (int)(blockIdx.x / heads);
-  const int bh = blockIdx.x % heads;
+  // head-major order: the CTAs in flight share a few heads, whose K / V stay in L2
+  const int qt = p.nq - 1 - (int)(blockIdx.x % p.nq);
+  const int bh = blockIdx.x / p.nq;
   const int b = bh / p.Hq, h = bh % p.Hq;
   const int kvh = h / (p.Hq / p.Hkv);
   const int len = load_len(p.varlen, p.varlen_is_i64, b, p.N);
@@ -99,12 +100,12 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   if (warp == 9) {
     if (lane == 0) {
       ptx::mbar_init(q_full, 1);
-      ptx::mbar_init(q_ready, kDqRowThreads);
+      ptx::mbar_init(q_ready, kDqRowThreads / 32);
       for (int s = 0; s < kDqKStages; ++s) { ptx::mbar_init(k_full + s, 1); ptx::mbar_init(k_empty + s, 1); }
       for (int s = 0; s < kDqVStages; ++s) { ptx::mbar_init(v_full + s, 1); ptx::mbar_init(v_empty + s, 1); }
       for (int s = 0; s < 2; ++s) {
         ptx::mbar_init(s_full + s, 1);
-        ptx::mbar_init(p_full + s, kDqRowThreads);
+        ptx::mbar_init(p_full + s, kDqRowThreads / 32);
         ptx::mbar_init(s_free + s, 1);
       }
       ptx::mbar_init(dp_full, 1);
@@ -244,7 +245,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     const int rb = wq >> 1;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(wq * 32) << 16);
     bool dead = false;
-    if (!ptx::mbar_wait(q_full, 0)) { raise_abort(cta_abort, p.status, kStTimeoutEpilogue); dead = true; }
+    if (!ptx::mbar_wait_warp(q_full, 0)) { raise_abort(cta_abort, p.status, kStTimeoutEpilogue); dead = true; }
     if (!dead) {
       const float sc = 0.5f * p.sm_scale;
       for (int v = threadIdx.x; v < L::tile_bytes / 16; v += kDqRowThreads) {
@@ -259,7 +260,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       }
       ptx::fence_proxy_async_smem();
     }
-    ptx::mbar_arrive(q_ready);
+    ptx::mbar_arrive_warp(q_ready);
     const float tau = row_ok ? p.taus[(size_t)bh * p.N + row] : 0.f;
     const float dl = row_ok ? p.delta[(size_t)bh * p.N + row] : 0.f;
     TileScan scan(bm_head, qt, T_tiles, p.rows_padded, p.n_words);
@@ -270,7 +271,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       n_active = j + 1;
       const bool sub_on = (flags >> (2 * rb + half)) & 1u;
       if (*cta_abort) { dead = true; break; }
-      if (!ptx::mbar_wait(s_full + buf, (j >> 1) & 1) || !ptx::mbar_wait(dp_full, j & 1)) {
+      if (!ptx::mbar_wait_warp(s_full + buf, (j >> 1) & 1) || !ptx::mbar_wait_warp(dp_full, j & 1)) {
         raise_abort(cta_abort, p.status, kStTimeoutEpilogue);
         dead = true;
         break;
@@ -307,10 +308,10 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       }
       ptx::tmem_st_wait();
       ptx::tc_fence_before_sync();
-      ptx::mbar_arrive(p_full + buf);
+      ptx::mbar_arrive_warp(p_full + buf);
     }
     if (!dead && n_active > 0) {
-      if (!ptx::mbar_wait(dq_full, 0)) { raise_abort(cta_abort, p.status, kStTimeoutEpilogue); dead = true; }
+      if (!ptx::mbar_wait_warp(dq_full, 0)) { raise_abort(cta_abort, p.status, kStTimeoutEpilogue); dead = true; }
     }
     if (!dead) {  // TMEM loads are warp-collective: only the global stores are per-row
       ptx::tc_fence_after_sync();
@@ -374,7 +375,7 @@ struct DkvSmem {
   static constexpr int n_bars = 2 + 2 * kDkvStages + 2 + 2 + 2 + 1;
   static constexpr int misc_off = bar_off + n_bars * 8;
   static constexpr int td_off = misc_off + 64;                  // [2][2][64] floats: tau, delta
-  static constexpr size_t bytes = 1024 + td_off + 2 * 2 * 64 * 4;
+  static constexpr size_t bytes = 1024 + td_off + 2 * 2 * 128 * 4;  // [2 groups][2 buffers][tau 64 | delta 64]
 };
 
 // Walks (q head of the group, 64-row query block) pairs whose bit is set in rows
@@ -446,8 +447,9 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kvheads = p.B * p.Hkv;
-  const int nt = (int)(blockIdx.x / kvheads);  // low key tiles (most work) first
-  const int bkv = blockIdx.x % kvheads;
+  // head-major order; inside a head the low key tiles (most query blocks) start first
+  const int nt = (int)(blockIdx.x % p.nq);
+  const int bkv = blockIdx.x / p.nq;
   const int b = bkv / p.Hkv, kvh = bkv % p.Hkv;
   const int G = p.Hq / p.Hkv;
   const int len = load_len(p.varlen, p.varlen_is_i64, b, p.N);
@@ -473,11 +475,11 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
   if (warp == 17) {
     if (lane == 0) {
       ptx::mbar_init(kv_full, 1);
-      ptx::mbar_init(k_ready, kDkvRowThreads);
+      ptx::mbar_init(k_ready, kDkvRowThreads / 32);
       for (int s = 0; s < kDkvStages; ++s) { ptx::mbar_init(x_full + s, 1); ptx::mbar_init(x_empty + s, 1); }
       for (int s = 0; s < 2; ++s) {
         ptx::mbar_init(s_full + s, 1);
-        ptx::mbar_init(p_full + s, kDkvGroupThreads);
+        ptx::mbar_init(p_full + s, kDkvGroupThreads / 32);
         ptx::mbar_init(s_free + s, 1);
       }
       ptx::mbar_init(acc_full, 1);
@@ -621,7 +623,7 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
     const int kh = wq >> 1;              // which 64-key half
     const uint32_t lane_addr = tmem_base + ((uint32_t)(wq * 32) << 16);
     bool dead = false;
-    if (!ptx::mbar_wait(kv_full, 0)) { raise_abort(cta_abort, p.status, kStTimeoutEpilogue); dead = true; }
+    if (!ptx::mbar_wait_warp(kv_full, 0)) { raise_abort(cta_abort, p.status, kStTimeoutEpilogue); dead = true; }
     if (!dead) {
       // K~ = rn(k * fp32(0.5/sqrt(D))) in place; rows >= len -> 0 in K and V
       const float sc = 0.5f * p.sm_scale;
@@ -638,36 +640,40 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
       }
       ptx::fence_proxy_async_smem();
     }
-    ptx::mbar_arrive(k_ready);
-    // tau / delta of a block's 64 query rows: fetched one own-step ahead into a register
-    // by the first 128 threads of the group, parked in shared memory at the step itself
+    ptx::mbar_arrive_warp(k_ready);
+    // tau / delta of a block's 64 query rows are staged in shared memory one own-step
+    // ahead (double buffered per group, fetched from global memory two own-steps ahead
+    // into a register by the first 128 threads of the group), so that neither the
+    // global-memory latency nor the group barrier sits between the arrival of S^T and
+    // the row work.
     auto fetch_td = [&](int g_, int m_) -> float {
       if (gtid >= 128) return 0.f;
       const int qrow = m_ * kQBlock + (gtid & 63);
       const float* src = (gtid < 64) ? p.taus : p.delta;
       return (qrow < len) ? src[(size_t)(b * p.Hq + kvh * G + g_) * p.N + qrow] : 0.f;
     };
-    float* td = s_td + group * 128;
+    float* tdb = s_td + group * 256;  // [2][128] floats of this group
+    int n_active = 0;
+    {
+      QBlockScan s0(p.bmask_t, b, p.Hq, G, kvh, nt, n_qblocks, p.rows_padded, p.n_words);
+      int g0, m0_; uint32_t f0;
+      n_active = s0.next(g0, m0_, f0) ? 1 : 0;
+    }
     QBlockScan scan(p.bmask_t, b, p.Hq, G, kvh, nt, n_qblocks, p.rows_padded, p.n_words);
-    int g, m, n_active = 0;
-    uint32_t flags;
-    // advance to this group's first step
-    bool have = scan.next(g, m, flags);
-    if (have) n_active = 1;
-    if (have && group == 1) { have = scan.next(g, m, flags); if (have) n_active = 2; }
-    float td_reg = have ? fetch_td(g, m) : 0.f;
-    for (int j = group; have; j += 2) {
-      // look ahead to this group's next step (skipping the other group's step)
-      int g2 = 0, m2 = 0;
-      uint32_t f2 = 0;
-      bool have2 = scan.next(g2, m2, f2);
-      if (have2) { n_active = j + 2; have2 = scan.next(g2, m2, f2); if (have2) n_active = j + 3; }
-      ptx::bar_sync(1 + group, kDkvGroupThreads);  // everyone is done reading the previous td
-      if (gtid < 128) td[gtid] = td_reg;
-      ptx::bar_sync(1 + group, kDkvGroupThreads);
-      td_reg = have2 ? fetch_td(g2, m2) : 0.f;
+    QBlockScan scan_f(p.bmask_t, b, p.Hq, G, kvh, nt, n_qblocks, p.rows_padded, p.n_words);
+    int g = 0, m = 0, gf = 0, mf = 0;
+    uint32_t flags = 0, ff = 0;
+    bool have = true, have_f = true;
+    for (int i = 0; i <= group && have; ++i) have = scan.next(g, m, flags);        // own first step
+    for (int i = 0; i <= group + 2 && have_f; ++i) have_f = scan_f.next(gf, mf, ff);  // own second step
+    if (have && gtid < 128) tdb[gtid] = fetch_td(g, m);
+    ptx::bar_sync(1 + group, kDkvGroupThreads);
+    float td_reg = have_f ? fetch_td(gf, mf) : 0.f;
+    for (int it = 0; have; ++it) {
+      const int cur = it & 1;
+      const float* td = tdb + cur * 128;
       if (!(dead || *cta_abort)) {
-        if (!ptx::mbar_wait(s_full + group, (j >> 1) & 1)) { raise_abort(cta_abort, p.status, kStTimeoutEpilogue); dead = true; }
+        if (!ptx::mbar_wait_warp(s_full + group, it & 1)) { raise_abort(cta_abort, p.status, kStTimeoutEpilogue); dead = true; }
       } else {
         dead = true;
       }
@@ -714,13 +720,18 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
         }
         ptx::tmem_st_wait();
         ptx::tc_fence_before_sync();
-        ptx::mbar_arrive(p_full + group);
+        ptx::mbar_arrive_warp(p_full + group);
       }
-      g = g2; m = m2; flags = f2;
-      have = have2;
+      // off the critical path: park the next own step's tau / delta, fetch the one after
+      if (gtid < 128) tdb[(cur ^ 1) * 128 + gtid] = td_reg;
+      ptx::bar_sync(1 + group, kDkvGroupThreads);
+      g = gf; m = mf; flags = ff;
+      have = have_f;
+      for (int i = 0; i < 2 && have_f; ++i) have_f = scan_f.next(gf, mf, ff);
+      td_reg = have_f ? fetch_td(gf, mf) : 0.f;
     }
     if (!dead && n_active > 0) {
-      if (!ptx::mbar_wait(acc_full, 0)) { raise_abort(cta_abort, p.status, kStTimeoutEpilogue); dead = true; }
+      if (!ptx::mbar_wait_warp(acc_full, 0)) { raise_abort(cta_abort, p.status, kStTimeoutEpilogue); dead = true; }
     }
     if (!dead) {  // TMEM loads are warp-collective: only the global stores are per-row
       ptx::tc_fence_after_sync();

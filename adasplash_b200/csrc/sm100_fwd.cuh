@@ -97,8 +97,10 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int heads = p.B * p.Hq;
-  const int qt = p.nq - 1 - (int)(blockIdx.x / heads);
-  const int bh = blockIdx.x % heads;
+  // head-major order: the CTAs in flight share a few heads, whose K / V stay in L2;
+  // inside a head the longest (latest) query tiles start first
+  const int qt = p.nq - 1 - (int)(blockIdx.x % p.nq);
+  const int bh = blockIdx.x / p.nq;
   const int b = bh / p.Hq, h = bh % p.Hq;
   const int kvh = h / (p.Hq / p.Hkv);
   const int len = load_len(p.varlen, p.varlen_is_i64, b, p.N);
@@ -126,12 +128,12 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
   if (warp == 17) {
     if (lane == 0) {
       ptx::mbar_init(q_full, 1);
-      ptx::mbar_init(q_ready, kFwdRowThreads);
+      ptx::mbar_init(q_ready, kFwdRowThreads / 32);
       for (int s = 0; s < kFwdKStages; ++s) { ptx::mbar_init(k_full + s, 1); ptx::mbar_init(k_empty + s, 1); }
       for (int s = 0; s < kFwdVStages; ++s) { ptx::mbar_init(v_full + s, 1); ptx::mbar_init(v_empty + s, 1); }
       for (int s = 0; s < 2; ++s) {
         ptx::mbar_init(s_full + s, 1);
-        ptx::mbar_init(p_full + s, kFwdGroupThreads);
+        ptx::mbar_init(p_full + s, kFwdGroupThreads / 32);
         ptx::mbar_init(s_free + s, 1);
       }
       ptx::mbar_init(o_full, 1);
@@ -259,7 +261,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     const uint32_t lane_addr = tmem_base + ((uint32_t)(wq * 32) << 16);
     float* s_supp = (float*)(smem + L::supp_off);
     bool dead = false;
-    if (!ptx::mbar_wait(q_full, 0)) { raise_abort(cta_abort, p.status, kStTimeoutEpilogue); dead = true; }
+    if (!ptx::mbar_wait_warp(q_full, 0)) { raise_abort(cta_abort, p.status, kStTimeoutEpilogue); dead = true; }
     if (!dead) {
       const float sc = 0.5f * p.sm_scale;
       for (int v = threadIdx.x; v < L::tile_bytes / 16; v += kFwdRowThreads) {
@@ -274,7 +276,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       }
       ptx::fence_proxy_async_smem();
     }
-    ptx::mbar_arrive(q_ready);
+    ptx::mbar_arrive_warp(q_ready);
     const float tau = row_ok ? p.taus[(size_t)bh * p.N + row] : 0.f;
     float supp = 0.f;
     TileScan scan(bm_head, qt, T_tiles, p.rows_padded, p.n_words);
@@ -286,7 +288,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       if (buf != group) continue;
       const bool sub_on = (flags >> (2 * rb + half)) & 1u;  // this thread's 64x64 sub-tile
       if (*cta_abort) { dead = true; break; }
-      if (!ptx::mbar_wait(s_full + buf, (j >> 1) & 1)) { raise_abort(cta_abort, p.status, kStTimeoutEpilogue); dead = true; break; }
+      if (!ptx::mbar_wait_warp(s_full + buf, (j >> 1) & 1)) { raise_abort(cta_abort, p.status, kStTimeoutEpilogue); dead = true; break; }
       ptx::tc_fence_after_sync();
       const int n0 = kt * kBlockN;
       const bool need_mask = (kt == qt) || (n0 + kBlockN > len);
@@ -330,7 +332,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       }
       ptx::tmem_st_wait();
       ptx::tc_fence_before_sync();
-      ptx::mbar_arrive(p_full + buf);
+      ptx::mbar_arrive_warp(p_full + buf);
     }
     // the four threads of a row add up their partial sums of u
     s_supp[(group * 2 + half) * 128 + r] = supp;
@@ -338,7 +340,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     supp = (s_supp[r] + s_supp[128 + r]) + (s_supp[256 + r] + s_supp[384 + r]);
     // epilogue: O, O2 -> global; the four threads of a row share the D/32 column chunks
     if (!dead && n_active > 0) {
-      if (!ptx::mbar_wait(o_full, 0)) { raise_abort(cta_abort, p.status, kStTimeoutEpilogue); dead = true; }
+      if (!ptx::mbar_wait_warp(o_full, 0)) { raise_abort(cta_abort, p.status, kStTimeoutEpilogue); dead = true; }
     }
     if (!dead) {  // TMEM loads are warp-collective: only the global stores are per-row
       ptx::tc_fence_after_sync();

@@ -33,6 +33,13 @@ __device__ __forceinline__ void fence_mbar_init() {
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// One arrival for a whole warp: every lane has finished (and fenced) its part, the
+// warp converges, lane 0 arrives.  Barriers waited on by warps are initialised with
+// the number of warps, which keeps hundreds of serialised arrivals off the critical path.
+__device__ __forceinline__ void mbar_arrive_warp(uint64_t* bar) {
+  __syncwarp();
+  if ((threadIdx.x & 31) == 0) mbar_arrive(bar);
+}
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
                "r"(bytes)
@@ -60,6 +67,13 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     if (clock64() - t0 > kMaxWaitCycles) return false;
   }
   return true;
+}
+
+// Same, called by all 32 lanes of a warp: the verdict is made warp-uniform so that
+// the lanes of a warp never part ways around the warp-collective tcgen05 / __syncwarp
+// operations that follow.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity) {
+  return __all_sync(0xffffffffu, mbar_wait(bar, parity));
 }
 
 // ---- fences -------------------------------------------------------------------

@@ -80,7 +80,7 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int heads = p.B * p.Hq;
   const int npair = (p.nq + 1) / 2;
-  const int pr_idx = npair - 1 - (int)(blockIdx.x / heads);  // heaviest row pairs first
+  const int pr_idx = npair - 1 - (int)(blockIdx.x / heads);  // heaviest row pairs first, across all heads
   const int bh = blockIdx.x % heads;
   const int b = bh / p.Hq, h = bh % p.Hq;
   const int kvh = h / (p.Hq / p.Hkv);
@@ -101,9 +101,9 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
   if (warp == 17) {
     if (lane == 0) {
       ptx::mbar_init(q_full, 1);
-      ptx::mbar_init(q_ready, kSolveRowThreads);
+      ptx::mbar_init(q_ready, kSolveRowThreads / 32);
       for (int s = 0; s < kSolveStages; ++s) { ptx::mbar_init(k_full + s, 1); ptx::mbar_init(k_empty + s, 1); }
-      for (int s = 0; s < 2; ++s) { ptx::mbar_init(s_full + s, 1); ptx::mbar_init(s_free + s, kSolveGroupThreads); }
+      for (int s = 0; s < 2; ++s) { ptx::mbar_init(s_full + s, 1); ptx::mbar_init(s_free + s, kSolveGroupThreads / 32); }
       ptx::fence_mbar_init();
     }
     __syncwarp();
@@ -195,7 +195,7 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
     bool dead = false;
     // Q~ = rn(q * fp32(0.5/sqrt(D))) (rows >= len -> 0), from the TMA tile in shared
     // memory into TMEM: the two threads of row r convert D/2 elements each (16-bit pairs, lane r)
-    if (!ptx::mbar_wait(q_full, 0)) { raise_abort(cta_abort, p.status, kStTimeoutEpilogue); dead = true; }
+    if (!ptx::mbar_wait_warp(q_full, 0)) { raise_abort(cta_abort, p.status, kStTimeoutEpilogue); dead = true; }
     if (!dead) {
       const float sc = row_ok ? 0.5f * p.sm_scale : 0.f;
       const uint8_t* qtile = sQ + grp * L::tile_bytes;
@@ -218,7 +218,7 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
       ptx::tmem_st_wait();
       ptx::tc_fence_before_sync();
     }
-    ptx::mbar_arrive(q_ready);
+    ptx::mbar_arrive_warp(q_ready);
 
     float mx = -1.0e3f, tau0 = 0.f;
     int cnt[8];
@@ -234,7 +234,7 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
       for (int c = 0; c < 8; ++c) cnt[c] = 0;
       for (int kt = 0; kt < T_g; ++kt, ++use) {
         if (dead || *cta_abort) { dead = true; continue; }
-        if (!ptx::mbar_wait(s_full + grp, use & 1)) {
+        if (!ptx::mbar_wait_warp(s_full + grp, use & 1)) {
           raise_abort(cta_abort, p.status, kStTimeoutEpilogue);
           dead = true;
           continue;
@@ -298,7 +298,7 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
           }
         }
         ptx::tc_fence_before_sync();
-        ptx::mbar_arrive(s_free + grp);
+        ptx::mbar_arrive_warp(s_free + grp);
         if (packed != 0ull) {
 #pragma unroll
           for (int bb = 0; bb < 8; ++bb) cnt[bb] += (int)((packed >> (8 * bb)) & 0xffull);

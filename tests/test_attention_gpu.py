@@ -196,22 +196,29 @@ def _check_grads_vs_reference(got, fx, tol):
 
 
 @pytest.mark.parametrize("path", ["tcgen05"])
-def test_tensor_core_path_matches_cuda_core_path(path):
-    # larger case than the CPU oracle handles comfortably: the two kernel
+@pytest.mark.parametrize("shape", [(2, 4, 2, 2048, 128, [2048, 1500]),
+                                   (1, 2, 1, 16384, 128, [16384]),      # 4-bin histogram (N >= 16384)
+                                   (1, 2, 1, 16500, 64, [16500]),       # N not a multiple of 128
+                                   (1, 1, 1, 65536, 128, [65536])])     # long-context tile counts
+def test_tensor_core_path_matches_cuda_core_path(path, shape):
+    # larger cases than the CPU oracle handles comfortably: the two kernel
     # families must agree (same rounding points, different summation order)
-    B, Hq, Hkv, N, D = 2, 4, 2, 2048, 128
+    B, Hq, Hkv, N, D, vl = shape
     q, k, v, do = (_randn(s, 50 + i, 1.5 if i < 3 else 1.0, torch.bfloat16) for i, s in
                    enumerate([(B, Hq, N, D), (B, Hkv, N, D), (B, Hkv, N, D), (B, Hq, N, D)]))
-    varlen = torch.tensor([2048, 1500], dtype=torch.int32)
+    varlen = torch.tensor(vl, dtype=torch.int32)
     do = _mask_rows(do, varlen)
     _use(path, q)
     a = _run(q, k, v, do, 1, varlen)
     _lib.set_kernel_path("simt")
     b = _run(q, k, v, do, 1, varlen)
-    assert (a["tau"][0] - b["tau"][0]).abs().max() < 1e-5
-    assert (a["tau"][1, :, :1500] - b["tau"][1, :, :1500]).abs().max() < 1e-5
-    diff_words = (a["bmask"] != b["bmask"]).sum().item()
-    assert diff_words == 0
+    for bi in range(B):
+        assert (a["tau"][bi, :, :vl[bi]] - b["tau"][bi, :, :vl[bi]]).abs().max() < 1e-5
+    # the two families sum the 128 products of a score in different orders, so a
+    # score within an ulp of its threshold may flip a bit: allow a handful per million tiles
+    diff_bits = sum(bin(int(x) & 0xFFFFFFFF).count("1") for x in (a["bmask"] ^ b["bmask"]).flatten().tolist())
+    nb = (N + 63) // 64
+    assert diff_bits <= 2 + 1e-5 * B * Hq * nb * nb
     for key in ("out", "out2", "dq", "dk", "dv"):
         scale = max(1.0, b[key].abs().max().item())
         assert (a[key] - b[key]).abs().max() < 2e-2 * scale, key
