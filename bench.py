@@ -52,7 +52,19 @@ SEED_BASE = 20260
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of a kernel, from the
 # ncu captures summarised under profiles/ (None = not captured for that workload)
-NCU_DRAM_BYTES_PER_LAUNCH = {}
+NCU_DRAM_BYTES_PER_LAUNCH = {
+    # headline workload: captured on the 32-head "mid" case (profiles/*_bf16_d128_mid.txt) and
+    # scaled by 4 to the 128 heads of C3 (traffic is per head: every head streams its own q/k/v)
+    ("c3", "solve"): 4 * (264.51e6 + 15.27e6),
+    ("c3", "fwd"): 4 * (202.59e6 + 102.43e6),
+    ("c3", "bwd_dq"): 4 * (270.73e6 + 53.04e6),
+    ("c3", "bwd_dkv"): 4 * (270.66e6 + 107.30e6),
+    ("mid", "solve"): 264.51e6 + 15.27e6,
+    ("mid", "fwd"): 202.59e6 + 102.43e6,
+    ("mid", "bwd_dkv"): 270.66e6 + 107.30e6,
+    # profiles/entmax_fwd_f32_16384x4096.txt
+    ("c2", "entmax_fwd"): 268.49e6 + 219.89e6,
+}
 
 
 def dense_equiv_flops(w, lens):
