@@ -92,7 +92,7 @@ __device__ __forceinline__ void tc_fence_after_sync() {
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
 }
-// 3-D tiled load (no multicast): coordinates are (x = element in row, y = row, z = head)
+// 3-D tiled load, one CTA as destination: coordinates are (x = element in row, y = row, z = head)
 __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* m, uint64_t* bar, int x,
                                             int y, int z) {
   asm volatile(
