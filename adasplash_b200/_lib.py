@@ -21,7 +21,8 @@ _PATH_NAMES = {"auto": PATH_AUTO, "simt": PATH_SIMT, "tcgen05": PATH_TCGEN05}
 
 class AttnShape(Structure):
     _fields_ = [(n, c_int32) for n in
-                ("B", "Hq", "Hkv", "N", "D", "dtype", "niter", "varlen_is_i64", "path", "bwd_stages")]
+                ("B", "Hq", "Hkv", "N", "D", "dtype", "niter", "varlen_is_i64", "path", "bwd_stages")] + [
+                    ("alpha", c_float), ("non_causal", c_int32)]
 
 
 # name -> (restype, argtypes); every symbol include/adasplash_b200.h declares

@@ -21,7 +21,7 @@ def _ptr(t):
     return None if t is None else t.data_ptr()
 
 
-def _check_inputs(q, k, v, varlen):
+def _check_inputs(q, k, v, varlen, require_pow2=True):
     assert q.dim() == 4, "q must have shape (batch, heads, seq_len, head_dim)"
     B, N_H, N_CTX, H_DIM = q.shape
     assert H_DIM in {16, 32, 64, 128, 256}
@@ -34,7 +34,7 @@ def _check_inputs(q, k, v, varlen):
         f"K/V must have shape (B={B}, N_KV_H, N_CTX={N_CTX}, H_DIM={H_DIM}); got {tuple(k.shape)}.")
     assert N_CTX >= BMASK_TILE, f"N_CTX={N_CTX} must be at least BMASK_TILE={BMASK_TILE}."
     if varlen is None:
-        assert (N_CTX & (N_CTX - 1)) == 0, "If varlen is None, N_CTX must be a power of two."
+        assert not require_pow2 or (N_CTX & (N_CTX - 1)) == 0, "If varlen is None, N_CTX must be a power of two."
     else:
         assert varlen.dim() == 1 and varlen.shape[0] == B, (
             f"varlen must be a 1-D tensor of shape (B={B},); got {tuple(varlen.shape)}.")
@@ -49,12 +49,13 @@ def _check_inputs(q, k, v, varlen):
         "q, k and v must be CUDA tensors on one device (there is no CPU path)")
 
 
-def make_shape(q, k, niter, varlen, path=None):
+def make_shape(q, k, niter, varlen, path=None, alpha=1.5, is_causal=True):
     B, Hq, N, D = q.shape
     return _lib.AttnShape(
         B=B, Hq=Hq, Hkv=k.shape[1], N=N, D=D, dtype=_lib.dtype_code(q.dtype), niter=int(niter),
         varlen_is_i64=int(varlen is not None and varlen.dtype == torch.int64),
-        path=_lib.kernel_path() if path is None else path)
+        path=_lib.kernel_path() if path is None else path,
+        alpha=float(alpha), non_causal=int(not is_causal))
 
 
 def bitmap_extent(shape):
@@ -78,10 +79,10 @@ def _maybe_check(ws, st):
         _lib.check(_lib.load().adasplash2_check_status(_ptr(ws), st))
 
 
-def solve(q, k, niter=1, varlen=None, path=None):
+def solve(q, k, niter=1, varlen=None, path=None, alpha=1.5, is_causal=True):
     """Thresholds and block mask only: (taus (B,Hq,N) fp32, bmask int32)."""
     lib = _lib.load()
-    shape = make_shape(q, k, niter, varlen, path)
+    shape = make_shape(q, k, niter, varlen, path, alpha, is_causal)
     rows, words = bitmap_extent(shape)
     B, Hq, N, _ = q.shape
     taus = torch.empty((B, Hq, N), device=q.device, dtype=torch.float32)
@@ -152,10 +153,10 @@ class _SparseAttention(torch.autograd.Function):
         return dq, dk, dv, None, None
 
 
-def forward_raw(q, k, v, taus, bmask, varlen=None, path=None):
+def forward_raw(q, k, v, taus, bmask, varlen=None, path=None, alpha=1.5, is_causal=True):
     """`adasplash2_fwd` alone for given thresholds and block mask: (out, out2)."""
     lib = _lib.load()
-    shape = make_shape(q, k, 0, varlen, path)
+    shape = make_shape(q, k, 0, varlen, path, alpha, is_causal)
     out = torch.empty_like(q)
     out2 = torch.empty_like(q)
     with torch.cuda.device(q.device):
@@ -169,12 +170,12 @@ def forward_raw(q, k, v, taus, bmask, varlen=None, path=None):
 
 
 def backward_raw(q, k, v, do, out2, taus, bmask, varlen=None, niter=1, stages=0, buffers=None,
-                 path=None):
+                 path=None, alpha=1.5, is_causal=True):
     """`adasplash2_bwd`: returns (dq, dk, dv, delta, bmask_t).  `stages` != 0 runs only
     the named kernels (ADS_BWD_* mask; a measurement aid), reusing `buffers` =
     (dq, dk, dv, delta, bmask_t) from an earlier full call."""
     lib = _lib.load()
-    shape = make_shape(q, k, niter, varlen, path)
+    shape = make_shape(q, k, niter, varlen, path, alpha, is_causal)
     shape.bwd_stages = int(stages)
     dev = q.device
     if buffers is None:

@@ -51,6 +51,10 @@ int check_shape(const ads_attn_shape* s, const char* who) {
     return ADS_ERR_BAD_ARG;
   }
   if (s->B > 65535 || s->Hq > 65535) { set_error("%s: B/Hq above 65535", who); return ADS_ERR_UNSUPPORTED; }
+  if (s->alpha != 0.f && !(s->alpha > 1.0f && s->alpha <= 2.0f)) {
+    set_error("%s: alpha=%f outside (1, 2]", who, s->alpha);
+    return ADS_ERR_BAD_ARG;
+  }
   if (s->path != ADS_PATH_AUTO && s->path != ADS_PATH_SIMT && s->path != ADS_PATH_TCGEN05) {
     set_error("%s: unknown path %d", who, s->path);
     return ADS_ERR_BAD_ARG;
@@ -59,7 +63,9 @@ int check_shape(const ads_attn_shape* s, const char* who) {
 }
 
 int resolve_path(const ads_attn_shape* s, const char* who, int* path) {
-  bool tc_ok = sm100::supported(s);
+  // the tensor-core kernels implement the causal alpha = 1.5 path only
+  const bool v2 = (s->alpha == 0.f || s->alpha == 1.5f) && s->non_causal == 0;
+  bool tc_ok = v2 && sm100::supported(s);
   if (s->path == ADS_PATH_TCGEN05 && !tc_ok) {
     set_error("%s: tcgen05 path needs fp16/bf16 inputs and a head dim it was built for (got dtype=%d D=%d)",
               who, s->dtype, s->D);
@@ -80,6 +86,9 @@ simt::Params make_params(const ads_attn_shape* s) {
   p.sm_scale = (float)(1.0 / std::sqrt((double)s->D));
   p.varlen_is_i64 = s->varlen_is_i64;
   p.bwd_stages = s->bwd_stages;
+  p.alpha = s->alpha == 0.f ? 1.5f : s->alpha;
+  p.causal = s->non_causal ? 0 : 1;
+  p.zscale = (p.alpha - 1.0f) * p.sm_scale;
   return p;
 }
 

@@ -90,14 +90,15 @@ __device__ __forceinline__ void tile_dot(const float* sA, const float* sB, const
 
 // The masked score tile of adasplash_v2.py:93-119: keep z where col <= row and
 // col < len, else -10000.
-__device__ __forceinline__ void mask_scores(float acc[4][4], const Idx& id, int m0, int n0, int len) {
+__device__ __forceinline__ void mask_scores(float acc[4][4], const Idx& id, int m0, int n0, int len,
+                                            bool causal = true) {
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     int row = m0 + id.ty + 16 * i;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       int col = n0 + id.tx + 16 * j;
-      bool ok = (col <= row) && (col < len);
+      bool ok = (!causal || col <= row) && (col < len);
       acc[i][j] = ok ? acc[i][j] : kMaskedScore;
     }
   }
@@ -159,6 +160,31 @@ __device__ __forceinline__ void tile_ptx(const float* sP, const float* sX, const
   }
 }
 
+// Powers of the clipped score u = [z - tau]_+ for a given alpha:
+//   p  = u^(1/(alpha-1))            attention weight
+//   g  = u^(1/(alpha-1) - 1)        = p^(2-alpha), the weight of the entmax Jacobian
+// alpha = 1.5 (u*u, u) and alpha = 2 (u, 1[u>0]) are exact multiplications; other
+// alphas go through the approximate lg2 / ex2 units on the support only.
+struct Powers {
+  float c0, c1;
+  int mode;  // 0: alpha = 1.5, 1: alpha = 2, 2: generic
+  __device__ __forceinline__ explicit Powers(float alpha) {
+    mode = (alpha == 1.5f) ? 0 : (alpha == 2.0f ? 1 : 2);
+    c0 = 1.0f / (alpha - 1.0f);
+    c1 = c0 - 1.0f;
+  }
+  __device__ __forceinline__ float p(float u) const {
+    if (mode == 0) return u * u;
+    if (mode == 1) return u;
+    return u > 0.f ? exp2f(c0 * __log2f(u)) : 0.f;
+  }
+  __device__ __forceinline__ float g(float u) const {
+    if (mode == 0) return u;
+    if (mode == 1) return u > 0.f ? 1.f : 0.f;
+    return u > 0.f ? exp2f(c1 * __log2f(u)) : 0.f;
+  }
+};
+
 struct Params {
   const void* q; const void* k; const void* v;
   const void* varlen; int varlen_is_i64;
@@ -171,6 +197,9 @@ struct Params {
   float sm_scale;   // fp32(1/sqrt(D))
   int tau_given;    // solve kernel: 1 = only build the bitmap from taus
   int bwd_stages;   // 0 = all kernels of the backward, else a mask of ADS_BWD_*
+  float alpha;      // entmax alpha in (1, 2]
+  int causal;       // 1 = causal mask
+  float zscale;     // fp32((alpha-1) * sm_scale): scores are z = zscale * q.k
 };
 
 // ---------------------------------------------------------------------------
@@ -193,9 +222,11 @@ __global__ void __launch_bounds__(kThreads) solve_kernel(Params p) {
   const T* kg = (const T*)p.k + ((size_t)b * p.Hkv + kvh) * (size_t)p.N * D;
   float* tg = p.taus + ((size_t)b * p.Hq + h) * (size_t)p.N;
   int32_t* bm = p.bmask + (((size_t)b * p.Hq + h) * p.rows_padded + m) * (size_t)p.n_words;
-  const float sc = 0.5f * p.sm_scale;
+  const float sc = p.zscale;
   load_tile<T, D, true>(sQ, qg, m0, len, sc);
-  const int up_to = min(m0 + kTile, len);
+  const bool causal = p.causal != 0;
+  const bool v2_path = causal && p.alpha == 1.5f;  // the reference's AdaSplash-2 trajectory
+  const int up_to = causal ? min(m0 + kTile, len) : len;
   const int ntiles = (up_to + kTile - 1) / kTile;
   float acc[4][4];
   HalleyState st[4];
@@ -206,7 +237,7 @@ __global__ void __launch_bounds__(kThreads) solve_kernel(Params p) {
       load_tile<T, D, false>(sK, kg, n * kTile, len, 1.0f);
       __syncthreads();
       tile_dot<D>(sQ, sK, id, acc);
-      mask_scores(acc, id, m0, n * kTile, len);
+      mask_scores(acc, id, m0, n * kTile, len, causal);
       per_tile(n);
     }
   };
@@ -223,6 +254,18 @@ __global__ void __launch_bounds__(kThreads) solve_kernel(Params p) {
     float tau0[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) tau0[i] = row16_max(mx[i]) - 1.0f;
+    if (!v2_path) {
+      // generic alpha / non-causal (adasplash_block_mask.py:170-176): bracket
+      // [max - 1, max - n^(1-alpha)], start at its midpoint
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int row = m0 + id.ty + 16 * i;
+        const float n = 1.0f + (float)(causal ? row : len);
+        st[i].lo = tau0[i];
+        st[i].hi = tau0[i] + 1.0f - exp2f((1.0f - p.alpha) * log2f(n));
+        st[i].t = 0.5f * (st[i].lo + st[i].hi);
+      }
+    } else {
     // sweep 2: histogram of z - tau0 on [0,1] (adasplash_v2.py:387-431), as
     // cumulative counts N_b = #{(z - tau0) * BINS >= b}
     int cnt[4][8];
@@ -252,6 +295,7 @@ __global__ void __launch_bounds__(kThreads) solve_kernel(Params p) {
       st[i].hi = t1 + 1.0f / fb;
       st[i].t = 0.5f * (st[i].lo + st[i].hi);
     }
+    }
   } else {
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -262,9 +306,13 @@ __global__ void __launch_bounds__(kThreads) solve_kernel(Params p) {
   }
   // refinement sweeps; the last one also records the bitmap for the tau that
   // enters it (adasplash_v2.py:567-675)
+  // Generic path: niter updates, then a bitmap-only sweep at the lower end of the
+  // bracket (tau_lo <= tau*, so no tile of the support can be missed).
+  const Powers pw(p.alpha);
   const int total = p.tau_given ? 1 : p.niter + 1;
   for (int it = 0; it < total; ++it) {
     const bool last = (it == total - 1);
+    const bool bitmap_only = last && !v2_path && !p.tau_given;
     float a0[4] = {0, 0, 0, 0}, a1[4] = {0, 0, 0, 0}, a2[4] = {0, 0, 0, 0};
     uint32_t cur = 0u;  // bitmap word under construction (thread 0 only)
     sweep([&](int n) {
@@ -274,12 +322,21 @@ __global__ void __launch_bounds__(kThreads) solve_kernel(Params p) {
         // rows at or beyond len carry q = 0 and never count as hits
         bool row_ok = (m0 + id.ty + 16 * i) < len;
 #pragma unroll
+        const float thr = bitmap_only ? st[i].lo : st[i].t;
+#pragma unroll
         for (int j = 0; j < 4; ++j) {
-          bool mk = acc[i][j] > st[i].t;
-          float u = mk ? (acc[i][j] - st[i].t) : 0.f;
-          a0[i] = fmaf(u, u, a0[i]);
-          a1[i] += u;
-          a2[i] += mk ? 1.f : 0.f;
+          bool mk = acc[i][j] > thr;
+          float u = mk ? (acc[i][j] - thr) : 0.f;
+          if (pw.mode == 0) {
+            a0[i] = fmaf(u, u, a0[i]);
+            a1[i] += u;
+            a2[i] += mk ? 1.f : 0.f;
+          } else if (mk) {
+            const float g = pw.g(u);
+            a0[i] += pw.p(u);
+            a1[i] += g;
+            a2[i] += (pw.mode == 2) ? g / u : 0.f;
+          }
           hit |= (mk && row_ok) ? 1 : 0;
         }
       }
@@ -294,10 +351,13 @@ __global__ void __launch_bounds__(kThreads) solve_kernel(Params p) {
         }
       }
     });
-    if (!p.tau_given) {
+    if (!p.tau_given && !bitmap_only) {
 #pragma unroll
-      for (int i = 0; i < 4; ++i)
-        halley_bisect_update(st[i], row16_sum(a0[i]), row16_sum(a1[i]), row16_sum(a2[i]));
+      for (int i = 0; i < 4; ++i) {
+        const float s0 = row16_sum(a0[i]), s1 = row16_sum(a1[i]), s2 = row16_sum(a2[i]);
+        if (v2_path) halley_bisect_update(st[i], s0, s1, s2);
+        else halley_bisect_update_generic(st[i], s0, s1, s2, pw.c0, pw.c1);
+      }
     }
   }
   if (!p.tau_given && id.tx == 0) {
@@ -333,6 +393,7 @@ __global__ void __launch_bounds__(kThreads) fwd_kernel(Params p) {
 #pragma unroll
     for (int c = 0; c < DC; ++c) { o[i][c] = 0.f; o2[i][c] = 0.f; }
   float supp[4] = {0, 0, 0, 0};
+  const Powers pw(p.alpha);
   if (m0 < len) {
     const int kvh = h / (p.Hq / p.Hkv);
     const T* qg = (const T*)p.q + qoff;
@@ -341,7 +402,7 @@ __global__ void __launch_bounds__(kThreads) fwd_kernel(Params p) {
     const T* vg = (const T*)p.v + kvoff;
     const float* tg = p.taus + ((size_t)b * p.Hq + h) * (size_t)p.N;
     const int32_t* bm = p.bmask + (((size_t)b * p.Hq + h) * p.rows_padded + m) * (size_t)p.n_words;
-    load_tile<T, D, true>(sQ, qg, m0, len, 0.5f * p.sm_scale);
+    load_tile<T, D, true>(sQ, qg, m0, len, p.zscale);
     float t[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -358,17 +419,18 @@ __global__ void __launch_bounds__(kThreads) fwd_kernel(Params p) {
         load_tile<T, D, false>(sKV, kg, n * kTile, len, 1.0f);
         __syncthreads();
         tile_dot<D>(sQ, sKV, id, acc);
-        mask_scores(acc, id, m0, n * kTile, len);
+        mask_scores(acc, id, m0, n * kTile, len, p.causal != 0);
         __syncthreads();
         load_tile<T, D, false>(sKV, vg, n * kTile, len, 1.0f);
 #pragma unroll
         for (int i = 0; i < 4; ++i)
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
-            float u = fmaxf(acc[i][j] - t[i], 0.f);
-            supp[i] += u;
-            sP[(id.ty + 16 * i) * kPPitch + id.tx + 16 * j] = round_to<T>(u * u);
-            sU[(id.ty + 16 * i) * kPPitch + id.tx + 16 * j] = round_to<T>(u);
+            const float u = fmaxf(acc[i][j] - t[i], 0.f);
+            const float gw = pw.g(u);
+            supp[i] += gw;
+            sP[(id.ty + 16 * i) * kPPitch + id.tx + 16 * j] = round_to<T>(pw.p(u));
+            sU[(id.ty + 16 * i) * kPPitch + id.tx + 16 * j] = round_to<T>(gw);
           }
         __syncthreads();
         tile_pv<D>(sP, sKV, id, o);
@@ -458,6 +520,7 @@ __global__ void __launch_bounds__(kThreads) bwd_dq_kernel(Params p) {
   for (int i = 0; i < 4; ++i)
 #pragma unroll
     for (int c = 0; c < DC; ++c) dq[i][c] = 0.f;
+  const Powers pw(p.alpha);
   if (m0 < len) {
     const int kvh = h / (p.Hq / p.Hkv);
     const size_t kvoff = ((size_t)b * p.Hkv + kvh) * (size_t)p.N * D;
@@ -465,7 +528,7 @@ __global__ void __launch_bounds__(kThreads) bwd_dq_kernel(Params p) {
     const T* vg = (const T*)p.v + kvoff;
     const size_t toff = ((size_t)b * p.Hq + h) * (size_t)p.N;
     const int32_t* bm = p.bmask + (((size_t)b * p.Hq + h) * p.rows_padded + m) * (size_t)p.n_words;
-    load_tile<T, D, true>(sQ, (const T*)p.q + qoff, m0, len, 0.5f * p.sm_scale);
+    load_tile<T, D, true>(sQ, (const T*)p.q + qoff, m0, len, p.zscale);
     load_tile<T, D, false>(sDO, (const T*)p.dout + qoff, m0, len, 1.0f);
     float t[4], dl[4];
 #pragma unroll
@@ -488,13 +551,13 @@ __global__ void __launch_bounds__(kThreads) bwd_dq_kernel(Params p) {
         load_tile<T, D, false>(sKV, kg, n * kTile, len, 1.0f);
         __syncthreads();
         tile_dot<D>(sQ, sKV, id, acc);
-        mask_scores(acc, id, m0, n * kTile, len);
+        mask_scores(acc, id, m0, n * kTile, len, p.causal != 0);
 #pragma unroll
         for (int i = 0; i < 4; ++i)
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
-            float u = fmaxf(acc[i][j] - t[i], 0.f);
-            sDS[(id.ty + 16 * i) * kPPitch + id.tx + 16 * j] = round_to<T>(u * (dp[i][j] - dl[i]));
+            const float gw = pw.g(fmaxf(acc[i][j] - t[i], 0.f));
+            sDS[(id.ty + 16 * i) * kPPitch + id.tx + 16 * j] = round_to<T>(gw * (dp[i][j] - dl[i]));
           }
         __syncthreads();
         tile_pv<D>(sDS, sKV, id, dq);
@@ -534,8 +597,9 @@ __global__ void __launch_bounds__(kThreads) bwd_dkv_kernel(Params p) {
   for (int i = 0; i < 4; ++i)
 #pragma unroll
     for (int c = 0; c < DC; ++c) { dk[i][c] = 0.f; dv[i][c] = 0.f; }
+  const Powers pw(p.alpha);
   if (n0 < len) {
-    load_tile<T, D, true>(sK, (const T*)p.k + kvoff, n0, len, 0.5f * p.sm_scale);
+    load_tile<T, D, true>(sK, (const T*)p.k + kvoff, n0, len, p.zscale);
     load_tile<T, D, false>(sV, (const T*)p.v + kvoff, n0, len, 1.0f);
     for (int g = 0; g < G; ++g) {
       const int h = kvh * G + g;
@@ -562,16 +626,16 @@ __global__ void __launch_bounds__(kThreads) bwd_dkv_kernel(Params p) {
           load_tile<T, D, false>(sX, qg, m0, len, 1.0f);
           __syncthreads();
           tile_dot<D>(sX, sK, id, s);   // s[i][j]: q row ty+16i, key tx+16j
-          mask_scores(s, id, m0, n0, len);
+          mask_scores(s, id, m0, n0, len, p.causal != 0);
           __syncthreads();
           load_tile<T, D, false>(sX, dog, m0, len, 1.0f);
 #pragma unroll
           for (int i = 0; i < 4; ++i)
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-              float u = fmaxf(s[i][j] - t[i], 0.f);
-              s[i][j] = u;
-              sP[(id.ty + 16 * i) * kPPitch + id.tx + 16 * j] = round_to<T>(u * u);
+              const float u = fmaxf(s[i][j] - t[i], 0.f);
+              s[i][j] = pw.g(u);
+              sP[(id.ty + 16 * i) * kPPitch + id.tx + 16 * j] = round_to<T>(pw.p(u));
             }
           __syncthreads();
           tile_dot<D>(sX, sV, id, dp);  // dP = dO V^T

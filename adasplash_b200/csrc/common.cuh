@@ -85,6 +85,22 @@ __device__ __forceinline__ void halley_bisect_update(HalleyState& s, float a0, f
   s.t = good ? nt : 0.5f * (s.lo + s.hi);
 }
 
+// The same step for f(t) = sum [z-t]_+^c0 - 1 with any alpha: a0 = sum u^c0,
+// a1 = sum u^(c0-1), a2 = sum u^(c0-2) (adasplash_block_mask.py:40-296; for
+// alpha = 2 the second derivative vanishes and the step is Newton's).
+__device__ __forceinline__ void halley_bisect_update_generic(HalleyState& s, float a0, float a1,
+                                                            float a2, float c0, float c1) {
+  const float eps = 1e-5f;
+  float ff = a0 - 1.0f;
+  float df = -c0 * a1;
+  float ddf = c0 * c1 * a2;
+  if (ff > 0.f) s.lo = s.t;
+  if (ff < 0.f) s.hi = s.t;
+  float nt = s.t - (2.0f * ff * df) / (2.0f * df * df - ff * ddf);
+  bool good = (nt > s.lo - eps) && (nt < s.hi + eps);
+  s.t = good ? nt : 0.5f * (s.lo + s.hi);
+}
+
 // Closed-form lower bound of tau from a BINS-bin histogram of z - tau0 on [0,1]
 // (adasplash_v2.py:434-461).  cnt[b] = raw count of bin b (top bin still
 // includes the row maximum itself).

@@ -40,7 +40,13 @@ enum {
   ADS_PATH_TCGEN05 = 2 /* tensor-core kernels only; error if not applicable        */
 };
 
-/* Shape of one attention problem.  q is (B,Hq,N,D) contiguous, k and v are
+/* alpha = 1.5 with the causal mask is the AdaSplash-2 path (adasplash/adasplash_v2.py).
+ * Any other alpha in (1, 2] and / or full attention are the semantics of the reference's
+ * first-generation kernels (adasplash/adasplash_block_mask.py:938-1232: `sparse_attn(q, k, v,
+ * alpha, is_causal, varlen, niter)`, no grouped-query heads); they run on the CUDA-core
+ * kernels with a Halley / bisection solver on [max-1, max-n^(1-alpha)].
+ *
+ * Shape of one attention problem.  q is (B,Hq,N,D) contiguous, k and v are
  * (B,Hkv,N,D) contiguous, Hq % Hkv == 0, D in {16,32,64,128,256}, N >= 64
  * (adasplash/adasplash_v2.py:1245-1276).  `varlen` is NULL or B lengths
  * (int32, or int64 when varlen_is_i64 != 0) on the device. */
@@ -51,6 +57,8 @@ typedef struct {
   int32_t varlen_is_i64;
   int32_t path;           /* ADS_PATH_*                                       */
   int32_t bwd_stages;     /* 0 = whole backward; else a mask of ADS_BWD_* (timing aid) */
+  float alpha;            /* entmax alpha in (1, 2]; 0 means 1.5                        */
+  int32_t non_causal;     /* 0 = causal mask (key <= query), 1 = full attention         */
 } ads_attn_shape;
 
 /* Kernels of adasplash2_bwd, for `bwd_stages` (measurement only: a partial

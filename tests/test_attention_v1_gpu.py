@@ -1,0 +1,96 @@
+"""GPU parity of the first-generation semantics (any alpha in (1, 2], causal or full
+attention; `adasplash_v1`, and `adasplash` with alpha != 1.5 or is_causal=False) against the
+exact dense definition and the reference's golden outputs.  Tolerances of the reference's
+tests/test_adasplash.py:96,144-146: fp32 forward 1e-4, gradients 1e-2; fp16 forward 1e-1."""
+import os
+
+import pytest
+import torch
+
+import adasplash_b200 as adasplash
+from adasplash_b200 import attention as att
+from oracle import entmax_oracle as O
+
+pytestmark = pytest.mark.gpu
+GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+def _randn(shape, seed, scale=1.0, dtype=torch.float32):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * scale).to(dtype)
+
+
+@pytest.fixture(autouse=True)
+def _status_checks():
+    att.DEBUG_STATUS = True
+    yield
+    att.DEBUG_STATUS = False
+
+
+def _run(fn, q, k, v, do, **kw):
+    qc, kc, vc = (t.cuda().requires_grad_(True) for t in (q, k, v))
+    out = fn(qc, kc, vc, **kw)
+    dq, dk, dv = torch.autograd.grad(out, (qc, kc, vc), do.cuda())
+    return {"out": out.detach().float().cpu(), "dq": dq.float().cpu(), "dk": dk.float().cpu(), "dv": dv.float().cpu()}
+
+
+@pytest.mark.parametrize("name", ["v1_a1333_causal", "v1_a1333_full", "v1_a15_full", "v1_a2_causal", "v1_a2_full"])
+def test_reference_golden(name):
+    fx = torch.load(os.path.join(GOLD, name + ".pt"), weights_only=False)
+    got = _run(adasplash.adasplash, fx["q"], fx["k"], fx["v"], fx["dout"], alpha=fx["alpha"],
+               is_causal=fx["is_causal"], niter=10)
+    assert (got["out"] - fx["out"]).abs().max() < 1e-4
+    for key in ("dq", "dk", "dv"):
+        assert (got[key] - fx[key]).abs().max() < 1e-3, key
+
+
+@pytest.mark.parametrize("alpha", [1.333, 1.5, 2.0])
+@pytest.mark.parametrize("causal", [True, False])
+@pytest.mark.parametrize("case", [(2, 2, 128, 32, None), (1, 3, 256, 64, [200]), (2, 1, 192, 16, [64, 191]),
+                                  (1, 2, 320, 128, None)])
+def test_fp32_matches_exact_definition(alpha, causal, case):
+    B, H, N, D, vl = case
+    q, k, v = (_randn((B, H, N, D), 60 + i) for i in range(3))
+    varlen = None if vl is None else torch.tensor(vl, dtype=torch.int32)
+    do = _randn((B, H, N, D), 64)
+    if varlen is not None:
+        do = do * (torch.arange(N)[None, None, :, None] < varlen[:, None, None, None])
+    got = _run(adasplash.adasplash_v1, q, k, v, do, alpha=alpha, is_causal=causal,
+               varlen=None if varlen is None else varlen.cuda(), niter=10)
+    ex = O.dense_entmax_attention(q, k, v, alpha, causal, varlen, do)
+    assert (got["out"].double() - ex["out"]).abs().max() < 1e-4
+    for key in ("dq", "dk", "dv"):
+        assert (got[key].double() - ex[key]).abs().max() < 1e-3, key
+    if vl is not None:
+        for b in range(B):
+            assert got["out"][b, :, vl[b]:].abs().max() == 0
+
+
+@pytest.mark.parametrize("alpha", [1.333, 2.0])
+def test_fp16_forward(alpha):
+    B, H, N, D = 1, 2, 128, 64
+    q, k, v = (_randn((B, H, N, D), 70 + i, 1.0, torch.float16) for i in range(3))
+    out = adasplash.adasplash_v1(q.cuda(), k.cuda(), v.cuda(), alpha=alpha, is_causal=True)
+    ex = O.dense_entmax_attention(q, k, v, alpha, True)
+    assert (out.float().cpu().double() - ex["out"]).abs().max() < 2e-2
+    assert torch.isfinite(out).all()
+
+
+def test_zero_scores_give_the_mean_of_v():
+    # all-zero q/k: uniform attention (tests/test_adasplash.py:173-184)
+    B, H, N, D = 1, 2, 128, 32
+    z = torch.zeros(B, H, N, D)
+    v = _randn((B, H, N, D), 80)
+    for alpha in (1.333, 1.5, 2.0):
+        out = adasplash.adasplash_v1(z.cuda(), z.cuda(), v.cuda(), alpha=alpha, is_causal=False)
+        assert (out.cpu() - v.mean(2, keepdim=True)).abs().max() < 1e-4, alpha
+
+
+def test_gqa_is_rejected_and_dispatcher_routes():
+    q = torch.zeros(1, 4, 64, 16, device="cuda")
+    kv = torch.zeros(1, 2, 64, 16, device="cuda")
+    with pytest.raises(AssertionError, match="grouped-query"):
+        adasplash.adasplash_v1(q, kv, kv)
+    a = adasplash.adasplash(q, q, q + 1.0, alpha=1.5, is_causal=False)      # v1 route
+    b = adasplash.adasplash_no_block_mask(q, q, q + 1.0, alpha=1.5, is_causal=False)
+    assert torch.equal(a, b)

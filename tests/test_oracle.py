@@ -105,3 +105,12 @@ def test_v2_oracle_vs_reference_golden(name, tol_out, tol_grad):
         ex = O.dense_entmax_attention(fx["q"], fx["k"], fx["v"], 1.5, True, vl, fx["dout"])
         for key in ("out", "dq", "dk", "dv"):
             assert (ex[key] - fx[key].double()).abs().max() < 1e-4, key
+
+
+@pytest.mark.parametrize("name", ["v1_a1333_causal", "v1_a1333_full", "v1_a15_full", "v1_a2_causal", "v1_a2_full"])
+def test_exact_oracle_vs_reference_v1_golden(name):
+    # generic alpha / full attention: the reference's first-generation kernels at niter = 10
+    fx = _load(name)
+    ex = O.dense_entmax_attention(fx["q"], fx["k"], fx["v"], fx["alpha"], fx["is_causal"], None, fx["dout"])
+    for key in ("out", "dq", "dk", "dv"):
+        assert (ex[key].float() - fx[key]).abs().max() < 2e-5, key
