@@ -22,7 +22,7 @@ namespace sm100 {
 // ---------------------------------------------------------------------------
 // dQ
 // ---------------------------------------------------------------------------
-constexpr int kDqThreads = 320;   // 8 row warps + TMA warp + MMA warp
+constexpr int kDqThreads = 384;   // 8 row warps + TMA warp + three MMA warps
 constexpr int kDqRowThreads = 256;
 constexpr int kDqKStages = 3;
 constexpr int kDqVStages = 2;
@@ -151,64 +151,80 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       }
     }
   } else if (warp == 9) {
+    // ---------------- S issuer: S_j = Q~ K_j^T into S buffer j&1 ----------------
+    // Three warps issue the three products of a tile, so that the waits and commits of one
+    // overlap the MMAs of the others (an issuing thread that waits leaves the tensor pipe idle).
     constexpr uint32_t idesc_s = ptx::make_idesc(FMT, kBlockM, kBlockN, 0, 0);
-    constexpr uint32_t idesc_dq = ptx::make_idesc(FMT, kBlockM, D, 0, 1);
     bool ok = true;
     if (lane == 0) ok = ptx::mbar_wait(q_ready, 0);
     ok = __shfl_sync(0xffffffffu, ok, 0);
-    if (!ok && lane == 0) raise_abort(cta_abort, p.status, kStTimeoutMma);
-
-    // S_j = Q~ K_j^T into S buffer j&1 (lane 0)
-    auto issue_s = [&](int j) -> bool {
+    TileScan scan(bm_head, qt, T_tiles, p.rows_padded, p.n_words);
+    int kt;
+    uint32_t flags;
+    for (int j = 0; ok && scan.next(kt, flags); ++j) {
       const int ks = j % kDqKStages, buf = j & 1;
-      if (!ptx::mbar_wait(k_full + ks, (j / kDqKStages) & 1) ||
-          !ptx::mbar_wait(s_free + buf, ((j >> 1) & 1) ^ 1))
-        return false;
-      ptx::tc_fence_after_sync();
-      const uint32_t a0 = ptx::smem_u32(sQ), b0 = ptx::smem_u32(sK + ks * L::tile_bytes);
+      if (*cta_abort) { ok = false; break; }
+      if (lane == 0) {
+        ok = ptx::mbar_wait(k_full + ks, (j / kDqKStages) & 1) && ptx::mbar_wait(s_free + buf, ((j >> 1) & 1) ^ 1);
+        if (ok) {
+          ptx::tc_fence_after_sync();
+          const uint32_t a0 = ptx::smem_u32(sQ), b0 = ptx::smem_u32(sK + ks * L::tile_bytes);
 #pragma unroll
-      for (int kk = 0; kk < KSTEPS; ++kk) {
-        const uint32_t off = (kk >> 2) * kPanelBytes + (kk & 3) * 32;
-        ptx::mma_ss(tmem_base + buf * kBlockN, ptx::make_smem_desc(a0 + off, 16, 1024),
-                    ptx::make_smem_desc(b0 + off, 16, 1024), idesc_s, kk > 0);
+          for (int kk = 0; kk < KSTEPS; ++kk) {
+            const uint32_t off = (kk >> 2) * kPanelBytes + (kk & 3) * 32;
+            ptx::mma_ss(tmem_base + buf * kBlockN, ptx::make_smem_desc(a0 + off, 16, 1024),
+                        ptx::make_smem_desc(b0 + off, 16, 1024), idesc_s, kk > 0);
+          }
+          ptx::mma_commit(s_full + buf);
+        }
       }
-      ptx::mma_commit(s_full + buf);
-      return true;
-    };
-    // dP_j = dO V_j^T into the single dP buffer (lane 0); the caller guarantees
-    // that the row warps have finished reading dP_{j-1}
-    auto issue_dp = [&](int j) -> bool {
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+    }
+    if (!ok && lane == 0 && !*cta_abort) raise_abort(cta_abort, p.status, kStTimeoutMma);
+  } else if (warp == 10) {
+    // ---------------- dP issuer: dP_j = dO V_j^T into the single dP buffer ----------------
+    constexpr uint32_t idesc_s = ptx::make_idesc(FMT, kBlockM, kBlockN, 0, 0);
+    bool ok = true;
+    if (lane == 0) ok = ptx::mbar_wait(q_ready, 0);
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    TileScan scan(bm_head, qt, T_tiles, p.rows_padded, p.n_words);
+    int kt;
+    uint32_t flags;
+    for (int j = 0; ok && scan.next(kt, flags); ++j) {
       const int vs = j % kDqVStages;
-      if (!ptx::mbar_wait(v_full + vs, (j / kDqVStages) & 1)) return false;
-      ptx::tc_fence_after_sync();
-      const uint32_t a0 = ptx::smem_u32(sDO), b0 = ptx::smem_u32(sV + vs * L::tile_bytes);
+      if (*cta_abort) { ok = false; break; }
+      if (lane == 0) {
+        ok = ptx::mbar_wait(v_full + vs, (j / kDqVStages) & 1);
+        // the row warps have finished reading dP_{j-1}
+        if (ok && j > 0) ok = ptx::mbar_wait(p_full + ((j - 1) & 1), ((j - 1) >> 1) & 1);
+        if (ok) {
+          ptx::tc_fence_after_sync();
+          const uint32_t a0 = ptx::smem_u32(sDO), b0 = ptx::smem_u32(sV + vs * L::tile_bytes);
 #pragma unroll
-      for (int kk = 0; kk < KSTEPS; ++kk) {
-        const uint32_t off = (kk >> 2) * kPanelBytes + (kk & 3) * 32;
-        ptx::mma_ss(tmem_base + DP_COL, ptx::make_smem_desc(a0 + off, 16, 1024),
-                    ptx::make_smem_desc(b0 + off, 16, 1024), idesc_s, kk > 0);
+          for (int kk = 0; kk < KSTEPS; ++kk) {
+            const uint32_t off = (kk >> 2) * kPanelBytes + (kk & 3) * 32;
+            ptx::mma_ss(tmem_base + DP_COL, ptx::make_smem_desc(a0 + off, 16, 1024),
+                        ptx::make_smem_desc(b0 + off, 16, 1024), idesc_s, kk > 0);
+          }
+          ptx::mma_commit(v_empty + vs);
+          ptx::mma_commit(dp_full);
+        }
       }
-      ptx::mma_commit(v_empty + vs);
-      ptx::mma_commit(dp_full);
-      return true;
-    };
-
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+    }
+    if (!ok && lane == 0 && !*cta_abort) raise_abort(cta_abort, p.status, kStTimeoutMma);
+  } else if (warp == 11) {
+    // ---------------- dQ issuer: dQ += dS_j K_j ----------------
+    constexpr uint32_t idesc_dq = ptx::make_idesc(FMT, kBlockM, D, 0, 1);
+    bool ok = true;
     TileScan scan(bm_head, qt, T_tiles, p.rows_padded, p.n_words);
     int kt, kt_next = 0;
     uint32_t flags;
     bool have = scan.next(kt, flags);
-    if (ok && have) {
-      if (lane == 0) ok = issue_s(0) && issue_dp(0);
-      ok = __shfl_sync(0xffffffffu, ok, 0);
-    }
-    int j = 0;
-    for (; ok && have; ++j) {
+    for (int j = 0; ok && have; ++j) {
       const int ks = j % kDqKStages, buf = j & 1;
       const bool have_next = scan.next(kt_next, flags);
       if (*cta_abort) { ok = false; break; }
-      if (lane == 0 && have_next) ok = issue_s(j + 1);
-      ok = __shfl_sync(0xffffffffu, ok, 0);
-      if (!ok) break;
       uint8_t* ktile = sK + ks * L::tile_bytes;
       // padded keys: K rows = 0 for the dS K product (S_j, the other reader of this
       // tile, has completed: its commit precedes p_full in program order of the row warps)
@@ -229,9 +245,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         ptx::mma_commit(k_empty + ks);
         ptx::mma_commit(s_free + buf);
         if (!have_next) ptx::mma_commit(dq_full);
-        else ok = issue_dp(j + 1);
       }
-      ok = __shfl_sync(0xffffffffu, ok, 0);
       kt = kt_next;
       have = have_next;
     }
@@ -355,7 +369,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
 // ---------------------------------------------------------------------------
 // dK, dV
 // ---------------------------------------------------------------------------
-constexpr int kDkvThreads = 576;    // 16 row warps (2 step groups x 2 column halves) + TMA warp + MMA warp
+constexpr int kDkvThreads = 672;    // 16 row warps (2 step groups x 2 column halves) + TMA warp + four MMA warps
 constexpr int kDkvRowThreads = 512;
 constexpr int kDkvGroupThreads = 256;
 constexpr int kDkvStages = 3;       // (Q block, dO block) pairs in flight
@@ -476,13 +490,13 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
     if (lane == 0) {
       ptx::mbar_init(kv_full, 1);
       ptx::mbar_init(k_ready, kDkvRowThreads / 32);
-      for (int s = 0; s < kDkvStages; ++s) { ptx::mbar_init(x_full + s, 1); ptx::mbar_init(x_empty + s, 1); }
+      for (int s = 0; s < kDkvStages; ++s) { ptx::mbar_init(x_full + s, 1); ptx::mbar_init(x_empty + s, 2); }
       for (int s = 0; s < 2; ++s) {
-        ptx::mbar_init(s_full + s, 1);
+        ptx::mbar_init(s_full + s, 2);
         ptx::mbar_init(p_full + s, kDkvGroupThreads / 32);
-        ptx::mbar_init(s_free + s, 1);
+        ptx::mbar_init(s_free + s, 2);
       }
-      ptx::mbar_init(acc_full, 1);
+      ptx::mbar_init(acc_full, 2);
       ptx::fence_mbar_init();
     }
     __syncwarp();
@@ -521,88 +535,79 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
         }
       }
     }
-  } else if (warp == 17) {
+  } else if (warp == 17 || warp == 18) {
+    // ---------------- S^T issuer (warp 17: K~ Q_j^T) and dP^T issuer (warp 18: V dO_j^T) ----------------
+    // Four warps issue the four products of a step, so that the waits and commits of one
+    // overlap the MMAs of the others (an issuing thread that waits leaves the tensor pipe idle).
     constexpr uint32_t idesc_s = ptx::make_idesc(FMT, kBlockN, kQBlock, 0, 0);   // 128 keys x 64 queries
-    constexpr uint32_t idesc_acc = ptx::make_idesc(FMT, kBlockN, D, 0, 1);        // 128 keys x D
+    const bool is_s = warp == 17;
     bool ok = true;
     if (lane == 0) ok = ptx::mbar_wait(k_ready, 0);
     ok = __shfl_sync(0xffffffffu, ok, 0);
-    if (!ok && lane == 0) raise_abort(cta_abort, p.status, kStTimeoutMma);
-
-    // S^T_j = K~ Q_j^T and dP^T_j = V dO_j^T into buffer j&1 (lane 0)
-    auto issue_s = [&](int j) -> bool {
+    QBlockScan scan(p.bmask_t, b, p.Hq, G, kvh, nt, n_qblocks, p.rows_padded, p.n_words);
+    int g, m;
+    uint32_t flags;
+    for (int j = 0; ok && scan.next(g, m, flags); ++j) {
       const int st = j % kDkvStages, buf = j & 1;
-      if (!ptx::mbar_wait(x_full + st, (j / kDkvStages) & 1) ||
-          !ptx::mbar_wait(s_free + buf, ((j >> 1) & 1) ^ 1))
-        return false;
-      ptx::tc_fence_after_sync();
-      const uint32_t k0 = ptx::smem_u32(sK), v0 = ptx::smem_u32(sV);
-      const uint32_t q0 = ptx::smem_u32(sQ + st * L::qblk_bytes), d0 = ptx::smem_u32(sDO + st * L::qblk_bytes);
+      if (*cta_abort) { ok = false; break; }
+      if (lane == 0) {
+        ok = ptx::mbar_wait(x_full + st, (j / kDkvStages) & 1) && ptx::mbar_wait(s_free + buf, ((j >> 1) & 1) ^ 1);
+        if (ok) {
+          ptx::tc_fence_after_sync();
+          const uint32_t a0 = ptx::smem_u32(is_s ? sK : sV);
+          const uint32_t b0 = ptx::smem_u32((is_s ? sQ : sDO) + st * L::qblk_bytes);
+          const uint32_t d = tmem_base + (is_s ? 0u : DP_COL0) + buf * kQBlock;
 #pragma unroll
-      for (int kk = 0; kk < KSTEPS; ++kk) {
-        const uint32_t offa = (kk >> 2) * kPanelBytes + (kk & 3) * 32;
-        const uint32_t offb = (kk >> 2) * kQPanelBytes + (kk & 3) * 32;
-        ptx::mma_ss(tmem_base + buf * kQBlock, ptx::make_smem_desc(k0 + offa, 16, 1024),
-                    ptx::make_smem_desc(q0 + offb, 16, 1024), idesc_s, kk > 0);
+          for (int kk = 0; kk < KSTEPS; ++kk) {
+            const uint32_t offa = (kk >> 2) * kPanelBytes + (kk & 3) * 32;
+            const uint32_t offb = (kk >> 2) * kQPanelBytes + (kk & 3) * 32;
+            ptx::mma_ss(d, ptx::make_smem_desc(a0 + offa, 16, 1024), ptx::make_smem_desc(b0 + offb, 16, 1024),
+                        idesc_s, kk > 0);
+          }
+          ptx::mma_commit(s_full + buf);
+        }
       }
-#pragma unroll
-      for (int kk = 0; kk < KSTEPS; ++kk) {
-        const uint32_t offa = (kk >> 2) * kPanelBytes + (kk & 3) * 32;
-        const uint32_t offb = (kk >> 2) * kQPanelBytes + (kk & 3) * 32;
-        ptx::mma_ss(tmem_base + DP_COL0 + buf * kQBlock, ptx::make_smem_desc(v0 + offa, 16, 1024),
-                    ptx::make_smem_desc(d0 + offb, 16, 1024), idesc_s, kk > 0);
-      }
-      ptx::mma_commit(s_full + buf);
-      return true;
-    };
-
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+    }
+    if (!ok && lane == 0 && !*cta_abort) raise_abort(cta_abort, p.status, kStTimeoutMma);
+  } else if (warp == 19 || warp == 20) {
+    // ---------------- dV issuer (warp 19: dV += P^T dO_j) and dK issuer (warp 20: dK += dS^T Q_j) ----------------
+    constexpr uint32_t idesc_acc = ptx::make_idesc(FMT, kBlockN, D, 0, 1);        // 128 keys x D
+    const bool is_dv = warp == 19;
+    bool ok = true;
     QBlockScan scan(p.bmask_t, b, p.Hq, G, kvh, nt, n_qblocks, p.rows_padded, p.n_words);
     int g, m, g_next = 0, m_next = 0;
     uint32_t flags;
     bool have = scan.next(g, m, flags);
-    if (ok && have) {
-      if (lane == 0) ok = issue_s(0);
-      ok = __shfl_sync(0xffffffffu, ok, 0);
-    }
-    int j = 0;
-    for (; ok && have; ++j) {
+    for (int j = 0; ok && have; ++j) {
       const int st = j % kDkvStages, buf = j & 1;
       const bool have_next = scan.next(g_next, m_next, flags);
       if (*cta_abort) { ok = false; break; }
-      if (lane == 0 && have_next) ok = issue_s(j + 1);
-      ok = __shfl_sync(0xffffffffu, ok, 0);
-      if (!ok) break;
       if (lane == 0) ok = ptx::mbar_wait(p_full + buf, (j >> 1) & 1);
       ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) break;
-      uint8_t* qt_ = sQ + st * L::qblk_bytes;
-      uint8_t* dot_ = sDO + st * L::qblk_bytes;
+      uint8_t* bt = (is_dv ? sDO : sQ) + st * L::qblk_bytes;  // B operand: dO for dV, Q for dK
       if ((m + 1) * kQBlock > len) {
-        // padded query rows: Q and dO rows = 0 for the transposed products
+        // padded query rows: rows = 0 for the transposed product (the S^T / dP^T products that
+        // read this block have completed before p_full)
         const int first = len - m * kQBlock;
         for (int pn = 0; pn < PANELS; ++pn) {
-          uint4* bq = reinterpret_cast<uint4*>(qt_ + pn * kQPanelBytes + first * 128);
-          uint4* bd = reinterpret_cast<uint4*>(dot_ + pn * kQPanelBytes + first * 128);
-          for (int v = lane; v < (kQBlock - first) * 8; v += 32) { bq[v] = make_uint4(0, 0, 0, 0); bd[v] = make_uint4(0, 0, 0, 0); }
+          uint4* bq = reinterpret_cast<uint4*>(bt + pn * kQPanelBytes + first * 128);
+          for (int v = lane; v < (kQBlock - first) * 8; v += 32) bq[v] = make_uint4(0, 0, 0, 0);
         }
         ptx::fence_proxy_async_smem();
         __syncwarp();
       }
       if (lane == 0) {
         ptx::tc_fence_after_sync();
-        const uint32_t q0 = ptx::smem_u32(qt_), d0 = ptx::smem_u32(dot_);
+        const uint32_t b0 = ptx::smem_u32(bt);
         // P^T / dS^T: 16 queries = 8 packed columns per k-step, at the start of each 16-column group
-        const uint32_t pa = tmem_base + buf * kQBlock;
-        const uint32_t da = tmem_base + DP_COL0 + buf * kQBlock;
+        const uint32_t a = tmem_base + (is_dv ? 0u : DP_COL0) + buf * kQBlock;
+        const uint32_t acc = tmem_base + (is_dv ? DV_COL : DK_COL);
 #pragma unroll
         for (int kk = 0; kk < kQBlock / 16; ++kk) {
-          ptx::mma_ts(tmem_base + DV_COL, pa + kk * 16, ptx::make_smem_desc(d0 + kk * 2048, kQPanelBytes, 1024),
-                      idesc_acc, (j > 0 || kk > 0));
-        }
-#pragma unroll
-        for (int kk = 0; kk < kQBlock / 16; ++kk) {
-          ptx::mma_ts(tmem_base + DK_COL, da + kk * 16, ptx::make_smem_desc(q0 + kk * 2048, kQPanelBytes, 1024),
-                      idesc_acc, (j > 0 || kk > 0));
+          ptx::mma_ts(acc, a + kk * 16, ptx::make_smem_desc(b0 + kk * 2048, kQPanelBytes, 1024), idesc_acc,
+                      (j > 0 || kk > 0));
         }
         ptx::mma_commit(x_empty + st);
         ptx::mma_commit(s_free + buf);

@@ -22,7 +22,7 @@
 namespace ads {
 namespace sm100 {
 
-constexpr int kFwdThreads = 576;  // 16 row warps (four per TMEM lane quarter) + TMA warp + MMA warp
+constexpr int kFwdThreads = 640;  // 16 row warps (four per TMEM lane quarter) + TMA warp + three MMA warps
 constexpr int kFwdRowThreads = 512;
 constexpr int kFwdGroupThreads = 256;  // row threads that work on one tile
 constexpr int kFwdKStages = 2;
@@ -130,13 +130,13 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       ptx::mbar_init(q_full, 1);
       ptx::mbar_init(q_ready, kFwdRowThreads / 32);
       for (int s = 0; s < kFwdKStages; ++s) { ptx::mbar_init(k_full + s, 1); ptx::mbar_init(k_empty + s, 1); }
-      for (int s = 0; s < kFwdVStages; ++s) { ptx::mbar_init(v_full + s, 1); ptx::mbar_init(v_empty + s, 1); }
+      for (int s = 0; s < kFwdVStages; ++s) { ptx::mbar_init(v_full + s, 1); ptx::mbar_init(v_empty + s, 2); }
       for (int s = 0; s < 2; ++s) {
         ptx::mbar_init(s_full + s, 1);
         ptx::mbar_init(p_full + s, kFwdGroupThreads / 32);
-        ptx::mbar_init(s_free + s, 1);
+        ptx::mbar_init(s_free + s, 2);
       }
-      ptx::mbar_init(o_full, 1);
+      ptx::mbar_init(o_full, 2);
       ptx::fence_mbar_init();
     }
     __syncwarp();
@@ -178,66 +178,69 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       }
     }
   } else if (warp == 17) {
-    // ---------------- MMA issuer (whole warp stays converged; lane 0 issues) ----------------
+    // ---------------- S issuer (whole warp stays converged; lane 0 issues) ----------------
+    // The tensor pipe only runs what has been issued, and an issuing thread that waits on a
+    // barrier or commits leaves it idle.  The S products and the P.V products therefore come
+    // from two warps: while one is between tiles the other keeps the pipe busy.
     constexpr uint32_t idesc_s = ptx::make_idesc(FMT, kBlockM, kBlockN, 0, 0);
-    constexpr uint32_t idesc_pv = ptx::make_idesc(FMT, kBlockM, D, 0, 1);
     bool ok = true;
     if (lane == 0) ok = ptx::mbar_wait(q_ready, 0);
     ok = __shfl_sync(0xffffffffu, ok, 0);
-    if (!ok && lane == 0) raise_abort(cta_abort, p.status, kStTimeoutMma);
-
-    auto issue_s = [&](int j) -> bool {  // lane 0 only
+    TileScan scan(bm_head, qt, T_tiles, p.rows_padded, p.n_words);
+    int kt;
+    uint32_t flags;
+    for (int j = 0; ok && scan.next(kt, flags); ++j) {
       const int ks = j % kFwdKStages, buf = j & 1;
-      if (!ptx::mbar_wait(k_full + ks, (j / kFwdKStages) & 1) ||
-          !ptx::mbar_wait(s_free + buf, ((j >> 1) & 1) ^ 1))
-        return false;
-      ptx::tc_fence_after_sync();
-      const uint32_t a0 = ptx::smem_u32(sQ), b0 = ptx::smem_u32(sK + ks * L::tile_bytes);
-      const uint32_t d = tmem_base + buf * kBlockN;
+      if (*cta_abort) { ok = false; break; }
+      if (lane == 0) {
+        ok = ptx::mbar_wait(k_full + ks, (j / kFwdKStages) & 1) && ptx::mbar_wait(s_free + buf, ((j >> 1) & 1) ^ 1);
+        if (ok) {
+          ptx::tc_fence_after_sync();
+          const uint32_t a0 = ptx::smem_u32(sQ), b0 = ptx::smem_u32(sK + ks * L::tile_bytes);
+          const uint32_t d = tmem_base + buf * kBlockN;
 #pragma unroll
-      for (int kk = 0; kk < KSTEPS; ++kk) {
-        const uint32_t off = (kk >> 2) * kPanelBytes + (kk & 3) * 32;
-        ptx::mma_ss(d, ptx::make_smem_desc(a0 + off, 16, 1024), ptx::make_smem_desc(b0 + off, 16, 1024),
-                    idesc_s, kk > 0);
+          for (int kk = 0; kk < KSTEPS; ++kk) {
+            const uint32_t off = (kk >> 2) * kPanelBytes + (kk & 3) * 32;
+            ptx::mma_ss(d, ptx::make_smem_desc(a0 + off, 16, 1024), ptx::make_smem_desc(b0 + off, 16, 1024),
+                        idesc_s, kk > 0);
+          }
+          ptx::mma_commit(k_empty + ks);
+          ptx::mma_commit(s_full + buf);
+        }
       }
-      ptx::mma_commit(k_empty + ks);
-      ptx::mma_commit(s_full + buf);
-      return true;
-    };
-
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+    }
+    if (!ok && lane == 0 && !*cta_abort) raise_abort(cta_abort, p.status, kStTimeoutMma);
+  } else if (warp == 18 || warp == 19) {
+    // ---------------- P.V issuer (warp 18: O += P V) and U.V issuer (warp 19: O2 += U V) ----------------
+    constexpr uint32_t idesc_pv = ptx::make_idesc(FMT, kBlockM, D, 0, 1);
+    const uint32_t acc = tmem_base + (warp == 18 ? O_COL : O2_COL);
+    const uint32_t a_shift = warp == 18 ? 0u : 16u;  // U sits 16 columns after P in every 32-column chunk
+    bool ok = true;
     TileScan scan(bm_head, qt, T_tiles, p.rows_padded, p.n_words);
     int kt, kt_next = 0;
     uint32_t flags;
     bool have = scan.next(kt, flags);
-    if (ok && have) {
-      if (lane == 0) ok = issue_s(0);
-      ok = __shfl_sync(0xffffffffu, ok, 0);
-    }
-    int j = 0;
-    for (; ok && have; ++j) {
+    for (int j = 0; ok && have; ++j) {
       const int vs = j % kFwdVStages, buf = j & 1;
       const bool have_next = scan.next(kt_next, flags);
       if (*cta_abort) { ok = false; break; }
-      if (lane == 0) {
-        if (have_next) ok = issue_s(j + 1);
-        if (ok) ok = ptx::mbar_wait(v_full + vs, (j / kFwdVStages) & 1);
-      }
+      if (lane == 0) ok = ptx::mbar_wait(v_full + vs, (j / kFwdVStages) & 1);
       ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) break;
       uint8_t* vt = sV + vs * L::tile_bytes;
-      if ((kt + 1) * kBlockN > len) zero_tile_rows(vt, PANELS, len - kt * kBlockN, lane);  // padded keys: V = 0
+      // padded keys: V = 0 (both issuers write the same zeros before their own products)
+      if ((kt + 1) * kBlockN > len) zero_tile_rows(vt, PANELS, len - kt * kBlockN, lane);
       if (lane == 0) {
         ok = ptx::mbar_wait(p_full + buf, (j >> 1) & 1);
         if (ok) {
           ptx::tc_fence_after_sync();
           const uint32_t v0 = ptx::smem_u32(vt);
-          const uint32_t pbase = tmem_base + buf * kBlockN;
+          const uint32_t pbase = tmem_base + buf * kBlockN + a_shift;
 #pragma unroll
           for (int kk = 0; kk < kBlockN / 16; ++kk) {
             const uint64_t bd = ptx::make_smem_desc(v0 + kk * 2048, kPanelBytes, 1024);
-            const uint32_t pa = pbase + (kk >> 1) * 32 + (kk & 1) * 8;
-            ptx::mma_ts(tmem_base + O_COL, pa, bd, idesc_pv, (j > 0 || kk > 0));
-            ptx::mma_ts(tmem_base + O2_COL, pa + 16, bd, idesc_pv, (j > 0 || kk > 0));
+            ptx::mma_ts(acc, pbase + (kk >> 1) * 32 + (kk & 1) * 8, bd, idesc_pv, (j > 0 || kk > 0));
           }
           ptx::mma_commit(v_empty + vs);
           ptx::mma_commit(s_free + buf);
