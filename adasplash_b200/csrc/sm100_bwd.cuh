@@ -277,6 +277,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     ptx::mbar_arrive_warp(q_ready);
     const float tau = row_ok ? p.taus[(size_t)bh * p.N + row] : 0.f;
     const float dl = row_ok ? p.delta[(size_t)bh * p.N + row] : 0.f;
+    const bool rows_full = m0 + kBlockM <= len;
     TileScan scan(bm_head, qt, T_tiles, p.rows_padded, p.n_words);
     int kt, n_active = 0;
     uint32_t flags;
@@ -308,14 +309,23 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
           ptx::tmem_ld_wait();
           const float* s = reinterpret_cast<const float*>(rs);
           const float* dp = reinterpret_cast<const float*>(rp);
-          const int lim = need_mask ? (min(row, len - 1) - (n0 + ch * 32)) : 64;  // columns c <= lim survive
+          if (!need_mask && rows_full) {
+            // every (row, key) pair of the tile is causal and inside the sequence
 #pragma unroll
-          for (int c = 0; c < 32; c += 2) {
-            const float u0 = s[c] - tau, u1 = s[c + 1] - tau;
-            // select, not multiply: dP of a padded key may be anything
-            const float d0 = (u0 > 0.f && c <= lim) ? u0 * (dp[c] - dl) : 0.f;
-            const float d1 = (u1 > 0.f && c + 1 <= lim) ? u1 * (dp[c + 1] - dl) : 0.f;
-            dk[c >> 1] = pack2<T>(d0, d1);
+            for (int c = 0; c < 32; c += 2) {
+              const float u0 = fmaxf(s[c] - tau, 0.f), u1 = fmaxf(s[c + 1] - tau, 0.f);
+              dk[c >> 1] = pack2<T>(u0 * (dp[c] - dl), u1 * (dp[c + 1] - dl));
+            }
+          } else {
+            const int lim = need_mask ? (min(row, len - 1) - (n0 + ch * 32)) : 64;  // columns c <= lim survive
+#pragma unroll
+            for (int c = 0; c < 32; c += 2) {
+              const float u0 = s[c] - tau, u1 = s[c + 1] - tau;
+              // select, not multiply: dP of a padded key or row may be anything
+              const float d0 = (u0 > 0.f && c <= lim) ? u0 * (dp[c] - dl) : 0.f;
+              const float d1 = (u1 > 0.f && c + 1 <= lim) ? u1 * (dp[c + 1] - dl) : 0.f;
+              dk[c >> 1] = pack2<T>(d0, d1);
+            }
           }
         }
         ptx::tmem_st16(caddr, dk);
@@ -388,8 +398,8 @@ struct DkvSmem {
   static constexpr int bar_off = do_off + kDkvStages * qblk_bytes;
   static constexpr int n_bars = 2 + 2 * kDkvStages + 2 + 2 + 2 + 1;
   static constexpr int misc_off = bar_off + n_bars * 8;
-  static constexpr int td_off = misc_off + 64;                  // [2][2][64] floats: tau, delta
-  static constexpr size_t bytes = 1024 + td_off + 2 * 2 * 128 * 4;  // [2 groups][2 buffers][tau 64 | delta 64]
+  static constexpr int td_off = (misc_off + 64 + 15) & ~15;     // [2 groups][2 buffers][tau 64 | delta 64] floats, 16-byte aligned (read as float4)
+  static constexpr size_t bytes = 1024 + td_off + 2 * 2 * 128 * 4;
 };
 
 // Walks (q head of the group, 64-row query block) pairs whose bit is set in rows
@@ -685,6 +695,7 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
       if (!dead) {
         ptx::tc_fence_after_sync();
         const bool sub_on = (flags >> kh) & 1u;  // warp-uniform: the TMEM loads below are warp-collective
+        const bool full = (n0 + kBlockN - 1 <= m * kQBlock) && ((m + 1) * kQBlock <= len);
 #pragma unroll
         for (int sc16 = 0; sc16 < 2; ++sc16) {
           const int c0 = half * 32 + sc16 * 16;     // first query column of this sub-chunk
@@ -704,6 +715,20 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
             const float* dp = reinterpret_cast<const float*>(rp);
             const float* tq = td + c0;
             const float* dq_ = td + 64 + c0;
+            if (full) {
+              // every (key, query) pair of the step is causal and inside the sequence
+#pragma unroll
+              for (int c = 0; c < 16; c += 4) {
+                const float4 t4 = *reinterpret_cast<const float4*>(tq + c);
+                const float4 l4 = *reinterpret_cast<const float4*>(dq_ + c);
+                const float u0 = fmaxf(s[c] - t4.x, 0.f), u1 = fmaxf(s[c + 1] - t4.y, 0.f);
+                const float u2 = fmaxf(s[c + 2] - t4.z, 0.f), u3 = fmaxf(s[c + 3] - t4.w, 0.f);
+                pk[c >> 1] = pack2<T>(u0 * u0, u1 * u1);
+                pk[(c >> 1) + 1] = pack2<T>(u2 * u2, u3 * u3);
+                dk[c >> 1] = pack2<T>(u0 * (dp[c] - l4.x), u1 * (dp[c + 1] - l4.y));
+                dk[(c >> 1) + 1] = pack2<T>(u2 * (dp[c + 2] - l4.z), u3 * (dp[c + 3] - l4.w));
+              }
+            } else {
             // query column c is valid iff key <= q0 + c < len  <=>  lo <= c < hi
             const int lo = key - q0, hi = key_ok ? len - q0 : 0;
 #pragma unroll
@@ -716,6 +741,7 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
               // select, not multiply: S / dP entries of padded rows may be anything
               pk[c >> 1] = pack2<T>(ok0 ? u0 * u0 : 0.f, ok1 ? u1 * u1 : 0.f);
               dk[c >> 1] = pack2<T>(ok0 ? u0 * (dp[c] - l2.x) : 0.f, ok1 ? u1 * (dp[c + 1] - l2.y) : 0.f);
+            }
             }
           }
           // 16 queries = 8 packed columns, written at the start of this thread's own

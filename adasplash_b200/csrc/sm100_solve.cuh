@@ -6,12 +6,12 @@
 // traffic per FLOP (a solver sweep has no other operand to amortise it: one
 // 32 KB K tile per 128x128x128 product made it L2-bandwidth-bound).
 //
-//   * the two Q tiles are scaled by fp32(0.5/sqrt(D)), rounded to the input
-//     dtype and parked in TMEM as A operands, so the MMA reads only K from
-//     shared memory;
-//   * S_A = Q~_A K^T and S_B = Q~_B K^T go to two 128-column fp32 TMEM buffers;
-//     row group A (8 warps) reduces S_A while the tensor pipe produces S_B, and
-//     vice versa;
+//   * the two Q tiles are scaled by fp32(0.5/sqrt(D)) and rounded to the input
+//     dtype in place in shared memory;
+//   * S_A = Q~_A K^T and S_B = Q~_B K^T each alternate between two 128-column fp32
+//     TMEM buffers, so that the product of a group's next tile overlaps its row
+//     work on the current one; each row tile has its own MMA-issuing warp, so that
+//     one tile waiting for its row group does not hold back the other;
 //   * inside a group, TMEM lane = score row, and the two warps that own the same
 //     32 lanes split the 128 keys of a tile in halves (the row work of a tile is
 //     a chain of TMEM round trips; two threads per row halve it).  The two
@@ -30,11 +30,10 @@ namespace ads {
 namespace sm100 {
 
 constexpr int kSolveStages = 3;  // each K tile feeds two products, three tiles in flight cover the TMA latency
-constexpr int kSolveThreads = 576;   // 2 row groups x 8 warps + TMA warp + MMA warp
+constexpr int kSolveThreads = 608;   // 2 row groups x 8 warps + TMA warp + 2 MMA warps
 constexpr int kSolveRowThreads = 512;
 constexpr int kSolveGroupThreads = 256;
-constexpr int kSolveTmemCols = 512;  // S_A, S_B at columns 0 / 128, Q~_A, Q~_B from column 256
-constexpr uint32_t kSolveQCol = 256;
+constexpr int kSolveTmemCols = 512;  // S_A[2] at columns 0 / 128, S_B[2] at 256 / 384
 constexpr int kSolveRows = 2 * kBlockM;  // query rows per CTA
 
 enum SweepMode : int { kModeMax = 0, kModeHist = 1, kModeHalley = 2, kModeFinal = 3 };
@@ -45,7 +44,7 @@ struct SolveSmem {
   static constexpr int q_off = 0;                                  // two Q tiles
   static constexpr int k_off = 2 * tile_bytes;
   static constexpr int bar_off = k_off + kSolveStages * tile_bytes;
-  static constexpr int n_bars = 2 + 2 * kSolveStages + 4;
+  static constexpr int n_bars = 2 + 2 * kSolveStages + 8;
   static constexpr int misc_off = bar_off + n_bars * 8;            // tmem base, abort flag, status
   static constexpr int xchg_off = misc_off + 64;                   // [2 sweep parities][2 groups][2 halves][8][128] floats
   static constexpr int bits_off = xchg_off + 2 * 2 * 2 * 8 * 128 * 4;  // [4][n_words] words
@@ -69,8 +68,8 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
   uint64_t* q_ready = bars + 1;
   uint64_t* k_full = bars + 2;
   uint64_t* k_empty = k_full + kSolveStages;
-  uint64_t* s_full = k_empty + kSolveStages;  // [2]: row tile A, B
-  uint64_t* s_free = s_full + 2;
+  uint64_t* s_full = k_empty + kSolveStages;  // [2 row tiles][2 buffers]
+  uint64_t* s_free = s_full + 4;
   uint32_t* tmem_holder = (uint32_t*)(smem + L::misc_off);
   volatile int* cta_abort = (volatile int*)(smem + L::misc_off + 4);
   int* start_status = (int*)(smem + L::misc_off + 8);
@@ -102,8 +101,8 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
     if (lane == 0) {
       ptx::mbar_init(q_full, 1);
       ptx::mbar_init(q_ready, kSolveRowThreads / 32);
-      for (int s = 0; s < kSolveStages; ++s) { ptx::mbar_init(k_full + s, 1); ptx::mbar_init(k_empty + s, 1); }
-      for (int s = 0; s < 2; ++s) { ptx::mbar_init(s_full + s, 1); ptx::mbar_init(s_free + s, kSolveGroupThreads / 32); }
+      for (int s = 0; s < kSolveStages; ++s) { ptx::mbar_init(k_full + s, 1); ptx::mbar_init(k_empty + s, b_on ? 2 : 1); }
+      for (int s = 0; s < 4; ++s) { ptx::mbar_init(s_full + s, 1); ptx::mbar_init(s_free + s, kSolveGroupThreads / 32); }
       ptx::fence_mbar_init();
     }
     __syncwarp();
@@ -143,42 +142,39 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
                            kt * kBlockN, kv_head);
       }
     }
-  } else if (warp == 17) {
-    // ---------------- MMA issuer ----------------
-    if (lane == 0) {
+  } else if (warp == 17 || warp == 18) {
+    // ---------------- MMA issuers: warp 17 row tile A, warp 18 row tile B ----------------
+    const int t = warp - 17;
+    if (lane == 0 && (t == 0 || b_on)) {
       constexpr uint32_t idesc = ptx::make_idesc(FMT, kBlockM, kBlockN, 0, 0);
       bool ok = ptx::mbar_wait(q_ready, 0);
       if (!ok) raise_abort(cta_abort, p.status, kStTimeoutMma);
-      int use_a = 0, use_b = 0;  // how often each S buffer has been filled
+      const uint32_t a0 = ptx::smem_u32(sQ + t * L::tile_bytes);
+      int use = 0;  // tiles of this row tile issued so far
       for (int i = 0; ok && i < total; ++i) {
         const int st = i % kSolveStages, kt = i % T_k;
         if (*cta_abort) break;
         if (!ptx::mbar_wait(k_full + st, (i / kSolveStages) & 1)) { raise_abort(cta_abort, p.status, kStTimeoutMma); break; }
+        if (t == 0 && kt >= T_a) {
+          // the diagonal key tile of B: nothing for A.  The stage is released by a commit, which
+          // arrives after A's earlier products, and only after the stage has been filled, so
+          // that this arrival cannot be counted for the previous use of the stage.
+          ptx::mma_commit(k_empty + st);
+          continue;
+        }
+        const int bf = use & 1;
+        if (!ptx::mbar_wait(s_free + t * 2 + bf, ((use >> 1) & 1) ^ 1)) { raise_abort(cta_abort, p.status, kStTimeoutMma); break; }
+        ptx::tc_fence_after_sync();
         const uint32_t b0 = ptx::smem_u32(sK + st * L::tile_bytes);
-        if (kt < T_a) {
-          if (!ptx::mbar_wait(s_free + 0, (use_a & 1) ^ 1)) { raise_abort(cta_abort, p.status, kStTimeoutMma); break; }
-          ptx::tc_fence_after_sync();
+        const uint32_t d = tmem_base + (t * 2 + bf) * kBlockN;
 #pragma unroll
-          for (int kk = 0; kk < KSTEPS; ++kk) {
-            const uint32_t off = (kk >> 2) * kPanelBytes + (kk & 3) * 32;
-            ptx::mma_ts(tmem_base, tmem_base + kSolveQCol + kk * 8, ptx::make_smem_desc(b0 + off, 16, 1024), idesc, kk > 0);
-          }
-          ptx::mma_commit(s_full + 0);
-          ++use_a;
+        for (int kk = 0; kk < KSTEPS; ++kk) {
+          const uint32_t off = (kk >> 2) * kPanelBytes + (kk & 3) * 32;
+          ptx::mma_ss(d, ptx::make_smem_desc(a0 + off, 16, 1024), ptx::make_smem_desc(b0 + off, 16, 1024), idesc, kk > 0);
         }
-        if (b_on) {
-          if (!ptx::mbar_wait(s_free + 1, (use_b & 1) ^ 1)) { raise_abort(cta_abort, p.status, kStTimeoutMma); break; }
-          ptx::tc_fence_after_sync();
-#pragma unroll
-          for (int kk = 0; kk < KSTEPS; ++kk) {
-            const uint32_t off = (kk >> 2) * kPanelBytes + (kk & 3) * 32;
-            ptx::mma_ts(tmem_base + kBlockN, tmem_base + kSolveQCol + D / 2 + kk * 8,
-                        ptx::make_smem_desc(b0 + off, 16, 1024), idesc, kk > 0);
-          }
-          ptx::mma_commit(s_full + 1);
-          ++use_b;
-        }
+        ptx::mma_commit(s_full + t * 2 + bf);
         ptx::mma_commit(k_empty + st);
+        ++use;
       }
     }
   } else {
@@ -193,30 +189,22 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
     const int T_g = qt + 1;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(wq * 32) << 16);
     bool dead = false;
-    // Q~ = rn(q * fp32(0.5/sqrt(D))) (rows >= len -> 0), from the TMA tile in shared
-    // memory into TMEM: the two threads of row r convert D/2 elements each (16-bit pairs, lane r)
+    // Q~ = rn(q * fp32(0.5/sqrt(D))) (rows >= len -> 0) in place in shared memory
     if (!ptx::mbar_wait_warp(q_full, 0)) { raise_abort(cta_abort, p.status, kStTimeoutEpilogue); dead = true; }
     if (!dead) {
-      const float sc = row_ok ? 0.5f * p.sm_scale : 0.f;
-      const uint8_t* qtile = sQ + grp * L::tile_bytes;
+      const float sc = 0.5f * p.sm_scale;
+      for (int v = threadIdx.x; v < 2 * L::tile_bytes / 16; v += kSolveRowThreads) {
+        uint4* ptr = reinterpret_cast<uint4*>(sQ) + v;
+        const int tile = (v * 16) / L::tile_bytes;
+        const int vrow = ((v * 16) % kPanelBytes) / 128;
+        uint4 val = *ptr;
+        T* e = reinterpret_cast<T*>(&val);
+        const bool keep = (m0 + tile * kBlockM + vrow) < len;
 #pragma unroll
-      for (int hh = 0; hh < D / 64; ++hh) {  // 32 elements -> 16 packed columns per store; D/2 elements per thread
-        const int h16 = half * (D / 64) + hh;
-        uint32_t pk[16];
-#pragma unroll
-        for (int cc = 0; cc < 4; ++cc) {
-          const int e0 = (h16 * 4 + cc) * 8;               // first element of the 16-byte chunk
-          const int pn = e0 >> 6, c = (e0 & 63) >> 3;      // panel, chunk inside the 128-byte row
-          const uint4 val = *reinterpret_cast<const uint4*>(qtile + pn * kPanelBytes + r * 128 + ((c ^ (r & 7)) << 4));
-          const T* e = reinterpret_cast<const T*>(&val);
-#pragma unroll
-          for (int j = 0; j < 4; ++j)
-            pk[cc * 4 + j] = pack2<T>(DT<T>::to_f(e[2 * j]) * sc, DT<T>::to_f(e[2 * j + 1]) * sc);
-        }
-        ptx::tmem_st16(lane_addr + kSolveQCol + grp * (D / 2) + h16 * 16, pk);
+        for (int j = 0; j < 8; ++j) e[j] = DT<T>::from_f(keep ? DT<T>::to_f(e[j]) * sc : 0.f);
+        *ptr = val;
       }
-      ptx::tmem_st_wait();
-      ptx::tc_fence_before_sync();
+      ptx::fence_proxy_async_smem();
     }
     ptx::mbar_arrive_warp(q_ready);
 
@@ -234,7 +222,8 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
       for (int c = 0; c < 8; ++c) cnt[c] = 0;
       for (int kt = 0; kt < T_g; ++kt, ++use) {
         if (dead || *cta_abort) { dead = true; continue; }
-        if (!ptx::mbar_wait_warp(s_full + grp, use & 1)) {
+        const int bf = use & 1;
+        if (!ptx::mbar_wait_warp(s_full + grp * 2 + bf, (use >> 1) & 1)) {
           raise_abort(cta_abort, p.status, kStTimeoutEpilogue);
           dead = true;
           continue;
@@ -249,7 +238,7 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
         for (int q32 = 0; q32 < 2; ++q32) {  // this thread's 64 keys, 32 at a time
           uint32_t raw[32];
           const int c0 = half * 64 + q32 * 32;
-          ptx::tmem_ld32(lane_addr + grp * kBlockN + c0, raw);
+          ptx::tmem_ld32(lane_addr + (grp * 2 + bf) * kBlockN + c0, raw);
           ptx::tmem_ld_wait();
           float* v = reinterpret_cast<float*>(raw);
           if (need_mask) {
@@ -298,7 +287,7 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
           }
         }
         ptx::tc_fence_before_sync();
-        ptx::mbar_arrive_warp(s_free + grp);
+        ptx::mbar_arrive_warp(s_free + grp * 2 + bf);
         if (packed != 0ull) {
 #pragma unroll
           for (int bb = 0; bb < 8; ++bb) cnt[bb] += (int)((packed >> (8 * bb)) & 0xffull);
