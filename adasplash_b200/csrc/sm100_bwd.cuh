@@ -379,9 +379,8 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
 // ---------------------------------------------------------------------------
 // dK, dV
 // ---------------------------------------------------------------------------
-constexpr int kDkvThreads = 672;    // 16 row warps (2 step groups x 2 column halves) + TMA warp + four MMA warps
+constexpr int kDkvThreads = 672;    // 16 row warps (4 lane quarters x 4 column slices) + TMA warp + four MMA warps
 constexpr int kDkvRowThreads = 512;
-constexpr int kDkvGroupThreads = 256;
 constexpr int kDkvStages = 3;       // (Q block, dO block) pairs in flight
 constexpr int kDkvTmemCols = 512;
 constexpr int kQBlock = 64;         // query rows per step (one block-mask row block)
@@ -398,8 +397,8 @@ struct DkvSmem {
   static constexpr int bar_off = do_off + kDkvStages * qblk_bytes;
   static constexpr int n_bars = 2 + 2 * kDkvStages + 2 + 2 + 2 + 1;
   static constexpr int misc_off = bar_off + n_bars * 8;
-  static constexpr int td_off = (misc_off + 64 + 15) & ~15;     // [2 groups][2 buffers][tau 64 | delta 64] floats, 16-byte aligned (read as float4)
-  static constexpr size_t bytes = 1024 + td_off + 2 * 2 * 128 * 4;
+  static constexpr int td_off = (misc_off + 64 + 15) & ~15;     // [stages][tau 64 | delta 64] floats, 16-byte aligned (read as float4)
+  static constexpr size_t bytes = 1024 + td_off + kDkvStages * 128 * 4;
 };
 
 // Walks (q head of the group, 64-row query block) pairs whose bit is set in rows
@@ -503,7 +502,7 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
       for (int s = 0; s < kDkvStages; ++s) { ptx::mbar_init(x_full + s, 1); ptx::mbar_init(x_empty + s, 2); }
       for (int s = 0; s < 2; ++s) {
         ptx::mbar_init(s_full + s, 2);
-        ptx::mbar_init(p_full + s, kDkvGroupThreads / 32);
+        ptx::mbar_init(p_full + s, kDkvRowThreads / 32);
         ptx::mbar_init(s_free + s, 2);
       }
       ptx::mbar_init(acc_full, 2);
@@ -523,6 +522,9 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
   const uint32_t tmem_base = *tmem_holder;
 
   if (warp == 16) {
+    // ---------------- producer: K / V tile, then per step the Q and dO blocks (TMA, lane 0) and
+    // the tau / delta of the block's 64 query rows (plain loads by the 32 lanes, fetched one
+    // step ahead into registers so that their latency is off the path) ----------------
     if (lane == 0) {
       ptx::prefetch_tmap(&tmK); ptx::prefetch_tmap(&tmV); ptx::prefetch_tmap(&tmQ64); ptx::prefetch_tmap(&tmDO64);
       ptx::mbar_arrive_expect_tx(kv_full, 2 * L::tile_bytes);
@@ -530,20 +532,45 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
         ptx::tma_load_3d(sK + pn * kPanelBytes, &tmK, kv_full, pn * 64, n0, bkv);
         ptx::tma_load_3d(sV + pn * kPanelBytes, &tmV, kv_full, pn * 64, n0, bkv);
       }
-      QBlockScan scan(p.bmask_t, b, p.Hq, G, kvh, nt, n_qblocks, p.rows_padded, p.n_words);
-      int g, m;
-      uint32_t flags;
-      for (int j = 0; scan.next(g, m, flags); ++j) {
-        const int st = j % kDkvStages;
-        const int qh = b * p.Hq + kvh * G + g;
-        if (*cta_abort) break;
-        if (!ptx::mbar_wait(x_empty + st, ((j / kDkvStages) & 1) ^ 1)) { raise_abort(cta_abort, p.status, kStTimeoutProducer); break; }
-        ptx::mbar_arrive_expect_tx(x_full + st, 2 * L::qblk_bytes);
+    }
+    // lane l carries tau / delta of query rows 2l and 2l+1 of a block (0 beyond the sequence)
+    auto fetch_td = [&](int g_, int m_, float (&r)[4]) {
+      const size_t base = (size_t)(b * p.Hq + kvh * G + g_) * p.N;
+      const int q0 = m_ * kQBlock + 2 * lane;
+      r[0] = (q0 < len) ? p.taus[base + q0] : 0.f;
+      r[1] = (q0 + 1 < len) ? p.taus[base + q0 + 1] : 0.f;
+      r[2] = (q0 < len) ? p.delta[base + q0] : 0.f;
+      r[3] = (q0 + 1 < len) ? p.delta[base + q0 + 1] : 0.f;
+    };
+    QBlockScan scan(p.bmask_t, b, p.Hq, G, kvh, nt, n_qblocks, p.rows_padded, p.n_words);
+    int g, m, g_next = 0, m_next = 0;
+    uint32_t flags;
+    bool have = scan.next(g, m, flags);
+    float td[4] = {0.f, 0.f, 0.f, 0.f};
+    if (have) fetch_td(g, m, td);
+    bool ok = true;
+    for (int j = 0; ok && have; ++j) {
+      const int st = j % kDkvStages;
+      const int qh = b * p.Hq + kvh * G + g;
+      const bool have_next = scan.next(g_next, m_next, flags);
+      if (*cta_abort) break;
+      if (lane == 0) ok = ptx::mbar_wait(x_empty + st, ((j / kDkvStages) & 1) ^ 1);
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) { if (lane == 0) raise_abort(cta_abort, p.status, kStTimeoutProducer); break; }
+      float* dst = s_td + st * 128;
+      *reinterpret_cast<float2*>(dst + 2 * lane) = make_float2(td[0], td[1]);
+      *reinterpret_cast<float2*>(dst + 64 + 2 * lane) = make_float2(td[2], td[3]);
+      __syncwarp();
+      if (lane == 0) {
+        ptx::mbar_arrive_expect_tx(x_full + st, 2 * L::qblk_bytes);  // releases the stores above to the waiters
         for (int pn = 0; pn < PANELS; ++pn) {
           ptx::tma_load_3d(sQ + st * L::qblk_bytes + pn * kQPanelBytes, &tmQ64, x_full + st, pn * 64, m * kQBlock, qh);
           ptx::tma_load_3d(sDO + st * L::qblk_bytes + pn * kQPanelBytes, &tmDO64, x_full + st, pn * 64, m * kQBlock, qh);
         }
       }
+      if (have_next) fetch_td(g_next, m_next, td);
+      g = g_next; m = m_next;
+      have = have_next;
     }
   } else if (warp == 17 || warp == 18) {
     // ---------------- S^T issuer (warp 17: K~ Q_j^T) and dP^T issuer (warp 18: V dO_j^T) ----------------
@@ -628,10 +655,12 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
     }
     if (!ok && lane == 0 && !*cta_abort) raise_abort(cta_abort, p.status, kStTimeoutMma);
   } else {
-    const int wq = warp & 3;             // TMEM lanes 32*wq .. 32*wq+31
-    const int half = (warp >> 2) & 1;    // query columns 32*half .. 32*half+31 of a block
-    const int group = warp >> 3;         // steps j with (j & 1) == group, buffer `group`
-    const int gtid = threadIdx.x & (kDkvGroupThreads - 1);
+    // All sixteen row warps work on every step: warp w owns TMEM lanes 32*(w & 3) .. +31 (key
+    // rows) and the sixteen query columns 16*(w >> 2) .. +15 of the block.  A short row phase
+    // matters more than two steps in flight: S^T_j -> row work -> dV/dK_j -> S^T_{j+2} is a
+    // dependent chain per buffer, and two groups of warps on different steps only slow each other.
+    const int wq = warp & 3;
+    const int slice = warp >> 2;
     const int r = wq * 32 + lane;        // key row inside the tile
     const int key = n0 + r;
     const bool key_ok = key < len;
@@ -656,39 +685,21 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
       ptx::fence_proxy_async_smem();
     }
     ptx::mbar_arrive_warp(k_ready);
-    // tau / delta of a block's 64 query rows are staged in shared memory one own-step
-    // ahead (double buffered per group, fetched from global memory two own-steps ahead
-    // into a register by the first 128 threads of the group), so that neither the
-    // global-memory latency nor the group barrier sits between the arrival of S^T and
-    // the row work.
-    auto fetch_td = [&](int g_, int m_) -> float {
-      if (gtid >= 128) return 0.f;
-      const int qrow = m_ * kQBlock + (gtid & 63);
-      const float* src = (gtid < 64) ? p.taus : p.delta;
-      return (qrow < len) ? src[(size_t)(b * p.Hq + kvh * G + g_) * p.N + qrow] : 0.f;
-    };
-    float* tdb = s_td + group * 256;  // [2][128] floats of this group
-    int n_active = 0;
-    {
-      QBlockScan s0(p.bmask_t, b, p.Hq, G, kvh, nt, n_qblocks, p.rows_padded, p.n_words);
-      int g0, m0_; uint32_t f0;
-      n_active = s0.next(g0, m0_, f0) ? 1 : 0;
-    }
+    // tau / delta of a step's 64 query rows arrive in shared memory with the step's Q / dO blocks
     QBlockScan scan(p.bmask_t, b, p.Hq, G, kvh, nt, n_qblocks, p.rows_padded, p.n_words);
-    QBlockScan scan_f(p.bmask_t, b, p.Hq, G, kvh, nt, n_qblocks, p.rows_padded, p.n_words);
-    int g = 0, m = 0, gf = 0, mf = 0;
-    uint32_t flags = 0, ff = 0;
-    bool have = true, have_f = true;
-    for (int i = 0; i <= group && have; ++i) have = scan.next(g, m, flags);        // own first step
-    for (int i = 0; i <= group + 2 && have_f; ++i) have_f = scan_f.next(gf, mf, ff);  // own second step
-    if (have && gtid < 128) tdb[gtid] = fetch_td(g, m);
-    ptx::bar_sync(1 + group, kDkvGroupThreads);
-    float td_reg = have_f ? fetch_td(gf, mf) : 0.f;
-    for (int it = 0; have; ++it) {
-      const int cur = it & 1;
-      const float* td = tdb + cur * 128;
+    int g = 0, m = 0, n_active = 0;
+    uint32_t flags = 0;
+    for (int j = 0; scan.next(g, m, flags); ++j) {
+      n_active = j + 1;
+      const int buf = j & 1, it = j >> 1, st = j % kDkvStages;
+      const float* td = s_td + st * 128;
       if (!(dead || *cta_abort)) {
-        if (!ptx::mbar_wait_warp(s_full + group, it & 1)) { raise_abort(cta_abort, p.status, kStTimeoutEpilogue); dead = true; }
+        // x_full completed before the products behind s_full were issued; waiting on it here
+        // as well makes the producer's tau / delta stores visible to this thread
+        if (!ptx::mbar_wait_warp(s_full + buf, it & 1) || !ptx::mbar_wait_warp(x_full + st, (j / kDkvStages) & 1)) {
+          raise_abort(cta_abort, p.status, kStTimeoutEpilogue);
+          dead = true;
+        }
       } else {
         dead = true;
       }
@@ -696,12 +707,11 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
         ptx::tc_fence_after_sync();
         const bool sub_on = (flags >> kh) & 1u;  // warp-uniform: the TMEM loads below are warp-collective
         const bool full = (n0 + kBlockN - 1 <= m * kQBlock) && ((m + 1) * kQBlock <= len);
-#pragma unroll
-        for (int sc16 = 0; sc16 < 2; ++sc16) {
-          const int c0 = half * 32 + sc16 * 16;     // first query column of this sub-chunk
+        {
+          const int c0 = slice * 16;                // first query column of this thread
           const int q0 = m * kQBlock + c0;
-          const uint32_t saddr = lane_addr + group * kQBlock + c0;
-          const uint32_t daddr = lane_addr + DP_COL0 + group * kQBlock + c0;
+          const uint32_t saddr = lane_addr + buf * kQBlock + c0;
+          const uint32_t daddr = lane_addr + DP_COL0 + buf * kQBlock + c0;
           uint32_t pk[8], dk[8];
           if (!sub_on) {
 #pragma unroll
@@ -751,22 +761,15 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
         }
         ptx::tmem_st_wait();
         ptx::tc_fence_before_sync();
-        ptx::mbar_arrive_warp(p_full + group);
+        ptx::mbar_arrive_warp(p_full + buf);
       }
-      // off the critical path: park the next own step's tau / delta, fetch the one after
-      if (gtid < 128) tdb[(cur ^ 1) * 128 + gtid] = td_reg;
-      ptx::bar_sync(1 + group, kDkvGroupThreads);
-      g = gf; m = mf; flags = ff;
-      have = have_f;
-      for (int i = 0; i < 2 && have_f; ++i) have_f = scan_f.next(gf, mf, ff);
-      td_reg = have_f ? fetch_td(gf, mf) : 0.f;
     }
     if (!dead && n_active > 0) {
       if (!ptx::mbar_wait_warp(acc_full, 0)) { raise_abort(cta_abort, p.status, kStTimeoutEpilogue); dead = true; }
     }
     if (!dead) {  // TMEM loads are warp-collective: only the global stores are per-row
       ptx::tc_fence_after_sync();
-      const int ch = group * 2 + half;  // the four threads of a key row share the D/32 column chunks
+      const int ch = slice;  // the four threads of a key row share the D/32 column chunks
       if (ch < D / 32) {
         uint32_t rk[32], rv[32];
         if (n_active > 0) {
