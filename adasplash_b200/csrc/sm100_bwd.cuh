@@ -4,13 +4,22 @@
 //   S = Q~ K^T, dP = dO V^T (operands in shared memory), u = max(S - tau, 0),
 //   dS = rn(u (dP - delta)) written over S in TMEM, dQ += dS K (A operand in TMEM,
 //   K read MN-major from the same shared-memory tile).  S is double buffered.
+//   Eight row warps (TMEM lane = score row, two threads per row), one TMA warp and
+//   three MMA-issuing warps, one per product.
 //
 // dK/dV kernel: one CTA per 128-key tile of one kv head, walking the q heads of
 //   the group and, per head, the 64-row query blocks whose bit is set in the
 //   transposed block mask.  S^T = K~ Q^T, dP^T = V dO^T (128 keys x 64 queries),
 //   P^T = rn(u^2) and dS^T = rn(u (dP - delta)) written over them in TMEM,
 //   dV += P^T dO, dK += dS^T Q.  K is the scaled + rounded operand here and Q is
-//   raw, as in the reference.  S^T / dP^T are double buffered.
+//   raw, as in the reference.  S^T / dP^T are double buffered.  Sixteen row warps
+//   (TMEM lane = key row, four threads per row), one producer warp (TMA for the
+//   blocks, plain loads for tau / delta) and four MMA-issuing warps, one per product.
+//
+// Why several issuing warps: the tensor pipe only runs what has been issued, and a
+// thread that waits on a barrier or commits leaves it idle for the length of that
+// round trip (~250-400 cycles per hop measured).  With one warp per product the gaps
+// of one are filled by the products of the others.
 #pragma once
 #include <type_traits>
 

@@ -216,10 +216,14 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
     const float fbins = (float)p.bins;
     int use = 0;  // tiles of this group consumed so far
     for (int s = 0; grp_on && s < nsweeps; ++s) {
-      const int mode = p.tau_given ? kModeFinal : (s == 0 ? kModeMax : (s == 1 ? kModeHist : (s == nsweeps - 1 ? kModeFinal : kModeHalley)));
+      const int mode_rt = p.tau_given ? kModeFinal : (s == 0 ? kModeMax : (s == 1 ? kModeHist : (s == nsweeps - 1 ? kModeFinal : kModeHalley)));
       float a0 = 0.f, a1 = 0.f, a2 = 0.f;
 #pragma unroll
       for (int c = 0; c < 8; ++c) cnt[c] = 0;
+      // the tile loop is instantiated once per sweep kind, so that the per-group code carries no
+      // mode tests and each sweep runs a compact loop
+      auto sweep_tiles = [&](auto mode_c) {
+      constexpr int mode = decltype(mode_c)::value;
       for (int kt = 0; kt < T_g; ++kt, ++use) {
         if (dead || *cta_abort) { dead = true; continue; }
         const int bf = use & 1;
@@ -257,26 +261,32 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
               m3_ = ptx::fmax3(m3_, v[c + 6], v[c + 7]);
             }
             mx = fmaxf(fmaxf(m0_, m1_), fmaxf(m2_, m3_));
+          } else if (mode == kModeHist) {
+            // the scores within 1 of the row maximum are a small part of a row: look at
+            // four at a time and only open a group that contains one
+#pragma unroll
+            for (int g4 = 0; g4 < 8; ++g4) {
+              const float cm = fmaxf(ptx::fmax3(v[g4 * 4], v[g4 * 4 + 1], v[g4 * 4 + 2]), v[g4 * 4 + 3]);
+              if (cm >= thr) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                  // bin = floor((z - tau0) * BINS) clamped to 7; one add of a byte pattern
+                  // bumps the cumulative counters N_0..N_bin (<= 64 hits per tile: no overflow)
+                  const float prj = (v[g4 * 4 + c] - tau0) * fbins;
+                  if (prj >= 0.f) {
+                    const int bsel = min(__float2int_rd(prj), 7);
+                    packed += 0x0101010101010101ull >> ((7 - bsel) * 8);
+                  }
+                }
+              }
+            }
           } else {
             // the scores above the threshold are a tiny part of a row: look at
             // four at a time and only open a group that contains one
 #pragma unroll
             for (int g4 = 0; g4 < 8; ++g4) {
               const float cm = fmaxf(ptx::fmax3(v[g4 * 4], v[g4 * 4 + 1], v[g4 * 4 + 2]), v[g4 * 4 + 3]);
-              if (mode == kModeHist) {
-                if (cm >= thr) {
-#pragma unroll
-                  for (int c = 0; c < 4; ++c) {
-                    // bin = floor((z - tau0) * BINS) clamped to 7; one add of a byte pattern
-                    // bumps the cumulative counters N_0..N_bin (<= 64 hits per tile: no overflow)
-                    const float prj = (v[g4 * 4 + c] - tau0) * fbins;
-                    if (prj >= 0.f) {
-                      const int bsel = min(__float2int_rd(prj), 7);
-                      packed += 0x0101010101010101ull >> ((7 - bsel) * 8);
-                    }
-                  }
-                }
-              } else if (cm > thr) {
+              if (cm > thr) {
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
                   const float d = v[g4 * 4 + c] - thr;
@@ -301,6 +311,14 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
           }
         }
       }
+      };
+      switch (mode_rt) {
+        case kModeMax: sweep_tiles(std::integral_constant<int, kModeMax>{}); break;
+        case kModeHist: sweep_tiles(std::integral_constant<int, kModeHist>{}); break;
+        case kModeHalley: sweep_tiles(std::integral_constant<int, kModeHalley>{}); break;
+        default: sweep_tiles(std::integral_constant<int, kModeFinal>{}); break;
+      }
+      const int mode = mode_rt;
       // end of sweep: the two threads of a row exchange their partial statistics
       // (double buffered by sweep parity; both compute the same new state)
       float* xb = xchg + ((s & 1) * 2 + grp) * (2 * 8 * 128);
