@@ -223,6 +223,10 @@ extern "C" int adasplash2_bwd(const void* q, const void* k, const void* v, const
     set_error("%s: null pointer", who);
     return ADS_ERR_BAD_ARG;
   }
+  if ((((uintptr_t)dout) | ((uintptr_t)out2)) & 15) {  // the delta kernel reads 16 bytes per lane
+    set_error("%s: dout and out2 must be 16-byte aligned", who);
+    return ADS_ERR_BAD_ARG;
+  }
   int path;
   if (int rc = resolve_path(s, who, &path)) return rc;
   cudaStream_t st = (cudaStream_t)stream;

@@ -458,26 +458,60 @@ __global__ void __launch_bounds__(kThreads) fwd_kernel(Params p) {
 // Backward
 // ---------------------------------------------------------------------------
 // delta[row] = sum_d out2[row,d] * dO[row,d] in fp32 (adasplash_v2.py:838-898)
+// HBM-bound: every lane moves 16 bytes per load, D*sizeof(T)/16 lanes share a row (D is a
+// power of two >= 16, so that count is a power of two), and a warp keeps kDeltaUnroll groups
+// of rows in flight.
+constexpr int kDeltaUnroll = 4;
+constexpr int kDeltaThreads = 256;
+
 template <typename T>
-__global__ void bwd_delta_kernel(const T* __restrict__ o2, const T* __restrict__ dout,
-                                 float* __restrict__ delta, const void* varlen, int is_i64,
-                                 int B, int H, int N, int D) {
-  long long row = (long long)blockIdx.x * (blockDim.x / 32) + threadIdx.x / 32;
-  long long total = (long long)B * H * N;
-  if (row >= total) return;
-  int lane = threadIdx.x & 31;
-  int b = (int)(row / ((long long)H * N));
-  int r = (int)(row % N);
-  int len = load_len(varlen, is_i64, b, N);
-  float s = 0.f;
-  if (r < len) {
-    const T* a = o2 + row * D;
-    const T* g = dout + row * D;
-    for (int d = lane; d < D; d += 32) s = fmaf(DT<T>::to_f(a[d]), DT<T>::to_f(g[d]), s);
+__host__ __device__ constexpr int delta_rows_per_warp(int D) {
+  const int vec = 16 / (int)sizeof(T);
+  const int lpr = D / vec < 32 ? D / vec : 32;   // lanes per row
+  return (32 / lpr) * kDeltaUnroll;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kDeltaThreads)
+bwd_delta_kernel(const T* __restrict__ o2, const T* __restrict__ dout, float* __restrict__ delta,
+                 const void* varlen, int is_i64, int B, int H, int N, int D) {
+  constexpr int VEC = 16 / (int)sizeof(T);
+  const int chunks = D / VEC;                     // 16-byte chunks per row
+  const int lpr = chunks < 32 ? chunks : 32;      // lanes per row
+  const int rows_pass = 32 / lpr;                 // rows a warp covers per pass
+  const int lane = threadIdx.x & 31;
+  const int sub = lane / lpr, li = lane % lpr;
+  const long long total = (long long)B * H * N;
+  const long long warp_id = (long long)blockIdx.x * (kDeltaThreads / 32) + threadIdx.x / 32;
+  const long long row0 = warp_id * (rows_pass * kDeltaUnroll);
+  float acc[kDeltaUnroll];
+#pragma unroll
+  for (int u = 0; u < kDeltaUnroll; ++u) {
+    acc[u] = 0.f;
+    const long long row = row0 + u * rows_pass + sub;
+    if (row < total) {
+      const int b = (int)(row / ((long long)H * N));
+      const int r = (int)(row % N);
+      if (r < load_len(varlen, is_i64, b, N)) {
+        const uint4* a = reinterpret_cast<const uint4*>(o2 + row * D);
+        const uint4* g = reinterpret_cast<const uint4*>(dout + row * D);
+        for (int c = li; c < chunks; c += lpr) {
+          const uint4 va = a[c], vg = g[c];
+          const T* ea = reinterpret_cast<const T*>(&va);
+          const T* eg = reinterpret_cast<const T*>(&vg);
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) acc[u] = fmaf(DT<T>::to_f(ea[e]), DT<T>::to_f(eg[e]), acc[u]);
+        }
+      }
+    }
   }
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-  if (lane == 0) delta[row] = s;
+  for (int u = 0; u < kDeltaUnroll; ++u) {
+    float s = acc[u];
+    for (int o = lpr >> 1; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    const long long row = row0 + u * rows_pass + sub;
+    if (li == 0 && row < total) delta[row] = s;
+  }
 }
 
 // out[n][w] bit j = in[32w+j][n/32] bit (n%32)   (adasplash_v2.py:901-940)

@@ -49,8 +49,9 @@ template <typename T> int launch_bwd(const Params& p, cudaStream_t st) {
   const int stages = p.bwd_stages ? p.bwd_stages : 0xF;
   if (stages & ADS_BWD_DELTA) {
     long long rows = (long long)p.B * p.Hq * p.N;
-    unsigned grid = (unsigned)((rows + 7) / 8);
-    bwd_delta_kernel<T><<<grid, 256, 0, st>>>((const T*)p.out2_in, (const T*)p.dout, p.delta,
+    const long long per_block = (long long)(kDeltaThreads / 32) * delta_rows_per_warp<T>(p.D);
+    unsigned grid = (unsigned)((rows + per_block - 1) / per_block);
+    bwd_delta_kernel<T><<<grid, kDeltaThreads, 0, st>>>((const T*)p.out2_in, (const T*)p.dout, p.delta,
                                               p.varlen, p.varlen_is_i64, p.B, p.Hq, p.N, p.D);
     if (int rc = check_launch("simt::bwd_delta")) return rc;
   }

@@ -101,8 +101,9 @@ int bwd_t(const simt::Params& p, void* ws, cudaStream_t st) {
   const int stages = p.bwd_stages ? p.bwd_stages : 0xF;
   if (stages & ADS_BWD_DELTA) {
     long long rows = (long long)p.B * p.Hq * p.N;
-    unsigned grid = (unsigned)((rows + 7) / 8);
-    simt::bwd_delta_kernel<T><<<grid, 256, 0, st>>>((const T*)p.out2_in, (const T*)p.dout, p.delta,
+    const long long per_block = (long long)(simt::kDeltaThreads / 32) * simt::delta_rows_per_warp<T>(p.D);
+    unsigned grid = (unsigned)((rows + per_block - 1) / per_block);
+    simt::bwd_delta_kernel<T><<<grid, simt::kDeltaThreads, 0, st>>>((const T*)p.out2_in, (const T*)p.dout, p.delta,
                                                     p.varlen, p.varlen_is_i64, p.B, p.Hq, p.N, D);
     if (int rc = check_launch("sm100::bwd_delta")) return rc;
   }

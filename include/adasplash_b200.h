@@ -119,7 +119,8 @@ int adasplash2_fwd(const void* q, const void* k, const void* v, const void* varl
 /* Backward.  Replaces `_bwd_preprocess`, `_bwd_q_kernel`, `transpose_bmask` and
  * `_bwd_kv_kernel` (adasplash/adasplash_v2.py:1441-1564).  `delta` (B,Hq,N fp32)
  * and `bmask_t` (same extent as bmask) are caller-owned scratch outputs.
- * dq (B,Hq,N,D), dk, dv (B,Hkv,N,D) in the input dtype; padded rows are zero. */
+ * dq (B,Hq,N,D), dk, dv (B,Hkv,N,D) in the input dtype; padded rows are zero.
+ * dout and out2 must be 16-byte aligned. */
 int adasplash2_bwd(const void* q, const void* k, const void* v, const void* dout,
                    const void* out2, const void* varlen, const float* taus,
                    const int32_t* bmask, int32_t* bmask_t, float* delta, void* dq, void* dk,
