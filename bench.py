@@ -116,17 +116,60 @@ def make_inputs(w, rank, pinned=True):
 
 
 class ClockSampler:
-    """Samples nvidia-smi clocks / throttle reasons while the timed region runs."""
+    """Samples SM clock, power and throttle reasons while the timed region runs.
+
+    Reads through NVML from a thread of this process every few milliseconds (a timed region of
+    a few steps lasts tens of milliseconds, too short for `nvidia-smi -lms`); if NVML cannot be
+    loaded it falls back to an `nvidia-smi` child.  Only reads: no setting is touched.
+    `sm_mhz` is the median clock of the samples taken under load, i.e. whose power draw is at
+    least half of the highest draw seen.
+    """
     FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
               "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    REASON_BITS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown",
+                   0x40: "hw_thermal_slowdown"}
 
     def __init__(self, gpu_index):
         self.gpu = gpu_index
         self.proc = None
         self.path = None
+        self.thread = None
+        self.samples = []       # (sm_mhz, watts)
+        self.reasons = set()
+        self.max_mhz = None
+        self._stop = False
+
+    def _nvml_loop(self, nv, handle):
+        while not self._stop:
+            try:
+                mhz = nv.nvmlDeviceGetClockInfo(handle, nv.NVML_CLOCK_SM)
+                watts = nv.nvmlDeviceGetPowerUsage(handle) / 1000.0
+                bits = nv.nvmlDeviceGetCurrentClocksThrottleReasons(handle)
+                self.samples.append((float(mhz), watts))
+                for bit, name in self.REASON_BITS.items():
+                    if bits & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.003)
 
     def start(self):
+        try:
+            import pynvml as nv
+            import threading
+            nv.nvmlInit()
+            try:
+                uuid = str(torch.cuda.get_device_properties(torch.cuda.current_device()).uuid)
+                handle = nv.nvmlDeviceGetHandleByUUID(("GPU-" + uuid) if not uuid.startswith("GPU-") else uuid)
+            except Exception:
+                handle = nv.nvmlDeviceGetHandleByIndex(self.gpu)
+            self.max_mhz = float(nv.nvmlDeviceGetMaxClockInfo(handle, nv.NVML_CLOCK_SM))
+            self.thread = threading.Thread(target=self._nvml_loop, args=(nv, handle), daemon=True)
+            self.thread.start()
+            return
+        except Exception:
+            self.thread = None
         try:
             fd, self.path = tempfile.mkstemp(suffix=".csv")
             os.close(fd)
@@ -139,39 +182,43 @@ class ClockSampler:
 
     def stop(self):
         out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
-        if self.proc is None:
+        if self.thread is not None:
+            self._stop = True
+            self.thread.join(timeout=2)
+        elif self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:
+                self.proc.kill()
+            try:
+                for line in open(self.path):
+                    f = [x.strip() for x in line.split(",")]
+                    if len(f) < 9:
+                        continue
+                    try:
+                        self.samples.append((float(f[1]), float(f[3])))
+                        self.max_mhz = float(f[2])
+                    except ValueError:
+                        continue
+                    for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown",
+                                          "sw_power_cap"), f[5:9]):
+                        if val.lower() == "active":
+                            self.reasons.add(name)
+                os.unlink(self.path)
+            except Exception:
+                pass
+        else:
             return out
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except Exception:
-            self.proc.kill()
-        sm, reasons, mx = [], set(), None
-        try:
-            for line in open(self.path):
-                f = [x.strip() for x in line.split(",")]
-                if len(f) < 9:
-                    continue
-                try:
-                    sm.append(float(f[1]))
-                    mx = float(f[2])
-                except ValueError:
-                    continue
-                for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown",
-                                      "sw_power_cap"), f[5:9]):
-                    if val.lower() == "active":
-                        reasons.add(name)
-            os.unlink(self.path)
-        except Exception:
-            pass
-        if sm:
-            sm.sort()
-            # median of the samples taken under load (upper half)
-            load = sm[len(sm) // 2:]
+        if self.samples:
+            top = max(w for _, w in self.samples)
+            load = sorted(m for m, w in self.samples if w >= 0.5 * top) or sorted(m for m, _ in self.samples)
             out["sm_mhz"] = load[len(load) // 2]
-            out["sm_max_mhz"] = mx
-            out["samples"] = len(sm)
-        out["reasons"] = sorted(reasons)
+            out["sm_max_mhz"] = self.max_mhz
+            out["samples"] = len(self.samples)
+            out["samples_under_load"] = len(load)
+            out["max_watts"] = round(top, 1)
+        out["reasons"] = sorted(self.reasons)
         return out
 
 
