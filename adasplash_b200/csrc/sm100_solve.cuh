@@ -1,17 +1,22 @@
 // Threshold solver + block-mask builder on the tensor cores.
 //
 // One CTA owns 256 query rows of one head -- two 128-row MMA tiles A and B --
-// and sweeps the causal key range (niter + 3) times without leaving the SM.
+// and runs the whole solve for them without leaving the SM.
 // Both row tiles use every K tile that TMA brings in, which halves the L2 -> SM
 // traffic per FLOP (a solver sweep has no other operand to amortise it: one
 // 32 KB K tile per 128x128x128 product made it L2-bandwidth-bound).
 //
-//   * the two Q tiles are scaled by fp32(0.5/sqrt(D)) and rounded to the input
-//     dtype in place in shared memory;
-//   * S_A = Q~_A K^T and S_B = Q~_B K^T each alternate between two 128-column fp32
-//     TMEM buffers, so that the product of a group's next tile overlaps its row
-//     work on the current one; each row tile has its own MMA-issuing warp, so that
-//     one tile waiting for its row group does not hold back the other;
+//   * the two Q tiles are scaled by fp32(0.5/sqrt(D)), rounded to the input dtype
+//     and parked in TMEM as A operands (columns 384..511), so the MMA reads only K
+//     from shared memory: with both operands there, a 128x128x16 product needs all
+//     of the 128 B/clk of shared-memory bandwidth and the TMA writes of K compete
+//     with it;
+//   * S_A = Q~_A K^T and S_B = Q~_B K^T rotate through three 128-column fp32 TMEM
+//     buffers (product n goes to buffer n % 3): one is read by row group A, one by
+//     row group B, one is being written, so the product of a group's next tile
+//     overlaps its row work.  One thread issues all products in order, so that it
+//     sees every phase of the three "buffer free" barriers; each row group has its
+//     own "product done" barriers per buffer for the same reason;
 //   * inside a group, TMEM lane = score row, and the two warps that own the same
 //     32 lanes split the 128 keys of a tile in halves (the row work of a tile is
 //     a chain of TMEM round trips; two threads per row halve it).  The two
@@ -21,6 +26,17 @@
 // Sweeps (adasplash_v2.py:151-681): row max -> tau0; BINS-bin histogram -> tau1;
 // niter Halley/bisection steps; a last sweep that records, per 64x64 sub-tile,
 // whether any score exceeds the tau entering the sweep, then one more step.
+//
+// Everything after the row maximum only looks at scores >= tau0 = max - 1: the
+// histogram covers [tau0, tau0 + 1], and tau never falls below tau0 (the largest
+// probability (z_max - tau)^2 is at most 1).  Those scores are a tiny part of a
+// row, so the kernel computes S twice, not (3 + niter) times: sweep 1 finds the
+// row maxima, sweep 2 appends every score >= tau0 (value and 64-key block index)
+// to a per-thread list in a shared-memory pool, and the histogram, the Halley
+// steps and the final bitmap + step run on the lists.  The counts and bitmap bits
+// are the same integers either way; the Halley sums add the same terms in list
+// order.  If the pool overflows (rows whose scores are nearly flat), the CTA
+// falls back to sweeping S for every step.
 #pragma once
 #include <type_traits>
 
@@ -30,13 +46,23 @@ namespace ads {
 namespace sm100 {
 
 constexpr int kSolveStages = 3;  // each K tile feeds two products, three tiles in flight cover the TMA latency
-constexpr int kSolveThreads = 608;   // 2 row groups x 8 warps + TMA warp + 2 MMA warps
+constexpr int kSolveThreads = 576;   // 2 row groups x 8 warps + TMA warp + MMA warp
 constexpr int kSolveRowThreads = 512;
 constexpr int kSolveGroupThreads = 256;
-constexpr int kSolveTmemCols = 512;  // S_A[2] at columns 0 / 128, S_B[2] at 256 / 384
+constexpr int kSolveTmemCols = 512;  // three S buffers at columns 0 / 128 / 256, Q~_A, Q~_B from column 384
+constexpr uint32_t kSolveQCol = 384;
+constexpr int kSolveBufs = 3;
 constexpr int kSolveRows = 2 * kBlockM;  // query rows per CTA
 
-enum SweepMode : int { kModeMax = 0, kModeHist = 1, kModeHalley = 2, kModeFinal = 3 };
+enum SweepMode : int { kModeMax = 0, kModeHist = 1, kModeHalley = 2, kModeFinal = 3, kModeCollect = 4 };
+
+// One entry of the candidate pool: a score >= tau0 of some row, the 64-key block it sits in,
+// and the previous entry of the same thread's list.
+struct Cand { float z; uint16_t kb; uint16_t next; };
+constexpr uint16_t kCandNil = 0xffff;
+// The pool lives in the shared memory of the two Q tiles, which is free once Q~ sits in TMEM:
+// 2 * 128 * D * 2 bytes = 8192 entries for D = 128 (16 per thread on average).  Each row warp
+// appends to its own sixteenth, so warps do not contend for a counter.
 
 template <int D>
 struct SolveSmem {
@@ -44,10 +70,12 @@ struct SolveSmem {
   static constexpr int q_off = 0;                                  // two Q tiles
   static constexpr int k_off = 2 * tile_bytes;
   static constexpr int bar_off = k_off + kSolveStages * tile_bytes;
-  static constexpr int n_bars = 2 + 2 * kSolveStages + 8;
+  static constexpr int n_bars = 2 + 2 * kSolveStages + 3 * kSolveBufs + 1;
   static constexpr int misc_off = bar_off + n_bars * 8;            // tmem base, abort flag, status
-  static constexpr int xchg_off = misc_off + 64;                   // [2 sweep parities][2 groups][2 halves][8][128] floats
-  static constexpr int bits_off = xchg_off + 2 * 2 * 2 * 8 * 128 * 4;  // [4][n_words] words
+  static constexpr int xchg_off = misc_off + 128;                  // [2 groups][2 halves][8][128] floats
+  static constexpr int bits_off = xchg_off + 2 * 2 * 8 * 128 * 4;  // [4][n_words] words
+  static constexpr int pool_entries = 2 * tile_bytes / 8;
+  static constexpr int warp_pool = pool_entries / 16;
   static size_t bytes(int n_words) { return 1024 + bits_off + 4 * (size_t)n_words * 4; }
 };
 
@@ -68,13 +96,17 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
   uint64_t* q_ready = bars + 1;
   uint64_t* k_full = bars + 2;
   uint64_t* k_empty = k_full + kSolveStages;
-  uint64_t* s_full = k_empty + kSolveStages;  // [2 row tiles][2 buffers]
-  uint64_t* s_free = s_full + 4;
+  uint64_t* s_full = k_empty + kSolveStages;  // [2 row tiles][3 S buffers]: each row group sees only its own products
+  uint64_t* s_free = s_full + 2 * kSolveBufs;  // [3 S buffers]
+  uint64_t* decide = s_free + kSolveBufs;              // the row warps have settled lists vs. full sweeps
   uint32_t* tmem_holder = (uint32_t*)(smem + L::misc_off);
   volatile int* cta_abort = (volatile int*)(smem + L::misc_off + 4);
   int* start_status = (int*)(smem + L::misc_off + 8);
+  int* pool_used = (int*)(smem + L::misc_off + 32);   // [16]: entries used in each row warp's region
+  volatile int* pool_ovf = (volatile int*)(smem + L::misc_off + 16);
   float* xchg = (float*)(smem + L::xchg_off);
   uint32_t* s_bits = (uint32_t*)(smem + L::bits_off);
+  Cand* pool = (Cand*)sQ;  // the Q tiles are dead once Q~ is in TMEM (before the first append)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int heads = p.B * p.Hq;
@@ -91,18 +123,31 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
   const int T_a = qtA + 1;                          // key tiles of A: 0 .. qtA
   const int T_k = b_on ? qtB + 1 : T_a;             // key tiles streamed per sweep
   const int nsweeps = p.tau_given ? 1 : p.niter + 3;
-  const int total = nsweeps * T_k;
+  // tiles streamed before the row warps decide (max sweep + collect sweep), and in all if
+  // the candidate pool overflows (max, collect, then histogram .. final over S)
+  const int total_first = p.tau_given ? T_k : 2 * T_k;
+  const int total_full = p.tau_given ? T_k : (nsweeps + 1) * T_k;
+  // Products are numbered in issue order (per K tile: A if it has one, then B); product n uses
+  // S buffer n % 3 for the (n / 3)-th time.
+  const int prods_per_sweep = b_on ? 2 * T_a + 1 : T_a;
+  auto product_index = [&](int sweep, int kt, int g) -> int {
+    return sweep * prods_per_sweep + (b_on ? (kt < T_a ? 2 * kt + g : 2 * T_a) : kt);
+  };
 
   if (threadIdx.x == 0) {
     *start_status = *(volatile int*)p.status;
     *cta_abort = 0;
+    for (int w = 0; w < 16; ++w) pool_used[w] = 0;
+    *pool_ovf = 0;
   }
   if (warp == 17) {
     if (lane == 0) {
       ptx::mbar_init(q_full, 1);
       ptx::mbar_init(q_ready, kSolveRowThreads / 32);
-      for (int s = 0; s < kSolveStages; ++s) { ptx::mbar_init(k_full + s, 1); ptx::mbar_init(k_empty + s, b_on ? 2 : 1); }
-      for (int s = 0; s < 4; ++s) { ptx::mbar_init(s_full + s, 1); ptx::mbar_init(s_free + s, kSolveGroupThreads / 32); }
+      ptx::mbar_init(decide, kSolveRowThreads / 32);
+      for (int s = 0; s < kSolveStages; ++s) { ptx::mbar_init(k_full + s, 1); ptx::mbar_init(k_empty + s, 1); }
+      for (int s = 0; s < 2 * kSolveBufs; ++s) ptx::mbar_init(s_full + s, 1);
+      for (int s = 0; s < kSolveBufs; ++s) ptx::mbar_init(s_free + s, kSolveGroupThreads / 32);
       ptx::fence_mbar_init();
     }
     __syncwarp();
@@ -129,7 +174,15 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
         for (int pn = 0; pn < PANELS; ++pn)
           ptx::tma_load_3d(sQ + t * L::tile_bytes + pn * kPanelBytes, &tmQ, q_full, pn * 64, m0 + t * kBlockM, bh);
       const int kv_head = b * p.Hkv + kvh;
-      for (int i = 0; i < total; ++i) {
+      int total = total_first;
+      for (int i = 0;; ++i) {
+        if (i == total) {
+          // the first sweeps are through: stream S again only if the row warps ask for it
+          if (total == total_full) break;
+          if (!ptx::mbar_wait(decide, 0)) { raise_abort(cta_abort, p.status, kStTimeoutProducer); break; }
+          if (!*pool_ovf) break;
+          total = total_full;
+        }
         const int st = i % kSolveStages, kt = i % T_k;
         if (*cta_abort) break;
         if (!ptx::mbar_wait(k_empty + st, ((i / kSolveStages) & 1) ^ 1)) {
@@ -142,39 +195,44 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
                            kt * kBlockN, kv_head);
       }
     }
-  } else if (warp == 17 || warp == 18) {
-    // ---------------- MMA issuers: warp 17 row tile A, warp 18 row tile B ----------------
-    const int t = warp - 17;
-    if (lane == 0 && (t == 0 || b_on)) {
+  } else if (warp == 17) {
+    // ---------------- MMA issuer ----------------
+    // One thread issues every product in order n = 0, 1, 2, ...: it is then the only waiter of
+    // the three "buffer free" barriers and sees each of their phases in turn (a thread that
+    // skips a phase of an mbarrier cannot tell the phase after it from the one before).
+    if (lane == 0) {
       constexpr uint32_t idesc = ptx::make_idesc(FMT, kBlockM, kBlockN, 0, 0);
       bool ok = ptx::mbar_wait(q_ready, 0);
       if (!ok) raise_abort(cta_abort, p.status, kStTimeoutMma);
-      const uint32_t a0 = ptx::smem_u32(sQ + t * L::tile_bytes);
-      int use = 0;  // tiles of this row tile issued so far
-      for (int i = 0; ok && i < total; ++i) {
+      int total = total_first;
+      int n = 0;  // products issued so far
+      for (int i = 0; ok; ++i) {
+        if (i == total) {
+          if (total == total_full) break;
+          if (!ptx::mbar_wait(decide, 0)) { raise_abort(cta_abort, p.status, kStTimeoutMma); break; }
+          if (!*pool_ovf) break;
+          total = total_full;
+        }
         const int st = i % kSolveStages, kt = i % T_k;
         if (*cta_abort) break;
         if (!ptx::mbar_wait(k_full + st, (i / kSolveStages) & 1)) { raise_abort(cta_abort, p.status, kStTimeoutMma); break; }
-        if (t == 0 && kt >= T_a) {
-          // the diagonal key tile of B: nothing for A.  The stage is released by a commit, which
-          // arrives after A's earlier products, and only after the stage has been filled, so
-          // that this arrival cannot be counted for the previous use of the stage.
-          ptx::mma_commit(k_empty + st);
-          continue;
-        }
-        const int bf = use & 1;
-        if (!ptx::mbar_wait(s_free + t * 2 + bf, ((use >> 1) & 1) ^ 1)) { raise_abort(cta_abort, p.status, kStTimeoutMma); break; }
-        ptx::tc_fence_after_sync();
         const uint32_t b0 = ptx::smem_u32(sK + st * L::tile_bytes);
-        const uint32_t d = tmem_base + (t * 2 + bf) * kBlockN;
+        for (int t = 0; t < 2 && ok; ++t) {
+          if (t == 0 ? kt >= T_a : !b_on) continue;  // the diagonal key tile of B has nothing for A
+          const int bf = n % kSolveBufs;
+          if (!ptx::mbar_wait(s_free + bf, ((n / kSolveBufs) & 1) ^ 1)) { raise_abort(cta_abort, p.status, kStTimeoutMma); ok = false; break; }
+          ptx::tc_fence_after_sync();
+          const uint32_t a_tmem = tmem_base + kSolveQCol + t * (D / 2);
+          const uint32_t d = tmem_base + bf * kBlockN;
 #pragma unroll
-        for (int kk = 0; kk < KSTEPS; ++kk) {
-          const uint32_t off = (kk >> 2) * kPanelBytes + (kk & 3) * 32;
-          ptx::mma_ss(d, ptx::make_smem_desc(a0 + off, 16, 1024), ptx::make_smem_desc(b0 + off, 16, 1024), idesc, kk > 0);
+          for (int kk = 0; kk < KSTEPS; ++kk) {
+            const uint32_t off = (kk >> 2) * kPanelBytes + (kk & 3) * 32;
+            ptx::mma_ts(d, a_tmem + kk * 8, ptx::make_smem_desc(b0 + off, 16, 1024), idesc, kk > 0);
+          }
+          ptx::mma_commit(s_full + t * kSolveBufs + bf);
+          ++n;
         }
-        ptx::mma_commit(s_full + t * 2 + bf);
         ptx::mma_commit(k_empty + st);
-        ++use;
       }
     }
   } else {
@@ -189,22 +247,30 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
     const int T_g = qt + 1;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(wq * 32) << 16);
     bool dead = false;
-    // Q~ = rn(q * fp32(0.5/sqrt(D))) (rows >= len -> 0) in place in shared memory
+    // Q~ = rn(q * fp32(0.5/sqrt(D))) (rows >= len -> 0), from the TMA tile in shared
+    // memory into TMEM: the two threads of row r convert D/2 elements each (16-bit pairs, lane r)
     if (!ptx::mbar_wait_warp(q_full, 0)) { raise_abort(cta_abort, p.status, kStTimeoutEpilogue); dead = true; }
     if (!dead) {
-      const float sc = 0.5f * p.sm_scale;
-      for (int v = threadIdx.x; v < 2 * L::tile_bytes / 16; v += kSolveRowThreads) {
-        uint4* ptr = reinterpret_cast<uint4*>(sQ) + v;
-        const int tile = (v * 16) / L::tile_bytes;
-        const int vrow = ((v * 16) % kPanelBytes) / 128;
-        uint4 val = *ptr;
-        T* e = reinterpret_cast<T*>(&val);
-        const bool keep = (m0 + tile * kBlockM + vrow) < len;
+      const float sc = row_ok ? 0.5f * p.sm_scale : 0.f;
+      const uint8_t* qtile = sQ + grp * L::tile_bytes;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) e[j] = DT<T>::from_f(keep ? DT<T>::to_f(e[j]) * sc : 0.f);
-        *ptr = val;
+      for (int hh = 0; hh < D / 64; ++hh) {  // 32 elements -> 16 packed columns per store; D/2 elements per thread
+        const int h16 = half * (D / 64) + hh;
+        uint32_t pk[16];
+#pragma unroll
+        for (int cc = 0; cc < 4; ++cc) {
+          const int e0 = (h16 * 4 + cc) * 8;               // first element of the 16-byte chunk
+          const int pn = e0 >> 6, c = (e0 & 63) >> 3;      // panel, chunk inside the 128-byte row
+          const uint4 val = *reinterpret_cast<const uint4*>(qtile + pn * kPanelBytes + r * 128 + ((c ^ (r & 7)) << 4));
+          const T* e = reinterpret_cast<const T*>(&val);
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            pk[cc * 4 + j] = pack2<T>(DT<T>::to_f(e[2 * j]) * sc, DT<T>::to_f(e[2 * j + 1]) * sc);
+        }
+        ptx::tmem_st16(lane_addr + kSolveQCol + grp * (D / 2) + h16 * 16, pk);
       }
-      ptx::fence_proxy_async_smem();
+      ptx::tmem_st_wait();
+      ptx::tc_fence_before_sync();
     }
     ptx::mbar_arrive_warp(q_ready);
 
@@ -214,20 +280,24 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
     hs.t = hs.lo = hs.hi = 0.f;
     if (p.tau_given) hs.t = row_ok ? p.taus[((size_t)bh) * p.N + row] : 0.f;
     const float fbins = (float)p.bins;
-    int use = 0;  // tiles of this group consumed so far
-    for (int s = 0; grp_on && s < nsweeps; ++s) {
-      const int mode_rt = p.tau_given ? kModeFinal : (s == 0 ? kModeMax : (s == 1 ? kModeHist : (s == nsweeps - 1 ? kModeFinal : kModeHalley)));
-      float a0 = 0.f, a1 = 0.f, a2 = 0.f;
-#pragma unroll
-      for (int c = 0; c < 8; ++c) cnt[c] = 0;
-      // the tile loop is instantiated once per sweep kind, so that the per-group code carries no
-      // mode tests and each sweep runs a compact loop
-      auto sweep_tiles = [&](auto mode_c) {
+    int sweep_no = 0;  // sweeps over S started so far (fixes the S buffer of every tile)
+    uint32_t full_par = 0;  // bit b: parity of this group's next product in S buffer b
+    float a0 = 0.f, a1 = 0.f, a2 = 0.f;
+    uint16_t head = kCandNil;  // this thread's list of scores >= tau0
+    bool ovf = false;
+
+    // One pass over the S tiles of this group's causal range.  Instantiated once per sweep
+    // kind, so that the per-group code carries no mode tests and each sweep runs a compact loop.
+    auto sweep_tiles = [&](auto mode_c) {
       constexpr int mode = decltype(mode_c)::value;
-      for (int kt = 0; kt < T_g; ++kt, ++use) {
+      const int sweep = sweep_no++;
+      for (int kt = 0; kt < T_g; ++kt) {
         if (dead || *cta_abort) { dead = true; continue; }
-        const int bf = use & 1;
-        if (!ptx::mbar_wait_warp(s_full + grp * 2 + bf, (use >> 1) & 1)) {
+        const int n = product_index(sweep, kt, grp);
+        const int bf = n % kSolveBufs;
+        const uint32_t par = (full_par >> bf) & 1u;
+        full_par ^= 1u << bf;
+        if (!ptx::mbar_wait_warp(s_full + grp * kSolveBufs + bf, par)) {
           raise_abort(cta_abort, p.status, kStTimeoutEpilogue);
           dead = true;
           continue;
@@ -237,14 +307,22 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
         const bool need_mask = (kt == qt) || (n0 + kBlockN > len);
         const float a2_mark = a2;  // support count before this thread's 64 keys of the tile
         unsigned long long packed = 0ull;  // eight 8-bit cumulative bin counters of this tile
-        const float thr = (mode == kModeHist) ? tau0 : hs.t;
-#pragma unroll 1
-        for (int q32 = 0; q32 < 2; ++q32) {  // this thread's 64 keys, 32 at a time
-          uint32_t raw[32];
+        // Collecting takes scores from a hair below tau0: a Halley step may land up to 1e-5
+        // below its bracket, and a sweep over S would then see those scores too.  The
+        // histogram over the list tests each score against tau0 itself.
+        const float thr = mode == kModeCollect ? tau0 - 2e-5f : (mode == kModeHist ? tau0 : hs.t);
+        // this thread's 64 keys go to registers at once, and the S buffer is handed back before
+        // any of the row work: the next product into this buffer does not wait for it
+        uint32_t raw64[64];
+        ptx::tmem_ld32(lane_addr + bf * kBlockN + half * 64, raw64);
+        ptx::tmem_ld32(lane_addr + bf * kBlockN + half * 64 + 32, raw64 + 32);
+        ptx::tmem_ld_wait();
+        ptx::tc_fence_before_sync();
+        ptx::mbar_arrive_warp(s_free + bf);
+#pragma unroll
+        for (int q32 = 0; q32 < 2; ++q32) {  // 32 at a time
           const int c0 = half * 64 + q32 * 32;
-          ptx::tmem_ld32(lane_addr + (grp * 2 + bf) * kBlockN + c0, raw);
-          ptx::tmem_ld_wait();
-          float* v = reinterpret_cast<float*>(raw);
+          float* v = reinterpret_cast<float*>(raw64 + q32 * 32);
           if (need_mask) {
             const int lim = min(row, len - 1) - (n0 + c0);  // columns c <= lim survive
 #pragma unroll
@@ -261,9 +339,33 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
               m3_ = ptx::fmax3(m3_, v[c + 6], v[c + 7]);
             }
             mx = fmaxf(fmaxf(m0_, m1_), fmaxf(m2_, m3_));
+          } else if (mode == kModeCollect) {
+            // the scores within 1 of the row maximum are a small part of a row: look at four
+            // at a time and only open a group that contains one; every such score goes to
+            // this thread's list
+#pragma unroll
+            for (int g4 = 0; g4 < 8; ++g4) {
+              const float cm = fmaxf(ptx::fmax3(v[g4 * 4], v[g4 * 4 + 1], v[g4 * 4 + 2]), v[g4 * 4 + 3]);
+              if (cm >= thr) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                  const float z = v[g4 * 4 + c];
+                  if (z >= thr) {
+                    const int idx = atomicAdd(pool_used + warp, 1);
+                    if (idx < L::warp_pool) {
+                      const int slot = warp * L::warp_pool + idx;
+                      Cand e;
+                      e.z = z; e.kb = (uint16_t)(2 * kt + half); e.next = head;
+                      pool[slot] = e;
+                      head = (uint16_t)slot;
+                    } else {
+                      ovf = true;
+                    }
+                  }
+                }
+              }
+            }
           } else if (mode == kModeHist) {
-            // the scores within 1 of the row maximum are a small part of a row: look at
-            // four at a time and only open a group that contains one
 #pragma unroll
             for (int g4 = 0; g4 < 8; ++g4) {
               const float cm = fmaxf(ptx::fmax3(v[g4 * 4], v[g4 * 4 + 1], v[g4 * 4 + 2]), v[g4 * 4 + 3]);
@@ -296,8 +398,6 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
             }
           }
         }
-        ptx::tc_fence_before_sync();
-        ptx::mbar_arrive_warp(s_free + grp * 2 + bf);
         if (packed != 0ull) {
 #pragma unroll
           for (int bb = 0; bb < 8; ++bb) cnt[bb] += (int)((packed >> (8 * bb)) & 0xffull);
@@ -311,17 +411,12 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
           }
         }
       }
-      };
-      switch (mode_rt) {
-        case kModeMax: sweep_tiles(std::integral_constant<int, kModeMax>{}); break;
-        case kModeHist: sweep_tiles(std::integral_constant<int, kModeHist>{}); break;
-        case kModeHalley: sweep_tiles(std::integral_constant<int, kModeHalley>{}); break;
-        default: sweep_tiles(std::integral_constant<int, kModeFinal>{}); break;
-      }
-      const int mode = mode_rt;
-      // end of sweep: the two threads of a row exchange their partial statistics
-      // (double buffered by sweep parity; both compute the same new state)
-      float* xb = xchg + ((s & 1) * 2 + grp) * (2 * 8 * 128);
+    };
+
+    // The two threads of a row exchange their partial statistics and both compute the same
+    // new state.
+    auto exchange = [&](int mode) {
+      float* xb = xchg + grp * (2 * 8 * 128);
       float* mine = xb + half * (8 * 128);
       const float* other = xb + (half ^ 1) * (8 * 128);
       if (mode == kModeMax) {
@@ -333,13 +428,17 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
         mine[r] = a0; mine[128 + r] = a1; mine[256 + r] = a2;
       }
       ptx::bar_sync(1 + grp, kSolveGroupThreads);
+      float o[8];
+#pragma unroll
+      for (int c = 0; c < 8; ++c) o[c] = other[c * 128 + r];
+      ptx::bar_sync(1 + grp, kSolveGroupThreads);  // everyone has read: the buffer may be rewritten
       if (mode == kModeMax) {
-        mx = fmaxf(mx, other[r]);
+        mx = fmaxf(mx, o[0]);
         tau0 = mx - 1.0f;
       } else if (mode == kModeHist) {
         int bins_cnt[8], cum[8];
 #pragma unroll
-        for (int c = 0; c < 8; ++c) cum[c] = cnt[c] + __float_as_int(other[c * 128 + r]);
+        for (int c = 0; c < 8; ++c) cum[c] = cnt[c] + __float_as_int(o[c]);
         for (int c = 0; c < p.bins; ++c) bins_cnt[c] = cum[c] - (c + 1 < p.bins ? cum[c + 1] : 0);
         const float t1 = hist_tau_alpha15<8>(bins_cnt, p.bins, tau0);
         hs.lo = t1;
@@ -347,10 +446,79 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
         hs.t = 0.5f * (hs.lo + hs.hi);
       } else if (!p.tau_given) {
         // fixed operand order so that both threads of a row get bit-identical sums
-        const float s0 = half == 0 ? a0 + other[r] : other[r] + a0;
-        const float s1 = half == 0 ? a1 + other[128 + r] : other[128 + r] + a1;
-        const float s2 = half == 0 ? a2 + other[256 + r] : other[256 + r] + a2;
+        const float s0 = half == 0 ? a0 + o[0] : o[0] + a0;
+        const float s1 = half == 0 ? a1 + o[1] : o[1] + a1;
+        const float s2 = half == 0 ? a2 + o[2] : o[2] + a2;
         halley_bisect_update(hs, s0, s1, s2);
+      }
+    };
+    auto reset_stats = [&]() {
+      a0 = a1 = a2 = 0.f;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) cnt[c] = 0;
+    };
+
+    if (p.tau_given) {
+      // bitmap for a given tau: one sweep over S
+      if (grp_on) {
+        reset_stats();
+        sweep_tiles(std::integral_constant<int, kModeFinal>{});
+      }
+    } else {
+      if (grp_on) {
+        reset_stats();
+        sweep_tiles(std::integral_constant<int, kModeMax>{});
+        exchange(kModeMax);
+        sweep_tiles(std::integral_constant<int, kModeCollect>{});
+      }
+      // lists or full sweeps: one decision for the CTA, which the producer and the MMA warps
+      // are waiting for
+      if (ovf) *pool_ovf = 1;
+      ptx::bar_sync(3, kSolveRowThreads);
+      const bool full_sweeps = *pool_ovf != 0;
+      ptx::mbar_arrive_warp(decide);
+      if (grp_on && !full_sweeps) {
+        // ---- histogram, Halley steps and the final step on this thread's list ----
+        reset_stats();
+        for (uint16_t e = head; e != kCandNil; e = pool[e].next) {
+          const float prj = (pool[e].z - tau0) * fbins;
+          if (prj >= 0.f) {
+            const int bsel = min(__float2int_rd(prj), 7);
+#pragma unroll
+            for (int bb = 0; bb < 8; ++bb) cnt[bb] += (bb <= bsel) ? 1 : 0;
+          }
+        }
+        exchange(kModeHist);
+        for (int it = 0; it <= p.niter; ++it) {
+          const bool last = it == p.niter;
+          reset_stats();
+          for (uint16_t e = head; e != kCandNil; e = pool[e].next) {
+            const Cand c = pool[e];
+            const float d = c.z - hs.t;
+            if (d > 0.f) {
+              a0 = fmaf(d, d, a0); a1 += d; a2 += 1.f;
+              // the final step also records the 64x64 sub-tiles that hold a score above the
+              // tau entering it (row block rb of this group, key block c.kb)
+              if (last && row_ok) atomicOr(&s_bits[(grp * 2 + rb) * p.n_words + (c.kb >> 5)], 1u << (c.kb & 31));
+            }
+          }
+          exchange(last ? kModeFinal : kModeHalley);
+        }
+      } else if (grp_on) {
+        // ---- the pool overflowed: every step sweeps S ----
+        for (int sw = 1; sw < nsweeps; ++sw) {
+          reset_stats();
+          if (sw == 1) {
+            sweep_tiles(std::integral_constant<int, kModeHist>{});
+            exchange(kModeHist);
+          } else if (sw == nsweeps - 1) {
+            sweep_tiles(std::integral_constant<int, kModeFinal>{});
+            exchange(kModeFinal);
+          } else {
+            sweep_tiles(std::integral_constant<int, kModeHalley>{});
+            exchange(kModeHalley);
+          }
+        }
       }
     }
     ptx::bar_sync(3, kSolveRowThreads);  // every atomicOr on s_bits is done
