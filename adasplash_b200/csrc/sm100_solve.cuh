@@ -36,7 +36,9 @@
 // steps and the final bitmap + step run on the lists.  The counts and bitmap bits
 // are the same integers either way; the Halley sums add the same terms in list
 // order.  If the pool overflows (rows whose scores are nearly flat), the CTA
-// falls back to sweeping S for every step.
+// falls back to sweeping S for every step.  (One sweep with a running maximum
+// does not work: the maximum of a row grows so slowly that three times as many
+// scores pass "within 1 of the maximum so far" as are within 1 of the final one.)
 #pragma once
 #include <type_traits>
 
@@ -60,23 +62,25 @@ enum SweepMode : int { kModeMax = 0, kModeHist = 1, kModeHalley = 2, kModeFinal 
 // and the previous entry of the same thread's list.
 struct Cand { float z; uint16_t kb; uint16_t next; };
 constexpr uint16_t kCandNil = 0xffff;
-// The pool lives in the shared memory of the two Q tiles, which is free once Q~ sits in TMEM:
-// 2 * 128 * D * 2 bytes = 8192 entries for D = 128 (16 per thread on average).  Each row warp
-// appends to its own sixteenth, so warps do not contend for a counter.
+// Shared memory: K stages, barriers, exchange buffers, bitmap staging, then the two Q tiles and
+// whatever is left of the budget.  The Q tiles are dead once Q~ sits in TMEM (before the first
+// append), so the candidate pool is their space plus that remainder (D = 128: ~110 KB, 14000
+// entries, 27 per thread on average).  Each row warp appends to its own sixteenth, so warps
+// do not contend for a counter.
+constexpr int kSolveSmemBudget = 225 * 1024;
 
 template <int D>
 struct SolveSmem {
   static constexpr int tile_bytes = (D / 64) * kPanelBytes;
-  static constexpr int q_off = 0;                                  // two Q tiles
-  static constexpr int k_off = 2 * tile_bytes;
+  static constexpr int k_off = 0;
   static constexpr int bar_off = k_off + kSolveStages * tile_bytes;
   static constexpr int n_bars = 2 + 2 * kSolveStages + 3 * kSolveBufs + 1;
-  static constexpr int misc_off = bar_off + n_bars * 8;            // tmem base, abort flag, status
+  static constexpr int misc_off = bar_off + n_bars * 8;            // tmem base, abort flag, status, pool counters
   static constexpr int xchg_off = misc_off + 128;                  // [2 groups][2 halves][8][128] floats
   static constexpr int bits_off = xchg_off + 2 * 2 * 8 * 128 * 4;  // [4][n_words] words
-  static constexpr int pool_entries = 2 * tile_bytes / 8;
-  static constexpr int warp_pool = pool_entries / 16;
-  static size_t bytes(int n_words) { return 1024 + bits_off + 4 * (size_t)n_words * 4; }
+  static __host__ __device__ int q_off(int n_words) { return (bits_off + 4 * n_words * 4 + 1023) & ~1023; }  // two Q tiles
+  static __host__ __device__ int pool_entries(int n_words) { return (kSolveSmemBudget - 1024 - q_off(n_words)) / 8; }
+  static size_t bytes(int) { return kSolveSmemBudget; }
 };
 
 template <typename T, int D>
@@ -89,7 +93,7 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
   constexpr int FMT = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  uint8_t* sQ = smem + L::q_off;
+  uint8_t* sQ = smem + L::q_off(p.n_words);
   uint8_t* sK = smem + L::k_off;
   uint64_t* bars = (uint64_t*)(smem + L::bar_off);
   uint64_t* q_full = bars + 0;
@@ -107,6 +111,7 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
   float* xchg = (float*)(smem + L::xchg_off);
   uint32_t* s_bits = (uint32_t*)(smem + L::bits_off);
   Cand* pool = (Cand*)sQ;  // the Q tiles are dead once Q~ is in TMEM (before the first append)
+  const int warp_pool = L::pool_entries(p.n_words) / 16;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int heads = p.B * p.Hq;
@@ -352,8 +357,8 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
                   const float z = v[g4 * 4 + c];
                   if (z >= thr) {
                     const int idx = atomicAdd(pool_used + warp, 1);
-                    if (idx < L::warp_pool) {
-                      const int slot = warp * L::warp_pool + idx;
+                    if (idx < warp_pool) {
+                      const int slot = warp * warp_pool + idx;
                       Cand e;
                       e.z = z; e.kb = (uint16_t)(2 * kt + half); e.next = head;
                       pool[slot] = e;
