@@ -6,17 +6,12 @@
 // traffic per FLOP (a solver sweep has no other operand to amortise it: one
 // 32 KB K tile per 128x128x128 product made it L2-bandwidth-bound).
 //
-//   * the two Q tiles are scaled by fp32(0.5/sqrt(D)), rounded to the input dtype
-//     and parked in TMEM as A operands (columns 384..511), so the MMA reads only K
-//     from shared memory: with both operands there, a 128x128x16 product needs all
-//     of the 128 B/clk of shared-memory bandwidth and the TMA writes of K compete
-//     with it;
-//   * S_A = Q~_A K^T and S_B = Q~_B K^T rotate through three 128-column fp32 TMEM
-//     buffers (product n goes to buffer n % 3): one is read by row group A, one by
-//     row group B, one is being written, so the product of a group's next tile
-//     overlaps its row work.  One thread issues all products in order, so that it
-//     sees every phase of the three "buffer free" barriers; each row group has its
-//     own "product done" barriers per buffer for the same reason;
+//   * the two Q tiles are scaled by fp32(0.5/sqrt(D)) and rounded to the input
+//     dtype in place in shared memory;
+//   * S_A = Q~_A K^T and S_B = Q~_B K^T each alternate between two 128-column fp32
+//     TMEM buffers, so that the product of a group's next tile overlaps its row
+//     work on the current one; each row tile has its own MMA-issuing warp, so that
+//     one tile waiting for its row group does not hold back the other;
 //   * inside a group, TMEM lane = score row, and the two warps that own the same
 //     32 lanes split the 128 keys of a tile in halves (the row work of a tile is
 //     a chain of TMEM round trips; two threads per row halve it).  The two
@@ -31,14 +26,16 @@
 // histogram covers [tau0, tau0 + 1], and tau never falls below tau0 (the largest
 // probability (z_max - tau)^2 is at most 1).  Those scores are a tiny part of a
 // row, so the kernel computes S twice, not (3 + niter) times: sweep 1 finds the
-// row maxima, sweep 2 appends every score >= tau0 (value and 64-key block index)
-// to a per-thread list in a shared-memory pool, and the histogram, the Halley
-// steps and the final bitmap + step run on the lists.  The counts and bitmap bits
-// are the same integers either way; the Halley sums add the same terms in list
-// order.  If the pool overflows (rows whose scores are nearly flat), the CTA
-// falls back to sweeping S for every step.  (One sweep with a running maximum
-// does not work: the maximum of a row grows so slowly that three times as many
-// scores pass "within 1 of the maximum so far" as are within 1 of the final one.)
+// row maxima; sweep 2 appends every score >= tau0 (value and 64-key block index)
+// to a per-thread list in a shared-memory pool; the histogram, the Halley steps
+// and the final bitmap + step run on the lists.  The counts and bitmap bits are
+// the same integers either way; the Halley sums add the same terms in list order.
+// If the pool fills up (rows whose scores are nearly flat), sweep 2 goes on as a
+// plain histogram sweep for the scores that find no room, and the CTA sweeps S
+// for the remaining steps as well -- what the solve cost without lists.
+// (One sweep with a running maximum does not work: the maximum of a row grows so
+// slowly that three times as many scores pass "within 1 of the maximum so far"
+// as are within 1 of the final one.)
 #pragma once
 #include <type_traits>
 
@@ -47,40 +44,34 @@
 namespace ads {
 namespace sm100 {
 
-constexpr int kSolveStages = 3;  // each K tile feeds two products, three tiles in flight cover the TMA latency
-constexpr int kSolveThreads = 576;   // 2 row groups x 8 warps + TMA warp + MMA warp
+constexpr int kSolveStages = 2;  // each K tile feeds two products (1024 pipe cycles); the shared memory a third stage would take holds the candidate pool
+constexpr int kSolveThreads = 608;   // 2 row groups x 8 warps + TMA warp + 2 MMA warps
 constexpr int kSolveRowThreads = 512;
 constexpr int kSolveGroupThreads = 256;
-constexpr int kSolveTmemCols = 512;  // three S buffers at columns 0 / 128 / 256, Q~_A, Q~_B from column 384
-constexpr uint32_t kSolveQCol = 384;
-constexpr int kSolveBufs = 3;
+constexpr int kSolveTmemCols = 512;  // S_A[2] at columns 0 / 128, S_B[2] at 256 / 384
 constexpr int kSolveRows = 2 * kBlockM;  // query rows per CTA
 
 enum SweepMode : int { kModeMax = 0, kModeHist = 1, kModeHalley = 2, kModeFinal = 3, kModeCollect = 4 };
 
 // One entry of the candidate pool: a score >= tau0 of some row, the 64-key block it sits in,
 // and the previous entry of the same thread's list.
-struct Cand { float z; uint16_t kb; uint16_t next; };
+struct __align__(8) Cand { float z; uint16_t kb; uint16_t next; };
+constexpr int kSolvePool = 9216;          // entries (72 KB): 18 per thread on average
+constexpr int kSolveWarpPool = kSolvePool / 16;  // each row warp appends to its own region: no contention between warps
 constexpr uint16_t kCandNil = 0xffff;
-// Shared memory: K stages, barriers, exchange buffers, bitmap staging, then the two Q tiles and
-// whatever is left of the budget.  The Q tiles are dead once Q~ sits in TMEM (before the first
-// append), so the candidate pool is their space plus that remainder (D = 128: ~110 KB, 14000
-// entries, 27 per thread on average).  Each row warp appends to its own sixteenth, so warps
-// do not contend for a counter.
-constexpr int kSolveSmemBudget = 225 * 1024;
 
 template <int D>
 struct SolveSmem {
   static constexpr int tile_bytes = (D / 64) * kPanelBytes;
-  static constexpr int k_off = 0;
+  static constexpr int q_off = 0;                                  // two Q tiles
+  static constexpr int k_off = 2 * tile_bytes;
   static constexpr int bar_off = k_off + kSolveStages * tile_bytes;
-  static constexpr int n_bars = 2 + 2 * kSolveStages + 3 * kSolveBufs + 1;
-  static constexpr int misc_off = bar_off + n_bars * 8;            // tmem base, abort flag, status, pool counters
+  static constexpr int n_bars = 2 + 2 * kSolveStages + 8 + 1;
+  static constexpr int misc_off = bar_off + n_bars * 8;            // tmem base, abort flag, status
   static constexpr int xchg_off = misc_off + 128;                  // [2 groups][2 halves][8][128] floats
   static constexpr int bits_off = xchg_off + 2 * 2 * 8 * 128 * 4;  // [4][n_words] words
-  static __host__ __device__ int q_off(int n_words) { return (bits_off + 4 * n_words * 4 + 1023) & ~1023; }  // two Q tiles
-  static __host__ __device__ int pool_entries(int n_words) { return (kSolveSmemBudget - 1024 - q_off(n_words)) / 8; }
-  static size_t bytes(int) { return kSolveSmemBudget; }
+  static __host__ __device__ int pool_off(int n_words) { return (bits_off + 4 * n_words * 4 + 15) & ~15; }
+  static size_t bytes(int n_words) { return 1024 + pool_off(n_words) + (size_t)kSolvePool * sizeof(Cand); }
 };
 
 template <typename T, int D>
@@ -93,16 +84,16 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
   constexpr int FMT = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  uint8_t* sQ = smem + L::q_off(p.n_words);
+  uint8_t* sQ = smem + L::q_off;
   uint8_t* sK = smem + L::k_off;
   uint64_t* bars = (uint64_t*)(smem + L::bar_off);
   uint64_t* q_full = bars + 0;
   uint64_t* q_ready = bars + 1;
   uint64_t* k_full = bars + 2;
   uint64_t* k_empty = k_full + kSolveStages;
-  uint64_t* s_full = k_empty + kSolveStages;  // [2 row tiles][3 S buffers]: each row group sees only its own products
-  uint64_t* s_free = s_full + 2 * kSolveBufs;  // [3 S buffers]
-  uint64_t* decide = s_free + kSolveBufs;              // the row warps have settled lists vs. full sweeps
+  uint64_t* s_full = k_empty + kSolveStages;  // [2 row tiles][2 buffers]
+  uint64_t* s_free = s_full + 4;
+  uint64_t* decide = s_free + 4;              // the row warps have settled lists vs. full sweeps
   uint32_t* tmem_holder = (uint32_t*)(smem + L::misc_off);
   volatile int* cta_abort = (volatile int*)(smem + L::misc_off + 4);
   int* start_status = (int*)(smem + L::misc_off + 8);
@@ -110,8 +101,7 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
   volatile int* pool_ovf = (volatile int*)(smem + L::misc_off + 16);
   float* xchg = (float*)(smem + L::xchg_off);
   uint32_t* s_bits = (uint32_t*)(smem + L::bits_off);
-  Cand* pool = (Cand*)sQ;  // the Q tiles are dead once Q~ is in TMEM (before the first append)
-  const int warp_pool = L::pool_entries(p.n_words) / 16;
+  Cand* pool = (Cand*)(smem + L::pool_off(p.n_words));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int heads = p.B * p.Hq;
@@ -131,13 +121,7 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
   // tiles streamed before the row warps decide (max sweep + collect sweep), and in all if
   // the candidate pool overflows (max, collect, then histogram .. final over S)
   const int total_first = p.tau_given ? T_k : 2 * T_k;
-  const int total_full = p.tau_given ? T_k : (nsweeps + 1) * T_k;
-  // Products are numbered in issue order (per K tile: A if it has one, then B); product n uses
-  // S buffer n % 3 for the (n / 3)-th time.
-  const int prods_per_sweep = b_on ? 2 * T_a + 1 : T_a;
-  auto product_index = [&](int sweep, int kt, int g) -> int {
-    return sweep * prods_per_sweep + (b_on ? (kt < T_a ? 2 * kt + g : 2 * T_a) : kt);
-  };
+  const int total_full = nsweeps * T_k;
 
   if (threadIdx.x == 0) {
     *start_status = *(volatile int*)p.status;
@@ -150,9 +134,8 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
       ptx::mbar_init(q_full, 1);
       ptx::mbar_init(q_ready, kSolveRowThreads / 32);
       ptx::mbar_init(decide, kSolveRowThreads / 32);
-      for (int s = 0; s < kSolveStages; ++s) { ptx::mbar_init(k_full + s, 1); ptx::mbar_init(k_empty + s, 1); }
-      for (int s = 0; s < 2 * kSolveBufs; ++s) ptx::mbar_init(s_full + s, 1);
-      for (int s = 0; s < kSolveBufs; ++s) ptx::mbar_init(s_free + s, kSolveGroupThreads / 32);
+      for (int s = 0; s < kSolveStages; ++s) { ptx::mbar_init(k_full + s, 1); ptx::mbar_init(k_empty + s, b_on ? 2 : 1); }
+      for (int s = 0; s < 4; ++s) { ptx::mbar_init(s_full + s, 1); ptx::mbar_init(s_free + s, kSolveGroupThreads / 32); }
       ptx::fence_mbar_init();
     }
     __syncwarp();
@@ -200,17 +183,16 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
                            kt * kBlockN, kv_head);
       }
     }
-  } else if (warp == 17) {
-    // ---------------- MMA issuer ----------------
-    // One thread issues every product in order n = 0, 1, 2, ...: it is then the only waiter of
-    // the three "buffer free" barriers and sees each of their phases in turn (a thread that
-    // skips a phase of an mbarrier cannot tell the phase after it from the one before).
-    if (lane == 0) {
+  } else if (warp == 17 || warp == 18) {
+    // ---------------- MMA issuers: warp 17 row tile A, warp 18 row tile B ----------------
+    const int t = warp - 17;
+    if (lane == 0 && (t == 0 || b_on)) {
       constexpr uint32_t idesc = ptx::make_idesc(FMT, kBlockM, kBlockN, 0, 0);
       bool ok = ptx::mbar_wait(q_ready, 0);
       if (!ok) raise_abort(cta_abort, p.status, kStTimeoutMma);
+      const uint32_t a0 = ptx::smem_u32(sQ + t * L::tile_bytes);
+      int use = 0;  // tiles of this row tile issued so far
       int total = total_first;
-      int n = 0;  // products issued so far
       for (int i = 0; ok; ++i) {
         if (i == total) {
           if (total == total_full) break;
@@ -221,23 +203,26 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
         const int st = i % kSolveStages, kt = i % T_k;
         if (*cta_abort) break;
         if (!ptx::mbar_wait(k_full + st, (i / kSolveStages) & 1)) { raise_abort(cta_abort, p.status, kStTimeoutMma); break; }
-        const uint32_t b0 = ptx::smem_u32(sK + st * L::tile_bytes);
-        for (int t = 0; t < 2 && ok; ++t) {
-          if (t == 0 ? kt >= T_a : !b_on) continue;  // the diagonal key tile of B has nothing for A
-          const int bf = n % kSolveBufs;
-          if (!ptx::mbar_wait(s_free + bf, ((n / kSolveBufs) & 1) ^ 1)) { raise_abort(cta_abort, p.status, kStTimeoutMma); ok = false; break; }
-          ptx::tc_fence_after_sync();
-          const uint32_t a_tmem = tmem_base + kSolveQCol + t * (D / 2);
-          const uint32_t d = tmem_base + bf * kBlockN;
-#pragma unroll
-          for (int kk = 0; kk < KSTEPS; ++kk) {
-            const uint32_t off = (kk >> 2) * kPanelBytes + (kk & 3) * 32;
-            ptx::mma_ts(d, a_tmem + kk * 8, ptx::make_smem_desc(b0 + off, 16, 1024), idesc, kk > 0);
-          }
-          ptx::mma_commit(s_full + t * kSolveBufs + bf);
-          ++n;
+        if (t == 0 && kt >= T_a) {
+          // the diagonal key tile of B: nothing for A.  The stage is released by a commit, which
+          // arrives after A's earlier products, and only after the stage has been filled, so
+          // that this arrival cannot be counted for the previous use of the stage.
+          ptx::mma_commit(k_empty + st);
+          continue;
         }
+        const int bf = use & 1;
+        if (!ptx::mbar_wait(s_free + t * 2 + bf, ((use >> 1) & 1) ^ 1)) { raise_abort(cta_abort, p.status, kStTimeoutMma); break; }
+        ptx::tc_fence_after_sync();
+        const uint32_t b0 = ptx::smem_u32(sK + st * L::tile_bytes);
+        const uint32_t d = tmem_base + (t * 2 + bf) * kBlockN;
+#pragma unroll
+        for (int kk = 0; kk < KSTEPS; ++kk) {
+          const uint32_t off = (kk >> 2) * kPanelBytes + (kk & 3) * 32;
+          ptx::mma_ss(d, ptx::make_smem_desc(a0 + off, 16, 1024), ptx::make_smem_desc(b0 + off, 16, 1024), idesc, kk > 0);
+        }
+        ptx::mma_commit(s_full + t * 2 + bf);
         ptx::mma_commit(k_empty + st);
+        ++use;
       }
     }
   } else {
@@ -252,30 +237,22 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
     const int T_g = qt + 1;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(wq * 32) << 16);
     bool dead = false;
-    // Q~ = rn(q * fp32(0.5/sqrt(D))) (rows >= len -> 0), from the TMA tile in shared
-    // memory into TMEM: the two threads of row r convert D/2 elements each (16-bit pairs, lane r)
+    // Q~ = rn(q * fp32(0.5/sqrt(D))) (rows >= len -> 0) in place in shared memory
     if (!ptx::mbar_wait_warp(q_full, 0)) { raise_abort(cta_abort, p.status, kStTimeoutEpilogue); dead = true; }
     if (!dead) {
-      const float sc = row_ok ? 0.5f * p.sm_scale : 0.f;
-      const uint8_t* qtile = sQ + grp * L::tile_bytes;
+      const float sc = 0.5f * p.sm_scale;
+      for (int v = threadIdx.x; v < 2 * L::tile_bytes / 16; v += kSolveRowThreads) {
+        uint4* ptr = reinterpret_cast<uint4*>(sQ) + v;
+        const int tile = (v * 16) / L::tile_bytes;
+        const int vrow = ((v * 16) % kPanelBytes) / 128;
+        uint4 val = *ptr;
+        T* e = reinterpret_cast<T*>(&val);
+        const bool keep = (m0 + tile * kBlockM + vrow) < len;
 #pragma unroll
-      for (int hh = 0; hh < D / 64; ++hh) {  // 32 elements -> 16 packed columns per store; D/2 elements per thread
-        const int h16 = half * (D / 64) + hh;
-        uint32_t pk[16];
-#pragma unroll
-        for (int cc = 0; cc < 4; ++cc) {
-          const int e0 = (h16 * 4 + cc) * 8;               // first element of the 16-byte chunk
-          const int pn = e0 >> 6, c = (e0 & 63) >> 3;      // panel, chunk inside the 128-byte row
-          const uint4 val = *reinterpret_cast<const uint4*>(qtile + pn * kPanelBytes + r * 128 + ((c ^ (r & 7)) << 4));
-          const T* e = reinterpret_cast<const T*>(&val);
-#pragma unroll
-          for (int j = 0; j < 4; ++j)
-            pk[cc * 4 + j] = pack2<T>(DT<T>::to_f(e[2 * j]) * sc, DT<T>::to_f(e[2 * j + 1]) * sc);
-        }
-        ptx::tmem_st16(lane_addr + kSolveQCol + grp * (D / 2) + h16 * 16, pk);
+        for (int j = 0; j < 8; ++j) e[j] = DT<T>::from_f(keep ? DT<T>::to_f(e[j]) * sc : 0.f);
+        *ptr = val;
       }
-      ptx::tmem_st_wait();
-      ptx::tc_fence_before_sync();
+      ptx::fence_proxy_async_smem();
     }
     ptx::mbar_arrive_warp(q_ready);
 
@@ -285,24 +262,18 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
     hs.t = hs.lo = hs.hi = 0.f;
     if (p.tau_given) hs.t = row_ok ? p.taus[((size_t)bh) * p.N + row] : 0.f;
     const float fbins = (float)p.bins;
-    int sweep_no = 0;  // sweeps over S started so far (fixes the S buffer of every tile)
-    uint32_t full_par = 0;  // bit b: parity of this group's next product in S buffer b
+    int use = 0;  // tiles of this group consumed so far
     float a0 = 0.f, a1 = 0.f, a2 = 0.f;
     uint16_t head = kCandNil;  // this thread's list of scores >= tau0
-    bool ovf = false;
 
     // One pass over the S tiles of this group's causal range.  Instantiated once per sweep
     // kind, so that the per-group code carries no mode tests and each sweep runs a compact loop.
     auto sweep_tiles = [&](auto mode_c) {
       constexpr int mode = decltype(mode_c)::value;
-      const int sweep = sweep_no++;
-      for (int kt = 0; kt < T_g; ++kt) {
+      for (int kt = 0; kt < T_g; ++kt, ++use) {
         if (dead || *cta_abort) { dead = true; continue; }
-        const int n = product_index(sweep, kt, grp);
-        const int bf = n % kSolveBufs;
-        const uint32_t par = (full_par >> bf) & 1u;
-        full_par ^= 1u << bf;
-        if (!ptx::mbar_wait_warp(s_full + grp * kSolveBufs + bf, par)) {
+        const int bf = use & 1;
+        if (!ptx::mbar_wait_warp(s_full + grp * 2 + bf, (use >> 1) & 1)) {
           raise_abort(cta_abort, p.status, kStTimeoutEpilogue);
           dead = true;
           continue;
@@ -311,23 +282,21 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
         const int n0 = kt * kBlockN;
         const bool need_mask = (kt == qt) || (n0 + kBlockN > len);
         const float a2_mark = a2;  // support count before this thread's 64 keys of the tile
+        // rows beyond the sequence have all-zero scores (every key would be a candidate) and
+        // need no tau; once any warp's share of the pool is full the lists are useless
+        const bool collecting = mode == kModeCollect && row_ok && !*pool_ovf;
         unsigned long long packed = 0ull;  // eight 8-bit cumulative bin counters of this tile
         // Collecting takes scores from a hair below tau0: a Halley step may land up to 1e-5
         // below its bracket, and a sweep over S would then see those scores too.  The
         // histogram over the list tests each score against tau0 itself.
-        const float thr = mode == kModeCollect ? tau0 - 2e-5f : (mode == kModeHist ? tau0 : hs.t);
-        // this thread's 64 keys go to registers at once, and the S buffer is handed back before
-        // any of the row work: the next product into this buffer does not wait for it
-        uint32_t raw64[64];
-        ptx::tmem_ld32(lane_addr + bf * kBlockN + half * 64, raw64);
-        ptx::tmem_ld32(lane_addr + bf * kBlockN + half * 64 + 32, raw64 + 32);
-        ptx::tmem_ld_wait();
-        ptx::tc_fence_before_sync();
-        ptx::mbar_arrive_warp(s_free + bf);
-#pragma unroll
-        for (int q32 = 0; q32 < 2; ++q32) {  // 32 at a time
+        const float thr = mode == kModeCollect ? tau0 - 2e-5f : hs.t;
+#pragma unroll 1
+        for (int q32 = 0; q32 < 2; ++q32) {  // this thread's 64 keys, 32 at a time
+          uint32_t raw[32];
           const int c0 = half * 64 + q32 * 32;
-          float* v = reinterpret_cast<float*>(raw64 + q32 * 32);
+          ptx::tmem_ld32(lane_addr + (grp * 2 + bf) * kBlockN + c0, raw);
+          ptx::tmem_ld_wait();
+          float* v = reinterpret_cast<float*>(raw);
           if (need_mask) {
             const int lim = min(row, len - 1) - (n0 + c0);  // columns c <= lim survive
 #pragma unroll
@@ -345,9 +314,10 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
             }
             mx = fmaxf(fmaxf(m0_, m1_), fmaxf(m2_, m3_));
           } else if (mode == kModeCollect) {
-            // the scores within 1 of the row maximum are a small part of a row: look at four
-            // at a time and only open a group that contains one; every such score goes to
-            // this thread's list
+            // The histogram sweep: every score within 1 of the row maximum goes to this
+            // thread's list while the pool has room (and is binned from there after the
+            // sweep), else straight into the histogram.  Those scores are a small part of a
+            // row: look at four at a time and only open a group that contains one.
 #pragma unroll
             for (int g4 = 0; g4 < 8; ++g4) {
               const float cm = fmaxf(ptx::fmax3(v[g4 * 4], v[g4 * 4 + 1], v[g4 * 4 + 2]), v[g4 * 4 + 3]);
@@ -356,33 +326,30 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
                 for (int c = 0; c < 4; ++c) {
                   const float z = v[g4 * 4 + c];
                   if (z >= thr) {
-                    const int idx = atomicAdd(pool_used + warp, 1);
-                    if (idx < warp_pool) {
-                      const int slot = warp * warp_pool + idx;
-                      Cand e;
-                      e.z = z; e.kb = (uint16_t)(2 * kt + half); e.next = head;
-                      pool[slot] = e;
-                      head = (uint16_t)slot;
-                    } else {
-                      ovf = true;
+                    // to the list while there is room, else straight into the histogram
+                    bool listed = false;
+                    if (collecting) {
+                      const int idx = atomicAdd(pool_used + warp, 1);
+                      if (idx < kSolveWarpPool) {
+                        const int slot = warp * kSolveWarpPool + idx;
+                        Cand e;
+                        e.z = z; e.kb = (uint16_t)(2 * kt + half); e.next = head;
+                        pool[slot] = e;
+                        head = (uint16_t)slot;
+                        listed = true;
+                      } else {
+                        *pool_ovf = 1;
+                      }
                     }
-                  }
-                }
-              }
-            }
-          } else if (mode == kModeHist) {
-#pragma unroll
-            for (int g4 = 0; g4 < 8; ++g4) {
-              const float cm = fmaxf(ptx::fmax3(v[g4 * 4], v[g4 * 4 + 1], v[g4 * 4 + 2]), v[g4 * 4 + 3]);
-              if (cm >= thr) {
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                  // bin = floor((z - tau0) * BINS) clamped to 7; one add of a byte pattern
-                  // bumps the cumulative counters N_0..N_bin (<= 64 hits per tile: no overflow)
-                  const float prj = (v[g4 * 4 + c] - tau0) * fbins;
-                  if (prj >= 0.f) {
-                    const int bsel = min(__float2int_rd(prj), 7);
-                    packed += 0x0101010101010101ull >> ((7 - bsel) * 8);
+                    if (!listed) {
+                      // bin = floor((z - tau0) * BINS) clamped to 7; one add of a byte pattern
+                      // bumps the cumulative counters N_0..N_bin (<= 64 hits per tile: no overflow)
+                      const float prj = (z - tau0) * fbins;
+                      if (prj >= 0.f) {
+                        const int bsel = min(__float2int_rd(prj), 7);
+                        packed += 0x0101010101010101ull >> ((7 - bsel) * 8);
+                      }
+                    }
                   }
                 }
               }
@@ -403,6 +370,8 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
             }
           }
         }
+        ptx::tc_fence_before_sync();
+        ptx::mbar_arrive_warp(s_free + grp * 2 + bf);
         if (packed != 0ull) {
 #pragma unroll
           for (int bb = 0; bb < 8; ++bb) cnt[bb] += (int)((packed >> (8 * bb)) & 0xffull);
@@ -475,29 +444,30 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
         sweep_tiles(std::integral_constant<int, kModeMax>{});
         exchange(kModeMax);
         sweep_tiles(std::integral_constant<int, kModeCollect>{});
-      }
-      // lists or full sweeps: one decision for the CTA, which the producer and the MMA warps
-      // are waiting for
-      if (ovf) *pool_ovf = 1;
-      ptx::bar_sync(3, kSolveRowThreads);
-      const bool full_sweeps = *pool_ovf != 0;
-      ptx::mbar_arrive_warp(decide);
-      if (grp_on && !full_sweeps) {
-        // ---- histogram, Halley steps and the final step on this thread's list ----
-        reset_stats();
-        for (uint16_t e = head; e != kCandNil; e = pool[e].next) {
-          const float prj = (pool[e].z - tau0) * fbins;
+        // the listed scores join the histogram
+        for (uint16_t e = head; e != kCandNil;) {
+          const Cand c = pool[e];
+          const float prj = (c.z - tau0) * fbins;
           if (prj >= 0.f) {
             const int bsel = min(__float2int_rd(prj), 7);
 #pragma unroll
             for (int bb = 0; bb < 8; ++bb) cnt[bb] += (bb <= bsel) ? 1 : 0;
           }
+          e = c.next;
         }
         exchange(kModeHist);
+      }
+      // lists or full sweeps: one decision for the CTA, which the producer and the MMA warps
+      // are waiting for
+      ptx::bar_sync(3, kSolveRowThreads);
+      const bool full_sweeps = *pool_ovf != 0;
+      ptx::mbar_arrive_warp(decide);
+      if (grp_on && !full_sweeps) {
+        // ---- Halley steps and the final step on this thread's list ----
         for (int it = 0; it <= p.niter; ++it) {
           const bool last = it == p.niter;
           reset_stats();
-          for (uint16_t e = head; e != kCandNil; e = pool[e].next) {
+          for (uint16_t e = head; e != kCandNil;) {
             const Cand c = pool[e];
             const float d = c.z - hs.t;
             if (d > 0.f) {
@@ -506,17 +476,15 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
               // tau entering it (row block rb of this group, key block c.kb)
               if (last && row_ok) atomicOr(&s_bits[(grp * 2 + rb) * p.n_words + (c.kb >> 5)], 1u << (c.kb & 31));
             }
+            e = c.next;
           }
           exchange(last ? kModeFinal : kModeHalley);
         }
       } else if (grp_on) {
-        // ---- the pool overflowed: every step sweeps S ----
-        for (int sw = 1; sw < nsweeps; ++sw) {
+        // ---- the pool overflowed: every remaining step sweeps S ----
+        for (int sw = 2; sw < nsweeps; ++sw) {
           reset_stats();
-          if (sw == 1) {
-            sweep_tiles(std::integral_constant<int, kModeHist>{});
-            exchange(kModeHist);
-          } else if (sw == nsweeps - 1) {
+          if (sw == nsweeps - 1) {
             sweep_tiles(std::integral_constant<int, kModeFinal>{});
             exchange(kModeFinal);
           } else {
