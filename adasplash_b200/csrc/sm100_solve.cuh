@@ -6,12 +6,17 @@
 // traffic per FLOP (a solver sweep has no other operand to amortise it: one
 // 32 KB K tile per 128x128x128 product made it L2-bandwidth-bound).
 //
-//   * the two Q tiles are scaled by fp32(0.5/sqrt(D)) and rounded to the input
-//     dtype in place in shared memory;
-//   * S_A = Q~_A K^T and S_B = Q~_B K^T each alternate between two 128-column fp32
-//     TMEM buffers, so that the product of a group's next tile overlaps its row
-//     work on the current one; each row tile has its own MMA-issuing warp, so that
-//     one tile waiting for its row group does not hold back the other;
+//   * the two Q tiles are scaled by fp32(0.5/sqrt(D)), rounded to the input dtype
+//     and parked in TMEM as A operands (columns 384..511), so the MMA reads only K
+//     from shared memory: with both operands there, a 128x128x16 product needs all
+//     of the 128 B/clk of shared-memory bandwidth and the TMA writes of K compete
+//     with it;
+//   * S_A = Q~_A K^T and S_B = Q~_B K^T rotate through three 128-column fp32 TMEM
+//     buffers (product n goes to buffer n % 3): one is read by row group A, one by
+//     row group B, one is being written, so the product of a group's next tile
+//     overlaps its row work.  One thread issues all products in order, so that it
+//     sees every phase of the three "buffer free" barriers; each row group has its
+//     own "product done" barriers per buffer for the same reason;
 //   * inside a group, TMEM lane = score row, and the two warps that own the same
 //     32 lanes split the 128 keys of a tile in halves (the row work of a tile is
 //     a chain of TMEM round trips; two threads per row halve it).  The two
@@ -44,34 +49,41 @@
 namespace ads {
 namespace sm100 {
 
-constexpr int kSolveStages = 2;  // each K tile feeds two products (1024 pipe cycles); the shared memory a third stage would take holds the candidate pool
-constexpr int kSolveThreads = 608;   // 2 row groups x 8 warps + TMA warp + 2 MMA warps
+constexpr int kSolveStages = 3;  // each K tile feeds two products, three tiles in flight cover the TMA latency
+constexpr int kSolveThreads = 576;   // 2 row groups x 8 warps + TMA warp + MMA warp
 constexpr int kSolveRowThreads = 512;
 constexpr int kSolveGroupThreads = 256;
-constexpr int kSolveTmemCols = 512;  // S_A[2] at columns 0 / 128, S_B[2] at 256 / 384
+constexpr int kSolveTmemCols = 512;  // three S buffers at columns 0 / 128 / 256, Q~_A, Q~_B from column 384
+constexpr uint32_t kSolveQCol = 384;
+constexpr int kSolveBufs = 3;
 constexpr int kSolveRows = 2 * kBlockM;  // query rows per CTA
 
 enum SweepMode : int { kModeMax = 0, kModeHist = 1, kModeHalley = 2, kModeFinal = 3, kModeCollect = 4 };
 
 // One entry of the candidate pool: a score >= tau0 of some row, the 64-key block it sits in,
-// and the previous entry of the same thread's list.
+// and the previous entry of the same thread's list (written with one 8-byte store).
 struct __align__(8) Cand { float z; uint16_t kb; uint16_t next; };
-constexpr int kSolvePool = 9216;          // entries (72 KB): 18 per thread on average
-constexpr int kSolveWarpPool = kSolvePool / 16;  // each row warp appends to its own region: no contention between warps
 constexpr uint16_t kCandNil = 0xffff;
+
+// Shared memory: K stages, barriers, exchange buffers, bitmap staging, then the two Q tiles and
+// whatever is left of the budget.  The Q tiles are dead once Q~ sits in TMEM (before the first
+// append), so the candidate pool is their space plus that remainder (D = 128: ~110 KB, 14000
+// entries, 27 per thread on average).  Each row warp appends to its own sixteenth, so warps
+// do not contend for a counter.
+constexpr int kSolveSmemBudget = 225 * 1024;
 
 template <int D>
 struct SolveSmem {
   static constexpr int tile_bytes = (D / 64) * kPanelBytes;
-  static constexpr int q_off = 0;                                  // two Q tiles
-  static constexpr int k_off = 2 * tile_bytes;
+  static constexpr int k_off = 0;
   static constexpr int bar_off = k_off + kSolveStages * tile_bytes;
-  static constexpr int n_bars = 2 + 2 * kSolveStages + 8 + 1;
-  static constexpr int misc_off = bar_off + n_bars * 8;            // tmem base, abort flag, status
+  static constexpr int n_bars = 2 + 2 * kSolveStages + 3 * kSolveBufs + 1;
+  static constexpr int misc_off = bar_off + n_bars * 8;            // tmem base, abort flag, status, pool counters
   static constexpr int xchg_off = misc_off + 128;                  // [2 groups][2 halves][8][128] floats
   static constexpr int bits_off = xchg_off + 2 * 2 * 8 * 128 * 4;  // [4][n_words] words
-  static __host__ __device__ int pool_off(int n_words) { return (bits_off + 4 * n_words * 4 + 15) & ~15; }
-  static size_t bytes(int n_words) { return 1024 + pool_off(n_words) + (size_t)kSolvePool * sizeof(Cand); }
+  static __host__ __device__ int q_off(int n_words) { return (bits_off + 4 * n_words * 4 + 1023) & ~1023; }  // two Q tiles
+  static __host__ __device__ int pool_entries(int n_words) { return (kSolveSmemBudget - 1024 - q_off(n_words)) / 8; }
+  static size_t bytes(int) { return kSolveSmemBudget; }
 };
 
 template <typename T, int D>
@@ -84,16 +96,16 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
   constexpr int FMT = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  uint8_t* sQ = smem + L::q_off;
+  uint8_t* sQ = smem + L::q_off(p.n_words);
   uint8_t* sK = smem + L::k_off;
   uint64_t* bars = (uint64_t*)(smem + L::bar_off);
   uint64_t* q_full = bars + 0;
   uint64_t* q_ready = bars + 1;
   uint64_t* k_full = bars + 2;
   uint64_t* k_empty = k_full + kSolveStages;
-  uint64_t* s_full = k_empty + kSolveStages;  // [2 row tiles][2 buffers]
-  uint64_t* s_free = s_full + 4;
-  uint64_t* decide = s_free + 4;              // the row warps have settled lists vs. full sweeps
+  uint64_t* s_full = k_empty + kSolveStages;  // [2 row tiles][3 S buffers]: each row group sees only its own products
+  uint64_t* s_free = s_full + 2 * kSolveBufs;  // [3 S buffers]
+  uint64_t* decide = s_free + kSolveBufs;              // the row warps have settled lists vs. full sweeps
   uint32_t* tmem_holder = (uint32_t*)(smem + L::misc_off);
   volatile int* cta_abort = (volatile int*)(smem + L::misc_off + 4);
   int* start_status = (int*)(smem + L::misc_off + 8);
@@ -101,7 +113,8 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
   volatile int* pool_ovf = (volatile int*)(smem + L::misc_off + 16);
   float* xchg = (float*)(smem + L::xchg_off);
   uint32_t* s_bits = (uint32_t*)(smem + L::bits_off);
-  Cand* pool = (Cand*)(smem + L::pool_off(p.n_words));
+  Cand* pool = (Cand*)sQ;  // the Q tiles are dead once Q~ is in TMEM (before the first append)
+  const int warp_pool = L::pool_entries(p.n_words) / 16;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int heads = p.B * p.Hq;
@@ -118,10 +131,16 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
   const int T_a = qtA + 1;                          // key tiles of A: 0 .. qtA
   const int T_k = b_on ? qtB + 1 : T_a;             // key tiles streamed per sweep
   const int nsweeps = p.tau_given ? 1 : p.niter + 3;
-  // tiles streamed before the row warps decide (max sweep + collect sweep), and in all if
-  // the candidate pool overflows (max, collect, then histogram .. final over S)
+  // tiles streamed before the row warps decide (max sweep, histogram + collect sweep), and in
+  // all if the candidate pool overflows (then the Halley .. final steps sweep S as well)
   const int total_first = p.tau_given ? T_k : 2 * T_k;
   const int total_full = nsweeps * T_k;
+  // Products are numbered in issue order (per K tile: A if it has one, then B); product n uses
+  // S buffer n % 3 for the (n / 3)-th time.
+  const int prods_per_sweep = b_on ? 2 * T_a + 1 : T_a;
+  auto product_index = [&](int sweep, int kt, int g) -> int {
+    return sweep * prods_per_sweep + (b_on ? (kt < T_a ? 2 * kt + g : 2 * T_a) : kt);
+  };
 
   if (threadIdx.x == 0) {
     *start_status = *(volatile int*)p.status;
@@ -134,8 +153,9 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
       ptx::mbar_init(q_full, 1);
       ptx::mbar_init(q_ready, kSolveRowThreads / 32);
       ptx::mbar_init(decide, kSolveRowThreads / 32);
-      for (int s = 0; s < kSolveStages; ++s) { ptx::mbar_init(k_full + s, 1); ptx::mbar_init(k_empty + s, b_on ? 2 : 1); }
-      for (int s = 0; s < 4; ++s) { ptx::mbar_init(s_full + s, 1); ptx::mbar_init(s_free + s, kSolveGroupThreads / 32); }
+      for (int s = 0; s < kSolveStages; ++s) { ptx::mbar_init(k_full + s, 1); ptx::mbar_init(k_empty + s, 1); }
+      for (int s = 0; s < 2 * kSolveBufs; ++s) ptx::mbar_init(s_full + s, 1);
+      for (int s = 0; s < kSolveBufs; ++s) ptx::mbar_init(s_free + s, kSolveGroupThreads / 32);
       ptx::fence_mbar_init();
     }
     __syncwarp();
@@ -183,16 +203,17 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
                            kt * kBlockN, kv_head);
       }
     }
-  } else if (warp == 17 || warp == 18) {
-    // ---------------- MMA issuers: warp 17 row tile A, warp 18 row tile B ----------------
-    const int t = warp - 17;
-    if (lane == 0 && (t == 0 || b_on)) {
+  } else if (warp == 17) {
+    // ---------------- MMA issuer ----------------
+    // One thread issues every product in order n = 0, 1, 2, ...: it is then the only waiter of
+    // the three "buffer free" barriers and sees each of their phases in turn (a thread that
+    // skips a phase of an mbarrier cannot tell the phase after it from the one before).
+    if (lane == 0) {
       constexpr uint32_t idesc = ptx::make_idesc(FMT, kBlockM, kBlockN, 0, 0);
       bool ok = ptx::mbar_wait(q_ready, 0);
       if (!ok) raise_abort(cta_abort, p.status, kStTimeoutMma);
-      const uint32_t a0 = ptx::smem_u32(sQ + t * L::tile_bytes);
-      int use = 0;  // tiles of this row tile issued so far
       int total = total_first;
+      int n = 0;  // products issued so far
       for (int i = 0; ok; ++i) {
         if (i == total) {
           if (total == total_full) break;
@@ -203,26 +224,23 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
         const int st = i % kSolveStages, kt = i % T_k;
         if (*cta_abort) break;
         if (!ptx::mbar_wait(k_full + st, (i / kSolveStages) & 1)) { raise_abort(cta_abort, p.status, kStTimeoutMma); break; }
-        if (t == 0 && kt >= T_a) {
-          // the diagonal key tile of B: nothing for A.  The stage is released by a commit, which
-          // arrives after A's earlier products, and only after the stage has been filled, so
-          // that this arrival cannot be counted for the previous use of the stage.
-          ptx::mma_commit(k_empty + st);
-          continue;
-        }
-        const int bf = use & 1;
-        if (!ptx::mbar_wait(s_free + t * 2 + bf, ((use >> 1) & 1) ^ 1)) { raise_abort(cta_abort, p.status, kStTimeoutMma); break; }
-        ptx::tc_fence_after_sync();
         const uint32_t b0 = ptx::smem_u32(sK + st * L::tile_bytes);
-        const uint32_t d = tmem_base + (t * 2 + bf) * kBlockN;
+        for (int t = 0; t < 2 && ok; ++t) {
+          if (t == 0 ? kt >= T_a : !b_on) continue;  // the diagonal key tile of B has nothing for A
+          const int bf = n % kSolveBufs;
+          if (!ptx::mbar_wait(s_free + bf, ((n / kSolveBufs) & 1) ^ 1)) { raise_abort(cta_abort, p.status, kStTimeoutMma); ok = false; break; }
+          ptx::tc_fence_after_sync();
+          const uint32_t a_tmem = tmem_base + kSolveQCol + t * (D / 2);
+          const uint32_t d = tmem_base + bf * kBlockN;
 #pragma unroll
-        for (int kk = 0; kk < KSTEPS; ++kk) {
-          const uint32_t off = (kk >> 2) * kPanelBytes + (kk & 3) * 32;
-          ptx::mma_ss(d, ptx::make_smem_desc(a0 + off, 16, 1024), ptx::make_smem_desc(b0 + off, 16, 1024), idesc, kk > 0);
+          for (int kk = 0; kk < KSTEPS; ++kk) {
+            const uint32_t off = (kk >> 2) * kPanelBytes + (kk & 3) * 32;
+            ptx::mma_ts(d, a_tmem + kk * 8, ptx::make_smem_desc(b0 + off, 16, 1024), idesc, kk > 0);
+          }
+          ptx::mma_commit(s_full + t * kSolveBufs + bf);
+          ++n;
         }
-        ptx::mma_commit(s_full + t * 2 + bf);
         ptx::mma_commit(k_empty + st);
-        ++use;
       }
     }
   } else {
@@ -237,22 +255,30 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
     const int T_g = qt + 1;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(wq * 32) << 16);
     bool dead = false;
-    // Q~ = rn(q * fp32(0.5/sqrt(D))) (rows >= len -> 0) in place in shared memory
+    // Q~ = rn(q * fp32(0.5/sqrt(D))) (rows >= len -> 0), from the TMA tile in shared
+    // memory into TMEM: the two threads of row r convert D/2 elements each (16-bit pairs, lane r)
     if (!ptx::mbar_wait_warp(q_full, 0)) { raise_abort(cta_abort, p.status, kStTimeoutEpilogue); dead = true; }
     if (!dead) {
-      const float sc = 0.5f * p.sm_scale;
-      for (int v = threadIdx.x; v < 2 * L::tile_bytes / 16; v += kSolveRowThreads) {
-        uint4* ptr = reinterpret_cast<uint4*>(sQ) + v;
-        const int tile = (v * 16) / L::tile_bytes;
-        const int vrow = ((v * 16) % kPanelBytes) / 128;
-        uint4 val = *ptr;
-        T* e = reinterpret_cast<T*>(&val);
-        const bool keep = (m0 + tile * kBlockM + vrow) < len;
+      const float sc = row_ok ? 0.5f * p.sm_scale : 0.f;
+      const uint8_t* qtile = sQ + grp * L::tile_bytes;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) e[j] = DT<T>::from_f(keep ? DT<T>::to_f(e[j]) * sc : 0.f);
-        *ptr = val;
+      for (int hh = 0; hh < D / 64; ++hh) {  // 32 elements -> 16 packed columns per store; D/2 elements per thread
+        const int h16 = half * (D / 64) + hh;
+        uint32_t pk[16];
+#pragma unroll
+        for (int cc = 0; cc < 4; ++cc) {
+          const int e0 = (h16 * 4 + cc) * 8;               // first element of the 16-byte chunk
+          const int pn = e0 >> 6, c = (e0 & 63) >> 3;      // panel, chunk inside the 128-byte row
+          const uint4 val = *reinterpret_cast<const uint4*>(qtile + pn * kPanelBytes + r * 128 + ((c ^ (r & 7)) << 4));
+          const T* e = reinterpret_cast<const T*>(&val);
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            pk[cc * 4 + j] = pack2<T>(DT<T>::to_f(e[2 * j]) * sc, DT<T>::to_f(e[2 * j + 1]) * sc);
+        }
+        ptx::tmem_st16(lane_addr + kSolveQCol + grp * (D / 2) + h16 * 16, pk);
       }
-      ptx::fence_proxy_async_smem();
+      ptx::tmem_st_wait();
+      ptx::tc_fence_before_sync();
     }
     ptx::mbar_arrive_warp(q_ready);
 
@@ -262,7 +288,8 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
     hs.t = hs.lo = hs.hi = 0.f;
     if (p.tau_given) hs.t = row_ok ? p.taus[((size_t)bh) * p.N + row] : 0.f;
     const float fbins = (float)p.bins;
-    int use = 0;  // tiles of this group consumed so far
+    int sweep_no = 0;  // sweeps over S started so far (fixes the S buffer of every tile)
+    uint32_t full_par = 0;  // bit b: parity of this group's next product in S buffer b
     float a0 = 0.f, a1 = 0.f, a2 = 0.f;
     uint16_t head = kCandNil;  // this thread's list of scores >= tau0
 
@@ -270,10 +297,14 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
     // kind, so that the per-group code carries no mode tests and each sweep runs a compact loop.
     auto sweep_tiles = [&](auto mode_c) {
       constexpr int mode = decltype(mode_c)::value;
-      for (int kt = 0; kt < T_g; ++kt, ++use) {
+      const int sweep = sweep_no++;
+      for (int kt = 0; kt < T_g; ++kt) {
         if (dead || *cta_abort) { dead = true; continue; }
-        const int bf = use & 1;
-        if (!ptx::mbar_wait_warp(s_full + grp * 2 + bf, (use >> 1) & 1)) {
+        const int n = product_index(sweep, kt, grp);
+        const int bf = n % kSolveBufs;
+        const uint32_t par = (full_par >> bf) & 1u;
+        full_par ^= 1u << bf;
+        if (!ptx::mbar_wait_warp(s_full + grp * kSolveBufs + bf, par)) {
           raise_abort(cta_abort, p.status, kStTimeoutEpilogue);
           dead = true;
           continue;
@@ -290,12 +321,18 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
         // below its bracket, and a sweep over S would then see those scores too.  The
         // histogram over the list tests each score against tau0 itself.
         const float thr = mode == kModeCollect ? tau0 - 2e-5f : hs.t;
+        // (Register budget: the kernel keeps nearly all of the SM's shared memory, which leaves
+        // almost no L1 for local memory -- a spill in this loop costs an L2 round trip.)
 #pragma unroll 1
         for (int q32 = 0; q32 < 2; ++q32) {  // this thread's 64 keys, 32 at a time
           uint32_t raw[32];
           const int c0 = half * 64 + q32 * 32;
-          ptx::tmem_ld32(lane_addr + (grp * 2 + bf) * kBlockN + c0, raw);
+          ptx::tmem_ld32(lane_addr + bf * kBlockN + c0, raw);
           ptx::tmem_ld_wait();
+          if (q32 == 1) {  // the last of this buffer is in registers: hand it back before the row work
+            ptx::tc_fence_before_sync();
+            ptx::mbar_arrive_warp(s_free + bf);
+          }
           float* v = reinterpret_cast<float*>(raw);
           if (need_mask) {
             const int lim = min(row, len - 1) - (n0 + c0);  // columns c <= lim survive
@@ -330,8 +367,8 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
                     bool listed = false;
                     if (collecting) {
                       const int idx = atomicAdd(pool_used + warp, 1);
-                      if (idx < kSolveWarpPool) {
-                        const int slot = warp * kSolveWarpPool + idx;
+                      if (idx < warp_pool) {
+                        const int slot = warp * warp_pool + idx;
                         Cand e;
                         e.z = z; e.kb = (uint16_t)(2 * kt + half); e.next = head;
                         pool[slot] = e;
@@ -370,8 +407,6 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
             }
           }
         }
-        ptx::tc_fence_before_sync();
-        ptx::mbar_arrive_warp(s_free + grp * 2 + bf);
         if (packed != 0ull) {
 #pragma unroll
           for (int bb = 0; bb < 8; ++bb) cnt[bb] += (int)((packed >> (8 * bb)) & 0xffull);
@@ -445,7 +480,8 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
         exchange(kModeMax);
         sweep_tiles(std::integral_constant<int, kModeCollect>{});
         // the listed scores join the histogram
-        for (uint16_t e = head; e != kCandNil;) {
+        // (a thread's list is no longer than its warp's share of the pool: the walks are bounded)
+        for (int e = head, left = warp_pool; e != kCandNil && left > 0; --left) {
           const Cand c = pool[e];
           const float prj = (c.z - tau0) * fbins;
           if (prj >= 0.f) {
@@ -467,7 +503,7 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
         for (int it = 0; it <= p.niter; ++it) {
           const bool last = it == p.niter;
           reset_stats();
-          for (uint16_t e = head; e != kCandNil;) {
+          for (int e = head, left = warp_pool; e != kCandNil && left > 0; --left) {
             const Cand c = pool[e];
             const float d = c.z - hs.t;
             if (d > 0.f) {
