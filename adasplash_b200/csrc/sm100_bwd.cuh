@@ -83,7 +83,6 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   int* start_status = (int*)(smem + L::misc_off + 8);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int heads = p.B * p.Hq;
   // head-major order: the CTAs in flight share a few heads, whose K / V stay in L2
   const int qt = p.nq - 1 - (int)(blockIdx.x % p.nq);
   const int bh = blockIdx.x / p.nq;
@@ -478,7 +477,6 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
   float* s_td = (float*)(smem + L::td_off);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int kvheads = p.B * p.Hkv;
   // head-major order; inside a head the low key tiles (most query blocks) start first
   const int nt = (int)(blockIdx.x % p.nq);
   const int bkv = blockIdx.x / p.nq;

@@ -96,7 +96,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
   int* start_status = (int*)(smem + L::misc_off + 8);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int heads = p.B * p.Hq;
   // head-major order: the CTAs in flight share a few heads, whose K / V stay in L2;
   // inside a head the longest (latest) query tiles start first
   const int qt = p.nq - 1 - (int)(blockIdx.x % p.nq);
