@@ -6,6 +6,13 @@
 // memory hop when a row spans several warps.  Rows too long for registers use a
 // streaming variant that re-reads the row from L2/HBM.
 //
+// Only the elements within 1 of the row maximum can be in the support (the largest
+// probability [z_max - tau]_+^(1/(alpha-1)) is at most 1, so tau >= z_max - 1): after the
+// maximum is known, one pass collects them into a short shared-memory list and the histogram
+// and every refinement step run on the list; rows with too many such elements (nearly flat
+// rows) take the full passes instead, and so do calls with so few steps that building the
+// list would cost more than it saves.
+//
 // The threshold search follows adasplash/triton_entmax_v2.py:361-536 (4-bin
 // histogram lower bound, quadratic start on the bin-centre model, Halley /
 // Newton / secant / bisection refinement); the backward follows :539-617.
@@ -238,11 +245,22 @@ struct StreamRow {  // re-reads the row from global memory on every pass
   }
 };
 
+constexpr int kListCap = 256;  // candidates per row kept in shared memory
+
+// Shared memory of the candidate lists of a CTA: per row group a counter and kListCap values,
+// and one flag for "some row of this CTA has more candidates than that".
+struct ListSmem {
+  float* vals;     // this group's kListCap floats
+  int* count;      // this group's counter
+  int* overflow;   // CTA-wide flag
+};
+
 template <typename T, int TPR, typename Row>
 __device__ __forceinline__ void entmax_fwd_row(Row& r, T* yrow, float* tau_out, long long row_idx,
                                                bool row_ok, float alpha, int n_iter, int use_hist,
-                                               int fast_math, float* smem) {
+                                               int fast_math, float* smem, ListSmem ls) {
   GroupReduce<TPR> red(smem);
+  const int tl_ = threadIdx.x % TPR;
   const int mode = (alpha == 1.5f) ? 0 : (alpha == 2.0f ? 1 : 2);
   const float c0 = 1.0f / (alpha - 1.0f), c1 = c0 - 1.0f, c2 = c1 - 1.0f;
   float red4[4];
@@ -252,13 +270,77 @@ __device__ __forceinline__ void entmax_fwd_row(Row& r, T* yrow, float* tau_out, 
   red4[0] = mx; red4[1] = red4[2] = red4[3] = -INFINITY;
   red.reduce4(red4, OpMax());
   mx = red4[0];
+  // Candidates: tau never falls below max - 1 (minus the 1e-6 slack of the bracket test), so
+  // nothing below that can enter a sum.  Rows groups of one warp decide for themselves; wider
+  // groups share CTA barriers and therefore decide together.
+  // Building the list costs about two passes over the row (atomics, a sort, barriers): it pays
+  // when more passes than that follow, i.e. for the many refinement steps of a generic alpha,
+  // not for the default "histogram + 2 steps" of alpha = 1.5 / 2.
+  const bool want_list = (use_hist && alpha <= 2.0f ? 1 : 0) + n_iter >= 5;
+  if (tl_ == 0) *ls.count = want_list ? 0 : kListCap + 1;
+  if constexpr (TPR > 32) __syncthreads(); else __syncwarp();
+  if (want_list) {
+    const float t_keep = mx - 1.0f - 1e-5f;
+    r.for_each([&](float x) {
+      if (x >= t_keep) {
+        const int slot = atomicAdd(ls.count, 1);
+        if (slot < kListCap) ls.vals[slot] = x;
+      }
+    });
+  }
+  if constexpr (TPR > 32) {
+    __syncthreads();
+    if (tl_ == 0 && *ls.count > kListCap) *ls.overflow = 1;
+    __syncthreads();
+  } else {
+    __syncwarp();
+  }
+  const int n_list = *ls.count;
+  const bool listed = want_list && ((TPR > 32) ? (*ls.overflow == 0) : (n_list <= kListCap));
+  if (listed) {
+    // The atomics filled the list in an order that differs from run to run; sort it (rank of
+    // each value among the few dozen) so that the sums over it are reproducible.
+    constexpr int EPT = (kListCap + TPR - 1) / TPR;
+    float mine[EPT];
+    int rank[EPT];
+#pragma unroll
+    for (int e = 0; e < EPT; ++e) {
+      const int i = tl_ + e * TPR;
+      mine[e] = 0.f;
+      rank[e] = 0;
+      if (i < n_list) {
+        const float v = ls.vals[i];
+        int rk = 0;
+        for (int j = 0; j < n_list; ++j) {
+          const float w = ls.vals[j];
+          rk += (w > v || (w == v && j < i)) ? 1 : 0;
+        }
+        mine[e] = v;
+        rank[e] = rk;
+      }
+    }
+    if constexpr (TPR > 32) __syncthreads(); else __syncwarp();
+#pragma unroll
+    for (int e = 0; e < EPT; ++e) {
+      if (tl_ + e * TPR < n_list) ls.vals[rank[e]] = mine[e];
+    }
+    if constexpr (TPR > 32) __syncthreads(); else __syncwarp();
+  }
+  // every later pass over the row: over the list if there is one
+  auto each = [&](auto f) {
+    if (listed) {
+      for (int i = tl_; i < n_list; i += TPR) f(ls.vals[i]);
+    } else {
+      r.for_each(f);
+    }
+  };
   Hybrid s;
   if (use_hist && alpha <= 2.0f) {
     // stage 2: 4-bin histogram of x - (max-1) on [0,1]; cumulative counts
     // N_b = #{proj*4 >= b} give the same bins as floor(proj*4) clamped to 3.
     float t_init = mx - 1.0f;
     float n0 = 0.f, n1 = 0.f, n2 = 0.f, n3 = 0.f;
-    r.for_each([&](float x) {
+    each([&](float x) {
       const float d = x - t_init;
       if (d >= 0.f) {  // only the few elements within 1 of the row maximum land in a bin
         const float p4 = d * (float)kBins;
@@ -300,16 +382,16 @@ __device__ __forceinline__ void entmax_fwd_row(Row& r, T* yrow, float* tau_out, 
     float a0 = 0.f, a1 = 0.f, a2 = 0.f;
     const float t = s.t;
     if (mode == 1) {
-      r.for_each([&](float x) { if (x > t) { a0 += x - t; a1 += 1.f; } });
+      each([&](float x) { if (x > t) { a0 += x - t; a1 += 1.f; } });
     } else if (mode == 0) {
-      r.for_each([&](float x) {
+      each([&](float x) {
         if (x > t) {  // the support is a small part of the row
           const float u = x - t;
           a0 = fmaf(u, u, a0); a1 += u; a2 += 1.f;
         }
       });
     } else {
-      r.for_each([&](float x) {
+      each([&](float x) {
         if (x > t) {  // the support is a small part of the row: skip the transcendental work elsewhere
           float p0, p1, p2;
           pow3(x - t, c0, fast_math, p0, p1, p2);
@@ -341,13 +423,20 @@ entmax_fwd_reg_kernel(const T* __restrict__ x, T* __restrict__ y, float* __restr
                       long long rows, int cols, float alpha, int n_iter, int use_hist,
                       int fast_math) {
   __shared__ float smem[2 * 32 * 4];
+  constexpr int RPC = TPR >= 128 ? 1 : 128 / TPR;  // row groups per CTA
+  __shared__ float s_list[RPC * kListCap];
+  __shared__ int s_count[RPC + 1];
   const int rows_per_cta = blockDim.x / TPR;
-  long long row = (long long)blockIdx.x * rows_per_cta + threadIdx.x / TPR;
+  const int grp = threadIdx.x / TPR;
+  long long row = (long long)blockIdx.x * rows_per_cta + grp;
   bool ok = row < rows;
   long long rr = ok ? row : rows - 1;
+  if (threadIdx.x == 0) s_count[RPC] = 0;
   RegRow<T, TPR, NV, VEC> r;
   r.load(x + rr * cols, cols, alpha - 1.0f);
-  entmax_fwd_row<T, TPR>(r, y + rr * cols, tau_out, rr, ok, alpha, n_iter, use_hist, fast_math, smem);
+  if constexpr (TPR > 32) __syncthreads();
+  ListSmem ls{s_list + grp * kListCap, s_count + grp, s_count + RPC};
+  entmax_fwd_row<T, TPR>(r, y + rr * cols, tau_out, rr, ok, alpha, n_iter, use_hist, fast_math, smem, ls);
 }
 
 template <typename T>
@@ -356,10 +445,15 @@ entmax_fwd_stream_kernel(const T* __restrict__ x, T* __restrict__ y, float* __re
                          long long rows, int cols, float alpha, int n_iter, int use_hist,
                          int fast_math) {
   __shared__ float smem[2 * 32 * 4];
+  __shared__ float s_list[kListCap];
+  __shared__ int s_count[2];
   long long row = blockIdx.x;
+  if (threadIdx.x == 0) s_count[1] = 0;
   StreamRow<T, 1024> r;
   r.load(x + row * cols, cols, alpha - 1.0f);
-  entmax_fwd_row<T, 1024>(r, y + row * cols, tau_out, row, true, alpha, n_iter, use_hist, fast_math, smem);
+  __syncthreads();
+  ListSmem ls{s_list, s_count, s_count + 1};
+  entmax_fwd_row<T, 1024>(r, y + row * cols, tau_out, row, true, alpha, n_iter, use_hist, fast_math, smem, ls);
 }
 
 // ---------------------------------------------------------------------------

@@ -63,6 +63,33 @@ def test_trajectory_matches_oracle(alpha, n_iter, hist):
     assert (y.cpu() - yo).abs().max() < tol
 
 
+@pytest.mark.parametrize("cols", [100, 1000, 4096, 9000, 40000])
+@pytest.mark.parametrize("alpha", [1.5, 2.0, 1.333])
+def test_nearly_flat_rows_take_the_full_passes(cols, alpha):
+    # Rows with a small spread have most of their elements within 1 of the maximum: more than
+    # the kernel's candidate list holds, so it sweeps the whole row at every step instead.
+    # Peaked rows of the same batch use the list; both must follow the oracle's trajectory.
+    flat = _randn((3, cols), 31, 0.2)
+    peaked = _randn((3, cols), 32, 4.0)
+    x = torch.cat([flat, peaked], 0)
+    for n_iter in (2, 6):   # 6 steps: the list is built (and overflows for the flat rows)
+        y, tau = em.entmax_with_tau(x.cuda(), alpha, n_iter, True)
+        yo, to = O.rowwise_entmax_v2(x, alpha, n_iter, True, return_tau=True)
+        tol = 2e-6 if alpha in (1.5, 2.0) else 1e-5
+        assert (tau.cpu() - to).abs().max() < tol
+        assert (y.cpu() - yo).abs().max() < tol
+
+
+def test_forward_is_reproducible():
+    # the candidate list is filled by atomics in arbitrary order and then sorted: two runs
+    # must agree bit for bit
+    x = _randn((256, 4096), 33, 4.0).cuda()
+    for alpha, n_iter in ((1.5, 8), (1.333, 10)):
+        a = adasplash.triton_entmax(x, alpha=alpha, n_iter=n_iter)
+        for _ in range(3):
+            assert torch.equal(a, adasplash.triton_entmax(x, alpha=alpha, n_iter=n_iter))
+
+
 def test_unaligned_rows_use_scalar_path():
     x = _randn((7, 1001), 31, 3.0)
     base = torch.zeros(7 * 1001 + 1, device="cuda")
