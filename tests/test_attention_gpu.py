@@ -224,11 +224,12 @@ def test_tensor_core_path_matches_cuda_core_path(path, shape):
         assert (a[key] - b[key]).abs().max() < 2e-2 * scale, key
 
 
-@pytest.mark.parametrize("scale, niter", [(0.05, 1), (0.05, 3), (0.4, 0)])
+@pytest.mark.parametrize("scale, niter", [(0.05, 1), (0.05, 3), (0.4, 0), (1.5, 10), (1.5, 0)])
 def test_solver_with_nearly_flat_rows(scale, niter):
     # Scores that are nearly flat put most of a row within 1 of its maximum: the solver's
-    # candidate pool overflows and the CTA sweeps S for every step instead.  Both routes must
-    # give what the CUDA-core kernels give.
+    # candidate pool overflows and the CTA sweeps S for every step instead.  Peaked rows
+    # (scale 1.5) stay on the candidate lists for all of their steps.  Both routes must give
+    # what the CUDA-core kernels give.
     B, Hq, Hkv, N, D = 1, 2, 1, 2048, 128
     q = _randn((B, Hq, N, D), 70, scale, torch.bfloat16)
     k = _randn((B, Hkv, N, D), 71, 1.0, torch.bfloat16)
