@@ -183,6 +183,9 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
           ptx::tma_load_3d(sQ + t * L::tile_bytes + pn * kPanelBytes, &tmQ, q_full, pn * 64, m0 + t * kBlockM, bh);
       const int kv_head = b * p.Hkv + kvh;
       int total = total_first;
+      // stage, its use parity and the key tile are carried along (no divisions in the loop)
+      int st = 0, kt = 0;
+      uint32_t use_par = 0;
       for (int i = 0;; ++i) {
         if (i == total) {
           // the first sweeps are through: stream S again only if the row warps ask for it
@@ -191,9 +194,8 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
           if (!*pool_ovf) break;
           total = total_full;
         }
-        const int st = i % kSolveStages, kt = i % T_k;
         if (*cta_abort) break;
-        if (!ptx::mbar_wait(k_empty + st, ((i / kSolveStages) & 1) ^ 1)) {
+        if (!ptx::mbar_wait(k_empty + st, use_par ^ 1)) {
           raise_abort(cta_abort, p.status, kStTimeoutProducer);
           break;
         }
@@ -201,6 +203,8 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
         for (int pn = 0; pn < PANELS; ++pn)
           ptx::tma_load_3d(sK + st * L::tile_bytes + pn * kPanelBytes, &tmK, k_full + st, pn * 64,
                            kt * kBlockN, kv_head);
+        if (++st == kSolveStages) { st = 0; use_par ^= 1; }
+        if (++kt == T_k) kt = 0;
       }
     }
   } else if (warp == 17) {
@@ -213,7 +217,9 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
       bool ok = ptx::mbar_wait(q_ready, 0);
       if (!ok) raise_abort(cta_abort, p.status, kStTimeoutMma);
       int total = total_first;
-      int n = 0;  // products issued so far
+      // stage / key tile / S buffer and their use parities are carried along (no divisions)
+      int st = 0, kt = 0, bf = 0;
+      uint32_t k_par = 0, buf_par = 0;
       for (int i = 0; ok; ++i) {
         if (i == total) {
           if (total == total_full) break;
@@ -221,14 +227,12 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
           if (!*pool_ovf) break;
           total = total_full;
         }
-        const int st = i % kSolveStages, kt = i % T_k;
         if (*cta_abort) break;
-        if (!ptx::mbar_wait(k_full + st, (i / kSolveStages) & 1)) { raise_abort(cta_abort, p.status, kStTimeoutMma); break; }
+        if (!ptx::mbar_wait(k_full + st, k_par)) { raise_abort(cta_abort, p.status, kStTimeoutMma); break; }
         const uint32_t b0 = ptx::smem_u32(sK + st * L::tile_bytes);
         for (int t = 0; t < 2 && ok; ++t) {
           if (t == 0 ? kt >= T_a : !b_on) continue;  // the diagonal key tile of B has nothing for A
-          const int bf = n % kSolveBufs;
-          if (!ptx::mbar_wait(s_free + bf, ((n / kSolveBufs) & 1) ^ 1)) { raise_abort(cta_abort, p.status, kStTimeoutMma); ok = false; break; }
+          if (!ptx::mbar_wait(s_free + bf, buf_par ^ 1)) { raise_abort(cta_abort, p.status, kStTimeoutMma); ok = false; break; }
           ptx::tc_fence_after_sync();
           const uint32_t a_tmem = tmem_base + kSolveQCol + t * (D / 2);
           const uint32_t d = tmem_base + bf * kBlockN;
@@ -238,9 +242,11 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
             ptx::mma_ts(d, a_tmem + kk * 8, ptx::make_smem_desc(b0 + off, 16, 1024), idesc, kk > 0);
           }
           ptx::mma_commit(s_full + t * kSolveBufs + bf);
-          ++n;
+          if (++bf == kSolveBufs) { bf = 0; buf_par ^= 1; }
         }
         ptx::mma_commit(k_empty + st);
+        if (++st == kSolveStages) { st = 0; k_par ^= 1; }
+        if (++kt == T_k) kt = 0;
       }
     }
   } else {
