@@ -298,6 +298,7 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
     uint32_t full_par = 0;  // bit b: parity of this group's next product in S buffer b
     float a0 = 0.f, a1 = 0.f, a2 = 0.f;
     uint16_t head = kCandNil;  // this thread's list of scores >= tau0
+    int ncand = 0;             // its length (counted on the first walk)
 
     // One pass over the S tiles of this group's causal range.  Instantiated once per sweep
     // kind, so that the per-group code carries no mode tests and each sweep runs a compact loop.
@@ -496,6 +497,7 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
             for (int bb = 0; bb < 8; ++bb) cnt[bb] += (bb <= bsel) ? 1 : 0;
           }
           e = c.next;
+          ++ncand;
         }
         exchange(kModeHist);
       }
@@ -506,11 +508,31 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
       ptx::mbar_arrive_warp(decide);
       if (grp_on && !full_sweeps) {
         // ---- Halley steps and the final step on this thread's list ----
+        // If the warp's share of the pool has room behind the entries in use, every thread
+        // first copies its list there as one contiguous run: the steps then read independent
+        // addresses instead of chasing links.
+        int incl = ncand;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const int up = __shfl_up_sync(0xffffffffu, incl, o);
+          if (lane >= o) incl += up;
+        }
+        const int used = min(pool_used[warp], warp_pool);
+        const bool compact = used + __shfl_sync(0xffffffffu, incl, 31) <= warp_pool;
+        const int run0 = warp * warp_pool + used + incl - ncand;
+        if (compact) {
+          int dst = run0;
+          for (int e = head, left = ncand; e != kCandNil && left > 0; --left) {
+            const Cand c = pool[e];
+            pool[dst++] = c;
+            e = c.next;
+          }
+        }
+        __syncwarp();
         for (int it = 0; it <= p.niter; ++it) {
           const bool last = it == p.niter;
           reset_stats();
-          for (int e = head, left = warp_pool; e != kCandNil && left > 0; --left) {
-            const Cand c = pool[e];
+          auto visit = [&](const Cand c) {
             const float d = c.z - hs.t;
             if (d > 0.f) {
               a0 = fmaf(d, d, a0); a1 += d; a2 += 1.f;
@@ -518,7 +540,15 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
               // tau entering it (row block rb of this group, key block c.kb)
               if (last && row_ok) atomicOr(&s_bits[(grp * 2 + rb) * p.n_words + (c.kb >> 5)], 1u << (c.kb & 31));
             }
-            e = c.next;
+          };
+          if (compact) {
+            for (int k = 0; k < ncand; ++k) visit(pool[run0 + k]);
+          } else {
+            for (int e = head, left = warp_pool; e != kCandNil && left > 0; --left) {
+              const Cand c = pool[e];
+              visit(c);
+              e = c.next;
+            }
           }
           exchange(last ? kModeFinal : kModeHalley);
         }
