@@ -45,7 +45,7 @@ struct DqSmem {
   static constexpr int k_off = 2 * tile_bytes;
   static constexpr int v_off = k_off + kDqKStages * tile_bytes;
   static constexpr int bar_off = v_off + kDqVStages * tile_bytes;
-  static constexpr int n_bars = 2 + 2 * kDqKStages + 2 * kDqVStages + 2 + 1 + 2 + 2 + 1;
+  static constexpr int n_bars = 2 + 2 * kDqKStages + 2 * kDqVStages + 2 + 1 + 2 + 2 + 1 + 1;
   static constexpr int misc_off = bar_off + n_bars * 8;
   static constexpr size_t bytes = 1024 + misc_off + 64;
 };
@@ -78,6 +78,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   uint64_t* p_full = dp_full + 1;            // [2] dS written, dP consumed
   uint64_t* s_free = p_full + 2;             // [2]
   uint64_t* dq_full = s_free + 2;
+  uint64_t* dp_free = dq_full + 1;           // the row warps hold dP in registers: the buffer may be rewritten
   uint32_t* tmem_holder = (uint32_t*)(smem + L::misc_off);
   volatile int* cta_abort = (volatile int*)(smem + L::misc_off + 4);
   int* start_status = (int*)(smem + L::misc_off + 8);
@@ -118,6 +119,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       }
       ptx::mbar_init(dp_full, 1);
       ptx::mbar_init(dq_full, 1);
+      ptx::mbar_init(dp_free, kDqRowThreads / 32);
       ptx::fence_mbar_init();
     }
     __syncwarp();
@@ -203,8 +205,8 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       if (*cta_abort) { ok = false; break; }
       if (lane == 0) {
         ok = ptx::mbar_wait(v_full + vs, (j / kDqVStages) & 1);
-        // the row warps have finished reading dP_{j-1}
-        if (ok && j > 0) ok = ptx::mbar_wait(p_full + ((j - 1) & 1), ((j - 1) >> 1) & 1);
+        // the row warps have dP_{j-1} in registers (they say so before their row work)
+        if (ok && j > 0) ok = ptx::mbar_wait(dp_free, (j - 1) & 1);
         if (ok) {
           ptx::tc_fence_after_sync();
           const uint32_t a0 = ptx::smem_u32(sDO), b0 = ptx::smem_u32(sV + vs * L::tile_bytes);
@@ -302,6 +304,16 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       ptx::tc_fence_after_sync();
       const int n0 = kt * kBlockN;
       const bool need_mask = (kt == qt) || (n0 + kBlockN > len);
+      // This thread's 64 values of dP go to registers first and the single dP buffer is handed
+      // back at once: dO V^T of the next tile runs during the row work of this one.
+      uint32_t rp[64];
+      if (sub_on) {
+        ptx::tmem_ld32(lane_addr + DP_COL + half * 64, rp);
+        ptx::tmem_ld32(lane_addr + DP_COL + half * 64 + 32, rp + 32);
+        ptx::tmem_ld_wait();
+      }
+      ptx::tc_fence_before_sync();
+      ptx::mbar_arrive_warp(dp_free);
 #pragma unroll
       for (int cc = 0; cc < 2; ++cc) {
         const int ch = 2 * half + cc;
@@ -311,12 +323,11 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
 #pragma unroll
           for (int c = 0; c < 16; ++c) dk[c] = 0u;
         } else {
-          uint32_t rs[32], rp[32];
+          uint32_t rs[32];
           ptx::tmem_ld32(caddr, rs);
-          ptx::tmem_ld32(lane_addr + DP_COL + ch * 32, rp);
           ptx::tmem_ld_wait();
           const float* s = reinterpret_cast<const float*>(rs);
-          const float* dp = reinterpret_cast<const float*>(rp);
+          const float* dp = reinterpret_cast<const float*>(rp + cc * 32);
           if (!need_mask && rows_full) {
             // every (row, key) pair of the tile is causal and inside the sequence
 #pragma unroll
