@@ -3,7 +3,8 @@
 // dQ kernel: one CTA per 128-row query tile, walking the active 128-key tiles.
 //   S = Q~ K^T, dP = dO V^T (operands in shared memory), u = max(S - tau, 0),
 //   dS = rn(u (dP - delta)) written over S in TMEM, dQ += dS K (A operand in TMEM,
-//   K read MN-major from the same shared-memory tile).  S is double buffered.
+//   K read MN-major from the same shared-memory tile).  S is double buffered; dP has one
+//   buffer, which the row warps copy to registers and hand back before their row work.
 //   Eight row warps (TMEM lane = score row, two threads per row), one TMA warp and
 //   three MMA-issuing warps, one per product.
 //
