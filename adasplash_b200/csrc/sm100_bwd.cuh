@@ -11,7 +11,8 @@
 // dK/dV kernel: one CTA per 128-key tile of one kv head, walking the q heads of
 //   the group and, per head, the 64-row query blocks whose bit is set in the
 //   transposed block mask.  S^T = K~ Q^T, dP^T = V dO^T (128 keys x 64 queries),
-//   P^T = rn(u^2) and dS^T = rn(u (dP - delta)) written over them in TMEM,
+//   P^T = rn(u^2) and dS^T = rn(u (dP - delta)) written over S^T in TMEM (the dP^T
+//   buffer is handed back as soon as the row warps hold it in registers),
 //   dV += P^T dO, dK += dS^T Q.  K is the scaled + rounded operand here and Q is
 //   raw, as in the reference.  S^T / dP^T are double buffered.  Sixteen row warps
 //   (TMEM lane = key row, four threads per row), one producer warp (TMA for the
@@ -415,7 +416,7 @@ struct DkvSmem {
   static constexpr int q_off = 2 * tile_bytes;
   static constexpr int do_off = q_off + kDkvStages * qblk_bytes;
   static constexpr int bar_off = do_off + kDkvStages * qblk_bytes;
-  static constexpr int n_bars = 2 + 2 * kDkvStages + 2 + 2 + 2 + 1;
+  static constexpr int n_bars = 2 + 2 * kDkvStages + 2 + 2 + 2 + 1 + 2;
   static constexpr int misc_off = bar_off + n_bars * 8;
   static constexpr int td_off = (misc_off + 64 + 15) & ~15;     // [stages][tau 64 | delta 64] floats, 16-byte aligned (read as float4)
   static constexpr size_t bytes = 1024 + td_off + kDkvStages * 128 * 4;
@@ -483,6 +484,7 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
   uint64_t* p_full = s_full + 2;             // [2] P^T and dS^T written
   uint64_t* s_free = p_full + 2;             // [2]
   uint64_t* acc_full = s_free + 2;
+  uint64_t* dp_free = acc_full + 1;          // [2] the row warps hold dP^T in registers: the buffer may be rewritten
   uint32_t* tmem_holder = (uint32_t*)(smem + L::misc_off);
   volatile int* cta_abort = (volatile int*)(smem + L::misc_off + 4);
   int* start_status = (int*)(smem + L::misc_off + 8);
@@ -523,6 +525,7 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
         ptx::mbar_init(s_full + s, 2);
         ptx::mbar_init(p_full + s, kDkvRowThreads / 32);
         ptx::mbar_init(s_free + s, 2);
+        ptx::mbar_init(dp_free + s, kDkvRowThreads / 32);
       }
       ptx::mbar_init(acc_full, 2);
       ptx::fence_mbar_init();
@@ -607,7 +610,10 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
       const int st = j % kDkvStages, buf = j & 1;
       if (*cta_abort) { ok = false; break; }
       if (lane == 0) {
-        ok = ptx::mbar_wait(x_full + st, (j / kDkvStages) & 1) && ptx::mbar_wait(s_free + buf, ((j >> 1) & 1) ^ 1);
+        // the S^T buffer holds P^T and dS^T until the dV / dK products are done; the dP^T buffer
+        // is free as soon as the row warps have copied it to registers
+        ok = ptx::mbar_wait(x_full + st, (j / kDkvStages) & 1) &&
+             ptx::mbar_wait((is_s ? s_free : dp_free) + buf, ((j >> 1) & 1) ^ 1);
         if (ok) {
           ptx::tc_fence_after_sync();
           const uint32_t a0 = ptx::smem_u32(is_s ? sK : sV);
@@ -658,7 +664,7 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
         ptx::tc_fence_after_sync();
         const uint32_t b0 = ptx::smem_u32(bt);
         // P^T / dS^T: 16 queries = 8 packed columns per k-step, at the start of each 16-column group
-        const uint32_t a = tmem_base + (is_dv ? 0u : DP_COL0) + buf * kQBlock;
+        const uint32_t a = tmem_base + buf * kQBlock + (is_dv ? 0u : 8u);  // dS^T sits 8 columns after P^T
         const uint32_t acc = tmem_base + (is_dv ? DV_COL : DK_COL);
 #pragma unroll
         for (int kk = 0; kk < kQBlock / 16; ++kk) {
@@ -733,6 +739,8 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
           const uint32_t daddr = lane_addr + DP_COL0 + buf * kQBlock + c0;
           uint32_t pk[8], dk[8];
           if (!sub_on) {
+            ptx::tc_fence_before_sync();
+            ptx::mbar_arrive_warp(dp_free + buf);
 #pragma unroll
             for (int c = 0; c < 8; ++c) { pk[c] = 0u; dk[c] = 0u; }
           } else {
@@ -740,6 +748,10 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
             ptx::tmem_ld16(saddr, rs);
             ptx::tmem_ld16(daddr, rp);
             ptx::tmem_ld_wait();
+            // dP^T is in registers: its buffer may take the next product already (dS^T goes
+            // into the free half of this thread's S^T columns, not back there)
+            ptx::tc_fence_before_sync();
+            ptx::mbar_arrive_warp(dp_free + buf);
             const float* s = reinterpret_cast<const float*>(rs);
             const float* dp = reinterpret_cast<const float*>(rp);
             const float* tq = td + c0;
@@ -773,10 +785,10 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
             }
             }
           }
-          // 16 queries = 8 packed columns, written at the start of this thread's own
-          // 16 columns: nobody else reads or writes those
+          // 16 queries = 8 packed columns each: P^T at the start of this thread's own 16
+          // columns of S^T, dS^T in the other 8 (nobody else reads or writes those)
           ptx::tmem_st8(saddr, pk);
-          ptx::tmem_st8(daddr, dk);
+          ptx::tmem_st8(saddr + 8, dk);
         }
         ptx::tmem_st_wait();
         ptx::tc_fence_before_sync();
