@@ -277,9 +277,11 @@ __device__ __forceinline__ void entmax_fwd_row(Row& r, T* yrow, float* tau_out, 
   // when more passes than that follow, i.e. for the many refinement steps of a generic alpha,
   // not for the default "histogram + 2 steps" of alpha = 1.5 / 2.
   const bool want_list = (use_hist && alpha <= 2.0f ? 1 : 0) + n_iter >= 5;
-  if (tl_ == 0) *ls.count = want_list ? 0 : kListCap + 1;
-  if constexpr (TPR > 32) __syncthreads(); else __syncwarp();
-  if (want_list) {
+  int n_list = 0;
+  bool listed = false;
+  if (want_list) {  // the same for every thread of the launch: the barriers below are uniform
+    if (tl_ == 0) *ls.count = 0;
+    if constexpr (TPR > 32) __syncthreads(); else __syncwarp();
     const float t_keep = mx - 1.0f - 1e-5f;
     r.for_each([&](float x) {
       if (x >= t_keep) {
@@ -287,16 +289,16 @@ __device__ __forceinline__ void entmax_fwd_row(Row& r, T* yrow, float* tau_out, 
         if (slot < kListCap) ls.vals[slot] = x;
       }
     });
+    if constexpr (TPR > 32) {
+      __syncthreads();
+      if (tl_ == 0 && *ls.count > kListCap) *ls.overflow = 1;
+      __syncthreads();
+    } else {
+      __syncwarp();
+    }
+    n_list = *ls.count;
+    listed = (TPR > 32) ? (*ls.overflow == 0) : (n_list <= kListCap);
   }
-  if constexpr (TPR > 32) {
-    __syncthreads();
-    if (tl_ == 0 && *ls.count > kListCap) *ls.overflow = 1;
-    __syncthreads();
-  } else {
-    __syncwarp();
-  }
-  const int n_list = *ls.count;
-  const bool listed = want_list && ((TPR > 32) ? (*ls.overflow == 0) : (n_list <= kListCap));
   if (listed) {
     // The atomics filled the list in an order that differs from run to run; sort it (rank of
     // each value among the few dozen) so that the sums over it are reproducible.
