@@ -41,6 +41,7 @@ SIGNATURES = {
     "adasplash2_bwd": (c_int32, [c_void_p] * 13 + [POINTER(AttnShape), c_void_p, c_size_t, c_void_p]),
     "adasplash2_bwd_static": (c_int32, [c_void_p] * 11 + [POINTER(AttnShape), c_void_p]),
     "adasplash2_check_status": (c_int32, [c_void_p, c_void_p]),
+    "adasplash2_debug_waits": (c_int32, [c_int64, c_int32]),
     "adasplash2_resolved_path": (c_int32, [POINTER(AttnShape)]),
     "adasplash_launch_count": (c_int64, []),
     "adasplash_last_error_string": (c_char_p, []),

@@ -158,11 +158,11 @@ static int solve_common(const void* q, const void* k, const void* varlen, float*
   if (e != cudaSuccess) { set_error("%s: memset bitmap: %s", who, cudaGetErrorString(e)); return ADS_ERR_CUDA; }
   if (int rc = clear_status(ws, ws_bytes, st, who)) return rc;
   if (path == ADS_PATH_TCGEN05) {
-    if (ws == nullptr || ws_bytes < sm100::workspace_bytes(s)) {
-      set_error("%s: workspace too small (%zu < %zu)", who, ws_bytes, sm100::workspace_bytes(s));
+    if (ws == nullptr || ws_bytes < sm100::min_workspace_bytes()) {
+      set_error("%s: workspace too small (%zu < %zu)", who, ws_bytes, sm100::min_workspace_bytes());
       return ADS_ERR_WORKSPACE;
     }
-    return sm100::solve(p, s->dtype, ws, st);
+    return sm100::solve(p, s->dtype, ws, ws_bytes, st);
   }
   return by_dtype(
       s->dtype, [&] { return simt::launch_solve<float>(p, st); },
@@ -200,8 +200,8 @@ extern "C" int adasplash2_fwd(const void* q, const void* k, const void* v, const
   p.out = out; p.out2 = out2;
   if (int rc = clear_status(ws, ws_bytes, st, who)) return rc;
   if (path == ADS_PATH_TCGEN05) {
-    if (ws == nullptr || ws_bytes < sm100::workspace_bytes(s)) {
-      set_error("%s: workspace too small (%zu < %zu)", who, ws_bytes, sm100::workspace_bytes(s));
+    if (ws == nullptr || ws_bytes < sm100::min_workspace_bytes()) {
+      set_error("%s: workspace too small (%zu < %zu)", who, ws_bytes, sm100::min_workspace_bytes());
       return ADS_ERR_WORKSPACE;
     }
     return sm100::fwd(p, s->dtype, ws, st);
@@ -236,8 +236,8 @@ extern "C" int adasplash2_bwd(const void* q, const void* k, const void* v, const
   p.bmask_t = bmask_t; p.delta = delta; p.dq = dq; p.dk = dk; p.dv = dv;
   if (int rc = clear_status(ws, ws_bytes, st, who)) return rc;
   if (path == ADS_PATH_TCGEN05) {
-    if (ws == nullptr || ws_bytes < sm100::workspace_bytes(s)) {
-      set_error("%s: workspace too small (%zu < %zu)", who, ws_bytes, sm100::workspace_bytes(s));
+    if (ws == nullptr || ws_bytes < sm100::min_workspace_bytes()) {
+      set_error("%s: workspace too small (%zu < %zu)", who, ws_bytes, sm100::min_workspace_bytes());
       return ADS_ERR_WORKSPACE;
     }
     return sm100::bwd(p, s->dtype, ws, st);
@@ -248,8 +248,20 @@ extern "C" int adasplash2_bwd(const void* q, const void* k, const void* v, const
       [&] { return simt::launch_bwd<__nv_bfloat16>(p, st); });
 }
 
+extern "C" int adasplash2_debug_waits(int64_t max_wait_cycles, int32_t withhold_loads) {
+  return sm100::debug_waits((long long)max_wait_cycles, (int)withhold_loads);
+}
+
+namespace ads { int static_scratch_base(void** out); }
+
 extern "C" int adasplash2_check_status(const void* workspace, void* stream) {
-  if (workspace == nullptr) { set_error("check_status: null workspace"); return ADS_ERR_BAD_ARG; }
+  if (workspace == nullptr) {
+    // the caller of adasplash2_bwd_static owns no workspace: read the status word of the
+    // library's built-in scratch on the current device
+    void* base = nullptr;
+    if (int rc = ads::static_scratch_base(&base)) return rc;
+    workspace = base;
+  }
   int host = 0;
   cudaStream_t st = (cudaStream_t)stream;
   cudaError_t e = cudaMemcpyAsync(&host, workspace, sizeof(int), cudaMemcpyDeviceToHost, st);

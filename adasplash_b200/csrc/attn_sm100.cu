@@ -2,6 +2,7 @@
 #include "attn_sm100.cuh"
 
 #include <mutex>
+#include <unordered_map>
 
 #include "sm100_bwd.cuh"
 #include "sm100_fwd.cuh"
@@ -32,12 +33,28 @@ EncodeTiledFn encode_fn() {
 
 constexpr size_t kStatusBytes = 256;
 
+constexpr int kMaxDevices = 128;
+
+// The dynamic shared-memory limit of a kernel is a per-device attribute: set it the first
+// time a kernel is launched on a device, not before every launch.
 template <typename K>
 int set_smem(K kernel, size_t bytes, const char* what) {
+  static std::mutex mu;
+  static size_t done[kMaxDevices] = {};  // per instantiation: bytes already granted on device d
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) dev = -1;
+  if (dev >= 0) {
+    std::lock_guard<std::mutex> lock(mu);
+    if (done[dev] >= bytes) return ADS_OK;
+  }
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
   if (e != cudaSuccess) {
     set_error("%s: cudaFuncSetAttribute(%zu): %s", what, bytes, cudaGetErrorString(e));
     return ADS_ERR_CUDA;
+  }
+  if (dev >= 0) {
+    std::lock_guard<std::mutex> lock(mu);
+    done[dev] = bytes;
   }
   return ADS_OK;
 }
@@ -51,6 +68,7 @@ TcParams to_tc(const simt::Params& p, void* ws) {
   t.dq = p.dq; t.dk = p.dk; t.dv = p.dv;
   t.B = p.B; t.Hq = p.Hq; t.Hkv = p.Hkv; t.N = p.N; t.niter = p.niter; t.bins = p.bins;
   t.n_words = p.n_words; t.rows_padded = p.rows_padded;
+  t.d_true = p.D;
   t.nq = (p.N + kBlockM - 1) / kBlockM;
   t.sm_scale = p.sm_scale;
   t.tau_given = p.tau_given;
@@ -58,12 +76,56 @@ TcParams to_tc(const simt::Params& p, void* ws) {
   return t;
 }
 
+// Number of SMs of the current device = CTAs of the solver that can be resident at once
+// (its shared memory and TMEM leave room for one per SM) = slots of the overflow area.
+int sm_count() {
+  static std::mutex mu;
+  static int count[kMaxDevices] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) { cudaGetLastError(); return 0; }
+  std::lock_guard<std::mutex> lock(mu);
+  if (count[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) { cudaGetLastError(); n = 0; }
+    count[dev] = n;
+  }
+  return count[dev];
+}
+
+size_t round256(size_t v) { return (v + 255) & ~(size_t)255; }
+
+// Workspace: [0, 256) status word; then, for the solver, one flag per slot and the slots of the
+// overflow area of its candidate lists.
+struct WsLayout { size_t flags_off, flags_bytes, spill_off, total; int slots; };
+WsLayout ws_layout(int N) {
+  WsLayout w{kStatusBytes, 0, kStatusBytes, kStatusBytes, 0};
+  const int sms = sm_count();
+  if (N >= 2048 && sms > 0) {  // shorter sequences: a CTA has few key tiles, full sweeps cost little
+    w.slots = sms;
+    w.flags_bytes = round256((size_t)sms * sizeof(int));
+    w.spill_off = w.flags_off + w.flags_bytes;
+    w.total = w.spill_off + (size_t)sms * kSpillSlotBytes;
+  }
+  return w;
+}
+
 template <typename T, int D>
-int solve_t(const simt::Params& p, void* ws, cudaStream_t st) {
+int solve_t(const simt::Params& p, void* ws, size_t ws_bytes, cudaStream_t st) {
   CUtensorMap tmQ, tmK;
-  if (int rc = make_tmap(&tmQ, p.q, p.B * p.Hq, p.N, D, kBlockM)) return rc;
-  if (int rc = make_tmap(&tmK, p.k, p.B * p.Hkv, p.N, D, kBlockN)) return rc;
+  if (int rc = make_tmap(&tmQ, p.q, p.B * p.Hq, p.N, p.D, kBlockM)) return rc;
+  if (int rc = make_tmap(&tmK, p.k, p.B * p.Hkv, p.N, p.D, kBlockN)) return rc;
   TcParams t = to_tc(p, ws);
+  const WsLayout w = ws_layout(p.N);
+  if (w.slots > 0 && ws_bytes >= w.total && !p.tau_given) {
+    // a workspace of the full size carries the overflow area; with the 256-byte minimum the
+    // solver works without it (full sweeps when its shared-memory lists overflow)
+    t.spill_flags = (int*)((uint8_t*)ws + w.flags_off);
+    t.spill = (uint4*)((uint8_t*)ws + w.spill_off);
+    t.spill_slots = w.slots;
+    t.spill_chunks = kSpillChunksPerSlot;
+    cudaError_t e = cudaMemsetAsync(t.spill_flags, 0, w.flags_bytes, st);
+    if (e != cudaSuccess) { set_error("sm100::solve: memset: %s", cudaGetErrorString(e)); return ADS_ERR_CUDA; }
+  }
   size_t sm = SolveSmem<D>::bytes(p.n_words);
   if (sm > 227 * 1024) { set_error("sm100::solve: sequence too long for the bitmap staging (%zu B smem)", sm); return ADS_ERR_UNSUPPORTED; }
   if (int rc = set_smem(solve_kernel<T, D>, sm, "sm100::solve")) return rc;
@@ -75,9 +137,9 @@ int solve_t(const simt::Params& p, void* ws, cudaStream_t st) {
 template <typename T, int D>
 int fwd_t(const simt::Params& p, void* ws, cudaStream_t st) {
   CUtensorMap tmQ, tmK, tmV;
-  if (int rc = make_tmap(&tmQ, p.q, p.B * p.Hq, p.N, D, kBlockM)) return rc;
-  if (int rc = make_tmap(&tmK, p.k, p.B * p.Hkv, p.N, D, kBlockN)) return rc;
-  if (int rc = make_tmap(&tmV, p.v, p.B * p.Hkv, p.N, D, kBlockN)) return rc;
+  if (int rc = make_tmap(&tmQ, p.q, p.B * p.Hq, p.N, p.D, kBlockM)) return rc;
+  if (int rc = make_tmap(&tmK, p.k, p.B * p.Hkv, p.N, p.D, kBlockN)) return rc;
+  if (int rc = make_tmap(&tmV, p.v, p.B * p.Hkv, p.N, p.D, kBlockN)) return rc;
   TcParams t = to_tc(p, ws);
   size_t sm = FwdSmem<D>::bytes;
   if (int rc = set_smem(fwd_kernel<T, D>, sm, "sm100::fwd")) return rc;
@@ -89,6 +151,7 @@ int fwd_t(const simt::Params& p, void* ws, cudaStream_t st) {
 template <typename T>
 int fwd_d(const simt::Params& p, void* ws, cudaStream_t st) {
   switch (p.D) {
+    case 16: case 32:  // zero-padded to 64 columns by the TMA loads
     case 64: return fwd_t<T, 64>(p, ws, st);
     case 128: return fwd_t<T, 128>(p, ws, st);
   }
@@ -104,7 +167,7 @@ int bwd_t(const simt::Params& p, void* ws, cudaStream_t st) {
     const long long per_block = (long long)(simt::kDeltaThreads / 32) * simt::delta_rows_per_warp<T>(p.D);
     unsigned grid = (unsigned)((rows + per_block - 1) / per_block);
     simt::bwd_delta_kernel<T><<<grid, simt::kDeltaThreads, 0, st>>>((const T*)p.out2_in, (const T*)p.dout, p.delta,
-                                                    p.varlen, p.varlen_is_i64, p.B, p.Hq, p.N, D);
+                                                    p.varlen, p.varlen_is_i64, p.B, p.Hq, p.N, p.D);
     if (int rc = check_launch("sm100::bwd_delta")) return rc;
   }
   if (stages & ADS_BWD_TRANSPOSE) {
@@ -114,12 +177,12 @@ int bwd_t(const simt::Params& p, void* ws, cudaStream_t st) {
     if (int rc = check_launch("sm100::transpose_bitmap")) return rc;
   }
   CUtensorMap tmQ, tmDO, tmK, tmV, tmQ64, tmDO64;
-  if (int rc = make_tmap(&tmQ, p.q, p.B * p.Hq, p.N, D, kBlockM)) return rc;
-  if (int rc = make_tmap(&tmDO, p.dout, p.B * p.Hq, p.N, D, kBlockM)) return rc;
-  if (int rc = make_tmap(&tmK, p.k, p.B * p.Hkv, p.N, D, kBlockN)) return rc;
-  if (int rc = make_tmap(&tmV, p.v, p.B * p.Hkv, p.N, D, kBlockN)) return rc;
-  if (int rc = make_tmap(&tmQ64, p.q, p.B * p.Hq, p.N, D, kQBlock)) return rc;
-  if (int rc = make_tmap(&tmDO64, p.dout, p.B * p.Hq, p.N, D, kQBlock)) return rc;
+  if (int rc = make_tmap(&tmQ, p.q, p.B * p.Hq, p.N, p.D, kBlockM)) return rc;
+  if (int rc = make_tmap(&tmDO, p.dout, p.B * p.Hq, p.N, p.D, kBlockM)) return rc;
+  if (int rc = make_tmap(&tmK, p.k, p.B * p.Hkv, p.N, p.D, kBlockN)) return rc;
+  if (int rc = make_tmap(&tmV, p.v, p.B * p.Hkv, p.N, p.D, kBlockN)) return rc;
+  if (int rc = make_tmap(&tmQ64, p.q, p.B * p.Hq, p.N, p.D, kQBlock)) return rc;
+  if (int rc = make_tmap(&tmDO64, p.dout, p.B * p.Hq, p.N, p.D, kQBlock)) return rc;
   TcParams t = to_tc(p, ws);
   if (stages & ADS_BWD_DQ) {
     size_t sm = DqSmem<D>::bytes;
@@ -141,6 +204,7 @@ int bwd_t(const simt::Params& p, void* ws, cudaStream_t st) {
 template <typename T>
 int bwd_d(const simt::Params& p, void* ws, cudaStream_t st) {
   switch (p.D) {
+    case 16: case 32:
     case 64: return bwd_t<T, 64>(p, ws, st);
     case 128: return bwd_t<T, 128>(p, ws, st);
   }
@@ -149,10 +213,11 @@ int bwd_d(const simt::Params& p, void* ws, cudaStream_t st) {
 }
 
 template <typename T>
-int solve_d(const simt::Params& p, void* ws, cudaStream_t st) {
+int solve_d(const simt::Params& p, void* ws, size_t ws_bytes, cudaStream_t st) {
   switch (p.D) {
-    case 64: return solve_t<T, 64>(p, ws, st);
-    case 128: return solve_t<T, 128>(p, ws, st);
+    case 16: case 32:
+    case 64: return solve_t<T, 64>(p, ws, ws_bytes, st);
+    case 128: return solve_t<T, 128>(p, ws, ws_bytes, st);
   }
   set_error("sm100: head dim %d not built", p.D);
   return ADS_ERR_UNSUPPORTED;
@@ -160,7 +225,33 @@ int solve_d(const simt::Params& p, void* ws, cudaStream_t st) {
 
 }  // namespace
 
+// Encoded tensor maps are a pure function of (base, heads, N, D, box rows): keep the last few
+// hundred so that repeated calls on the same tensors (training steps, benchmarks, graph replays)
+// skip the driver call.  A map holds no reference to the memory, so a stale entry is harmless: the
+// same key always encodes the same map.
+struct TmapKey {
+  const void* base; int heads, N, D, box_rows;
+  bool operator==(const TmapKey& o) const {
+    return base == o.base && heads == o.heads && N == o.N && D == o.D && box_rows == o.box_rows;
+  }
+};
+struct TmapKeyHash {
+  size_t operator()(const TmapKey& k) const {
+    size_t h = std::hash<const void*>()(k.base);
+    for (int v : {k.heads, k.N, k.D, k.box_rows}) h = h * 1000003u ^ std::hash<int>()(v);
+    return h;
+  }
+};
+
 int make_tmap(CUtensorMap* map, const void* base, int heads, int N, int D, int box_rows) {
+  static std::mutex mu;
+  static std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash> cache;
+  const TmapKey key{base, heads, N, D, box_rows};
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) { *map = it->second; return ADS_OK; }
+  }
   EncodeTiledFn fn = encode_fn();
   if (fn == nullptr) { set_error("cuTensorMapEncodeTiled not available from the driver"); return ADS_ERR_CUDA; }
   if (((uintptr_t)base & 15) != 0) { set_error("tensor base %p is not 16-byte aligned", base); return ADS_ERR_BAD_ARG; }
@@ -172,21 +263,37 @@ int make_tmap(CUtensorMap* map, const void* base, int heads, int N, int D, int b
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled failed (%d)", (int)r); return ADS_ERR_CUDA; }
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (cache.size() >= 512) cache.clear();
+    cache.emplace(key, *map);
+  }
+  return ADS_OK;
+}
+
+// Test hook behind adasplash2_debug_waits: wait limit (SM clocks) and "issue no streamed loads"
+// flag of the tensor-core kernels on the current device.
+int debug_waits(long long max_wait_cycles, int withhold_loads) {
+  if (max_wait_cycles <= 0) max_wait_cycles = ptx::kMaxWaitCycles;
+  cudaError_t e = cudaMemcpyToSymbol(ptx::c_wait_limit, &max_wait_cycles, sizeof(max_wait_cycles));
+  if (e == cudaSuccess) e = cudaMemcpyToSymbol(ptx::c_withhold_loads, &withhold_loads, sizeof(withhold_loads));
+  if (e != cudaSuccess) { set_error("debug_waits: %s", cudaGetErrorString(e)); return ADS_ERR_CUDA; }
   return ADS_OK;
 }
 
 bool supported(const ads_attn_shape* s) {
   if (s->dtype != ADS_F16 && s->dtype != ADS_BF16) return false;
-  if (s->D != 64 && s->D != 128) return false;
+  if (s->D != 16 && s->D != 32 && s->D != 64 && s->D != 128) return false;
   if (s->N > 262144) return false;
   return true;
 }
 
-size_t workspace_bytes(const ads_attn_shape*) { return kStatusBytes; }
+size_t workspace_bytes(const ads_attn_shape* s) { return ws_layout(s->N).total; }
+size_t min_workspace_bytes() { return kStatusBytes; }
 
-int solve(const simt::Params& p, int dtype, void* ws, cudaStream_t st) {
-  if (dtype == ADS_F16) return solve_d<__half>(p, ws, st);
-  return solve_d<__nv_bfloat16>(p, ws, st);
+int solve(const simt::Params& p, int dtype, void* ws, size_t ws_bytes, cudaStream_t st) {
+  if (dtype == ADS_F16) return solve_d<__half>(p, ws, ws_bytes, st);
+  return solve_d<__nv_bfloat16>(p, ws, ws_bytes, st);
 }
 
 int fwd(const simt::Params& p, int dtype, void* ws, cudaStream_t st) {

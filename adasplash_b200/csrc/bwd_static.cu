@@ -23,7 +23,9 @@ std::mutex g_scratch_mu;
 inline size_t round256(size_t v) { return (v + 255) & ~(size_t)255; }
 
 // `g_static_scratch` in host code is only a handle for the symbol, not a device
-// address; the address on the current device comes from the runtime, once.
+// address; the address on the current device comes from the runtime, once.  The cached
+// address belongs to the device's primary context: it is valid as long as that context
+// lives (a cudaDeviceReset in the host program invalidates it).
 int static_scratch_address(unsigned char** out) {
   int dev = -1;
   cudaError_t e = cudaGetDevice(&dev);
@@ -47,12 +49,29 @@ int static_scratch_address(unsigned char** out) {
 
 }  // namespace
 
+// Address of the built-in scratch on the current device (the status word of the backward's
+// bounded waits sits at its start); used by adasplash2_check_status(NULL, stream).
+namespace ads {
+int static_scratch_base(void** out) {
+  unsigned char* base = nullptr;
+  if (int rc = static_scratch_address(&base)) return rc;
+  *out = base;
+  return ADS_OK;
+}
+}  // namespace ads
+
 extern "C" int adasplash2_bwd_static(const void* q, const void* k, const void* v, const void* dout,
                                      const void* out2, const void* varlen, const float* taus,
                                      const int32_t* bmask, void* dq, void* dk, void* dv,
                                      const ads_attn_shape* shape, void* stream) {
   if (shape == nullptr || shape->B < 1 || shape->Hq < 1 || shape->N < 1) {
     ads::set_error("adasplash2_bwd_static: bad shape");
+    return ADS_ERR_BAD_ARG;
+  }
+  if (shape->bwd_stages != 0) {
+    // a partial backward would read delta / the transposed mask that an earlier call, possibly
+    // of another shape, left in the shared array
+    ads::set_error("adasplash2_bwd_static: bwd_stages must be 0 (the whole backward)");
     return ADS_ERR_BAD_ARG;
   }
   int32_t rows_padded = 0, n_words = 0;

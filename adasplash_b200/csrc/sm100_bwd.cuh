@@ -93,11 +93,12 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   const int kvh = h / (p.Hq / p.Hkv);
   const int len = load_len(p.varlen, p.varlen_is_i64, b, p.N);
   const int m0 = qt * kBlockM;
-  T* dqg = (T*)p.dq + (size_t)bh * p.N * D;
+  const int Dg = p.d_true;  // head dim in global memory (16 / 32 run the D = 64 instantiation)
+  T* dqg = (T*)p.dq + (size_t)bh * p.N * Dg;
   if (m0 >= len) {
-    for (int v = threadIdx.x; v < kBlockM * (D / 8); v += kDqThreads) {
-      const int rr = m0 + v / (D / 8);
-      if (rr < p.N) reinterpret_cast<uint4*>(dqg + (size_t)rr * D)[v % (D / 8)] = make_uint4(0, 0, 0, 0);
+    for (int v = threadIdx.x; v < kBlockM * (Dg / 8); v += kDqThreads) {
+      const int rr = m0 + v / (Dg / 8);
+      if (rr < p.N) reinterpret_cast<uint4*>(dqg + (size_t)rr * Dg)[v % (Dg / 8)] = make_uint4(0, 0, 0, 0);
     }
     return;
   }
@@ -149,7 +150,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       TileScan scan(bm_head, qt, T_tiles, p.rows_padded, p.n_words);
       int kt;
       uint32_t flags;
-      for (int j = 0; scan.next(kt, flags); ++j) {
+      for (int j = 0; !ptx::c_withhold_loads && scan.next(kt, flags); ++j) {
         const int ks = j % kDqKStages, vs = j % kDqVStages;
         if (*cta_abort) break;
         if (!ptx::mbar_wait(k_empty + ks, ((j / kDqKStages) & 1) ^ 1)) { raise_abort(cta_abort, p.status, kStTimeoutProducer); break; }
@@ -376,10 +377,11 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
 #pragma unroll
         for (int c = 0; c < 32; c += 2)
           po[c >> 1] = row_ok ? pack2<T>(fo[c] * p.sm_scale, fo[c + 1] * p.sm_scale) : 0u;
-        uint4* dst = reinterpret_cast<uint4*>(dqg + (size_t)row * D + ch * 32);
+        uint4* dst = reinterpret_cast<uint4*>(dqg + (size_t)row * Dg + ch * 32);
         if (row < p.N) {
 #pragma unroll
-          for (int q4 = 0; q4 < 4; ++q4) dst[q4] = make_uint4(po[q4 * 4], po[q4 * 4 + 1], po[q4 * 4 + 2], po[q4 * 4 + 3]);
+          for (int q4 = 0; q4 < 4; ++q4)
+            if (ch * 32 + q4 * 8 < Dg) dst[q4] = make_uint4(po[q4 * 4], po[q4 * 4 + 1], po[q4 * 4 + 2], po[q4 * 4 + 3]);
         }
       }
     }
@@ -498,14 +500,15 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
   const int G = p.Hq / p.Hkv;
   const int len = load_len(p.varlen, p.varlen_is_i64, b, p.N);
   const int n0 = nt * kBlockN;
-  T* dkg = (T*)p.dk + (size_t)bkv * p.N * D;
-  T* dvg = (T*)p.dv + (size_t)bkv * p.N * D;
+  const int Dg = p.d_true;  // head dim in global memory (16 / 32 run the D = 64 instantiation)
+  T* dkg = (T*)p.dk + (size_t)bkv * p.N * Dg;
+  T* dvg = (T*)p.dv + (size_t)bkv * p.N * Dg;
   if (n0 >= len) {
-    for (int v = threadIdx.x; v < kBlockN * (D / 8); v += kDkvThreads) {
-      const int rr = n0 + v / (D / 8);
+    for (int v = threadIdx.x; v < kBlockN * (Dg / 8); v += kDkvThreads) {
+      const int rr = n0 + v / (Dg / 8);
       if (rr < p.N) {
-        reinterpret_cast<uint4*>(dkg + (size_t)rr * D)[v % (D / 8)] = make_uint4(0, 0, 0, 0);
-        reinterpret_cast<uint4*>(dvg + (size_t)rr * D)[v % (D / 8)] = make_uint4(0, 0, 0, 0);
+        reinterpret_cast<uint4*>(dkg + (size_t)rr * Dg)[v % (Dg / 8)] = make_uint4(0, 0, 0, 0);
+        reinterpret_cast<uint4*>(dvg + (size_t)rr * Dg)[v % (Dg / 8)] = make_uint4(0, 0, 0, 0);
       }
     }
     return;
@@ -570,7 +573,7 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
     bool have = scan.next(g, m, flags);
     float td[4] = {0.f, 0.f, 0.f, 0.f};
     if (have) fetch_td(g, m, td);
-    bool ok = true;
+    bool ok = !ptx::c_withhold_loads;
     for (int j = 0; ok && have; ++j) {
       const int st = j % kDkvStages;
       const int qh = b * p.Hq + kvh * G + g;
@@ -819,14 +822,16 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
           ok_[c >> 1] = key_ok ? pack2<T>(fk[c] * p.sm_scale, fk[c + 1] * p.sm_scale) : 0u;
           ov_[c >> 1] = key_ok ? pack2<T>(fv[c], fv[c + 1]) : 0u;
         }
-        uint4* dst = reinterpret_cast<uint4*>(dkg + (size_t)key * D + ch * 32);
-        uint4* dst2 = reinterpret_cast<uint4*>(dvg + (size_t)key * D + ch * 32);
+        uint4* dst = reinterpret_cast<uint4*>(dkg + (size_t)key * Dg + ch * 32);
+        uint4* dst2 = reinterpret_cast<uint4*>(dvg + (size_t)key * Dg + ch * 32);
         if (key < p.N) {
 #pragma unroll
           for (int q4 = 0; q4 < 4; ++q4) {
-          dst[q4] = make_uint4(ok_[q4 * 4], ok_[q4 * 4 + 1], ok_[q4 * 4 + 2], ok_[q4 * 4 + 3]);
-          dst2[q4] = make_uint4(ov_[q4 * 4], ov_[q4 * 4 + 1], ov_[q4 * 4 + 2], ov_[q4 * 4 + 3]);
-        }
+            if (ch * 32 + q4 * 8 < Dg) {
+              dst[q4] = make_uint4(ok_[q4 * 4], ok_[q4 * 4 + 1], ok_[q4 * 4 + 2], ok_[q4 * 4 + 3]);
+              dst2[q4] = make_uint4(ov_[q4 * 4], ov_[q4 * 4 + 1], ov_[q4 * 4 + 2], ov_[q4 * 4 + 3]);
+            }
+          }
         }
       }
     }

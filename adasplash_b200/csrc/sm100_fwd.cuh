@@ -104,15 +104,19 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
   const int kvh = h / (p.Hq / p.Hkv);
   const int len = load_len(p.varlen, p.varlen_is_i64, b, p.N);
   const int m0 = qt * kBlockM;
-  T* og = (T*)p.out + (size_t)bh * p.N * D;
-  T* o2g = (T*)p.out2 + (size_t)bh * p.N * D;
+  // Dg = head dim of the tensors in global memory (p.d_true).  It equals D except for head dims
+  // 16 and 32, which run the D = 64 instantiation: TMA fills the missing columns of every tile
+  // with zeros (they add nothing to any product) and only the first Dg columns are stored.
+  const int Dg = p.d_true;
+  T* og = (T*)p.out + (size_t)bh * p.N * Dg;
+  T* o2g = (T*)p.out2 + (size_t)bh * p.N * Dg;
   if (m0 >= len) {
     // fully padded query tile: its output rows are zero
-    for (int v = threadIdx.x; v < kBlockM * (D / 8); v += kFwdThreads) {
-      const int rr = m0 + v / (D / 8);
+    for (int v = threadIdx.x; v < kBlockM * (Dg / 8); v += kFwdThreads) {
+      const int rr = m0 + v / (Dg / 8);
       if (rr < p.N) {
-        reinterpret_cast<uint4*>(og + (size_t)rr * D)[v % (D / 8)] = make_uint4(0, 0, 0, 0);
-        reinterpret_cast<uint4*>(o2g + (size_t)rr * D)[v % (D / 8)] = make_uint4(0, 0, 0, 0);
+        reinterpret_cast<uint4*>(og + (size_t)rr * Dg)[v % (Dg / 8)] = make_uint4(0, 0, 0, 0);
+        reinterpret_cast<uint4*>(o2g + (size_t)rr * Dg)[v % (Dg / 8)] = make_uint4(0, 0, 0, 0);
       }
     }
     return;
@@ -163,7 +167,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       TileScan scan(bm_head, qt, T_tiles, p.rows_padded, p.n_words);
       int kt;
       uint32_t flags;
-      for (int j = 0; scan.next(kt, flags); ++j) {
+      for (int j = 0; !ptx::c_withhold_loads && scan.next(kt, flags); ++j) {
         const int ks = j % kFwdKStages, vs = j % kFwdVStages;
         if (*cta_abort) break;
         if (!ptx::mbar_wait(k_empty + ks, ((j / kFwdKStages) & 1) ^ 1)) { raise_abort(cta_abort, p.status, kStTimeoutProducer); break; }
@@ -366,14 +370,16 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
           po[c >> 1] = row_ok ? pack2<T>(fo[c], fo[c + 1]) : 0u;
           po2[c >> 1] = row_ok ? pack2<T>(fo2[c] * inv, fo2[c + 1] * inv) : 0u;
         }
-        uint4* dst = reinterpret_cast<uint4*>(og + (size_t)row * D + ch * 32);
-        uint4* dst2 = reinterpret_cast<uint4*>(o2g + (size_t)row * D + ch * 32);
+        uint4* dst = reinterpret_cast<uint4*>(og + (size_t)row * Dg + ch * 32);
+        uint4* dst2 = reinterpret_cast<uint4*>(o2g + (size_t)row * Dg + ch * 32);
         if (row < p.N) {
 #pragma unroll
           for (int q4 = 0; q4 < 4; ++q4) {
-          dst[q4] = make_uint4(po[q4 * 4], po[q4 * 4 + 1], po[q4 * 4 + 2], po[q4 * 4 + 3]);
-          dst2[q4] = make_uint4(po2[q4 * 4], po2[q4 * 4 + 1], po2[q4 * 4 + 2], po2[q4 * 4 + 3]);
-        }
+            if (ch * 32 + q4 * 8 < Dg) {
+              dst[q4] = make_uint4(po[q4 * 4], po[q4 * 4 + 1], po[q4 * 4 + 2], po[q4 * 4 + 3]);
+              dst2[q4] = make_uint4(po2[q4 * 4], po2[q4 * 4 + 1], po2[q4 * 4 + 2], po2[q4 * 4 + 3]);
+            }
+          }
         }
       }
     }

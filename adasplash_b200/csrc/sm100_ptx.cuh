@@ -59,15 +59,21 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait: gives up after kMaxWaitCycles SM clocks (about 0.1 s; a healthy
-// kernel waits microseconds) and returns false, so a protocol bug surfaces as an
-// error status instead of a hung GPU.
+// Bounded wait: gives up after c_wait_limit SM clocks (2^28, about 0.1 s, unless the test
+// hook adasplash2_debug_waits shortened it; a healthy kernel waits microseconds) and
+// returns false, so a protocol bug surfaces as an error status instead of a hung GPU.
+// The limit is read on the slow path only.
 constexpr long long kMaxWaitCycles = 1ll << 28;
+__constant__ long long c_wait_limit = kMaxWaitCycles;
+// Test hook: when non-zero the TMA producer warps issue no streamed loads, so that the
+// first wait for one runs into its limit (the only way the give-up path is exercised).
+__constant__ int c_withhold_loads = 0;
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
+  const long long limit = c_wait_limit;
   while (!mbar_try_wait(bar, parity)) {
-    if (clock64() - t0 > kMaxWaitCycles) return false;
+    if (clock64() - t0 > limit) return false;
   }
   return true;
 }

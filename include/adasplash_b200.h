@@ -80,8 +80,12 @@ int adasplash_entmax_fwd(const void* x, void* y, float* tau_out, int64_t rows, i
 int adasplash_entmax_bwd(const void* y, const void* dy, void* dx, int64_t rows, int64_t cols,
                          float alpha, int32_t fast_math, int32_t dtype, void* stream);
 
-/* Bytes of scratch the attention entry points need for `shape` (forward and
- * backward use the same buffer; 256-byte aligned base expected). */
+/* Bytes of scratch recommended for `shape` on the current device (256-byte aligned base
+ * expected).  Every attention entry point accepts any size >= 256: the first 256 bytes hold
+ * the status word of the bounded device-side waits.  adasplash2_solve uses the rest, when it
+ * is given the full size, as the overflow area of its candidate lists (one 1.25 MiB slot per
+ * SM, about 190 MiB on a B200; only touched for rows whose scores are nearly flat); with less
+ * it still gives the same result and re-computes the score tiles for such rows instead. */
 size_t adasplash2_workspace_bytes(const ads_attn_shape* shape);
 
 /* Number of int32 words of one bitmap tensor (B,Hq,rows_padded,n_words) and its
@@ -146,7 +150,11 @@ int adasplash2_bwd(const void* q, const void* k, const void* v, const void* dout
  *  - all calls on one device share the array and it keeps the previous call's
  *    contents (the backward rewrites every word before reading it); two calls
  *    that overlap on the GPU -- different streams, or graphs replayed
- *    concurrently -- race on it.  Serialise them. */
+ *    concurrently -- race on it.  Serialise them;
+ *  - shape->bwd_stages must be 0 (ADS_ERR_BAD_ARG otherwise): a partial backward would read
+ *    what an earlier call left in the array;
+ *  - adasplash2_check_status(NULL, stream) reads the status word of this array;
+ *  - the cached address lives as long as the device's primary context. */
 #define ADS_STATIC_SCRATCH_BYTES (8u << 20)
 int adasplash2_bwd_static(const void* q, const void* k, const void* v, const void* dout,
                           const void* out2, const void* varlen, const float* taus,
@@ -155,9 +163,19 @@ int adasplash2_bwd_static(const void* q, const void* k, const void* v, const voi
 
 /* Debug aid, the one entry point that synchronises: waits for `stream`, reads
  * the status word that the tensor-core kernels keep at the start of `workspace`
+ * (NULL = the built-in scratch of adasplash2_bwd_static on the current device)
  * and returns ADS_ERR_TIMEOUT if a bounded device-side wait gave up (the code is
  * in the error string), ADS_OK otherwise.  No counterpart in the reference. */
 int adasplash2_check_status(const void* workspace, void* stream);
+
+/* Test hook for the give-up path of the bounded waits (no counterpart in the reference).
+ * Sets, on the current device, the wait limit of the tensor-core kernels in SM clocks
+ * (<= 0 restores the default 2^28) and whether their producer warps withhold the streamed
+ * TMA loads, so that a wait runs into the limit: the kernel then records its code in the
+ * status word, drains, frees its TMEM and returns; adasplash2_check_status reports
+ * ADS_ERR_TIMEOUT.  Synchronous (two small copies to constant memory); call it with no
+ * kernel of this library in flight, and restore (0, 0) afterwards. */
+int adasplash2_debug_waits(int64_t max_wait_cycles, int32_t withhold_loads);
 
 /* Which kernel family `ADS_PATH_AUTO` resolves to for `shape`
  * (ADS_PATH_SIMT or ADS_PATH_TCGEN05). */

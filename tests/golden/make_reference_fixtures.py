@@ -5,11 +5,14 @@ script is run once on a B200 box with the unmodified reference installed under
 baseline/_ref (``python -m pip install --no-index --no-build-isolation --no-deps
 --target baseline/_ref <reference checkout>``; that folder is git-ignored):
 
-    python tests/golden/make_reference_fixtures.py --out tests/golden [--time]
+    python tests/golden/make_reference_fixtures.py --out tests/golden [--time] [--big-slices]
 
 Inputs are drawn from seeded CPU generators and stored with the outputs, so the
-tests never need the reference.  ``--time`` additionally times the reference's
-kernels (CUDA events, median of 20 after warm-up) and writes
+tests never need the reference.  ``--big-slices`` writes the fixtures at the
+sequence lengths of the benchmark configurations (inputs are regenerated from the
+stored seed, outputs are kept for every ``row_stride``-th row, thresholds and
+block masks in full).  ``--time`` additionally times the reference's kernels
+(CUDA events, median after warm-up) and merges the result into
 ``reference_timings.json``.
 """
 from __future__ import annotations
@@ -40,6 +43,17 @@ ATTN_CASES = {
     "v2_fp16_d64": (1, 1, 1, 256, 64, torch.float16, 1.0, 1, None),
     "v2_bf16_d128_n2048": (1, 1, 1, 2048, 128, torch.bfloat16, 1.5, 1, None),
 }
+
+# Slices of the benchmark configurations: same sequence length, head dim, dtype, input scale
+# and niter, few heads.  name: (B, Hq, Hkv, N, D, input scale, niter, varlen, row_stride)
+BIG_CASES = {
+    "v2_bf16_c3_slice": (1, 2, 2, 8192, 128, 1.5, 1, None, 32),
+    # 4-bin histogram (N >= 16384), grouped-query heads, one full and one short sequence
+    "v2_bf16_c4_slice": (2, 4, 1, 16384, 128, 1.0, 1, [16384, 5000], 128),
+    "v2_bf16_c5_slice": (1, 1, 1, 65536, 128, 1.5, 1, None, 128),
+}
+BIG_ROW_OFFSET = 5
+BIG_SEED0 = 5000
 
 V1_CASES = {
     # name: (alpha, is_causal)
@@ -83,6 +97,45 @@ def make_attention(adasplash, out_dir):
             fx["row_stride"] = 8
         torch.save(fx, os.path.join(out_dir, name + ".pt"))
         print("wrote", name, flush=True)
+
+
+def big_case_inputs(name):
+    """q, k, v, dO, varlen of a BIG_CASES entry (CPU tensors); the tests call this too."""
+    idx = list(BIG_CASES).index(name)
+    B, Hq, Hkv, N, D, sc, niter, vl, stride = BIG_CASES[name]
+    seed = BIG_SEED0 + 10 * idx
+    dt = torch.bfloat16
+    q = _gen((B, Hq, N, D), seed, sc, dt)
+    k = _gen((B, Hkv, N, D), seed + 1, sc, dt)
+    v = _gen((B, Hkv, N, D), seed + 2, sc, dt)
+    do = _gen((B, Hq, N, D), seed + 3, 1.0, dt)
+    varlen = None if vl is None else torch.tensor(vl, dtype=torch.int32)
+    if varlen is not None:
+        do = do * (torch.arange(N)[None, None, :, None] < varlen[:, None, None, None])
+    return q, k, v, do, varlen, niter, stride
+
+
+def make_big_slices(adasplash, out_dir, only=None):
+    for name in BIG_CASES:
+        if only and name not in only:
+            continue
+        q, k, v, do, varlen, niter, stride = big_case_inputs(name)
+        qc, kc, vc = (t.cuda().requires_grad_(True) for t in (q, k, v))
+        out = adasplash.adasplash_v2(qc, kc, vc, niter=niter,
+                                     varlen=None if varlen is None else varlen.cuda())
+        saved = out.grad_fn.saved_tensors
+        out2, taus, bmask = saved[3], saved[4], saved[5]
+        dq, dk, dv = torch.autograd.grad(out, (qc, kc, vc), do.cuda())
+        rows = slice(BIG_ROW_OFFSET, None, stride)
+        fx = {"case": name, "row_stride": stride, "row_offset": BIG_ROW_OFFSET, "niter": niter,
+              "varlen": varlen, "taus": taus.cpu(), "bmask": bmask.cpu()}
+        for key, t in (("out", out.detach()), ("out2", out2), ("dq", dq), ("dk", dk), ("dv", dv)):
+            fx[key] = t[:, :, rows].contiguous().cpu()
+            fx[key + "_absmax"] = float(t.float().abs().max())
+        torch.save(fx, os.path.join(out_dir, name + ".pt"))
+        print("wrote", name, flush=True)
+        del qc, kc, vc, out, dq, dk, dv
+        torch.cuda.empty_cache()
 
 
 def make_v1(adasplash, out_dir):
@@ -142,57 +195,86 @@ def _time(fn, reps=20, warm=3):
     return ts[len(ts) // 2]
 
 
-def time_reference(adasplash, out_dir, big, skip_rowwise=False):
-    res = {"device": torch.cuda.get_device_name(0), "torch": torch.__version__}
+def _time_attention_case(adasplash, res, tag, B, Hq, Hkv, N, D, sc, reps, varlen_seed=None):
+    g = torch.Generator(device="cuda").manual_seed(1234)
+
+    def rn(shape, s):
+        return (torch.randn(shape, device="cuda", generator=g) * s).bfloat16()
+    q, k, v = (rn((B, h, N, D), sc).requires_grad_(True) for h in (Hq, Hkv, Hkv))
+    do = rn((B, Hq, N, D), 1.0)
+    varlen = None
+    if varlen_seed is not None:
+        gc = torch.Generator().manual_seed(varlen_seed)
+        varlen = torch.randint(N // 4, N + 1, (B,), generator=gc, dtype=torch.int32)
+        res[tag + "_varlen"] = [int(x) for x in varlen]
+        do = do * (torch.arange(N, device="cuda")[None, None, :, None] < varlen.cuda()[:, None, None, None])
+        varlen = varlen.cuda()
+    t0 = time.time()
+    out = adasplash.adasplash_v2(q, k, v, niter=1, varlen=varlen)
+    bm = out.grad_fn.saved_tensors[5][0, 0].clone()
+    torch.autograd.grad(out, (q, k, v), do)
+    torch.cuda.synchronize()
+    res[tag + "_first_call_s"] = time.time() - t0
+    res[tag + "_fwd_ms"] = _time(lambda: adasplash.adasplash_v2(q, k, v, niter=1, varlen=varlen), reps)
+
+    def fb():
+        o = adasplash.adasplash_v2(q, k, v, niter=1, varlen=varlen)
+        torch.autograd.grad(o, (q, k, v), do)
+    res[tag + "_fwdbwd_ms"] = _time(fb, reps)
+    L = N if varlen is None else int(varlen[0])
+    nb = (L + 63) // 64
+    active = sum(bin(int(w) & 0xFFFFFFFF).count("1") for w in bm.flatten().tolist())
+    res[tag + "_block_sparsity_head0"] = 1.0 - active / (nb * (nb + 1) / 2)
+    print(tag, res[tag + "_fwd_ms"], res[tag + "_fwdbwd_ms"], flush=True)
+
+
+TIME_CASES = {
+    # tag: (B, Hq, Hkv, N, D, input scale, reps, varlen seed)
+    "small": ("B1_H2_N256_D64", (1, 2, 2, 256, 64, 1.0, 50, None)),
+    "n4096": ("B1_H8_N4096_D128", (1, 8, 8, 4096, 128, 1.5, 10, None)),
+    "c3": ("C3_B4_H32_N8192_D128", (4, 32, 32, 8192, 128, 1.5, 5, None)),
+    "c4": ("C4_B8_Hq32_Hkv8_N16384_D128_varlen", (8, 32, 8, 16384, 128, 1.0, 3, 20263)),
+    # one (batch, kv-head) shard of the long-context configuration: 1/16 of its work
+    "c5shard": ("C5shard_B1_Hq8_Hkv1_N65536_D128", (1, 8, 1, 65536, 128, 1.5, 3, None)),
+}
+
+
+def time_reference(adasplash, out_dir, cases):
+    path = os.path.join(out_dir, "reference_timings.json")
+    res = json.load(open(path)) if os.path.exists(path) else {}
+    res.update({"device": torch.cuda.get_device_name(0), "torch": torch.__version__})
     import triton
     res["triton"] = triton.__version__
-    # row-wise, 16384 x 4096 fp32
-    x = (torch.randn(16384, 4096, device="cuda") * 4).requires_grad_(True)
-    dy = torch.randn(16384, 4096, device="cuda")
-    for tag, kw in () if skip_rowwise else (("a15_hist", dict(alpha=1.5, n_iter=2, use_histogram=True)),
-                    ("a2_default", dict(alpha=2.0)), ("a1333", dict(alpha=1.333, use_histogram=False))):
-        y = adasplash.triton_entmax(x, **kw)
-        res["rowwise_fwd_ms_" + tag] = _time(lambda: adasplash.triton_entmax(x, **kw))
-        res["rowwise_bwd_ms_" + tag] = _time(lambda: torch.autograd.grad(y, x, dy, retain_graph=True))
-        print(tag, res["rowwise_fwd_ms_" + tag], res["rowwise_bwd_ms_" + tag], flush=True)
-    del x, dy
-    cfgs = {"B1_H8_N4096_D128": (1, 8, 8, 4096, 128, 1.5, 10)}
-    if big:
-        cfgs["C3_B4_H32_N8192_D128"] = (4, 32, 32, 8192, 128, 1.5, 5)
-    for tag, (B, Hq, Hkv, N, D, sc, reps) in cfgs.items():
-        q = (torch.randn(B, Hq, N, D, device="cuda") * sc).bfloat16().requires_grad_(True)
-        k = (torch.randn(B, Hkv, N, D, device="cuda") * sc).bfloat16().requires_grad_(True)
-        v = (torch.randn(B, Hkv, N, D, device="cuda") * sc).bfloat16().requires_grad_(True)
-        do = torch.randn(B, Hq, N, D, device="cuda").bfloat16()
-        t0 = time.time()
-        out = adasplash.adasplash_v2(q, k, v, niter=1)
-        bm = out.grad_fn.saved_tensors[5].clone()
-        torch.autograd.grad(out, (q, k, v), do)
-        torch.cuda.synchronize()
-        res[tag + "_first_call_s"] = time.time() - t0
-        res[tag + "_fwd_ms"] = _time(lambda: adasplash.adasplash_v2(q, k, v, niter=1), reps)
 
-        def fb():
-            o = adasplash.adasplash_v2(q, k, v, niter=1)
-            torch.autograd.grad(o, (q, k, v), do)
-        res[tag + "_fwdbwd_ms"] = _time(fb, reps)
-        nb = N // 64
-        active = sum(bin(int(w) & 0xFFFFFFFF).count("1") for w in bm[0, 0].flatten().tolist())
-        res[tag + "_block_sparsity_head0"] = 1.0 - active / (nb * (nb + 1) / 2)
-        print(tag, res[tag + "_fwd_ms"], res[tag + "_fwdbwd_ms"], flush=True)
-        del q, k, v, do, out
-        with open(os.path.join(out_dir, "reference_timings.json"), "w") as f:
+    def flush():
+        with open(path, "w") as f:
             json.dump(res, f, indent=1)
+    if "rowwise" in cases:
+        # row-wise, 16384 x 4096 fp32
+        x = (torch.randn(16384, 4096, device="cuda") * 4).requires_grad_(True)
+        dy = torch.randn(16384, 4096, device="cuda")
+        for tag, kw in (("a15_hist", dict(alpha=1.5, n_iter=2, use_histogram=True)),
+                        ("a2_default", dict(alpha=2.0)), ("a1333", dict(alpha=1.333, use_histogram=False))):
+            y = adasplash.triton_entmax(x, **kw)
+            res["rowwise_fwd_ms_" + tag] = _time(lambda: adasplash.triton_entmax(x, **kw))
+            res["rowwise_bwd_ms_" + tag] = _time(lambda: torch.autograd.grad(y, x, dy, retain_graph=True))
+            print(tag, res["rowwise_fwd_ms_" + tag], res["rowwise_bwd_ms_" + tag], flush=True)
+        del x, dy
+        flush()
+    for name, (tag, cfg) in TIME_CASES.items():
+        if name in cases:
+            _time_attention_case(adasplash, res, tag, *cfg)
+            torch.cuda.empty_cache()
+            flush()
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--out", default=os.path.join(ROOT, "tests", "golden"))
     ap.add_argument("--ref", default=os.path.join(ROOT, "baseline", "_ref"))
-    ap.add_argument("--time", action="store_true")
-    ap.add_argument("--big", action="store_true", help="also time the B=4,H=32,N=8192 config")
-    ap.add_argument("--skip-fixtures", action="store_true")
-    ap.add_argument("--skip-rowwise-timing", action="store_true")
+    ap.add_argument("--time", default="", help="comma list of: rowwise," + ",".join(TIME_CASES) + " (or 'all')")
+    ap.add_argument("--skip-fixtures", action="store_true", help="do not rewrite the small fixtures")
+    ap.add_argument("--big-slices", action="store_true", help="write the benchmark-length slice fixtures")
     a = ap.parse_args()
     sys.path.insert(0, a.ref)
     import adasplash
@@ -202,8 +284,12 @@ def main():
         make_rowwise(adasplash, a.out)
         make_attention(adasplash, a.out)
         make_v1(adasplash, a.out)
+    # timing first: the fixtures of the same (sequence length, head dim) then reuse its autotuning
     if a.time:
-        time_reference(adasplash, a.out, a.big, a.skip_rowwise_timing)
+        cases = ["rowwise"] + list(TIME_CASES) if a.time == "all" else a.time.split(",")
+        time_reference(adasplash, a.out, cases)
+    if a.big_slices:
+        make_big_slices(adasplash, a.out)
 
 
 if __name__ == "__main__":

@@ -5,7 +5,9 @@ Tolerances: fp32 1e-4 on out/dq/dk/dv and tau (the reference's own test
 tolerance, tests/test_adasplash_v2.py:94-97); bf16/fp16 max-abs 2e-2 on outputs
 and gradients against the reference; bitmaps bit-exact for identical fp32 tau.
 """
+import json
 import os
+import sys
 
 import pytest
 import torch
@@ -95,7 +97,8 @@ def test_fp32_matches_exact_definition(path, case):
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("case", [(1, 2, 1, 256, 64, None, 1.0), (1, 2, 2, 512, 128, None, 1.5),
                                   (2, 4, 1, 320, 128, [300, 129], 1.0), (1, 1, 1, 192, 64, [191], 1.0),
-                                  (1, 2, 2, 128, 32, None, 1.0)])
+                                  (1, 2, 2, 128, 32, None, 1.0), (2, 4, 2, 200, 16, [200, 77], 1.0),
+                                  (1, 2, 1, 384, 32, [300], 1.5)])
 def test_16bit_matches_trajectory_oracle(path, dtype, case):
     B, Hq, Hkv, N, D, vl, sc = case
     q, k, v = (_randn(s, i, sc, dtype) for i, s in
@@ -193,6 +196,74 @@ def _check_grads_vs_reference(got, fx, tol):
             mine = (got[key].double() - exact[key]).abs().max().item()
             theirs = (ref.double() - exact[key]).abs().max().item()
             assert mine <= 1.25 * theirs + 1e-3, (key, mine, theirs)
+
+
+def _popcount(t):
+    return sum(bin(int(x) & 0xFFFFFFFF).count("1") for x in t.flatten().tolist())
+
+
+def _log_parity(record):
+    """Append the achieved errors of a fixture comparison to the file named by
+    ADASPLASH_PARITY_LOG (one JSON object per line), if that variable is set."""
+    path = os.environ.get("ADASPLASH_PARITY_LOG")
+    if path:
+        with open(path, "a") as f:
+            f.write(json.dumps(record) + "\n")
+
+
+def _strided_fixture(name):
+    """A fixture whose inputs are regenerated from seeds and whose outputs are kept for every
+    `row_stride`-th row (thresholds and block mask in full)."""
+    fpath = os.path.join(GOLD, name + ".pt")
+    if not os.path.exists(fpath):
+        pytest.fail(f"tests/golden/{name}.pt missing (tests/golden/make_reference_fixtures.py --big-slices)")
+    fx = torch.load(fpath, weights_only=False)
+    if "case" in fx:
+        sys.path.insert(0, GOLD)
+        import make_reference_fixtures as mk
+        q, k, v, do, varlen, niter, stride = mk.big_case_inputs(fx["case"])
+    else:  # v2_bf16_d128_n2048: B = Hq = Hkv = 1, seeds seed + 0/100/200/300
+        N, D = fx["taus"].shape[2], fx["out"].shape[3]
+        q, k, v = (_randn((1, 1, N, D), fx["seed"] + 100 * i, fx["scale"], torch.bfloat16) for i in range(3))
+        do = _randn((1, 1, N, D), fx["seed"] + 300, 1.0, torch.bfloat16)
+        varlen, niter = None, fx["niter"]
+    return fx, q, k, v, do, varlen, niter
+
+
+@pytest.mark.parametrize("path", PATHS)
+@pytest.mark.parametrize("name", ["v2_bf16_d128_n2048", "v2_bf16_c3_slice", "v2_bf16_c4_slice",
+                                  "v2_bf16_c5_slice"])
+def test_reference_golden_at_benchmark_lengths(path, name):
+    """Against the reference's own outputs at the sequence lengths of the benchmark
+    configurations (8192; 16384 with grouped heads, a short sequence and the 4-bin histogram;
+    65536).  tau <= 1e-4; block mask equal to the reference's up to bits that a score within
+    rounding of its threshold decides; out, out2, dq, dk, dv within 2e-2 of the tensor's scale."""
+    fx, q, k, v, do, varlen, niter = _strided_fixture(name)
+    _use(path, q)
+    got = _run(q, k, v, do, niter, varlen)
+    B, Hq, N, D = q.shape
+    rec = {"fixture": name, "path": path}
+    tau_err = 0.0
+    for b in range(B):
+        L = N if varlen is None else int(varlen[b])
+        tau_err = max(tau_err, (got["tau"][b, :, :L] - fx["taus"][b, :, :L]).abs().max().item())
+    rec["tau"] = tau_err
+    assert tau_err < 1e-4
+    flips = _popcount(got["bmask"] ^ fx["bmask"])
+    rec["bitmap_flips"] = flips
+    rec["bitmap_bits_set"] = _popcount(fx["bmask"])
+    nb = (N + 63) // 64
+    # a different summation order inside a score may move it across its threshold by an ulp
+    assert flips <= 2 + 1e-5 * B * Hq * nb * nb, flips
+    rows = slice(fx.get("row_offset", 0), None, fx["row_stride"])
+    for key in ("out", "out2", "dq", "dk", "dv"):
+        ref = fx[key].float()
+        scale = max(1.0, fx.get(key + "_absmax", ref.abs().max().item()))
+        err = (got[key][:, :, rows] - ref).abs().max().item()
+        rec[key] = err
+        rec[key + "_scale"] = scale
+        assert err < 2e-2 * scale, (key, err, scale)
+    _log_parity(rec)
 
 
 @pytest.mark.parametrize("path", ["tcgen05"])

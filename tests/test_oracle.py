@@ -107,6 +107,27 @@ def test_v2_oracle_vs_reference_golden(name, tol_out, tol_grad):
             assert (ex[key] - fx[key].double()).abs().max() < 1e-4, key
 
 
+def test_v2_solver_oracle_four_bin_histogram_vs_reference():
+    """N >= 16384 selects the 4-bin histogram (adasplash_v2.py:273-289).  The short sequence of
+    the 16384-long fixture (5000 valid rows) pins that route of the oracle on the CPU: thresholds
+    and block mask of one head against what the reference stored."""
+    import sys
+    fx = _load("v2_bf16_c4_slice")
+    sys.path.insert(0, GOLD)
+    import make_reference_fixtures as mk
+    q, k, v, do, varlen, niter, _ = mk.big_case_inputs("v2_bf16_c4_slice")
+    b, h, L, N = 1, 2, int(varlen[1]), q.shape[2]
+    assert O.select_bins(N) == 4
+    nbL = (L + 63) // 64
+    z = O.v2_scaled_scores(q[b, h, :nbL * 64], k[b, 0, :nbL * 64], L, q.dtype)
+    sol = O.v2_solve_head(z, L, N, niter)
+    assert (sol["tau"][:L] - fx["taus"][b, h, :L]).abs().max() < 1e-5
+    words = O.pack_bitmap(sol["bits"])
+    ref = fx["bmask"][b, h]
+    assert (words[:nbL, :words.shape[1]] == ref[:nbL, :words.shape[1]]).all()
+    assert (ref[nbL:] == 0).all() and (ref[:, words.shape[1]:] == 0).all()
+
+
 @pytest.mark.parametrize("name", ["v1_a1333_causal", "v1_a1333_full", "v1_a15_full", "v1_a2_causal", "v1_a2_full"])
 def test_exact_oracle_vs_reference_v1_golden(name):
     # generic alpha / full attention: the reference's first-generation kernels at niter = 10

@@ -44,11 +44,53 @@ def test_static_backward_matches_ordinary_backward_twice(case):
         rc = lib.adasplash2_bwd_static(ptr(q), ptr(k), ptr(v), ptr(do), ptr(out2), ptr(varlen), ptr(taus),
                                        ptr(bmask), ptr(dq), ptr(dk), ptr(dv), ctypes.byref(shape), st)
         assert rc == 0, lib.adasplash_last_error_string()
+        # the caller owns no workspace: a NULL workspace reads the status word of the built-in array
+        assert lib.adasplash2_check_status(None, st) == 0, lib.adasplash_last_error_string()
         torch.cuda.synchronize()
         # same kernels, same inputs, deterministic: the results must be identical
         tol = 0.0
         for name, a, b in (("dq", dq, ref_dq), ("dk", dk, ref_dk), ("dv", dv, ref_dv)):
             assert (a.float() - b.float()).abs().max().item() <= tol, (trial, name)
+
+
+def test_static_backward_allocates_nothing():
+    """The property the entry point exists for: once its address is cached, a call leaves both
+    torch's allocator counters and the device's free memory untouched."""
+    from adasplash_b200 import _lib, attention as att
+    lib = _lib.load()
+    B, Hq, Hkv, N, D = 1, 2, 1, 256, 64
+    q, k, v, do = (_randn((B, h, N, D), 20 + i) for i, h in enumerate((Hq, Hkv, Hkv, Hq)))
+    taus, bmask = att.solve(q, k, 1, None)
+    out, out2 = att.forward_raw(q, k, v, taus, bmask, None)
+    shape = att.make_shape(q, k, 1, None)
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    st = torch.cuda.current_stream().cuda_stream
+    args = [t.data_ptr() for t in (q, k, v, do, out2)] + [None] + [t.data_ptr() for t in (taus, bmask, dq, dk, dv)]
+
+    def call():
+        assert lib.adasplash2_bwd_static(*args, ctypes.byref(shape), st) == 0, lib.adasplash_last_error_string()
+        torch.cuda.synchronize()
+    call()  # first call on the device: looks up and caches the array's address
+    stats0 = torch.cuda.memory_stats()
+    free0, _ = torch.cuda.mem_get_info()
+    call()
+    free1, _ = torch.cuda.mem_get_info()
+    stats1 = torch.cuda.memory_stats()
+    assert free1 == free0
+    for key in ("allocation.all.allocated", "segment.all.allocated", "allocated_bytes.all.current",
+                "reserved_bytes.all.current"):
+        assert stats1[key] == stats0[key], key
+
+
+def test_static_backward_rejects_partial_backward():
+    from adasplash_b200 import _lib
+    lib = _lib.load()
+    sh = _lib.AttnShape(B=1, Hq=2, Hkv=2, N=128, D=64, dtype=_lib.BF16, niter=1, varlen_is_i64=0, path=0)
+    sh.bwd_stages = 4   # dQ alone would read delta left behind by an earlier call
+    one = torch.zeros(1, device="cuda")
+    p = one.data_ptr()
+    rc = lib.adasplash2_bwd_static(p, p, p, p, p, None, p, p, p, p, p, ctypes.byref(sh), None)
+    assert rc == 1 and b"bwd_stages" in lib.adasplash_last_error_string()
 
 
 def test_static_backward_rejects_oversized_problems():
