@@ -64,19 +64,11 @@ def bitmap_extent(shape):
     return rows.value, words.value
 
 
-MIN_WORKSPACE = 256   # the status word; all that the forward and backward kernels use
-
-
-def _workspace(shape, device, full=False):
-    """Scratch for one call: the recommended size for the solver (`full`; its candidate lists
-    overflow into it), the 256-byte minimum otherwise."""
-    nbytes = MIN_WORKSPACE
-    if full:
-        nbytes = int(_lib.load().adasplash2_workspace_bytes(ctypes.byref(shape)))
-        if nbytes == 0:
-            _lib.check(_lib.load().adasplash2_resolved_path(ctypes.byref(shape)) < 0)
-        nbytes = max(nbytes, MIN_WORKSPACE)
-    return torch.empty(nbytes, device=device, dtype=torch.uint8), nbytes
+def _workspace(shape, device):
+    nbytes = int(_lib.load().adasplash2_workspace_bytes(ctypes.byref(shape)))
+    if nbytes == 0:
+        _lib.check(_lib.load().adasplash2_resolved_path(ctypes.byref(shape)) < 0)
+    return torch.empty(max(nbytes, 256), device=device, dtype=torch.uint8), nbytes
 
 
 DEBUG_STATUS = False  # tests set this: check the device status word after every call (synchronises)
@@ -96,7 +88,7 @@ def solve(q, k, niter=1, varlen=None, path=None, alpha=1.5, is_causal=True):
     taus = torch.empty((B, Hq, N), device=q.device, dtype=torch.float32)
     bmask = torch.empty((B, Hq, rows, words), device=q.device, dtype=torch.int32)
     with torch.cuda.device(q.device):
-        ws, nbytes = _workspace(shape, q.device, full=True)
+        ws, nbytes = _workspace(shape, q.device)
         st = torch.cuda.current_stream().cuda_stream
         _lib.check(lib.adasplash2_solve(_ptr(q), _ptr(k), _ptr(varlen), _ptr(taus), _ptr(bmask),
                                         ctypes.byref(shape), _ptr(ws), nbytes, st))
@@ -136,7 +128,7 @@ class _SparseAttention(torch.autograd.Function):
         out = torch.empty_like(q)
         out2 = torch.empty_like(q)
         with torch.cuda.device(dev):
-            ws, nbytes = _workspace(shape, dev, full=True)
+            ws, nbytes = _workspace(shape, dev)
             st = torch.cuda.current_stream().cuda_stream
             sp = ctypes.byref(shape)
             _lib.check(lib.adasplash2_solve(_ptr(q), _ptr(k), _ptr(varlen), _ptr(taus),

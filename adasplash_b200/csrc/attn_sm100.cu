@@ -36,16 +36,18 @@ constexpr size_t kStatusBytes = 256;
 constexpr int kMaxDevices = 128;
 
 // The dynamic shared-memory limit of a kernel is a per-device attribute: set it the first
-// time a kernel is launched on a device, not before every launch.
+// time a kernel is launched on a device, not before every launch.  (Keyed by the kernel's
+// address: kernels with the same signature share one instantiation of this template.)
 template <typename K>
 int set_smem(K kernel, size_t bytes, const char* what) {
   static std::mutex mu;
-  static size_t done[kMaxDevices] = {};  // per instantiation: bytes already granted on device d
+  static std::unordered_map<const void*, size_t> done[kMaxDevices];  // kernel -> bytes granted on device d
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) dev = -1;
   if (dev >= 0) {
     std::lock_guard<std::mutex> lock(mu);
-    if (done[dev] >= bytes) return ADS_OK;
+    auto it = done[dev].find((const void*)kernel);
+    if (it != done[dev].end() && it->second >= bytes) return ADS_OK;
   }
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
   if (e != cudaSuccess) {
@@ -54,7 +56,7 @@ int set_smem(K kernel, size_t bytes, const char* what) {
   }
   if (dev >= 0) {
     std::lock_guard<std::mutex> lock(mu);
-    done[dev] = bytes;
+    done[dev][(const void*)kernel] = bytes;
   }
   return ADS_OK;
 }
@@ -76,56 +78,12 @@ TcParams to_tc(const simt::Params& p, void* ws) {
   return t;
 }
 
-// Number of SMs of the current device = CTAs of the solver that can be resident at once
-// (its shared memory and TMEM leave room for one per SM) = slots of the overflow area.
-int sm_count() {
-  static std::mutex mu;
-  static int count[kMaxDevices] = {};
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) { cudaGetLastError(); return 0; }
-  std::lock_guard<std::mutex> lock(mu);
-  if (count[dev] == 0) {
-    int n = 0;
-    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) { cudaGetLastError(); n = 0; }
-    count[dev] = n;
-  }
-  return count[dev];
-}
-
-size_t round256(size_t v) { return (v + 255) & ~(size_t)255; }
-
-// Workspace: [0, 256) status word; then, for the solver, one flag per slot and the slots of the
-// overflow area of its candidate lists.
-struct WsLayout { size_t flags_off, flags_bytes, spill_off, total; int slots; };
-WsLayout ws_layout(int N) {
-  WsLayout w{kStatusBytes, 0, kStatusBytes, kStatusBytes, 0};
-  const int sms = sm_count();
-  if (N >= 2048 && sms > 0) {  // shorter sequences: a CTA has few key tiles, full sweeps cost little
-    w.slots = sms;
-    w.flags_bytes = round256((size_t)sms * sizeof(int));
-    w.spill_off = w.flags_off + w.flags_bytes;
-    w.total = w.spill_off + (size_t)sms * kSpillSlotBytes;
-  }
-  return w;
-}
-
 template <typename T, int D>
 int solve_t(const simt::Params& p, void* ws, size_t ws_bytes, cudaStream_t st) {
   CUtensorMap tmQ, tmK;
   if (int rc = make_tmap(&tmQ, p.q, p.B * p.Hq, p.N, p.D, kBlockM)) return rc;
   if (int rc = make_tmap(&tmK, p.k, p.B * p.Hkv, p.N, p.D, kBlockN)) return rc;
   TcParams t = to_tc(p, ws);
-  const WsLayout w = ws_layout(p.N);
-  if (w.slots > 0 && ws_bytes >= w.total && !p.tau_given) {
-    // a workspace of the full size carries the overflow area; with the 256-byte minimum the
-    // solver works without it (full sweeps when its shared-memory lists overflow)
-    t.spill_flags = (int*)((uint8_t*)ws + w.flags_off);
-    t.spill = (uint4*)((uint8_t*)ws + w.spill_off);
-    t.spill_slots = w.slots;
-    t.spill_chunks = kSpillChunksPerSlot;
-    cudaError_t e = cudaMemsetAsync(t.spill_flags, 0, w.flags_bytes, st);
-    if (e != cudaSuccess) { set_error("sm100::solve: memset: %s", cudaGetErrorString(e)); return ADS_ERR_CUDA; }
-  }
   size_t sm = SolveSmem<D>::bytes(p.n_words);
   if (sm > 227 * 1024) { set_error("sm100::solve: sequence too long for the bitmap staging (%zu B smem)", sm); return ADS_ERR_UNSUPPORTED; }
   if (int rc = set_smem(solve_kernel<T, D>, sm, "sm100::solve")) return rc;
@@ -288,7 +246,7 @@ bool supported(const ads_attn_shape* s) {
   return true;
 }
 
-size_t workspace_bytes(const ads_attn_shape* s) { return ws_layout(s->N).total; }
+size_t workspace_bytes(const ads_attn_shape*) { return kStatusBytes; }
 size_t min_workspace_bytes() { return kStatusBytes; }
 
 int solve(const simt::Params& p, int dtype, void* ws, size_t ws_bytes, cudaStream_t st) {

@@ -34,18 +34,8 @@ struct TcParams {
   float sm_scale;
   int tau_given;
   int* status;       // device status word (0 = ok)
-  // Solver only: overflow area of the candidate lists in global memory (stays in L2), or null.
-  // `spill_flags[s]` != 0 while a CTA holds slot s; a slot is `spill_chunks` chunks of 128 bytes.
-  int* spill_flags;
-  uint4* spill;
-  int spill_slots, spill_chunks;
 };
 
-// Overflow area of the solver's candidate lists: 128-byte chunks = one 8-byte header (index of the
-// thread's next chunk) + 15 entries {fp32 score, 64-key block}.
-constexpr int kSpillChunkEntries = 15;
-constexpr int kSpillChunksPerSlot = 10240;                 // 1.25 MiB per resident CTA, ~150 k scores
-constexpr size_t kSpillSlotBytes = (size_t)kSpillChunksPerSlot * 128;
 
 // One wait failed: publish the code globally (first failure wins) and tell the CTA.
 __device__ __forceinline__ void raise_abort(volatile int* cta_abort, int* status, int code) {

@@ -35,13 +35,9 @@
 // to a per-thread list in a shared-memory pool; the histogram, the Halley steps
 // and the final bitmap + step run on the lists.  The counts and bitmap bits are
 // the same integers either way; the Halley sums add the same terms in list order.
-// If a warp's share of the pool fills up (rows whose scores are nearly flat: with
-// unit-variance inputs 3 % of a row is within 1 of its maximum), its threads go on
-// appending to 128-byte chunks of an overflow area in global memory that the caller
-// passes with the workspace (one slot per resident CTA; it stays in L2), and the list
-// passes walk both parts.  Only if there is no such area, or it fills up too, sweep 2
-// goes on as a plain histogram sweep for the scores that find no room and the CTA
-// sweeps S for the remaining steps as well -- what the solve cost without lists.
+// If the pool fills up (rows whose scores are nearly flat), sweep 2 goes on as a
+// plain histogram sweep for the scores that find no room, and the CTA sweeps S
+// for the remaining steps as well -- what the solve cost without lists.
 // (One sweep with a running maximum does not work: the maximum of a row grows so
 // slowly that three times as many scores pass "within 1 of the maximum so far"
 // as are within 1 of the final one.)
@@ -115,8 +111,6 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
   int* start_status = (int*)(smem + L::misc_off + 8);
   int* pool_used = (int*)(smem + L::misc_off + 32);   // [16]: entries used in each row warp's region
   volatile int* pool_ovf = (volatile int*)(smem + L::misc_off + 16);
-  int* spill_slot = (int*)(smem + L::misc_off + 20);   // this CTA's slot of the overflow area, or -1
-  int* spill_used = (int*)(smem + L::misc_off + 24);   // chunks handed out so far
   float* xchg = (float*)(smem + L::xchg_off);
   uint32_t* s_bits = (uint32_t*)(smem + L::bits_off);
   Cand* pool = (Cand*)sQ;  // the Q tiles are dead once Q~ is in TMEM (before the first append)
@@ -153,19 +147,6 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
     *cta_abort = 0;
     for (int w = 0; w < 16; ++w) pool_used[w] = 0;
     *pool_ovf = 0;
-    *spill_used = 0;
-    // Take a slot of the overflow area: at most one CTA of this kernel is resident per SM and
-    // there is a slot per SM, so a free one exists; the search is bounded all the same.
-    int got = -1;
-    if (p.spill != nullptr && !p.tau_given) {
-      uint32_t smid;
-      asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
-      for (int i = 0; i < 2 * p.spill_slots && got < 0; ++i) {
-        const int sidx = (int)((smid + (uint32_t)i) % (uint32_t)p.spill_slots);
-        if (atomicCAS(p.spill_flags + sidx, 0, 1) == 0) got = sidx;
-      }
-    }
-    *spill_slot = got;
   }
   if (warp == 17) {
     if (lane == 0) {
@@ -187,7 +168,6 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
   ptx::tc_fence_after_sync();
   if (*start_status != 0) {  // an earlier CTA of this launch already failed: do nothing
     if (warp == 17) ptx::tmem_dealloc(*tmem_holder, kSolveTmemCols);
-    if (threadIdx.x == 0 && *spill_slot >= 0) atomicExch(p.spill_flags + *spill_slot, 0);
     return;
   }
   const uint32_t tmem_base = *tmem_holder;
@@ -319,10 +299,6 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
     float a0 = 0.f, a1 = 0.f, a2 = 0.f;
     uint16_t head = kCandNil;  // this thread's list of scores >= tau0
     int ncand = 0;             // its length (counted on the first walk)
-    // the part of the list that found no room in shared memory: chunks in global memory
-    uint2* const spill = *spill_slot >= 0
-        ? reinterpret_cast<uint2*>(p.spill) + (size_t)*spill_slot * (kSpillChunksPerSlot * 16) : nullptr;
-    int sp_head = -1, sp_cur = 0, sp_n = 0;  // first chunk, next free entry (0 = none yet), entries
 
     // One pass over the S tiles of this group's causal range.  Instantiated once per sweep
     // kind, so that the per-group code carries no mode tests and each sweep runs a compact loop.
@@ -405,25 +381,6 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
                         pool[slot] = e;
                         head = (uint16_t)slot;
                         listed = true;
-                      } else if (spill != nullptr) {
-                        // no room in shared memory: into this thread's current chunk of the
-                        // overflow area (entry 0 of a chunk is the link to the thread's next one)
-                        if ((sp_cur & 15) == 0) {
-                          const int c = atomicAdd(spill_used, 1);
-                          if (c < p.spill_chunks) {
-                            if (sp_head < 0) sp_head = c;
-                            else spill[(size_t)((sp_cur - 1) >> 4) * 16] = make_uint2((uint32_t)c, 0u);
-                            sp_cur = c * 16 + 1;
-                          }
-                        }
-                        if ((sp_cur & 15) != 0) {
-                          spill[sp_cur] = make_uint2(__float_as_uint(z), (uint32_t)(2 * kt + half));
-                          ++sp_cur;
-                          ++sp_n;
-                          listed = true;
-                        } else {
-                          *pool_ovf = 1;
-                        }
                       } else {
                         *pool_ovf = 1;
                       }
@@ -516,24 +473,6 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
 #pragma unroll
       for (int c = 0; c < 8; ++c) cnt[c] = 0;
     };
-    // The entries of this thread in the overflow area, chunk by chunk (a chunk is read with
-    // eight independent 16-byte loads; the walk is bounded by the number of entries written).
-    auto walk_spill = [&](auto f) {
-      int c = sp_head;
-      for (int left = sp_n; left > 0 && (unsigned)c < (unsigned)p.spill_chunks;) {
-        const uint4* ch = reinterpret_cast<const uint4*>(spill + (size_t)c * 16);
-        uint4 raw4[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) raw4[i] = ch[i];
-        const uint2* e = reinterpret_cast<const uint2*>(raw4);
-        const int n = min(left, kSpillChunkEntries);
-#pragma unroll
-        for (int i = 1; i <= kSpillChunkEntries; ++i)
-          if (i <= n) f(__uint_as_float(e[i].x), e[i].y);
-        left -= n;
-        c = (int)e[0].x;
-      }
-    };
 
     if (p.tau_given) {
       // bitmap for a given tau: one sweep over S
@@ -549,21 +488,17 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
         sweep_tiles(std::integral_constant<int, kModeCollect>{});
         // the listed scores join the histogram
         // (a thread's list is no longer than its warp's share of the pool: the walks are bounded)
-        auto bin_one = [&](float z) {
-          const float prj = (z - tau0) * fbins;
+        for (int e = head, left = warp_pool; e != kCandNil && left > 0; --left) {
+          const Cand c = pool[e];
+          const float prj = (c.z - tau0) * fbins;
           if (prj >= 0.f) {
             const int bsel = min(__float2int_rd(prj), 7);
 #pragma unroll
             for (int bb = 0; bb < 8; ++bb) cnt[bb] += (bb <= bsel) ? 1 : 0;
           }
-        };
-        for (int e = head, left = warp_pool; e != kCandNil && left > 0; --left) {
-          const Cand c = pool[e];
-          bin_one(c.z);
           e = c.next;
           ++ncand;
         }
-        walk_spill([&](float z, uint32_t) { bin_one(z); });
         exchange(kModeHist);
       }
       // lists or full sweeps: one decision for the CTA, which the producer and the MMA warps
@@ -597,25 +532,24 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
         for (int it = 0; it <= p.niter; ++it) {
           const bool last = it == p.niter;
           reset_stats();
-          auto visit = [&](float z, uint32_t kb) {
-            const float d = z - hs.t;
+          auto visit = [&](const Cand c) {
+            const float d = c.z - hs.t;
             if (d > 0.f) {
               a0 = fmaf(d, d, a0); a1 += d; a2 += 1.f;
               // the final step also records the 64x64 sub-tiles that hold a score above the
-              // tau entering it (row block rb of this group, key block kb)
-              if (last && row_ok) atomicOr(&s_bits[(grp * 2 + rb) * p.n_words + (kb >> 5)], 1u << (kb & 31));
+              // tau entering it (row block rb of this group, key block c.kb)
+              if (last && row_ok) atomicOr(&s_bits[(grp * 2 + rb) * p.n_words + (c.kb >> 5)], 1u << (c.kb & 31));
             }
           };
           if (compact) {
-            for (int k = 0; k < ncand; ++k) { const Cand c = pool[run0 + k]; visit(c.z, c.kb); }
+            for (int k = 0; k < ncand; ++k) visit(pool[run0 + k]);
           } else {
             for (int e = head, left = warp_pool; e != kCandNil && left > 0; --left) {
               const Cand c = pool[e];
-              visit(c.z, c.kb);
+              visit(c);
               e = c.next;
             }
           }
-          walk_spill(visit);
           exchange(last ? kModeFinal : kModeHalley);
         }
       } else if (grp_on) {
@@ -653,7 +587,6 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
     for (int i = 0; i < 64; ++i) __nanosleep(1000);
   }
   __syncthreads();
-  if (threadIdx.x == 0 && *spill_slot >= 0) atomicExch(p.spill_flags + *spill_slot, 0);  // every walk is done
   if (warp == 17) {
     ptx::tc_fence_after_sync();
     ptx::tmem_dealloc(tmem_base, kSolveTmemCols);

@@ -80,12 +80,8 @@ int adasplash_entmax_fwd(const void* x, void* y, float* tau_out, int64_t rows, i
 int adasplash_entmax_bwd(const void* y, const void* dy, void* dx, int64_t rows, int64_t cols,
                          float alpha, int32_t fast_math, int32_t dtype, void* stream);
 
-/* Bytes of scratch recommended for `shape` on the current device (256-byte aligned base
- * expected).  Every attention entry point accepts any size >= 256: the first 256 bytes hold
- * the status word of the bounded device-side waits.  adasplash2_solve uses the rest, when it
- * is given the full size, as the overflow area of its candidate lists (one 1.25 MiB slot per
- * SM, about 190 MiB on a B200; only touched for rows whose scores are nearly flat); with less
- * it still gives the same result and re-computes the score tiles for such rows instead. */
+/* Bytes of scratch the attention entry points need for `shape` (forward and
+ * backward use the same buffer; 256-byte aligned base expected). */
 size_t adasplash2_workspace_bytes(const ads_attn_shape* shape);
 
 /* Number of int32 words of one bitmap tensor (B,Hq,rows_padded,n_words) and its

@@ -239,7 +239,7 @@ TIME_CASES = {
 }
 
 
-def time_reference(adasplash, out_dir, cases):
+def time_reference(adasplash, out_dir, cases, suffix=""):
     path = os.path.join(out_dir, "reference_timings.json")
     res = json.load(open(path)) if os.path.exists(path) else {}
     res.update({"device": torch.cuda.get_device_name(0), "torch": torch.__version__})
@@ -263,7 +263,7 @@ def time_reference(adasplash, out_dir, cases):
         flush()
     for name, (tag, cfg) in TIME_CASES.items():
         if name in cases:
-            _time_attention_case(adasplash, res, tag, *cfg)
+            _time_attention_case(adasplash, res, tag + suffix, *cfg)
             torch.cuda.empty_cache()
             flush()
 
@@ -274,8 +274,15 @@ def main():
     ap.add_argument("--ref", default=os.path.join(ROOT, "baseline", "_ref"))
     ap.add_argument("--time", default="", help="comma list of: rowwise," + ",".join(TIME_CASES) + " (or 'all')")
     ap.add_argument("--skip-fixtures", action="store_true", help="do not rewrite the small fixtures")
-    ap.add_argument("--big-slices", action="store_true", help="write the benchmark-length slice fixtures")
+    ap.add_argument("--big-slices", default=None, nargs="?", const="all",
+                    help="write the benchmark-length slice fixtures (all, or a comma list of names)")
+    ap.add_argument("--single-config", action="store_true",
+                    help="set the reference's ADASPLASH_TEST_FAST_AUTOTUNE=1 (one tuning candidate per kernel, "
+                         "as its own test suite does): at 65536 positions the full autotune compiles for more "
+                         "than 16 minutes.  Timings taken this way get the suffix _single_config.")
     a = ap.parse_args()
+    if a.single_config:
+        os.environ["ADASPLASH_TEST_FAST_AUTOTUNE"] = "1"
     sys.path.insert(0, a.ref)
     import adasplash
     assert os.path.abspath(adasplash.__file__).startswith(os.path.abspath(a.ref)), adasplash.__file__
@@ -284,12 +291,15 @@ def main():
         make_rowwise(adasplash, a.out)
         make_attention(adasplash, a.out)
         make_v1(adasplash, a.out)
-    # timing first: the fixtures of the same (sequence length, head dim) then reuse its autotuning
+    # Slices first: the reference's autotuner is keyed on (sequence length, head dim) only, so the
+    # few-head slice tunes in a minute or two and a timing case of the same length that follows in
+    # this process reuses the choice.  (Tuning on a full-size batch runs every candidate on it:
+    # the 16384-long configuration took 560 s that way.)
+    if a.big_slices:
+        make_big_slices(adasplash, a.out, None if a.big_slices == "all" else a.big_slices.split(","))
     if a.time:
         cases = ["rowwise"] + list(TIME_CASES) if a.time == "all" else a.time.split(",")
-        time_reference(adasplash, a.out, cases)
-    if a.big_slices:
-        make_big_slices(adasplash, a.out)
+        time_reference(adasplash, a.out, cases, "_single_config" if a.single_config else "")
 
 
 if __name__ == "__main__":
