@@ -7,11 +7,12 @@
 // streaming variant that re-reads the row from L2/HBM.
 //
 // Only the elements within 1 of the row maximum can be in the support (the largest
-// probability [z_max - tau]_+^(1/(alpha-1)) is at most 1, so tau >= z_max - 1): after the
-// maximum is known, one pass collects them into a short shared-memory list and the histogram
-// and every refinement step run on the list; rows with too many such elements (nearly flat
-// rows) take the full passes instead, and so do calls with so few steps that building the
-// list would cost more than it saves.
+// probability [z_max - tau]_+^(1/(alpha-1)) is at most 1, so tau >= z_max - 1).  After the
+// maximum is known, every thread notes which of its own elements those are -- a handful per
+// row for peaked inputs -- in a few private shared-memory slots, in the order it holds them;
+// the histogram and every refinement step then run over the slots.  A thread with more
+// candidates than slots (nearly flat rows) sweeps all of its elements instead; both ways add
+// the same terms in the same order, so the result does not depend on which one ran.
 //
 // The threshold search follows adasplash/triton_entmax_v2.py:361-536 (4-bin
 // histogram lower bound, quadratic start on the bin-centre model, Halley /
@@ -201,6 +202,28 @@ struct RegRow {
 #pragma unroll
     for (int i = 0; i < NV * 4; ++i) f(v[i]);
   }
+  // maximum of this thread's elements (independent chains instead of one dependent one)
+  __device__ __forceinline__ float max() const {
+    float m0 = -INFINITY, m1 = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < NV * 4; i += 4) {
+      m0 = fmaxf(m0, fmaxf(v[i], v[i + 1]));
+      m1 = fmaxf(m1, fmaxf(v[i + 2], v[i + 3]));
+    }
+    return fmaxf(m0, m1);
+  }
+  // f(x) for every element >= thr, in element order; groups of four are skipped with one test
+  template <typename F> __device__ __forceinline__ void for_each_at_least(float thr, F f) const {
+#pragma unroll
+    for (int i = 0; i < NV * 4; i += 4) {
+      const float m4 = fmaxf(fmaxf(v[i], v[i + 1]), fmaxf(v[i + 2], v[i + 3]));
+      if (m4 >= thr) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          if (v[i + e] >= thr) f(v[i + e]);
+      }
+    }
+  }
   template <typename F> __device__ __forceinline__ void store(T* row, F f) const {
 #pragma unroll
     for (int c = 0; c < NV; ++c) {
@@ -240,98 +263,76 @@ struct StreamRow {  // re-reads the row from global memory on every pass
   template <typename F> __device__ __forceinline__ void for_each(F f) const {
     for (int c = tl; c < cols; c += TPR) f(DT<T>::to_f(row[c]) * sc);
   }
+  __device__ __forceinline__ float max() const {
+    float m = -INFINITY;
+    for (int c = tl; c < cols; c += TPR) m = fmaxf(m, DT<T>::to_f(row[c]) * sc);
+    return m;
+  }
+  template <typename F> __device__ __forceinline__ void for_each_at_least(float thr, F f) const {
+    for (int c = tl; c < cols; c += TPR) {
+      const float x = DT<T>::to_f(row[c]) * sc;
+      if (x >= thr) f(x);
+    }
+  }
   template <typename F> __device__ __forceinline__ void store(T* out, F f) const {
     for (int c = tl; c < cols; c += TPR) out[c] = DT<T>::from_f(f(DT<T>::to_f(row[c]) * sc));
   }
 };
 
-constexpr int kListCap = 256;  // candidates per row kept in shared memory
+constexpr int kCandSlots = 8;  // candidates a thread keeps in shared memory (slot j of thread t: [j * blockDim.x + t])
 
-// Shared memory of the candidate lists of a CTA: per row group a counter and kListCap values,
-// and one flag for "some row of this CTA has more candidates than that".
-struct ListSmem {
-  float* vals;     // this group's kListCap floats
-  int* count;      // this group's counter
-  int* overflow;   // CTA-wide flag
-};
+// Maximum over the TPR threads of a row group.  Inside a warp it is one integer reduction on an
+// order-preserving image of the float (redux.sync has no float form before this image).
+__device__ __forceinline__ int ordered_int(float x) {
+  const int i = __float_as_int(x);
+  return i >= 0 ? i : i ^ 0x7fffffff;
+}
+__device__ __forceinline__ float ordered_float(int i) { return __int_as_float(i >= 0 ? i : i ^ 0x7fffffff); }
+
+template <int TPR>
+__device__ __forceinline__ float group_max(float x, float* smem_max) {
+  float m = ordered_float(__reduce_max_sync(0xffffffffu, ordered_int(x)));
+  if constexpr (TPR > 32) {
+    const int w = threadIdx.x / 32, g0 = (threadIdx.x / TPR) * (TPR / 32);
+    if ((threadIdx.x & 31) == 0) smem_max[w] = m;
+    __syncthreads();
+    m = smem_max[g0];
+    for (int g = 1; g < TPR / 32; ++g) m = fmaxf(m, smem_max[g0 + g]);
+    // smem_max is not written again by this kernel: no second barrier needed
+  }
+  return m;
+}
 
 template <typename T, int TPR, typename Row>
 __device__ __forceinline__ void entmax_fwd_row(Row& r, T* yrow, float* tau_out, long long row_idx,
                                                bool row_ok, float alpha, int n_iter, int use_hist,
-                                               int fast_math, float* smem, ListSmem ls) {
+                                               int fast_math, float* smem, float* smem_max,
+                                               float* s_cand) {
   GroupReduce<TPR> red(smem);
-  const int tl_ = threadIdx.x % TPR;
   const int mode = (alpha == 1.5f) ? 0 : (alpha == 2.0f ? 1 : 2);
   const float c0 = 1.0f / (alpha - 1.0f), c1 = c0 - 1.0f, c2 = c1 - 1.0f;
+  (void)c2;
   float red4[4];
   // stage 1: maximum of the scaled row
-  float mx = -INFINITY;
-  r.for_each([&](float x) { mx = fmaxf(mx, x); });
-  red4[0] = mx; red4[1] = red4[2] = red4[3] = -INFINITY;
-  red.reduce4(red4, OpMax());
-  mx = red4[0];
+  const float mx = group_max<TPR>(r.max(), smem_max);
   // Candidates: tau never falls below max - 1 (minus the 1e-6 slack of the bracket test), so
-  // nothing below that can enter a sum.  Rows groups of one warp decide for themselves; wider
-  // groups share CTA barriers and therefore decide together.
-  // Building the list costs about two passes over the row (atomics, a sort, barriers): it pays
-  // when more passes than that follow, i.e. for the many refinement steps of a generic alpha,
-  // not for the default "histogram + 2 steps" of alpha = 1.5 / 2.
-  const bool want_list = (use_hist && alpha <= 2.0f ? 1 : 0) + n_iter >= 5;
-  int n_list = 0;
-  bool listed = false;
-  if (want_list) {  // the same for every thread of the launch: the barriers below are uniform
-    if (tl_ == 0) *ls.count = 0;
-    if constexpr (TPR > 32) __syncthreads(); else __syncwarp();
-    const float t_keep = mx - 1.0f - 1e-5f;
-    r.for_each([&](float x) {
-      if (x >= t_keep) {
-        const int slot = atomicAdd(ls.count, 1);
-        if (slot < kListCap) ls.vals[slot] = x;
-      }
+  // nothing below that can enter a sum.  Each thread keeps its own in its own slots.
+  int n_cand = 0;
+  {
+    float* mine = s_cand + threadIdx.x;
+    const int stride = blockDim.x;
+    r.for_each_at_least(mx - 1.0f - 1e-5f, [&](float x) {
+      if (n_cand < kCandSlots) mine[n_cand * stride] = x;
+      ++n_cand;
     });
-    if constexpr (TPR > 32) {
-      __syncthreads();
-      if (tl_ == 0 && *ls.count > kListCap) *ls.overflow = 1;
-      __syncthreads();
-    } else {
-      __syncwarp();
-    }
-    n_list = *ls.count;
-    listed = (TPR > 32) ? (*ls.overflow == 0) : (n_list <= kListCap);
   }
-  if (listed) {
-    // The atomics filled the list in an order that differs from run to run; sort it (rank of
-    // each value among the few dozen) so that the sums over it are reproducible.
-    constexpr int EPT = (kListCap + TPR - 1) / TPR;
-    float mine[EPT];
-    int rank[EPT];
-#pragma unroll
-    for (int e = 0; e < EPT; ++e) {
-      const int i = tl_ + e * TPR;
-      mine[e] = 0.f;
-      rank[e] = 0;
-      if (i < n_list) {
-        const float v = ls.vals[i];
-        int rk = 0;
-        for (int j = 0; j < n_list; ++j) {
-          const float w = ls.vals[j];
-          rk += (w > v || (w == v && j < i)) ? 1 : 0;
-        }
-        mine[e] = v;
-        rank[e] = rk;
-      }
-    }
-    if constexpr (TPR > 32) __syncthreads(); else __syncwarp();
-#pragma unroll
-    for (int e = 0; e < EPT; ++e) {
-      if (tl_ + e * TPR < n_list) ls.vals[rank[e]] = mine[e];
-    }
-    if constexpr (TPR > 32) __syncthreads(); else __syncwarp();
-  }
-  // every later pass over the row: over the list if there is one
+  // every later pass: over this thread's slots, or over all of its elements if they did not fit
+  // (same elements above any threshold >= max - 1 - 1e-5, same order)
   auto each = [&](auto f) {
-    if (listed) {
-      for (int i = tl_; i < n_list; i += TPR) f(ls.vals[i]);
+    if (n_cand <= kCandSlots) {
+      const float* mine = s_cand + threadIdx.x;
+      const int stride = blockDim.x;
+      for (int j = 0; j < n_cand; ++j) f(mine[j * stride]);
     } else {
       r.for_each(f);
     }
@@ -424,21 +425,19 @@ __global__ void __launch_bounds__((TPR > 128 ? TPR : 128))
 entmax_fwd_reg_kernel(const T* __restrict__ x, T* __restrict__ y, float* __restrict__ tau_out,
                       long long rows, int cols, float alpha, int n_iter, int use_hist,
                       int fast_math) {
+  constexpr int THREADS = TPR > 128 ? TPR : 128;
   __shared__ float smem[2 * 32 * 4];
-  constexpr int RPC = TPR >= 128 ? 1 : 128 / TPR;  // row groups per CTA
-  __shared__ float s_list[RPC * kListCap];
-  __shared__ int s_count[RPC + 1];
+  __shared__ float smem_max[32];
+  __shared__ float s_cand[kCandSlots * THREADS];
   const int rows_per_cta = blockDim.x / TPR;
   const int grp = threadIdx.x / TPR;
   long long row = (long long)blockIdx.x * rows_per_cta + grp;
   bool ok = row < rows;
   long long rr = ok ? row : rows - 1;
-  if (threadIdx.x == 0) s_count[RPC] = 0;
   RegRow<T, TPR, NV, VEC> r;
   r.load(x + rr * cols, cols, alpha - 1.0f);
-  if constexpr (TPR > 32) __syncthreads();
-  ListSmem ls{s_list + grp * kListCap, s_count + grp, s_count + RPC};
-  entmax_fwd_row<T, TPR>(r, y + rr * cols, tau_out, rr, ok, alpha, n_iter, use_hist, fast_math, smem, ls);
+  entmax_fwd_row<T, TPR>(r, y + rr * cols, tau_out, rr, ok, alpha, n_iter, use_hist, fast_math, smem,
+                         smem_max, s_cand);
 }
 
 template <typename T>
@@ -447,15 +446,13 @@ entmax_fwd_stream_kernel(const T* __restrict__ x, T* __restrict__ y, float* __re
                          long long rows, int cols, float alpha, int n_iter, int use_hist,
                          int fast_math) {
   __shared__ float smem[2 * 32 * 4];
-  __shared__ float s_list[kListCap];
-  __shared__ int s_count[2];
+  __shared__ float smem_max[32];
+  __shared__ float s_cand[kCandSlots * 1024];
   long long row = blockIdx.x;
-  if (threadIdx.x == 0) s_count[1] = 0;
   StreamRow<T, 1024> r;
   r.load(x + row * cols, cols, alpha - 1.0f);
-  __syncthreads();
-  ListSmem ls{s_list, s_count, s_count + 1};
-  entmax_fwd_row<T, 1024>(r, y + row * cols, tau_out, row, true, alpha, n_iter, use_hist, fast_math, smem, ls);
+  entmax_fwd_row<T, 1024>(r, y + row * cols, tau_out, row, true, alpha, n_iter, use_hist, fast_math, smem,
+                          smem_max, s_cand);
 }
 
 // ---------------------------------------------------------------------------
