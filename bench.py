@@ -79,7 +79,7 @@ NCU_DRAM_BYTES_PER_LAUNCH = {
     ("mid", "bwd_dq"): 270.74e6 + 52.86e6,
     ("mid", "bwd_dkv"): 270.71e6 + 108.38e6,
     # profiles/entmax_fwd_f32_16384x4096.txt
-    ("c2", "entmax_fwd"): 268.49e6 + 219.89e6,
+    ("c2", "entmax_fwd"): 268.54e6 + 213.76e6,
 }
 
 
@@ -884,7 +884,7 @@ def run_rowwise(args):
         "e2e": {"value": round((fb + bb) / ms_e2e / 1e6, 1), "unit": "GB/s", "ms_per_step": round(ms_e2e, 3),
                 "h2d_bytes_per_step": 2 * rows * cols * 4, "d2h_bytes_per_step": rows * cols * 4},
         "gpu_launches": int(launches), "clocks": clocks,
-        "roofline": {"bound": "hbm", "kernel": "entmax_fwd_reg_kernel<float,128,8>", "achieved": f["fwd_gbs"],
+        "roofline": {"bound": "hbm", "kernel": "entmax_fwd_pipe_kernel<float,128,8>", "achieved": f["fwd_gbs"],
                      "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": round(f["fwd_gbs"] / pk["hbm_gbs"], 4),
                      "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get(("c2", "entmax_fwd")),
                      "peak_source": pk["source"] + " (STREAM-style copy)",
