@@ -62,13 +62,15 @@ int check_shape(const ads_attn_shape* s, const char* who) {
   return ADS_OK;
 }
 
+// causal alpha = 1.5: the AdaSplash-2 kernels; anything else: the first-generation semantics
+bool is_v2(const ads_attn_shape* s) { return (s->alpha == 0.f || s->alpha == 1.5f) && s->non_causal == 0; }
+
 int resolve_path(const ads_attn_shape* s, const char* who, int* path) {
-  // the tensor-core kernels implement the causal alpha = 1.5 path only
-  const bool v2 = (s->alpha == 0.f || s->alpha == 1.5f) && s->non_causal == 0;
-  bool tc_ok = v2 && sm100::supported(s);
+  // tensor cores: 16-bit inputs, head dim up to 128, alpha 1.5 or 2 (causal or full attention)
+  bool tc_ok = is_v2(s) ? sm100::supported(s) : sm100::v1::supported(s);
   if (s->path == ADS_PATH_TCGEN05 && !tc_ok) {
-    set_error("%s: tcgen05 path needs fp16/bf16 inputs and a head dim it was built for (got dtype=%d D=%d)",
-              who, s->dtype, s->D);
+    set_error("%s: tcgen05 path needs fp16/bf16 inputs, a head dim it was built for and alpha 1.5 or 2 "
+              "(got dtype=%d D=%d alpha=%g)", who, s->dtype, s->D, s->alpha);
     return ADS_ERR_UNSUPPORTED;
   }
   *path = (s->path == ADS_PATH_SIMT || !tc_ok) ? ADS_PATH_SIMT : ADS_PATH_TCGEN05;
@@ -162,7 +164,7 @@ static int solve_common(const void* q, const void* k, const void* varlen, float*
       set_error("%s: workspace too small (%zu < %zu)", who, ws_bytes, sm100::min_workspace_bytes());
       return ADS_ERR_WORKSPACE;
     }
-    return sm100::solve(p, s->dtype, ws, ws_bytes, st);
+    return is_v2(s) ? sm100::solve(p, s->dtype, ws, ws_bytes, st) : sm100::v1::solve(p, s->dtype, ws, ws_bytes, st);
   }
   return by_dtype(
       s->dtype, [&] { return simt::launch_solve<float>(p, st); },
@@ -204,7 +206,7 @@ extern "C" int adasplash2_fwd(const void* q, const void* k, const void* v, const
       set_error("%s: workspace too small (%zu < %zu)", who, ws_bytes, sm100::min_workspace_bytes());
       return ADS_ERR_WORKSPACE;
     }
-    return sm100::fwd(p, s->dtype, ws, st);
+    return is_v2(s) ? sm100::fwd(p, s->dtype, ws, st) : sm100::v1::fwd(p, s->dtype, ws, st);
   }
   return by_dtype(
       s->dtype, [&] { return simt::launch_fwd<float>(p, st); },
@@ -240,7 +242,7 @@ extern "C" int adasplash2_bwd(const void* q, const void* k, const void* v, const
       set_error("%s: workspace too small (%zu < %zu)", who, ws_bytes, sm100::min_workspace_bytes());
       return ADS_ERR_WORKSPACE;
     }
-    return sm100::bwd(p, s->dtype, ws, st);
+    return is_v2(s) ? sm100::bwd(p, s->dtype, ws, st) : sm100::v1::bwd(p, s->dtype, ws, st);
   }
   return by_dtype(
       s->dtype, [&] { return simt::launch_bwd<float>(p, st); },

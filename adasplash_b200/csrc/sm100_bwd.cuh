@@ -52,7 +52,8 @@ struct DqSmem {
   static constexpr size_t bytes = 1024 + misc_off + 64;
 };
 
-template <typename T, int D>
+// AM / CAUSAL as in the forward kernel (sm100_fwd.cuh).
+template <typename T, int D, int AM = 0, bool CAUSAL = true>
 __global__ void __launch_bounds__(kDqThreads, 1)
 bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDO,
               const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
@@ -102,7 +103,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     }
     return;
   }
-  const int T_tiles = qt + 1;
+  const int T_tiles = CAUSAL ? qt + 1 : (len + kBlockN - 1) / kBlockN;
   const int32_t* bm_head = p.bmask + (size_t)bh * p.rows_padded * p.n_words;
 
   if (threadIdx.x == 0) {
@@ -274,7 +275,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     bool dead = false;
     if (!ptx::mbar_wait_warp(q_full, 0)) { raise_abort(cta_abort, p.status, kStTimeoutEpilogue); dead = true; }
     if (!dead) {
-      const float sc = 0.5f * p.sm_scale;
+      const float sc = (AM == 0 && CAUSAL) ? 0.5f * p.sm_scale : p.zscale;
       for (int v = threadIdx.x; v < L::tile_bytes / 16; v += kDqRowThreads) {
         uint4* ptr = reinterpret_cast<uint4*>(sQ) + v;
         const int vrow = ((v * 16) % kPanelBytes) / 128;
@@ -306,7 +307,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       }
       ptx::tc_fence_after_sync();
       const int n0 = kt * kBlockN;
-      const bool need_mask = (kt == qt) || (n0 + kBlockN > len);
+      const bool need_mask = (CAUSAL && kt == qt) || (n0 + kBlockN > len);
       // This thread's 64 values of dP go to registers first and the single dP buffer is handed
       // back at once: dO V^T of the next tile runs during the row work of this one.
       uint32_t rp[64];
@@ -335,17 +336,22 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             // every (row, key) pair of the tile is causal and inside the sequence
 #pragma unroll
             for (int c = 0; c < 32; c += 2) {
-              const float u0 = fmaxf(s[c] - tau, 0.f), u1 = fmaxf(s[c + 1] - tau, 0.f);
-              dk[c >> 1] = pack2<T>(u0 * (dp[c] - dl), u1 * (dp[c + 1] - dl));
+              if constexpr (AM == 0) {
+                const float u0 = fmaxf(s[c] - tau, 0.f), u1 = fmaxf(s[c + 1] - tau, 0.f);
+                dk[c >> 1] = pack2<T>(u0 * (dp[c] - dl), u1 * (dp[c + 1] - dl));
+              } else {  // alpha = 2: the Jacobian weight is 1 on the support
+                dk[c >> 1] = pack2<T>(s[c] > tau ? dp[c] - dl : 0.f, s[c + 1] > tau ? dp[c + 1] - dl : 0.f);
+              }
             }
           } else {
-            const int lim = need_mask ? (min(row, len - 1) - (n0 + ch * 32)) : 64;  // columns c <= lim survive
+            const int lim = need_mask ? ((CAUSAL ? min(row, len - 1) : len - 1) - (n0 + ch * 32)) : 64;  // columns c <= lim survive
 #pragma unroll
             for (int c = 0; c < 32; c += 2) {
               const float u0 = s[c] - tau, u1 = s[c + 1] - tau;
               // select, not multiply: dP of a padded key or row may be anything
-              const float d0 = (u0 > 0.f && c <= lim) ? u0 * (dp[c] - dl) : 0.f;
-              const float d1 = (u1 > 0.f && c + 1 <= lim) ? u1 * (dp[c + 1] - dl) : 0.f;
+              const float w0 = AM == 0 ? u0 : 1.f, w1 = AM == 0 ? u1 : 1.f;
+              const float d0 = (u0 > 0.f && c <= lim) ? w0 * (dp[c] - dl) : 0.f;
+              const float d1 = (u1 > 0.f && c + 1 <= lim) ? w1 * (dp[c + 1] - dl) : 0.f;
               dk[c >> 1] = pack2<T>(d0, d1);
             }
           }
@@ -427,6 +433,7 @@ struct DkvSmem {
 // Walks (q head of the group, 64-row query block) pairs whose bit is set in rows
 // 2nt / 2nt+1 of the transposed block mask.  flags: bit0 = keys 0..63 of the
 // tile, bit1 = keys 64..127.
+template <bool CAUSAL = true>
 struct QBlockScan {
   const int32_t* bmt;
   int G, h0, rows_padded, n_words, nt, n_qblocks;
@@ -447,7 +454,7 @@ struct QBlockScan {
         if (++g >= G) return false;
         r0 = reinterpret_cast<const uint32_t*>(bmt) + ((size_t)(h0 + g) * rows_padded + 2 * nt) * n_words;
         r1 = (2 * nt + 1) < rows_padded ? r0 + n_words : nullptr;
-        m = 2 * nt;  // causal: query blocks before the key tile never see it
+        m = CAUSAL ? 2 * nt : 0;  // causal: query blocks before the key tile never see it
         w0 = r0[m >> 5];
         w1 = r1 ? r1[m >> 5] : 0u;
       }
@@ -461,7 +468,7 @@ struct QBlockScan {
   }
 };
 
-template <typename T, int D>
+template <typename T, int D, int AM = 0, bool CAUSAL = true>
 __global__ void __launch_bounds__(kDkvThreads, 1)
 bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                const __grid_constant__ CUtensorMap tmQ64, const __grid_constant__ CUtensorMap tmDO64,
@@ -567,7 +574,7 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
       r[2] = (q0 < len) ? p.delta[base + q0] : 0.f;
       r[3] = (q0 + 1 < len) ? p.delta[base + q0 + 1] : 0.f;
     };
-    QBlockScan scan(p.bmask_t, b, p.Hq, G, kvh, nt, n_qblocks, p.rows_padded, p.n_words);
+    QBlockScan<CAUSAL> scan(p.bmask_t, b, p.Hq, G, kvh, nt, n_qblocks, p.rows_padded, p.n_words);
     int g, m, g_next = 0, m_next = 0;
     uint32_t flags;
     bool have = scan.next(g, m, flags);
@@ -606,7 +613,7 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
     bool ok = true;
     if (lane == 0) ok = ptx::mbar_wait(k_ready, 0);
     ok = __shfl_sync(0xffffffffu, ok, 0);
-    QBlockScan scan(p.bmask_t, b, p.Hq, G, kvh, nt, n_qblocks, p.rows_padded, p.n_words);
+    QBlockScan<CAUSAL> scan(p.bmask_t, b, p.Hq, G, kvh, nt, n_qblocks, p.rows_padded, p.n_words);
     int g, m;
     uint32_t flags;
     for (int j = 0; ok && scan.next(g, m, flags); ++j) {
@@ -640,7 +647,7 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
     constexpr uint32_t idesc_acc = ptx::make_idesc(FMT, kBlockN, D, 0, 1);        // 128 keys x D
     const bool is_dv = warp == 19;
     bool ok = true;
-    QBlockScan scan(p.bmask_t, b, p.Hq, G, kvh, nt, n_qblocks, p.rows_padded, p.n_words);
+    QBlockScan<CAUSAL> scan(p.bmask_t, b, p.Hq, G, kvh, nt, n_qblocks, p.rows_padded, p.n_words);
     int g, m, g_next = 0, m_next = 0;
     uint32_t flags;
     bool have = scan.next(g, m, flags);
@@ -698,7 +705,7 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
     if (!ptx::mbar_wait_warp(kv_full, 0)) { raise_abort(cta_abort, p.status, kStTimeoutEpilogue); dead = true; }
     if (!dead) {
       // K~ = rn(k * fp32(0.5/sqrt(D))) in place; rows >= len -> 0 in K and V
-      const float sc = 0.5f * p.sm_scale;
+      const float sc = (AM == 0 && CAUSAL) ? 0.5f * p.sm_scale : p.zscale;
       for (int v = threadIdx.x; v < L::tile_bytes / 16; v += kDkvRowThreads) {
         const int vrow = ((v * 16) % kPanelBytes) / 128;
         const bool keep = (n0 + vrow) < len;
@@ -714,7 +721,7 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
     }
     ptx::mbar_arrive_warp(k_ready);
     // tau / delta of a step's 64 query rows arrive in shared memory with the step's Q / dO blocks
-    QBlockScan scan(p.bmask_t, b, p.Hq, G, kvh, nt, n_qblocks, p.rows_padded, p.n_words);
+    QBlockScan<CAUSAL> scan(p.bmask_t, b, p.Hq, G, kvh, nt, n_qblocks, p.rows_padded, p.n_words);
     int g = 0, m = 0, n_active = 0;
     uint32_t flags = 0;
     for (int j = 0; scan.next(g, m, flags); ++j) {
@@ -734,7 +741,8 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
       if (!dead) {
         ptx::tc_fence_after_sync();
         const bool sub_on = (flags >> kh) & 1u;  // warp-uniform: the TMEM loads below are warp-collective
-        const bool full = (n0 + kBlockN - 1 <= m * kQBlock) && ((m + 1) * kQBlock <= len);
+        const bool full = CAUSAL ? (n0 + kBlockN - 1 <= m * kQBlock) && ((m + 1) * kQBlock <= len)
+                                 : (n0 + kBlockN <= len) && ((m + 1) * kQBlock <= len);
         {
           const int c0 = slice * 16;                // first query column of this thread
           const int q0 = m * kQBlock + c0;
@@ -767,14 +775,21 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
                 const float4 l4 = *reinterpret_cast<const float4*>(dq_ + c);
                 const float u0 = fmaxf(s[c] - t4.x, 0.f), u1 = fmaxf(s[c + 1] - t4.y, 0.f);
                 const float u2 = fmaxf(s[c + 2] - t4.z, 0.f), u3 = fmaxf(s[c + 3] - t4.w, 0.f);
-                pk[c >> 1] = pack2<T>(u0 * u0, u1 * u1);
-                pk[(c >> 1) + 1] = pack2<T>(u2 * u2, u3 * u3);
-                dk[c >> 1] = pack2<T>(u0 * (dp[c] - l4.x), u1 * (dp[c + 1] - l4.y));
-                dk[(c >> 1) + 1] = pack2<T>(u2 * (dp[c + 2] - l4.z), u3 * (dp[c + 3] - l4.w));
+                if constexpr (AM == 0) {
+                  pk[c >> 1] = pack2<T>(u0 * u0, u1 * u1);
+                  pk[(c >> 1) + 1] = pack2<T>(u2 * u2, u3 * u3);
+                  dk[c >> 1] = pack2<T>(u0 * (dp[c] - l4.x), u1 * (dp[c + 1] - l4.y));
+                  dk[(c >> 1) + 1] = pack2<T>(u2 * (dp[c + 2] - l4.z), u3 * (dp[c + 3] - l4.w));
+                } else {  // alpha = 2: p = u, Jacobian weight 1 on the support
+                  pk[c >> 1] = pack2<T>(u0, u1);
+                  pk[(c >> 1) + 1] = pack2<T>(u2, u3);
+                  dk[c >> 1] = pack2<T>(u0 > 0.f ? dp[c] - l4.x : 0.f, u1 > 0.f ? dp[c + 1] - l4.y : 0.f);
+                  dk[(c >> 1) + 1] = pack2<T>(u2 > 0.f ? dp[c + 2] - l4.z : 0.f, u3 > 0.f ? dp[c + 3] - l4.w : 0.f);
+                }
               }
             } else {
             // query column c is valid iff key <= q0 + c < len  <=>  lo <= c < hi
-            const int lo = key - q0, hi = key_ok ? len - q0 : 0;
+            const int lo = CAUSAL ? key - q0 : -(1 << 30), hi = key_ok ? len - q0 : 0;
 #pragma unroll
             for (int c = 0; c < 16; c += 2) {
               const float2 t2 = *reinterpret_cast<const float2*>(tq + c);
@@ -783,8 +798,13 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
               const bool ok0 = (u0 > 0.f) && (c >= lo) && (c < hi);
               const bool ok1 = (u1 > 0.f) && (c + 1 >= lo) && (c + 1 < hi);
               // select, not multiply: S / dP entries of padded rows may be anything
-              pk[c >> 1] = pack2<T>(ok0 ? u0 * u0 : 0.f, ok1 ? u1 * u1 : 0.f);
-              dk[c >> 1] = pack2<T>(ok0 ? u0 * (dp[c] - l2.x) : 0.f, ok1 ? u1 * (dp[c + 1] - l2.y) : 0.f);
+              if constexpr (AM == 0) {
+                pk[c >> 1] = pack2<T>(ok0 ? u0 * u0 : 0.f, ok1 ? u1 * u1 : 0.f);
+                dk[c >> 1] = pack2<T>(ok0 ? u0 * (dp[c] - l2.x) : 0.f, ok1 ? u1 * (dp[c + 1] - l2.y) : 0.f);
+              } else {
+                pk[c >> 1] = pack2<T>(ok0 ? u0 : 0.f, ok1 ? u1 : 0.f);
+                dk[c >> 1] = pack2<T>(ok0 ? dp[c] - l2.x : 0.f, ok1 ? dp[c + 1] - l2.y : 0.f);
+              }
             }
             }
           }

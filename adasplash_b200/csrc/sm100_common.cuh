@@ -32,6 +32,9 @@ struct TcParams {
   int d_true;        // head dim of the tensors in global memory (<= the kernel's template D)
   int nq;            // number of 128-row tiles = ceil(N / 128)
   float sm_scale;
+  float zscale;      // fp32((alpha-1) * sm_scale): the Q (or K) operand is scaled by it, so S = z
+  float alpha;       // 1.5 or 2.0 on these kernels
+  int causal;        // 0 = full attention (first-generation semantics only)
   int tau_given;
   int* status;       // device status word (0 = ok)
 };

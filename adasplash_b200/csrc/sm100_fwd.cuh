@@ -66,7 +66,10 @@ __device__ __forceinline__ void zero_tile_rows(uint8_t* tile, int panels, int fi
   __syncwarp();
 }
 
-template <typename T, int D>
+// AM selects the row math: 0 = alpha 1.5 (p = u^2, weight u), 1 = alpha 2 (p = u, weight 1[u>0]);
+// CAUSAL = false is full attention (every key tile up to the sequence length, no diagonal mask).
+// <0, true> is the AdaSplash-2 path; the others serve the first-generation semantics.
+template <typename T, int D, int AM = 0, bool CAUSAL = true>
 __global__ void __launch_bounds__(kFwdThreads, 1)
 fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
            const __grid_constant__ CUtensorMap tmV, TcParams p) {
@@ -121,7 +124,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     }
     return;
   }
-  const int T_tiles = qt + 1;
+  const int T_tiles = CAUSAL ? qt + 1 : (len + kBlockN - 1) / kBlockN;
 
   if (threadIdx.x == 0) {
     *start_status = *(volatile int*)p.status;
@@ -269,7 +272,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     bool dead = false;
     if (!ptx::mbar_wait_warp(q_full, 0)) { raise_abort(cta_abort, p.status, kStTimeoutEpilogue); dead = true; }
     if (!dead) {
-      const float sc = 0.5f * p.sm_scale;
+      const float sc = (AM == 0 && CAUSAL) ? 0.5f * p.sm_scale : p.zscale;
       for (int v = threadIdx.x; v < L::tile_bytes / 16; v += kFwdRowThreads) {
         uint4* ptr = reinterpret_cast<uint4*>(sQ) + v;
         const int vrow = ((v * 16) % kPanelBytes) / 128;
@@ -297,7 +300,20 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       if (!ptx::mbar_wait_warp(s_full + buf, (j >> 1) & 1)) { raise_abort(cta_abort, p.status, kStTimeoutEpilogue); dead = true; break; }
       ptx::tc_fence_after_sync();
       const int n0 = kt * kBlockN;
-      const bool need_mask = (kt == qt) || (n0 + kBlockN > len);
+      const bool need_mask = (CAUSAL && kt == qt) || (n0 + kBlockN > len);
+      // score -> (rn(p), rn(weight)) of two neighbours, and the row's sum of weights
+      auto emit = [&](float u0, float u1, uint32_t& pw, uint32_t& uw) {
+        if constexpr (AM == 0) {
+          supp += u0 + u1;
+          pw = pack2<T>(u0 * u0, u1 * u1);
+          uw = pack2<T>(u0, u1);
+        } else {
+          const float g0 = u0 > 0.f ? 1.f : 0.f, g1 = u1 > 0.f ? 1.f : 0.f;
+          supp += g0 + g1;
+          pw = pack2<T>(u0, u1);
+          uw = pack2<T>(g0, g1);
+        }
+      };
 #pragma unroll
       for (int cc = 0; cc < 2; ++cc) {
         const int ch = 2 * half + cc;
@@ -313,23 +329,19 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
           const float* v = reinterpret_cast<const float*>(raw);
           if (need_mask) {
             const int col0 = n0 + ch * 32;
-            const int lim = min(row, len - 1) - col0;  // columns c <= lim survive
+            const int lim = (CAUSAL ? min(row, len - 1) : len - 1) - col0;  // columns c <= lim survive
 #pragma unroll
             for (int c = 0; c < 32; c += 2) {
               float u0 = fmaxf(v[c] - tau, 0.f), u1 = fmaxf(v[c + 1] - tau, 0.f);
               if (c > lim) u0 = 0.f;
               if (c + 1 > lim) u1 = 0.f;
-              supp += u0 + u1;
-              pk[c >> 1] = pack2<T>(u0 * u0, u1 * u1);
-              uk[c >> 1] = pack2<T>(u0, u1);
+              emit(u0, u1, pk[c >> 1], uk[c >> 1]);
             }
           } else {
 #pragma unroll
             for (int c = 0; c < 32; c += 2) {
               const float u0 = fmaxf(v[c] - tau, 0.f), u1 = fmaxf(v[c + 1] - tau, 0.f);
-              supp += u0 + u1;
-              pk[c >> 1] = pack2<T>(u0 * u0, u1 * u1);
-              uk[c >> 1] = pack2<T>(u0, u1);
+              emit(u0, u1, pk[c >> 1], uk[c >> 1]);
             }
           }
         }

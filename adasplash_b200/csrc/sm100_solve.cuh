@@ -86,7 +86,13 @@ struct SolveSmem {
   static size_t bytes(int) { return kSolveSmemBudget; }
 };
 
-template <typename T, int D>
+// V1 = false is the AdaSplash-2 solver described above.  V1 = true serves the first-generation
+// semantics on the same machinery (alpha = 1.5 or 2, causal or full attention;
+// adasplash_block_mask.py:40-296): the same two sweeps (row maxima, candidates within 1 of the
+// maximum), then no histogram: the bracket is [max - 1, max - n^(1-alpha)] with n the row's number
+// of valid keys, niter Halley / bisection steps run on the candidates, and the block mask is
+// taken at the lower end of the final bracket (tau_lo <= tau*: no tile of the support is missed).
+template <typename T, int D, bool V1 = false>
 __global__ void __launch_bounds__(kSolveThreads, 1)
 solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
              TcParams p) {
@@ -128,8 +134,10 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
   if (m0 >= len) return;
   const bool b_on = (m0 + kBlockM) < len;           // row tile B has at least one valid row
   const int qtA = 2 * pr_idx, qtB = qtA + 1;        // their 128-row tile indices
-  const int T_a = qtA + 1;                          // key tiles of A: 0 .. qtA
-  const int T_k = b_on ? qtB + 1 : T_a;             // key tiles streamed per sweep
+  const bool full_attn = V1 && p.causal == 0;
+  const int T_all = (len + kBlockN - 1) / kBlockN;  // key tiles of a row without the causal mask
+  const int T_a = full_attn ? T_all : qtA + 1;      // key tiles of A: 0 .. qtA
+  const int T_k = full_attn ? T_all : (b_on ? qtB + 1 : T_a);  // key tiles streamed per sweep
   const int nsweeps = p.tau_given ? 1 : p.niter + 3;
   // tiles streamed before the row warps decide (max sweep, histogram + collect sweep), and in
   // all if the candidate pool overflows (then the Halley .. final steps sweep S as well)
@@ -137,9 +145,9 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
   const int total_full = nsweeps * T_k;
   // Products are numbered in issue order (per K tile: A if it has one, then B); product n uses
   // S buffer n % 3 for the (n / 3)-th time.
-  const int prods_per_sweep = b_on ? 2 * T_a + 1 : T_a;
+  const int prods_per_sweep = b_on ? T_a + T_k : T_a;   // causal: T_k = T_a + 1
   auto product_index = [&](int sweep, int kt, int g) -> int {
-    return sweep * prods_per_sweep + (b_on ? (kt < T_a ? 2 * kt + g : 2 * T_a) : kt);
+    return sweep * prods_per_sweep + (b_on ? (kt < T_a ? 2 * kt + g : T_a + kt) : kt);
   };
 
   if (threadIdx.x == 0) {
@@ -258,14 +266,14 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
     const int rb = wq >> 1;
     const int qt = grp == 0 ? qtA : qtB;            // this group's 128-row tile index
     const bool grp_on = grp == 0 || b_on;
-    const int T_g = qt + 1;
+    const int T_g = full_attn ? T_all : qt + 1;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(wq * 32) << 16);
     bool dead = false;
     // Q~ = rn(q * fp32(0.5/sqrt(D))) (rows >= len -> 0), from the TMA tile in shared
     // memory into TMEM: the two threads of row r convert D/2 elements each (16-bit pairs, lane r)
     if (!ptx::mbar_wait_warp(q_full, 0)) { raise_abort(cta_abort, p.status, kStTimeoutEpilogue); dead = true; }
     if (!dead) {
-      const float sc = row_ok ? 0.5f * p.sm_scale : 0.f;
+      const float sc = row_ok ? (V1 ? p.zscale : 0.5f * p.sm_scale) : 0.f;
       const uint8_t* qtile = sQ + grp * L::tile_bytes;
 #pragma unroll
       for (int hh = 0; hh < D / 64; ++hh) {  // 32 elements -> 16 packed columns per store; D/2 elements per thread
@@ -318,7 +326,7 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
         }
         ptx::tc_fence_after_sync();
         const int n0 = kt * kBlockN;
-        const bool need_mask = (kt == qt) || (n0 + kBlockN > len);
+        const bool need_mask = (!full_attn && kt == qt) || (n0 + kBlockN > len);
         const float a2_mark = a2;  // support count before this thread's 64 keys of the tile
         // rows beyond the sequence have all-zero scores (every key would be a candidate) and
         // need no tau; once any warp's share of the pool is full the lists are useless
@@ -327,7 +335,7 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
         // Collecting takes scores from a hair below tau0: a Halley step may land up to 1e-5
         // below its bracket, and a sweep over S would then see those scores too.  The
         // histogram over the list tests each score against tau0 itself.
-        const float thr = mode == kModeCollect ? tau0 - 2e-5f : hs.t;
+        const float thr = mode == kModeCollect ? tau0 - 2e-5f : ((V1 && mode == kModeFinal) ? hs.lo : hs.t);
         // (Register budget: the kernel keeps nearly all of the SM's shared memory, which leaves
         // almost no L1 for local memory -- a spill in this loop costs an L2 round trip.)
 #pragma unroll 1
@@ -342,7 +350,7 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
           }
           float* v = reinterpret_cast<float*>(raw);
           if (need_mask) {
-            const int lim = min(row, len - 1) - (n0 + c0);  // columns c <= lim survive
+            const int lim = (full_attn ? len - 1 : min(row, len - 1)) - (n0 + c0);  // columns c <= lim survive
 #pragma unroll
             for (int c = 0; c < 32; ++c) v[c] = (c <= lim) ? v[c] : kMaskedScore;
           }
@@ -408,7 +416,11 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
                   const float d = v[g4 * 4 + c] - thr;
-                  if (d > 0.f) { a0 = fmaf(d, d, a0); a1 += d; a2 += 1.f; }
+                  if (V1 && mode == kModeHalley && p.alpha == 2.0f) {
+                    if (d > 0.f) { a0 += d; a1 += 1.f; }   // sum u, support size
+                  } else {
+                    if (d > 0.f) { a0 = fmaf(d, d, a0); a1 += d; a2 += 1.f; }
+                  }
                 }
               }
             }
@@ -465,7 +477,11 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
         const float s0 = half == 0 ? a0 + o[0] : o[0] + a0;
         const float s1 = half == 0 ? a1 + o[1] : o[1] + a1;
         const float s2 = half == 0 ? a2 + o[2] : o[2] + a2;
-        halley_bisect_update(hs, s0, s1, s2);
+        if constexpr (V1) {
+          if (mode == kModeHalley) halley_bisect_update_generic(hs, s0, s1, s2, 1.0f / (p.alpha - 1.0f), 1.0f / (p.alpha - 1.0f) - 1.0f);
+        } else {
+          halley_bisect_update(hs, s0, s1, s2);
+        }
       }
     };
     auto reset_stats = [&]() {
@@ -490,16 +506,27 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
         // (a thread's list is no longer than its warp's share of the pool: the walks are bounded)
         for (int e = head, left = warp_pool; e != kCandNil && left > 0; --left) {
           const Cand c = pool[e];
-          const float prj = (c.z - tau0) * fbins;
-          if (prj >= 0.f) {
-            const int bsel = min(__float2int_rd(prj), 7);
+          if constexpr (!V1) {
+            const float prj = (c.z - tau0) * fbins;
+            if (prj >= 0.f) {
+              const int bsel = min(__float2int_rd(prj), 7);
 #pragma unroll
-            for (int bb = 0; bb < 8; ++bb) cnt[bb] += (bb <= bsel) ? 1 : 0;
+              for (int bb = 0; bb < 8; ++bb) cnt[bb] += (bb <= bsel) ? 1 : 0;
+            }
           }
           e = c.next;
           ++ncand;
         }
-        exchange(kModeHist);
+        if constexpr (V1) {
+          // first-generation start (adasplash_block_mask.py:167-175): no histogram, the bracket
+          // [max - 1, max - n^(1-alpha)], n = 1 + row index (causal) or 1 + sequence length
+          const float nkeys = 1.0f + (float)(p.causal ? row : len);
+          hs.lo = tau0;
+          hs.hi = tau0 + 1.0f - exp2f((1.0f - p.alpha) * log2f(nkeys));
+          hs.t = 0.5f * (hs.lo + hs.hi);
+        } else {
+          exchange(kModeHist);
+        }
       }
       // lists or full sweeps: one decision for the CTA, which the producer and the MMA warps
       // are waiting for
@@ -533,12 +560,26 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
           const bool last = it == p.niter;
           reset_stats();
           auto visit = [&](const Cand c) {
-            const float d = c.z - hs.t;
-            if (d > 0.f) {
-              a0 = fmaf(d, d, a0); a1 += d; a2 += 1.f;
-              // the final step also records the 64x64 sub-tiles that hold a score above the
-              // tau entering it (row block rb of this group, key block c.kb)
-              if (last && row_ok) atomicOr(&s_bits[(grp * 2 + rb) * p.n_words + (c.kb >> 5)], 1u << (c.kb & 31));
+            if constexpr (V1) {
+              // niter steps on sum u^(1/(alpha-1)) - 1; the last round only records the 64x64
+              // sub-tiles that hold a score above the lower end of the bracket
+              if (last) {
+                if (c.z > hs.lo && row_ok) atomicOr(&s_bits[(grp * 2 + rb) * p.n_words + (c.kb >> 5)], 1u << (c.kb & 31));
+              } else {
+                const float d = c.z - hs.t;
+                if (d > 0.f) {
+                  if (p.alpha == 2.0f) { a0 += d; a1 += 1.f; }
+                  else { a0 = fmaf(d, d, a0); a1 += d; a2 += 1.f; }
+                }
+              }
+            } else {
+              const float d = c.z - hs.t;
+              if (d > 0.f) {
+                a0 = fmaf(d, d, a0); a1 += d; a2 += 1.f;
+                // the final step also records the 64x64 sub-tiles that hold a score above the
+                // tau entering it (row block rb of this group, key block c.kb)
+                if (last && row_ok) atomicOr(&s_bits[(grp * 2 + rb) * p.n_words + (c.kb >> 5)], 1u << (c.kb & 31));
+              }
             }
           };
           if (compact) {

@@ -2,7 +2,7 @@
 """Benchmark of the sparse entmax attention hot path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload c3|c4|c5|mid|small|c2] [--path auto|simt|tcgen05]
+                    [--workload c3|c4|c5|mid|small|c2|v1] [--path auto|simt|tcgen05]
                     [--sections LIST|none]
 
 One step = one forward + backward of causal entmax-1.5 `adasplash_v2` over one
@@ -802,6 +802,48 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+V1_METRIC = "adasplash (alpha=2, full attention) fwd+bwd dense-equivalent TFLOP/s, bf16"
+
+
+def run_v1(args):
+    """Secondary workload: the first-generation semantics on the tensor-core kernels --
+    `adasplash(q, k, v, alpha=2.0, is_causal=False)` (sparsemax, full attention, niter = 10),
+    B=4, H=32, N=8192, D=64, bf16, inputs N(0,1) -- beside the same call on the CUDA-core
+    kernels (one step: they take seconds).  Dense-equivalent FLOPs: 14 * H * D * N^2 per batch item."""
+    import adasplash_b200 as adasplash
+    from adasplash_b200 import _lib
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    B, H, N, D = 4, 32, 8192, 64
+    g = torch.Generator(device=dev).manual_seed(SEED_BASE + 5)
+    q, k, v, do = ((torch.randn(B, H, N, D, generator=g, device=dev)).bfloat16() for _ in range(4))
+
+    def step():
+        qq, kk, vv = q.requires_grad_(True), k.requires_grad_(True), v.requires_grad_(True)
+        out = adasplash.adasplash(qq, kk, vv, alpha=2.0, is_causal=False)
+        torch.autograd.grad(out, (qq, kk, vv), do)
+    sampler = ClockSampler(dev.index).start()
+    l0 = _lib.launch_count()
+    ms = timed_steps(step, args.steps, max(3, args.warmup))
+    launches = _lib.launch_count() - l0
+    clocks = sampler.stop()
+    _lib.set_kernel_path("simt")
+    ms_simt = timed_steps(step, 1, 1)
+    _lib.set_kernel_path(None)
+    flops = 14.0 * B * H * D * float(N) * N
+    line = {
+        "metric": V1_METRIC, "value": round(flops / ms / 1e9, 1), "unit": "TFLOP/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": round(ms, 3), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "adasplash alpha=2.0 is_causal=False niter=10, bf16 B=4 H=32 N=8192 D=64",
+                   "l2": "q, k, v, dO are 134 MB each (> 126 MB L2)"},
+        "gpu_launches": int(launches), "clocks": clocks,
+        "cuda_core_kernels_ms_per_step": round(ms_simt, 1),
+        "tensor_core_over_cuda_core": round(ms_simt / ms, 1),
+    }
+    print(json.dumps(line), flush=True)
+
+
 ROWWISE_METRIC = "triton_entmax fwd+bwd algorithmic GB/s (x 16384x4096 fp32, alpha=1.5, n_iter=2, histogram)"
 
 
@@ -953,7 +995,7 @@ def main():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS) + ["c2"])
+    ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS) + ["c2", "v1"])
     ap.add_argument("--path", default=None, choices=["auto", "simt", "tcgen05"])
     ap.add_argument("--sections", default="all",
                     help="'all', 'none' or a comma list of: " + ",".join(ALL_SECTIONS))
@@ -963,6 +1005,8 @@ def main():
         run_reference(args)
     elif args.workload == "c2":
         run_rowwise(args)
+    elif args.workload == "v1":
+        run_v1(args)
     else:
         run_ours(args)
 

@@ -94,3 +94,76 @@ def test_gqa_is_rejected_and_dispatcher_routes():
     a = adasplash.adasplash(q, q, q + 1.0, alpha=1.5, is_causal=False)      # v1 route
     b = adasplash.adasplash_no_block_mask(q, q, q + 1.0, alpha=1.5, is_causal=False)
     assert torch.equal(a, b)
+
+
+# ---- the same semantics on the tensor-core kernels (16-bit inputs, alpha 1.5 or 2) ----
+
+def _resolved(q, alpha, causal):
+    import ctypes
+    from adasplash_b200 import _lib
+    sh = att.make_shape(q, q, 10, None, None, alpha, causal)
+    return _lib.load().adasplash2_resolved_path(ctypes.byref(sh))
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("alpha,causal", [(1.5, False), (2.0, True), (2.0, False)])
+@pytest.mark.parametrize("case", [(1, 2, 256, 64, None, 1.0), (2, 2, 320, 128, [300, 129], 1.0), (1, 1, 192, 32, [191], 1.0),
+                                  (1, 2, 1024, 128, None, 1.5), (2, 1, 200, 16, [200, 70], 1.0)])
+def test_16bit_tensor_core_path_matches_exact_definition(dtype, alpha, causal, case):
+    from adasplash_b200 import _lib
+    B, H, N, D, vl, sc = case
+    q, k, v = (_randn((B, H, N, D), 90 + i, sc, dtype) for i in range(3))
+    varlen = None if vl is None else torch.tensor(vl, dtype=torch.int32)
+    do = _randn((B, H, N, D), 94, 1.0, dtype)
+    if varlen is not None:
+        do = do * (torch.arange(N)[None, None, :, None] < varlen[:, None, None, None]).to(dtype)
+    assert _resolved(q.cuda(), alpha, causal) == _lib.PATH_TCGEN05
+    kw = dict(alpha=alpha, is_causal=causal, varlen=None if varlen is None else varlen.cuda(), niter=10)
+    got = _run(adasplash.adasplash, q, k, v, do, **kw)
+    ex = O.dense_entmax_attention(q, k, v, alpha, causal, varlen, do)
+    for key in ("out", "dq", "dk", "dv"):
+        scale = max(1.0, ex[key].abs().max().item())
+        err = (got[key].double() - ex[key]).abs()
+        if alpha == 2.0 and key != "out":
+            # sparsemax: the Jacobian weight is 1 on the support and 0 off it, so a score that the
+            # 16-bit rounding of the scaled operand moves across its threshold changes a few
+            # gradient entries by O(1) (the CUDA-core kernels on the same inputs do the same,
+            # see below); all but a few entries must be within tolerance
+            assert (err < 2e-2 * scale).double().mean() > 0.98, key
+        else:
+            assert err.max() < 2e-2 * scale, key
+    if vl is not None:
+        for b in range(B):
+            if vl[b] < N:
+                for key in ("out", "dq", "dk", "dv"):
+                    assert got[key][b, :, vl[b]:].abs().max() == 0, key
+    # the CUDA-core kernels on the same 16-bit inputs: same rounding points, so much closer than
+    # either is to the exact result
+    _lib.set_kernel_path("simt")
+    try:
+        ref = _run(adasplash.adasplash, q, k, v, do, **kw)
+    finally:
+        _lib.set_kernel_path(None)
+    for key in ("out", "dq", "dk", "dv"):
+        scale = max(1.0, ref[key].abs().max().item())
+        assert (got[key] - ref[key]).abs().max() < 1e-2 * scale, key
+
+
+@pytest.mark.parametrize("alpha,causal", [(1.5, False), (2.0, True), (2.0, False)])
+def test_tensor_core_thresholds_match_cuda_core_thresholds(alpha, causal):
+    # thresholds and block masks of the two kernel families after the same ten steps from the
+    # same bracket; nearly flat rows (scale 0.05) overflow the candidate pool and sweep S instead
+    from adasplash_b200 import _lib
+    for scale in (1.5, 0.05):
+        q = _randn((1, 2, 2048, 128), 100, scale, torch.bfloat16).cuda()
+        k = _randn((1, 2, 2048, 128), 101, 1.0, torch.bfloat16).cuda()
+        ta, ma = att.solve(q, k, 10, None, None, alpha, causal)
+        _lib.set_kernel_path("simt")
+        try:
+            tb, mb = att.solve(q, k, 10, None, None, alpha, causal)
+        finally:
+            _lib.set_kernel_path(None)
+        torch.cuda.synchronize()
+        assert (ta - tb).abs().max() < 1e-5, (scale, (ta - tb).abs().max().item())
+        diff = sum(bin(int(x) & 0xFFFFFFFF).count("1") for x in (ma ^ mb).flatten().tolist())
+        assert diff <= 2, (scale, diff)
