@@ -66,11 +66,11 @@ int check_shape(const ads_attn_shape* s, const char* who) {
 bool is_v2(const ads_attn_shape* s) { return (s->alpha == 0.f || s->alpha == 1.5f) && s->non_causal == 0; }
 
 int resolve_path(const ads_attn_shape* s, const char* who, int* path) {
-  // tensor cores: 16-bit inputs, head dim up to 128, alpha 1.5 or 2 (causal or full attention)
+  // tensor cores: 16-bit inputs, head dim up to 128 (any alpha, causal or full attention)
   bool tc_ok = is_v2(s) ? sm100::supported(s) : sm100::v1::supported(s);
   if (s->path == ADS_PATH_TCGEN05 && !tc_ok) {
-    set_error("%s: tcgen05 path needs fp16/bf16 inputs, a head dim it was built for and alpha 1.5 or 2 "
-              "(got dtype=%d D=%d alpha=%g)", who, s->dtype, s->D, s->alpha);
+    set_error("%s: tcgen05 path needs fp16/bf16 inputs and a head dim it was built for (got dtype=%d D=%d)",
+              who, s->dtype, s->D);
     return ADS_ERR_UNSUPPORTED;
   }
   *path = (s->path == ADS_PATH_SIMT || !tc_ok) ? ADS_PATH_SIMT : ADS_PATH_TCGEN05;

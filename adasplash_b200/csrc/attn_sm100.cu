@@ -121,11 +121,8 @@ bool supported(const ads_attn_shape* s) {
   return true;
 }
 
-// Shapes the first-generation kernels cover: what `supported` covers, with alpha 1.5 or 2.
-bool v1::supported(const ads_attn_shape* s) {
-  const float a = s->alpha == 0.f ? 1.5f : s->alpha;
-  return sm100::supported(s) && (a == 1.5f || a == 2.0f);
-}
+// Shapes the first-generation kernels cover: what `supported` covers, any alpha in (1, 2].
+bool v1::supported(const ads_attn_shape* s) { return sm100::supported(s); }
 
 size_t workspace_bytes(const ads_attn_shape*) { return kStatusBytes; }
 size_t min_workspace_bytes() { return kStatusBytes; }

@@ -1,5 +1,5 @@
 // Tensor-core kernels for the first-generation semantics (adasplash/adasplash_block_mask.py:
-// `sparse_attn(q, k, v, alpha, is_causal, varlen, niter)`): alpha = 1.5 or 2, causal or full
+// `sparse_attn(q, k, v, alpha, is_causal, varlen, niter)`): any alpha in (1, 2], causal or full
 // attention.  The same kernel templates as the AdaSplash-2 path, instantiated with the other row
 // math (alpha = 2: p = u, Jacobian weight 1 on the support) and without the causal tile ranges;
 // a translation unit of its own so that the two sets of kernels compile side by side.
@@ -16,18 +16,31 @@ int solve_td(const simt::Params& p, void* ws, size_t ws_bytes, cudaStream_t st) 
   return solve_t<T, D, true>(p, ws, ws_bytes, st);   // alpha and the mask are run-time parameters of the solver
 }
 
+// row math of the kernels: 0 = alpha 1.5, 1 = alpha 2, 2 = any other alpha (lg2 / ex2 powers)
+inline int alpha_mode(float alpha) { return alpha == 1.5f ? 0 : (alpha == 2.0f ? 1 : 2); }
+
 template <typename T, int D>
 int fwd_td(const simt::Params& p, void* ws, cudaStream_t st) {
-  const bool a2 = p.alpha == 2.0f;
-  if (p.causal) return a2 ? fwd_t<T, D, 1, true>(p, ws, st) : fwd_t<T, D, 0, true>(p, ws, st);
-  return a2 ? fwd_t<T, D, 1, false>(p, ws, st) : fwd_t<T, D, 0, false>(p, ws, st);
+  switch (alpha_mode(p.alpha) * 2 + (p.causal ? 1 : 0)) {
+    case 0: return fwd_t<T, D, 0, false>(p, ws, st);
+    case 1: return fwd_t<T, D, 0, true>(p, ws, st);
+    case 2: return fwd_t<T, D, 1, false>(p, ws, st);
+    case 3: return fwd_t<T, D, 1, true>(p, ws, st);
+    case 4: return fwd_t<T, D, 2, false>(p, ws, st);
+    default: return fwd_t<T, D, 2, true>(p, ws, st);
+  }
 }
 
 template <typename T, int D>
 int bwd_td(const simt::Params& p, void* ws, cudaStream_t st) {
-  const bool a2 = p.alpha == 2.0f;
-  if (p.causal) return a2 ? bwd_t<T, D, 1, true>(p, ws, st) : bwd_t<T, D, 0, true>(p, ws, st);
-  return a2 ? bwd_t<T, D, 1, false>(p, ws, st) : bwd_t<T, D, 0, false>(p, ws, st);
+  switch (alpha_mode(p.alpha) * 2 + (p.causal ? 1 : 0)) {
+    case 0: return bwd_t<T, D, 0, false>(p, ws, st);
+    case 1: return bwd_t<T, D, 0, true>(p, ws, st);
+    case 2: return bwd_t<T, D, 1, false>(p, ws, st);
+    case 3: return bwd_t<T, D, 1, true>(p, ws, st);
+    case 4: return bwd_t<T, D, 2, false>(p, ws, st);
+    default: return bwd_t<T, D, 2, true>(p, ws, st);
+  }
 }
 
 template <typename F64, typename F128>

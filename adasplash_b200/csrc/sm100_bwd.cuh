@@ -291,6 +291,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     ptx::mbar_arrive_warp(q_ready);
     const float tau = row_ok ? p.taus[(size_t)bh * p.N + row] : 0.f;
     const float dl = row_ok ? p.delta[(size_t)bh * p.N + row] : 0.f;
+    const simt::Powers powers(p.alpha);   // used by the generic-alpha instantiation only
     const bool rows_full = m0 + kBlockM <= len;
     TileScan scan(bm_head, qt, T_tiles, p.rows_padded, p.n_words);
     int kt, n_active = 0;
@@ -339,8 +340,11 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
               if constexpr (AM == 0) {
                 const float u0 = fmaxf(s[c] - tau, 0.f), u1 = fmaxf(s[c + 1] - tau, 0.f);
                 dk[c >> 1] = pack2<T>(u0 * (dp[c] - dl), u1 * (dp[c + 1] - dl));
-              } else {  // alpha = 2: the Jacobian weight is 1 on the support
+              } else if constexpr (AM == 1) {  // alpha = 2: the Jacobian weight is 1 on the support
                 dk[c >> 1] = pack2<T>(s[c] > tau ? dp[c] - dl : 0.f, s[c + 1] > tau ? dp[c + 1] - dl : 0.f);
+              } else {  // any alpha: weight u^(1/(alpha-1) - 1)
+                dk[c >> 1] = pack2<T>(powers.g(fmaxf(s[c] - tau, 0.f)) * (dp[c] - dl),
+                                      powers.g(fmaxf(s[c + 1] - tau, 0.f)) * (dp[c + 1] - dl));
               }
             }
           } else {
@@ -349,7 +353,8 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             for (int c = 0; c < 32; c += 2) {
               const float u0 = s[c] - tau, u1 = s[c + 1] - tau;
               // select, not multiply: dP of a padded key or row may be anything
-              const float w0 = AM == 0 ? u0 : 1.f, w1 = AM == 0 ? u1 : 1.f;
+              const float w0 = AM == 0 ? u0 : (AM == 1 ? 1.f : powers.g(fmaxf(u0, 0.f)));
+              const float w1 = AM == 0 ? u1 : (AM == 1 ? 1.f : powers.g(fmaxf(u1, 0.f)));
               const float d0 = (u0 > 0.f && c <= lim) ? w0 * (dp[c] - dl) : 0.f;
               const float d1 = (u1 > 0.f && c + 1 <= lim) ? w1 * (dp[c + 1] - dl) : 0.f;
               dk[c >> 1] = pack2<T>(d0, d1);
@@ -700,6 +705,7 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
     const int key = n0 + r;
     const bool key_ok = key < len;
     const int kh = wq >> 1;              // which 64-key half
+    const simt::Powers powers(p.alpha);  // used by the generic-alpha instantiation only
     const uint32_t lane_addr = tmem_base + ((uint32_t)(wq * 32) << 16);
     bool dead = false;
     if (!ptx::mbar_wait_warp(kv_full, 0)) { raise_abort(cta_abort, p.status, kStTimeoutEpilogue); dead = true; }
@@ -780,11 +786,16 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
                   pk[(c >> 1) + 1] = pack2<T>(u2 * u2, u3 * u3);
                   dk[c >> 1] = pack2<T>(u0 * (dp[c] - l4.x), u1 * (dp[c + 1] - l4.y));
                   dk[(c >> 1) + 1] = pack2<T>(u2 * (dp[c + 2] - l4.z), u3 * (dp[c + 3] - l4.w));
-                } else {  // alpha = 2: p = u, Jacobian weight 1 on the support
+                } else if constexpr (AM == 1) {  // alpha = 2: p = u, Jacobian weight 1 on the support
                   pk[c >> 1] = pack2<T>(u0, u1);
                   pk[(c >> 1) + 1] = pack2<T>(u2, u3);
                   dk[c >> 1] = pack2<T>(u0 > 0.f ? dp[c] - l4.x : 0.f, u1 > 0.f ? dp[c + 1] - l4.y : 0.f);
                   dk[(c >> 1) + 1] = pack2<T>(u2 > 0.f ? dp[c + 2] - l4.z : 0.f, u3 > 0.f ? dp[c + 3] - l4.w : 0.f);
+                } else {  // any alpha
+                  pk[c >> 1] = pack2<T>(powers.p(u0), powers.p(u1));
+                  pk[(c >> 1) + 1] = pack2<T>(powers.p(u2), powers.p(u3));
+                  dk[c >> 1] = pack2<T>(powers.g(u0) * (dp[c] - l4.x), powers.g(u1) * (dp[c + 1] - l4.y));
+                  dk[(c >> 1) + 1] = pack2<T>(powers.g(u2) * (dp[c + 2] - l4.z), powers.g(u3) * (dp[c + 3] - l4.w));
                 }
               }
             } else {
@@ -801,9 +812,13 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
               if constexpr (AM == 0) {
                 pk[c >> 1] = pack2<T>(ok0 ? u0 * u0 : 0.f, ok1 ? u1 * u1 : 0.f);
                 dk[c >> 1] = pack2<T>(ok0 ? u0 * (dp[c] - l2.x) : 0.f, ok1 ? u1 * (dp[c + 1] - l2.y) : 0.f);
-              } else {
+              } else if constexpr (AM == 1) {
                 pk[c >> 1] = pack2<T>(ok0 ? u0 : 0.f, ok1 ? u1 : 0.f);
                 dk[c >> 1] = pack2<T>(ok0 ? dp[c] - l2.x : 0.f, ok1 ? dp[c + 1] - l2.y : 0.f);
+              } else {
+                const float v0 = ok0 ? u0 : 0.f, v1 = ok1 ? u1 : 0.f;
+                pk[c >> 1] = pack2<T>(powers.p(v0), powers.p(v1));
+                dk[c >> 1] = pack2<T>(ok0 ? powers.g(v0) * (dp[c] - l2.x) : 0.f, ok1 ? powers.g(v1) * (dp[c + 1] - l2.y) : 0.f);
               }
             }
             }

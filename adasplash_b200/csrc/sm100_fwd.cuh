@@ -66,7 +66,8 @@ __device__ __forceinline__ void zero_tile_rows(uint8_t* tile, int panels, int fi
   __syncwarp();
 }
 
-// AM selects the row math: 0 = alpha 1.5 (p = u^2, weight u), 1 = alpha 2 (p = u, weight 1[u>0]);
+// AM selects the row math: 0 = alpha 1.5 (p = u^2, weight u), 1 = alpha 2 (p = u, weight 1[u>0]),
+// 2 = any alpha in (1, 2) through the lg2 / ex2 units (p = u^(1/(alpha-1)), weight p / u);
 // CAUSAL = false is full attention (every key tile up to the sequence length, no diagonal mask).
 // <0, true> is the AdaSplash-2 path; the others serve the first-generation semantics.
 template <typename T, int D, int AM = 0, bool CAUSAL = true>
@@ -287,6 +288,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     }
     ptx::mbar_arrive_warp(q_ready);
     const float tau = row_ok ? p.taus[(size_t)bh * p.N + row] : 0.f;
+    const simt::Powers powers(p.alpha);   // used by the generic-alpha instantiation only
     float supp = 0.f;
     TileScan scan(bm_head, qt, T_tiles, p.rows_padded, p.n_words);
     int kt, n_active = 0;
@@ -307,10 +309,15 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
           supp += u0 + u1;
           pw = pack2<T>(u0 * u0, u1 * u1);
           uw = pack2<T>(u0, u1);
-        } else {
+        } else if constexpr (AM == 1) {
           const float g0 = u0 > 0.f ? 1.f : 0.f, g1 = u1 > 0.f ? 1.f : 0.f;
           supp += g0 + g1;
           pw = pack2<T>(u0, u1);
+          uw = pack2<T>(g0, g1);
+        } else {
+          const float g0 = powers.g(u0), g1 = powers.g(u1);
+          supp += g0 + g1;
+          pw = pack2<T>(powers.p(u0), powers.p(u1));
           uw = pack2<T>(g0, g1);
         }
       };

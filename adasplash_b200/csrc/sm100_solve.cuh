@@ -87,7 +87,7 @@ struct SolveSmem {
 };
 
 // V1 = false is the AdaSplash-2 solver described above.  V1 = true serves the first-generation
-// semantics on the same machinery (alpha = 1.5 or 2, causal or full attention;
+// semantics on the same machinery (any alpha in (1, 2], causal or full attention;
 // adasplash_block_mask.py:40-296): the same two sweeps (row maxima, candidates within 1 of the
 // maximum), then no histogram: the bracket is [max - 1, max - n^(1-alpha)] with n the row's number
 // of valid keys, niter Halley / bisection steps run on the candidates, and the block mask is
@@ -305,6 +305,7 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
     int sweep_no = 0;  // sweeps over S started so far (fixes the S buffer of every tile)
     uint32_t full_par = 0;  // bit b: parity of this group's next product in S buffer b
     float a0 = 0.f, a1 = 0.f, a2 = 0.f;
+    const simt::Powers powers(V1 ? p.alpha : 1.5f);   // first-generation instantiation only
     uint16_t head = kCandNil;  // this thread's list of scores >= tau0
     int ncand = 0;             // its length (counted on the first walk)
 
@@ -416,8 +417,12 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
                   const float d = v[g4 * 4 + c] - thr;
-                  if (V1 && mode == kModeHalley && p.alpha == 2.0f) {
-                    if (d > 0.f) { a0 += d; a1 += 1.f; }   // sum u, support size
+                  if (V1 && mode == kModeHalley && p.alpha != 1.5f) {
+                    // sum u^(1/(alpha-1)), sum of the Jacobian weights g, sum g / u
+                    if (d > 0.f) {
+                      const float gw = powers.g(d);
+                      a0 += powers.p(d); a1 += gw; a2 += powers.mode == 2 ? gw / d : 0.f;
+                    }
                   } else {
                     if (d > 0.f) { a0 = fmaf(d, d, a0); a1 += d; a2 += 1.f; }
                   }
@@ -568,8 +573,11 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
               } else {
                 const float d = c.z - hs.t;
                 if (d > 0.f) {
-                  if (p.alpha == 2.0f) { a0 += d; a1 += 1.f; }
-                  else { a0 = fmaf(d, d, a0); a1 += d; a2 += 1.f; }
+                  if (powers.mode == 0) { a0 = fmaf(d, d, a0); a1 += d; a2 += 1.f; }
+                  else {
+                    const float gw = powers.g(d);
+                    a0 += powers.p(d); a1 += gw; a2 += powers.mode == 2 ? gw / d : 0.f;
+                  }
                 }
               }
             } else {

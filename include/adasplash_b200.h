@@ -43,8 +43,9 @@ enum {
 /* alpha = 1.5 with the causal mask is the AdaSplash-2 path (adasplash/adasplash_v2.py).
  * Any other alpha in (1, 2] and / or full attention are the semantics of the reference's
  * first-generation kernels (adasplash/adasplash_block_mask.py:938-1232: `sparse_attn(q, k, v,
- * alpha, is_causal, varlen, niter)`, no grouped-query heads); they run on the CUDA-core
- * kernels with a Halley / bisection solver on [max-1, max-n^(1-alpha)].
+ * alpha, is_causal, varlen, niter)`, no grouped-query heads): a Halley / bisection solver on
+ * [max-1, max-n^(1-alpha)], block mask at the lower end of the final bracket.  Both run on the
+ * tensor-core kernels for 16-bit inputs with head dim <= 128, else on the CUDA-core kernels.
  *
  * Shape of one attention problem.  q is (B,Hq,N,D) contiguous, k and v are
  * (B,Hkv,N,D) contiguous, Hq % Hkv == 0, D in {16,32,64,128,256}, N >= 64

@@ -153,6 +153,53 @@ def make_v1(adasplash, out_dir):
         print("wrote", name, flush=True)
 
 
+V1_BF16_CASES = {
+    # name: (alpha, is_causal) -- bf16 inputs: the cases the tensor-core kernels serve
+    "v1_bf16_a2_full": (2.0, False), "v1_bf16_a2_causal": (2.0, True), "v1_bf16_a15_full": (1.5, False),
+}
+
+
+def make_v1_bf16(adasplash, out_dir):
+    B, H, N, D = 1, 2, 256, 64
+    for idx, (name, (alpha, causal)) in enumerate(V1_BF16_CASES.items()):
+        seed = 2500 + idx
+        q, k, v = (_gen((B, H, N, D), seed + 100 * i, 1.0, torch.bfloat16) for i in range(3))
+        do = _gen((B, H, N, D), seed + 300, 1.0, torch.bfloat16)
+        qc, kc, vc = (t.cuda().requires_grad_(True) for t in (q, k, v))
+        out = adasplash.adasplash(qc, kc, vc, alpha=alpha, is_causal=causal, niter=10)
+        try:
+            dq, dk, dv = (g.cpu() for g in torch.autograd.grad(out, (qc, kc, vc), do.cuda()))
+        except Exception as e:  # noqa: BLE001  (a backward that does not compile for this dtype)
+            print(name, "backward failed:", type(e).__name__, str(e)[:200], flush=True)
+            dq = dk = dv = None
+        torch.save({"q": q, "k": k, "v": v, "dout": do, "alpha": alpha, "is_causal": causal,
+                    "out": out.detach().cpu(), "dq": dq, "dk": dk, "dv": dv},
+                   os.path.join(out_dir, name + ".pt"))
+        print("wrote", name, flush=True)
+
+
+def time_v1(adasplash, out_dir):
+    """alpha = 2, full attention, B=4 H=32 N=8192 D=64 bf16: the first-generation kernels."""
+    path = os.path.join(out_dir, "reference_timings.json")
+    res = json.load(open(path)) if os.path.exists(path) else {}
+    g = torch.Generator(device="cuda").manual_seed(77)
+    q, k, v, do = (torch.randn(4, 32, 8192, 64, device="cuda", generator=g).bfloat16() for _ in range(4))
+    q, k, v = (t.requires_grad_(True) for t in (q, k, v))
+
+    def fb():
+        o = adasplash.adasplash(q, k, v, alpha=2.0, is_causal=False)
+        torch.autograd.grad(o, (q, k, v), do)
+    t0 = time.time()
+    fb()
+    torch.cuda.synchronize()
+    res["V1_a2_full_B4_H32_N8192_D64_first_call_s"] = time.time() - t0
+    res["V1_a2_full_B4_H32_N8192_D64_fwd_ms"] = _time(lambda: adasplash.adasplash(q, k, v, alpha=2.0, is_causal=False), 5)
+    res["V1_a2_full_B4_H32_N8192_D64_fwdbwd_ms"] = _time(fb, 5)
+    print("v1", res["V1_a2_full_B4_H32_N8192_D64_fwd_ms"], res["V1_a2_full_B4_H32_N8192_D64_fwdbwd_ms"], flush=True)
+    with open(path, "w") as f:
+        json.dump(res, f, indent=1)
+
+
 def make_rowwise(adasplash, out_dir):
     fx = {}
     x = _gen((16, 4096), 3000, 4.0)
@@ -276,6 +323,7 @@ def main():
     ap.add_argument("--skip-fixtures", action="store_true", help="do not rewrite the small fixtures")
     ap.add_argument("--big-slices", default=None, nargs="?", const="all",
                     help="write the benchmark-length slice fixtures (all, or a comma list of names)")
+    ap.add_argument("--v1-bf16", action="store_true", help="write the bf16 first-generation fixtures and time that path")
     ap.add_argument("--single-config", action="store_true",
                     help="set the reference's ADASPLASH_TEST_FAST_AUTOTUNE=1 (one tuning candidate per kernel, "
                          "as its own test suite does): at 65536 positions the full autotune compiles for more "
@@ -295,6 +343,9 @@ def main():
     # few-head slice tunes in a minute or two and a timing case of the same length that follows in
     # this process reuses the choice.  (Tuning on a full-size batch runs every candidate on it:
     # the 16384-long configuration took 560 s that way.)
+    if a.v1_bf16:
+        make_v1_bf16(adasplash, a.out)
+        time_v1(adasplash, a.out)
     if a.big_slices:
         make_big_slices(adasplash, a.out, None if a.big_slices == "all" else a.big_slices.split(","))
     if a.time:

@@ -106,7 +106,7 @@ def _resolved(q, alpha, causal):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
-@pytest.mark.parametrize("alpha,causal", [(1.5, False), (2.0, True), (2.0, False)])
+@pytest.mark.parametrize("alpha,causal", [(1.5, False), (2.0, True), (2.0, False), (1.333, True), (1.75, False)])
 @pytest.mark.parametrize("case", [(1, 2, 256, 64, None, 1.0), (2, 2, 320, 128, [300, 129], 1.0), (1, 1, 192, 32, [191], 1.0),
                                   (1, 2, 1024, 128, None, 1.5), (2, 1, 200, 16, [200, 70], 1.0)])
 def test_16bit_tensor_core_path_matches_exact_definition(dtype, alpha, causal, case):
@@ -124,11 +124,12 @@ def test_16bit_tensor_core_path_matches_exact_definition(dtype, alpha, causal, c
     for key in ("out", "dq", "dk", "dv"):
         scale = max(1.0, ex[key].abs().max().item())
         err = (got[key].double() - ex[key]).abs()
-        if alpha == 2.0 and key != "out":
-            # sparsemax: the Jacobian weight is 1 on the support and 0 off it, so a score that the
-            # 16-bit rounding of the scaled operand moves across its threshold changes a few
-            # gradient entries by O(1) (the CUDA-core kernels on the same inputs do the same,
-            # see below); all but a few entries must be within tolerance
+        if alpha > 1.5 and key != "out":
+            # alpha > 1.5: the Jacobian weight u^((2-alpha)/(alpha-1)) is not Lipschitz at the
+            # threshold (for sparsemax it jumps from 0 to 1), so a score that the 16-bit rounding
+            # of the scaled operand moves by 1e-2 near its threshold changes a few gradient
+            # entries by O(1) (the CUDA-core kernels on the same inputs do the same, see below);
+            # all but a few entries must be within tolerance
             assert (err < 2e-2 * scale).double().mean() > 0.98, key
         else:
             assert err.max() < 2e-2 * scale, key
@@ -149,7 +150,7 @@ def test_16bit_tensor_core_path_matches_exact_definition(dtype, alpha, causal, c
         assert (got[key] - ref[key]).abs().max() < 1e-2 * scale, key
 
 
-@pytest.mark.parametrize("alpha,causal", [(1.5, False), (2.0, True), (2.0, False)])
+@pytest.mark.parametrize("alpha,causal", [(1.5, False), (2.0, True), (2.0, False), (1.333, False)])
 def test_tensor_core_thresholds_match_cuda_core_thresholds(alpha, causal):
     # thresholds and block masks of the two kernel families after the same ten steps from the
     # same bracket; nearly flat rows (scale 0.05) overflow the candidate pool and sweep S instead
@@ -164,6 +165,37 @@ def test_tensor_core_thresholds_match_cuda_core_thresholds(alpha, causal):
         finally:
             _lib.set_kernel_path(None)
         torch.cuda.synchronize()
-        assert (ta - tb).abs().max() < 1e-5, (scale, (ta - tb).abs().max().item())
+        # generic alpha goes through the approximate lg2 / ex2 units in both families
+        assert (ta - tb).abs().max() < (1e-5 if alpha in (1.5, 2.0) else 1e-4), (scale, (ta - tb).abs().max().item())
         diff = sum(bin(int(x) & 0xFFFFFFFF).count("1") for x in (ma ^ mb).flatten().tolist())
         assert diff <= 2, (scale, diff)
+
+
+@pytest.mark.parametrize("path", ["tcgen05", "simt"])
+@pytest.mark.parametrize("name", ["v1_bf16_a2_full", "v1_bf16_a2_causal", "v1_bf16_a15_full"])
+def test_reference_golden_bf16(name, path):
+    """bf16 outputs of the reference's first-generation kernels (niter = 10), on both kernel
+    families.  Output within 2e-2 of the tensor's scale; gradients likewise, except that for
+    sparsemax a score which the two implementations' different 16-bit rounding points put on
+    different sides of its threshold moves a few entries by O(1)."""
+    from adasplash_b200 import _lib
+    fx = torch.load(os.path.join(GOLD, name + ".pt"), weights_only=False)
+    _lib.set_kernel_path(path)
+    try:
+        if path == "tcgen05":
+            assert _resolved(fx["q"].cuda(), fx["alpha"], fx["is_causal"]) == _lib.PATH_TCGEN05
+        got = _run(adasplash.adasplash, fx["q"], fx["k"], fx["v"], fx["dout"], alpha=fx["alpha"],
+                   is_causal=fx["is_causal"], niter=10)
+    finally:
+        _lib.set_kernel_path(None)
+    assert (got["out"] - fx["out"].float()).abs().max() < 2e-2 * max(1.0, fx["out"].float().abs().max().item())
+    for key in ("dq", "dk", "dv"):
+        if fx[key] is None:
+            continue
+        ref = fx[key].float()
+        err = (got[key] - ref).abs()
+        tol = 2e-2 * max(1.0, ref.abs().max().item())
+        if fx["alpha"] == 2.0:
+            assert (err < tol).float().mean() > 0.98, key
+        else:
+            assert err.max() < tol, key
