@@ -21,7 +21,7 @@ def _ptr(t):
     return None if t is None else t.data_ptr()
 
 
-def _check_inputs(q, k, v, varlen, require_pow2=True):
+def _check_inputs(q, k, v, varlen, require_pow2=True, min_len=BMASK_TILE):
     assert q.dim() == 4, "q must have shape (batch, heads, seq_len, head_dim)"
     B, N_H, N_CTX, H_DIM = q.shape
     assert H_DIM in {16, 32, 64, 128, 256}
@@ -32,7 +32,7 @@ def _check_inputs(q, k, v, varlen, require_pow2=True):
         f"N_H ({N_H}) must be a positive multiple of N_KV_H ({N_KV_H}).")
     assert k.shape[0] == B and k.shape[2] == N_CTX and k.shape[3] == H_DIM, (
         f"K/V must have shape (B={B}, N_KV_H, N_CTX={N_CTX}, H_DIM={H_DIM}); got {tuple(k.shape)}.")
-    assert N_CTX >= BMASK_TILE, f"N_CTX={N_CTX} must be at least BMASK_TILE={BMASK_TILE}."
+    assert N_CTX >= min_len, f"N_CTX={N_CTX} must be at least {min_len}."
     if varlen is None:
         assert not require_pow2 or (N_CTX & (N_CTX - 1)) == 0, "If varlen is None, N_CTX must be a power of two."
     else:

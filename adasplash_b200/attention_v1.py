@@ -20,7 +20,7 @@ from . import attention as att
 class _SparseAttentionV1(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, alpha=1.5, is_causal=False, varlen=None, niter=10):
-        att._check_inputs(q, k, v, varlen, require_pow2=False)
+        att._check_inputs(q, k, v, varlen, require_pow2=False, min_len=1)   # the v1 kernels take any length
         assert k.shape[1] == q.shape[1], "adasplash_v1 does not support grouped-query attention"
         assert 1.0 < alpha <= 2.0, f"alpha must be in (1, 2]; got {alpha}"
         taus, bmask = att.solve(q, k, niter, varlen, None, alpha, is_causal)

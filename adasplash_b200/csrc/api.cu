@@ -36,9 +36,11 @@ Geometry geometry(int N) {
 
 int check_shape(const ads_attn_shape* s, const char* who) {
   if (s == nullptr) { set_error("%s: null shape", who); return ADS_ERR_BAD_ARG; }
-  if (s->B < 1 || s->Hq < 1 || s->Hkv < 1 || s->N < kTile || s->niter < 0) {
-    set_error("%s: bad shape B=%d Hq=%d Hkv=%d N=%d niter=%d (need N >= 64)", who, s->B, s->Hq,
-              s->Hkv, s->N, s->niter);
+  // AdaSplash-2 requires N >= 64 (adasplash_v2.py:1265); the first-generation kernels take any N
+  const bool v2_shape = (s->alpha == 0.f || s->alpha == 1.5f) && s->non_causal == 0;
+  if (s->B < 1 || s->Hq < 1 || s->Hkv < 1 || s->N < (v2_shape ? kTile : 1) || s->niter < 0) {
+    set_error("%s: bad shape B=%d Hq=%d Hkv=%d N=%d niter=%d (causal alpha = 1.5 needs N >= 64)", who, s->B,
+              s->Hq, s->Hkv, s->N, s->niter);
     return ADS_ERR_BAD_ARG;
   }
   if (s->Hq % s->Hkv != 0) { set_error("%s: Hq=%d not a multiple of Hkv=%d", who, s->Hq, s->Hkv); return ADS_ERR_BAD_ARG; }
