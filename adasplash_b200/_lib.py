@@ -33,12 +33,15 @@ SIGNATURES = {
                                        c_int32, c_int32, c_void_p]),
     "adasplash2_workspace_bytes": (c_size_t, [POINTER(AttnShape)]),
     "adasplash2_bitmap_words": (c_int64, [POINTER(AttnShape), POINTER(c_int32), POINTER(c_int32)]),
+    "adasplash2_support_bytes": (c_size_t, [POINTER(AttnShape)]),
     "adasplash2_solve": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                                   POINTER(AttnShape), c_void_p, c_size_t, c_void_p]),
+                                   POINTER(AttnShape), c_void_p, c_size_t, c_void_p, c_size_t, c_void_p]),
     "adasplash2_mask_from_tau": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                            POINTER(AttnShape), c_void_p, c_size_t, c_void_p]),
-    "adasplash2_fwd": (c_int32, [c_void_p] * 8 + [POINTER(AttnShape), c_void_p, c_size_t, c_void_p]),
-    "adasplash2_bwd": (c_int32, [c_void_p] * 13 + [POINTER(AttnShape), c_void_p, c_size_t, c_void_p]),
+    "adasplash2_fwd": (c_int32, [c_void_p] * 8 + [POINTER(AttnShape), c_void_p, c_size_t, c_void_p, c_size_t,
+                                 c_void_p]),
+    "adasplash2_bwd": (c_int32, [c_void_p] * 13 + [POINTER(AttnShape), c_void_p, c_size_t, c_void_p, c_size_t,
+                                 c_void_p]),
     "adasplash2_bwd_static": (c_int32, [c_void_p] * 11 + [POINTER(AttnShape), c_void_p]),
     "adasplash2_check_status": (c_int32, [c_void_p, c_void_p]),
     "adasplash2_debug_waits": (c_int32, [c_int64, c_int32]),

@@ -71,6 +71,21 @@ def _workspace(shape, device):
     return torch.empty(max(nbytes, 256), device=device, dtype=torch.uint8), nbytes
 
 
+ROW_SUPPORTS = True   # let the solver export the rows' supports, so that sparse heads run as gathers
+
+
+def support_buffer(shape, device):
+    """Buffer for the rows' supports of one problem (None where the library has no such route)."""
+    nbytes = int(_lib.load().adasplash2_support_bytes(ctypes.byref(shape)))
+    if nbytes == 0 or not ROW_SUPPORTS:
+        return None
+    return torch.empty(nbytes, device=device, dtype=torch.uint8)
+
+
+def _sup_args(support):
+    return (None, 0) if support is None else (support.data_ptr(), support.numel())
+
+
 DEBUG_STATUS = False  # tests set this: check the device status word after every call (synchronises)
 
 
@@ -79,8 +94,9 @@ def _maybe_check(ws, st):
         _lib.check(_lib.load().adasplash2_check_status(_ptr(ws), st))
 
 
-def solve(q, k, niter=1, varlen=None, path=None, alpha=1.5, is_causal=True):
-    """Thresholds and block mask only: (taus (B,Hq,N) fp32, bmask int32)."""
+def solve(q, k, niter=1, varlen=None, path=None, alpha=1.5, is_causal=True, support=None):
+    """Thresholds and block mask only: (taus (B,Hq,N) fp32, bmask int32).  `support`: a buffer
+    from `support_buffer` that receives the rows' supports."""
     lib = _lib.load()
     shape = make_shape(q, k, niter, varlen, path, alpha, is_causal)
     rows, words = bitmap_extent(shape)
@@ -91,7 +107,7 @@ def solve(q, k, niter=1, varlen=None, path=None, alpha=1.5, is_causal=True):
         ws, nbytes = _workspace(shape, q.device)
         st = torch.cuda.current_stream().cuda_stream
         _lib.check(lib.adasplash2_solve(_ptr(q), _ptr(k), _ptr(varlen), _ptr(taus), _ptr(bmask),
-                                        ctypes.byref(shape), _ptr(ws), nbytes, st))
+                                        ctypes.byref(shape), _ptr(ws), nbytes, *_sup_args(support), st))
         _maybe_check(ws, st)
     return taus, bmask
 
@@ -129,16 +145,18 @@ class _SparseAttention(torch.autograd.Function):
         out2 = torch.empty_like(q)
         with torch.cuda.device(dev):
             ws, nbytes = _workspace(shape, dev)
+            support = support_buffer(shape, dev)
             st = torch.cuda.current_stream().cuda_stream
             sp = ctypes.byref(shape)
             _lib.check(lib.adasplash2_solve(_ptr(q), _ptr(k), _ptr(varlen), _ptr(taus),
-                                            _ptr(bmask), sp, _ptr(ws), nbytes, st))
+                                            _ptr(bmask), sp, _ptr(ws), nbytes, *_sup_args(support), st))
             _maybe_check(ws, st)
             _lib.check(lib.adasplash2_fwd(_ptr(q), _ptr(k), _ptr(v), _ptr(varlen), _ptr(taus),
                                           _ptr(bmask), _ptr(out), _ptr(out2), sp, _ptr(ws),
-                                          nbytes, st))
+                                          nbytes, *_sup_args(support), st))
             _maybe_check(ws, st)
         ctx.save_for_backward(q, k, v, out2, taus, bmask)
+        ctx.support = support
         ctx.varlen = varlen
         ctx.niter = niter
         return out
@@ -149,12 +167,14 @@ class _SparseAttention(torch.autograd.Function):
         do = do.contiguous()
         if do.dtype != q.dtype:
             do = do.to(q.dtype)
-        dq, dk, dv, _, _ = backward_raw(q, k, v, do, out2, taus, bmask, ctx.varlen, ctx.niter)
+        dq, dk, dv, _, _ = backward_raw(q, k, v, do, out2, taus, bmask, ctx.varlen, ctx.niter,
+                                        support=ctx.support)
         return dq, dk, dv, None, None
 
 
-def forward_raw(q, k, v, taus, bmask, varlen=None, path=None, alpha=1.5, is_causal=True):
-    """`adasplash2_fwd` alone for given thresholds and block mask: (out, out2)."""
+def forward_raw(q, k, v, taus, bmask, varlen=None, path=None, alpha=1.5, is_causal=True, support=None):
+    """`adasplash2_fwd` alone for given thresholds and block mask: (out, out2).  `support`: the
+    buffer a `solve` of the same problem filled."""
     lib = _lib.load()
     shape = make_shape(q, k, 0, varlen, path, alpha, is_causal)
     out = torch.empty_like(q)
@@ -164,13 +184,13 @@ def forward_raw(q, k, v, taus, bmask, varlen=None, path=None, alpha=1.5, is_caus
         st = torch.cuda.current_stream().cuda_stream
         _lib.check(lib.adasplash2_fwd(_ptr(q), _ptr(k), _ptr(v), _ptr(varlen), _ptr(taus),
                                       _ptr(bmask), _ptr(out), _ptr(out2), ctypes.byref(shape),
-                                      _ptr(ws), nbytes, st))
+                                      _ptr(ws), nbytes, *_sup_args(support), st))
         _maybe_check(ws, st)
     return out, out2
 
 
 def backward_raw(q, k, v, do, out2, taus, bmask, varlen=None, niter=1, stages=0, buffers=None,
-                 path=None, alpha=1.5, is_causal=True):
+                 path=None, alpha=1.5, is_causal=True, support=None):
     """`adasplash2_bwd`: returns (dq, dk, dv, delta, bmask_t).  `stages` != 0 runs only
     the named kernels (ADS_BWD_* mask; a measurement aid), reusing `buffers` =
     (dq, dk, dv, delta, bmask_t) from an earlier full call."""
@@ -188,7 +208,7 @@ def backward_raw(q, k, v, do, out2, taus, bmask, varlen=None, niter=1, stages=0,
         _lib.check(lib.adasplash2_bwd(_ptr(q), _ptr(k), _ptr(v), _ptr(do), _ptr(out2),
                                       _ptr(varlen), _ptr(taus), _ptr(bmask), _ptr(bmask_t),
                                       _ptr(delta), _ptr(dq), _ptr(dk), _ptr(dv),
-                                      ctypes.byref(shape), _ptr(ws), nbytes, st))
+                                      ctypes.byref(shape), _ptr(ws), nbytes, *_sup_args(support), st))
         _maybe_check(ws, st)
     return dq, dk, dv, delta, bmask_t
 

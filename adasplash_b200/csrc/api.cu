@@ -6,6 +6,7 @@
 
 #include "attn_simt.cuh"
 #include "attn_sm100.cuh"
+#include "sparse_rows.cuh"
 
 namespace ads {
 
@@ -106,6 +107,22 @@ int clear_status(void* ws, size_t ws_bytes, cudaStream_t st, const char* who) {
   return ADS_OK;
 }
 
+// The row-support buffer takes part only on the tensor-core path of shapes the gather kernels
+// cover; anywhere else it is ignored.  A buffer that is too small is an error.
+int resolve_support(const ads_attn_shape* s, int path, void* support, size_t support_bytes, const char* who,
+                    void** out) {
+  *out = nullptr;
+  if (support == nullptr || path != ADS_PATH_TCGEN05 || !sparse::supported(s)) return ADS_OK;
+  const size_t need = sparse::support_bytes(s);
+  if (support_bytes < need) {
+    set_error("%s: support buffer too small (%zu < %zu)", who, support_bytes, need);
+    return ADS_ERR_WORKSPACE;
+  }
+  if (((uintptr_t)support & 255) != 0) { set_error("%s: support buffer must be 256-byte aligned", who); return ADS_ERR_BAD_ARG; }
+  *out = support;
+  return ADS_OK;
+}
+
 template <typename F32, typename F16, typename BF16>
 int by_dtype(int dtype, F32 f32, F16 f16, BF16 bf16) {
   switch (dtype) {
@@ -139,6 +156,14 @@ extern "C" int adasplash2_resolved_path(const ads_attn_shape* shape) {
   return path;
 }
 
+extern "C" size_t adasplash2_support_bytes(const ads_attn_shape* shape) {
+  if (check_shape(shape, "support_bytes")) return 0;
+  int path;
+  if (resolve_path(shape, "support_bytes", &path)) return 0;
+  if (path != ADS_PATH_TCGEN05 || !sparse::supported(shape)) return 0;
+  return sparse::support_bytes(shape);
+}
+
 extern "C" size_t adasplash2_workspace_bytes(const ads_attn_shape* shape) {
   if (check_shape(shape, "workspace_bytes")) return 0;
   int path;
@@ -149,7 +174,7 @@ extern "C" size_t adasplash2_workspace_bytes(const ads_attn_shape* shape) {
 
 static int solve_common(const void* q, const void* k, const void* varlen, float* taus,
                         int32_t* bmask, const ads_attn_shape* s, void* ws, size_t ws_bytes,
-                        void* stream, int tau_given, const char* who) {
+                        void* support, size_t support_bytes, void* stream, int tau_given, const char* who) {
   if (int rc = check_shape(s, who)) return rc;
   if (!q || !k || !taus || !bmask) { set_error("%s: null pointer", who); return ADS_ERR_BAD_ARG; }
   int path;
@@ -157,6 +182,7 @@ static int solve_common(const void* q, const void* k, const void* varlen, float*
   cudaStream_t st = (cudaStream_t)stream;
   simt::Params p = make_params(s);
   p.q = q; p.k = k; p.varlen = varlen; p.taus = taus; p.bmask = bmask; p.tau_given = tau_given;
+  if (int rc = resolve_support(s, path, support, support_bytes, who, &p.support)) return rc;
   size_t bm_bytes = (size_t)s->B * s->Hq * p.rows_padded * p.n_words * sizeof(int32_t);
   cudaError_t e = cudaMemsetAsync(bmask, 0, bm_bytes, st);
   if (e != cudaSuccess) { set_error("%s: memset bitmap: %s", who, cudaGetErrorString(e)); return ADS_ERR_CUDA; }
@@ -165,6 +191,9 @@ static int solve_common(const void* q, const void* k, const void* varlen, float*
     if (ws == nullptr || ws_bytes < sm100::min_workspace_bytes()) {
       set_error("%s: workspace too small (%zu < %zu)", who, ws_bytes, sm100::min_workspace_bytes());
       return ADS_ERR_WORKSPACE;
+    }
+    if (p.support != nullptr) {
+      if (int rc = sparse::clear_header(p, st)) return rc;
     }
     return is_v2(s) ? sm100::solve(p, s->dtype, ws, ws_bytes, st) : sm100::v1::solve(p, s->dtype, ws, ws_bytes, st);
   }
@@ -176,9 +205,10 @@ static int solve_common(const void* q, const void* k, const void* varlen, float*
 
 extern "C" int adasplash2_solve(const void* q, const void* k, const void* varlen, float* taus,
                                 int32_t* bmask, const ads_attn_shape* shape, void* workspace,
-                                size_t workspace_bytes, void* stream) {
-  return solve_common(q, k, varlen, taus, bmask, shape, workspace, workspace_bytes, stream, 0,
-                      "adasplash2_solve");
+                                size_t workspace_bytes, void* support, size_t support_bytes,
+                                void* stream) {
+  return solve_common(q, k, varlen, taus, bmask, shape, workspace, workspace_bytes, support,
+                      support_bytes, stream, 0, "adasplash2_solve");
 }
 
 extern "C" int adasplash2_mask_from_tau(const void* q, const void* k, const void* varlen,
@@ -186,12 +216,13 @@ extern "C" int adasplash2_mask_from_tau(const void* q, const void* k, const void
                                         const ads_attn_shape* shape, void* workspace,
                                         size_t workspace_bytes, void* stream) {
   return solve_common(q, k, varlen, const_cast<float*>(taus), bmask, shape, workspace,
-                      workspace_bytes, stream, 1, "adasplash2_mask_from_tau");
+                      workspace_bytes, nullptr, 0, stream, 1, "adasplash2_mask_from_tau");
 }
 
 extern "C" int adasplash2_fwd(const void* q, const void* k, const void* v, const void* varlen,
                               const float* taus, const int32_t* bmask, void* out, void* out2,
-                              const ads_attn_shape* s, void* ws, size_t ws_bytes, void* stream) {
+                              const ads_attn_shape* s, void* ws, size_t ws_bytes, void* support,
+                              size_t support_bytes, void* stream) {
   const char* who = "adasplash2_fwd";
   if (int rc = check_shape(s, who)) return rc;
   if (!q || !k || !v || !taus || !bmask || !out || !out2) { set_error("%s: null pointer", who); return ADS_ERR_BAD_ARG; }
@@ -202,11 +233,15 @@ extern "C" int adasplash2_fwd(const void* q, const void* k, const void* v, const
   p.q = q; p.k = k; p.v = v; p.varlen = varlen;
   p.taus = const_cast<float*>(taus); p.bmask = const_cast<int32_t*>(bmask);
   p.out = out; p.out2 = out2;
+  if (int rc = resolve_support(s, path, support, support_bytes, who, &p.support)) return rc;
   if (int rc = clear_status(ws, ws_bytes, st, who)) return rc;
   if (path == ADS_PATH_TCGEN05) {
     if (ws == nullptr || ws_bytes < sm100::min_workspace_bytes()) {
       set_error("%s: workspace too small (%zu < %zu)", who, ws_bytes, sm100::min_workspace_bytes());
       return ADS_ERR_WORKSPACE;
+    }
+    if (p.support != nullptr) {  // heads whose supports were exported: a gather; the others: tiles
+      if (int rc = sparse::fwd(p, s->dtype, st)) return rc;
     }
     return is_v2(s) ? sm100::fwd(p, s->dtype, ws, st) : sm100::v1::fwd(p, s->dtype, ws, st);
   }
@@ -220,7 +255,7 @@ extern "C" int adasplash2_bwd(const void* q, const void* k, const void* v, const
                               const void* out2, const void* varlen, const float* taus,
                               const int32_t* bmask, int32_t* bmask_t, float* delta, void* dq,
                               void* dk, void* dv, const ads_attn_shape* s, void* ws,
-                              size_t ws_bytes, void* stream) {
+                              size_t ws_bytes, void* support, size_t support_bytes, void* stream) {
   const char* who = "adasplash2_bwd";
   if (int rc = check_shape(s, who)) return rc;
   if (!q || !k || !v || !dout || !out2 || !taus || !bmask || !bmask_t || !delta || !dq || !dk || !dv) {

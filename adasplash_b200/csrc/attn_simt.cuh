@@ -200,6 +200,7 @@ struct Params {
   float alpha;      // entmax alpha in (1, 2]
   int causal;       // 1 = causal mask
   float zscale;     // fp32((alpha-1) * sm_scale): scores are z = zscale * q.k
+  void* support;    // row-support buffer of the tensor-core path (support.cuh), or null
 };
 
 // ---------------------------------------------------------------------------

@@ -95,5 +95,5 @@ extern "C" int adasplash2_bwd_static(const void* q, const void* k, const void* v
   // itself, delta and the transposed mask are fully rewritten by its first two
   // kernels before anything reads them.
   return adasplash2_bwd(q, k, v, dout, out2, varlen, taus, bmask, bmask_t, delta, dq, dk, dv, shape,
-                        base, status_bytes, stream);
+                        base, status_bytes, nullptr, 0, stream);
 }

@@ -92,6 +92,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   const int bh = blockIdx.x / p.nq;
   const int b = bh / p.Hq, h = bh % p.Hq;
   const int kvh = h / (p.Hq / p.Hkv);
+  if (p.sup_on && p.sup.dense[b * p.Hkv + kvh] == 0) return;  // the gather kernels own this head
   const int len = load_len(p.varlen, p.varlen_is_i64, b, p.N);
   const int m0 = qt * kBlockM;
   const int Dg = p.d_true;  // head dim in global memory (16 / 32 run the D = 64 instantiation)
@@ -509,6 +510,7 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
   const int nt = (int)(blockIdx.x % p.nq);
   const int bkv = blockIdx.x / p.nq;
   const int b = bkv / p.Hkv, kvh = bkv % p.Hkv;
+  if (p.sup_on && p.sup.dense[bkv] == 0) return;  // the gather kernels own this head
   const int G = p.Hq / p.Hkv;
   const int len = load_len(p.varlen, p.varlen_is_i64, b, p.N);
   const int n0 = nt * kBlockN;

@@ -6,6 +6,7 @@
 
 #include "attn_simt.cuh"
 #include "sm100_ptx.cuh"
+#include "support.cuh"
 
 namespace ads {
 namespace sm100 {
@@ -37,6 +38,8 @@ struct TcParams {
   int causal;        // 0 = full attention (first-generation semantics only)
   int tau_given;
   int* status;       // device status word (0 = ok)
+  int sup_on;        // the caller gave a row-support buffer (support.cuh)
+  sup::View sup;
 };
 
 

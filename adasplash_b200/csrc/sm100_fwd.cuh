@@ -106,6 +106,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
   const int bh = blockIdx.x / p.nq;
   const int b = bh / p.Hq, h = bh % p.Hq;
   const int kvh = h / (p.Hq / p.Hkv);
+  // rows whose supports the solver exported are done by the gather kernels (support.cuh)
+  if (p.sup_on && p.sup.dense[b * p.Hkv + kvh] == 0) return;
   const int len = load_len(p.varlen, p.varlen_is_i64, b, p.N);
   const int m0 = qt * kBlockM;
   // Dg = head dim of the tensors in global memory (p.d_true).  It equals D except for head dims

@@ -60,9 +60,10 @@ constexpr int kSolveRows = 2 * kBlockM;  // query rows per CTA
 
 enum SweepMode : int { kModeMax = 0, kModeHist = 1, kModeHalley = 2, kModeFinal = 3, kModeCollect = 4 };
 
-// One entry of the candidate pool: a score >= tau0 of some row, the 64-key block it sits in,
-// and the previous entry of the same thread's list (written with one 8-byte store).
-struct __align__(8) Cand { float z; uint16_t kb; uint16_t next; };
+// One entry of the candidate pool: a score >= tau0 of some row, its key index (sequences of more
+// than 65536 keys: only the 64-key block it sits in), and the previous entry of the same
+// thread's list (written with one 8-byte store).
+struct __align__(8) Cand { float z; uint16_t key; uint16_t next; };
 constexpr uint16_t kCandNil = 0xffff;
 
 // Shared memory: K stages, barriers, exchange buffers, bitmap staging, then the two Q tiles and
@@ -308,6 +309,10 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
     const simt::Powers powers(V1 ? p.alpha : 1.5f);   // first-generation instantiation only
     uint16_t head = kCandNil;  // this thread's list of scores >= tau0
     int ncand = 0;             // its length (counted on the first walk)
+    const bool wide = p.N > 65536;  // key indices do not fit the 16 bits of a list entry
+    const int kb_shift = wide ? 0 : 6;
+    bool compact = false;      // the list was copied to one contiguous run starting at run0
+    int run0 = 0;
 
     // One pass over the S tiles of this group's causal range.  Instantiated once per sweep
     // kind, so that the per-group code carries no mode tests and each sweep runs a compact loop.
@@ -350,6 +355,8 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
             ptx::mbar_arrive_warp(s_free + bf);
           }
           float* v = reinterpret_cast<float*>(raw);
+          const int keybase = wide ? 2 * kt + half : n0 + c0;
+          const int kmask = wide ? 0 : 0xffff;
           if (need_mask) {
             const int lim = (full_attn ? len - 1 : min(row, len - 1)) - (n0 + c0);  // columns c <= lim survive
 #pragma unroll
@@ -386,7 +393,8 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
                       if (idx < warp_pool) {
                         const int slot = warp * warp_pool + idx;
                         Cand e;
-                        e.z = z; e.kb = (uint16_t)(2 * kt + half); e.next = head;
+                        e.z = z; e.next = head;
+                        e.key = (uint16_t)(keybase + ((g4 * 4 + c) & kmask));
                         pool[slot] = e;
                         head = (uint16_t)slot;
                         listed = true;
@@ -495,6 +503,7 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
       for (int c = 0; c < 8; ++c) cnt[c] = 0;
     };
 
+    bool full_sweeps = false;  // the candidate pool overflowed: every step sweeps S
     if (p.tau_given) {
       // bitmap for a given tau: one sweep over S
       if (grp_on) {
@@ -536,7 +545,7 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
       // lists or full sweeps: one decision for the CTA, which the producer and the MMA warps
       // are waiting for
       ptx::bar_sync(3, kSolveRowThreads);
-      const bool full_sweeps = *pool_ovf != 0;
+      full_sweeps = *pool_ovf != 0;
       ptx::mbar_arrive_warp(decide);
       if (grp_on && !full_sweeps) {
         // ---- Halley steps and the final step on this thread's list ----
@@ -550,8 +559,8 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
           if (lane >= o) incl += up;
         }
         const int used = min(pool_used[warp], warp_pool);
-        const bool compact = used + __shfl_sync(0xffffffffu, incl, 31) <= warp_pool;
-        const int run0 = warp * warp_pool + used + incl - ncand;
+        compact = used + __shfl_sync(0xffffffffu, incl, 31) <= warp_pool;
+        run0 = warp * warp_pool + used + incl - ncand;
         if (compact) {
           int dst = run0;
           for (int e = head, left = ncand; e != kCandNil && left > 0; --left) {
@@ -569,7 +578,8 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
               // niter steps on sum u^(1/(alpha-1)) - 1; the last round only records the 64x64
               // sub-tiles that hold a score above the lower end of the bracket
               if (last) {
-                if (c.z > hs.lo && row_ok) atomicOr(&s_bits[(grp * 2 + rb) * p.n_words + (c.kb >> 5)], 1u << (c.kb & 31));
+                const int kb = c.key >> kb_shift;
+                if (c.z > hs.lo && row_ok) atomicOr(&s_bits[(grp * 2 + rb) * p.n_words + (kb >> 5)], 1u << (kb & 31));
               } else {
                 const float d = c.z - hs.t;
                 if (d > 0.f) {
@@ -586,7 +596,8 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
                 a0 = fmaf(d, d, a0); a1 += d; a2 += 1.f;
                 // the final step also records the 64x64 sub-tiles that hold a score above the
                 // tau entering it (row block rb of this group, key block c.kb)
-                if (last && row_ok) atomicOr(&s_bits[(grp * 2 + rb) * p.n_words + (c.kb >> 5)], 1u << (c.kb & 31));
+                const int kb = c.key >> kb_shift;
+                if (last && row_ok) atomicOr(&s_bits[(grp * 2 + rb) * p.n_words + (kb >> 5)], 1u << (kb & 31));
               }
             }
           };
@@ -624,6 +635,73 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
           p.bmask[((size_t)bh * p.rows_padded + mrow) * p.n_words + w] = (int32_t)s_bits[t];
       }
       if (!p.tau_given && grp_on && half == 0 && row_ok) p.taus[(size_t)bh * p.N + row] = hs.t;
+    }
+    if (p.sup_on && !p.tau_given) {
+      // ---- the rows' supports, for the gather kernels ----
+      // Entry = (key, u = z - tau > 0) for every listed score above the final tau whose 64x64
+      // tile is in the block mask just built (what the tile kernels would visit); one run per
+      // row: the keys of the row's first thread (low halves of the key tiles), then the second's.
+      const bool can = !full_sweeps && !wide && !*cta_abort;  // the same for every thread of the CTA
+      int* cnts = reinterpret_cast<int*>(xchg) + grp * (2 * 8 * 128);
+      int* extra = reinterpret_cast<int*>(xchg) + 128;        // [0..7] entries of each 32-row quarter, [8] base (beside the counts)
+      const uint32_t* my_bits = s_bits + (grp * 2 + rb) * p.n_words;
+      auto in_support = [&](const Cand c) -> bool {
+        const int kb = c.key >> 6;
+        return c.z > hs.t && ((my_bits[kb >> 5] >> (kb & 31)) & 1u);
+      };
+      auto for_each = [&](auto&& f) {
+        if (!(grp_on && row_ok)) return;
+        if (compact) {
+          for (int k = 0; k < ncand; ++k) f(pool[run0 + k]);
+        } else {
+          for (int e = head, left = warp_pool; e != kCandNil && left > 0; --left) {
+            const Cand c = pool[e];
+            f(c);
+            e = c.next;
+          }
+        }
+      };
+      int n_mine = 0;
+      if (can) for_each([&](const Cand c) { n_mine += in_support(c) ? 1 : 0; });
+      cnts[half * (8 * 128) + r] = n_mine;
+      ptx::bar_sync(3, kSolveRowThreads);
+      const int n_other = cnts[(half ^ 1) * (8 * 128) + r];
+      const int tot = n_mine + n_other;   // both threads of a row hold the row's count
+      int incl = tot;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int up = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += up;
+      }
+      if (half == 0 && lane == 31) extra[grp * 4 + wq] = incl;
+      ptx::bar_sync(3, kSolveRowThreads);
+      int before = 0, total = 0;
+#pragma unroll
+      for (int w = 0; w < 8; ++w) {
+        const int t = extra[w];
+        before += (w < grp * 4 + wq) ? t : 0;
+        total += t;
+      }
+      if (threadIdx.x == 0) {
+        // one reservation per CTA; a CTA that cannot export hands its kv head to the tile kernels
+        uint32_t base = 0xffffffffu;
+        if (can) {
+          base = atomicAdd(p.sup.cursor, (uint32_t)total);
+          if (base > p.sup.cap || (uint32_t)total > p.sup.cap - base) base = 0xffffffffu;
+        }
+        if (base == 0xffffffffu) atomicAdd(p.sup.dense + b * p.Hkv + kvh, 1);
+        extra[8] = (int)base;
+      }
+      ptx::bar_sync(3, kSolveRowThreads);
+      const uint32_t base = (uint32_t)extra[8];
+      if (base != 0xffffffffu) {
+        const uint32_t row_first = base + (uint32_t)(before + incl - tot);
+        if (grp_on && row_ok && half == 0) p.sup.rows[(size_t)bh * p.N + row] = make_uint2(row_first, (uint32_t)tot);
+        uint2* dst = p.sup.entries + row_first + (half ? n_other : 0);
+        for_each([&](const Cand c) {
+          if (in_support(c)) *dst++ = make_uint2((uint32_t)c.key, __float_as_uint(c.z - hs.t));
+        });
+      }
     }
   }
 

@@ -1,0 +1,18 @@
+// Gather kernels over the row supports exported by the tensor-core solver (support.cuh,
+// sparse_rows.cu).
+#pragma once
+#include "attn_simt.cuh"
+
+namespace ads {
+namespace sparse {
+
+// Shapes for which the solver exports supports: what its candidate lists can express.
+bool supported(const ads_attn_shape* s);
+size_t support_bytes(const ads_attn_shape* s);
+// Cursor and per-head counters -> 0 (before the solver runs).
+int clear_header(const simt::Params& p, cudaStream_t st);
+// out / out2 of every head whose supports were exported; other heads are left alone.
+int fwd(const simt::Params& p, int dtype, cudaStream_t st);
+
+}  // namespace sparse
+}  // namespace ads

@@ -1,0 +1,65 @@
+// Row supports: the element-sparse side of the attention path.
+//
+// An entmax-1.5 row has few non-zero probabilities (a handful to a few dozen out of thousands of
+// keys), and the tensor-core solver ends its work holding every one of them in shared memory: its
+// candidate lists are the scores within 1 of the row maximum, a superset of the support.  When a
+// caller hands the solver a `support` buffer, each CTA writes, for its 256 query rows, the
+// (key, score - tau) pairs of the support -- restricted to the 64x64 tiles of the block mask, so
+// that the set is exactly what the tile kernels would visit -- as one contiguous run per row.
+// The forward and the backward of those rows are then gathers over a few K / V / Q / dO rows per
+// query instead of dense tiles (csrc/sparse_rows.cu).
+//
+// The choice between the two routes is made per (batch, kv head): a solver CTA that cannot
+// export (its candidate pool overflowed and it fell back to sweeping S, or the entry array is
+// full) bumps the head's `dense` counter; the tile kernels of a head return at once while the
+// counter is zero, the gather kernels while it is not.
+//
+// Layout of the buffer (all offsets multiples of 256 bytes):
+//   [0]      uint32 cursor: entries handed out so far (one atomicAdd per solver CTA)
+//   [256]    int32 dense[B*Hkv]
+//   rows     uint2 [B*Hq*N]: (index of the row's first entry, number of entries)
+//   entries  uint2 [cap]: (key index, fp32 bits of u = z - tau_final > 0)
+#pragma once
+#include <cstddef>
+#include <cstdint>
+
+#include <cuda_runtime.h>
+
+namespace ads {
+namespace sup {
+
+constexpr int kEntriesPerRow = 16;  // capacity of the entry array, per query row of the problem
+
+struct View {
+  uint32_t* cursor;
+  int32_t* dense;
+  uint2* rows;
+  uint2* entries;
+  uint32_t cap;
+};
+
+__host__ __device__ inline size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
+
+inline size_t bytes(int B, int Hq, int Hkv, int N) {
+  const size_t rows = (size_t)B * Hq * N;
+  return 256 + align256((size_t)B * Hkv * 4) + align256(rows * 8) + align256(rows * kEntriesPerRow * 8);
+}
+
+// Bytes at the start of the buffer that the solver's launcher clears (cursor and counters).
+inline size_t header_bytes(int B, int Hkv) { return 256 + align256((size_t)B * Hkv * 4); }
+
+inline View view(void* base, int B, int Hq, int Hkv, int N) {
+  View v;
+  uint8_t* p = (uint8_t*)base;
+  const size_t rows = (size_t)B * Hq * N;
+  v.cursor = (uint32_t*)p;
+  v.dense = (int32_t*)(p + 256);
+  v.rows = (uint2*)(p + 256 + align256((size_t)B * Hkv * 4));
+  v.entries = (uint2*)((uint8_t*)v.rows + align256(rows * 8));
+  const size_t cap = rows * kEntriesPerRow;
+  v.cap = cap > 0xffffffffull ? 0xffffffffu : (uint32_t)cap;
+  return v;
+}
+
+}  // namespace sup
+}  // namespace ads

@@ -85,6 +85,19 @@ int adasplash_entmax_bwd(const void* y, const void* dy, void* dx, int64_t rows, 
  * backward use the same buffer; 256-byte aligned base expected). */
 size_t adasplash2_workspace_bytes(const ads_attn_shape* shape);
 
+/* Row supports (optional; no counterpart in the reference, whose kernels are block-sparse only).
+ * An entmax row has few non-zero probabilities, and the tensor-core solver ends up holding all of
+ * them on chip.  Given a `support` buffer of this many bytes (256-byte aligned), adasplash2_solve
+ * also writes each query row's (key, score - tau) pairs -- exactly the entries the tile kernels
+ * would visit under the block mask -- and adasplash2_fwd / adasplash2_bwd, handed the same
+ * buffer, compute those rows as gathers over a few K / V / Q / dO rows instead of dense tiles.
+ * The route is chosen per (batch, kv head) on the device: heads whose rows are too dense for the
+ * solver's lists, or that find the buffer full, take the tile kernels as if no buffer had been
+ * given.  Returns 0 for shapes without this route (CUDA-core path, first-generation semantics,
+ * more than 65536 keys); NULL / 0 may always be passed instead of a buffer.  The buffer belongs
+ * to one solve: pass it to the forward and backward of the same problem, unchanged. */
+size_t adasplash2_support_bytes(const ads_attn_shape* shape);
+
 /* Number of int32 words of one bitmap tensor (B,Hq,rows_padded,n_words) and its
  * two inner extents, in the layout of adasplash/adasplash_v2.py:1345-1350:
  * rows_padded = max(32, ceil32(ceil(N/64))), n_words = ceil(ceil(N/64)/32);
@@ -99,7 +112,7 @@ int64_t adasplash2_bitmap_words(const ads_attn_shape* shape, int32_t* rows_padde
  * reference does (adasplash_v2.py:618-681). */
 int adasplash2_solve(const void* q, const void* k, const void* varlen, float* taus,
                      int32_t* bmask, const ads_attn_shape* shape, void* workspace,
-                     size_t workspace_bytes, void* stream);
+                     size_t workspace_bytes, void* support, size_t support_bytes, void* stream);
 
 /* Block-mask builder alone: bit(m,n) = any(z > taus) on each valid 64x64 tile,
  * for thresholds supplied by the caller.  No reference entry point does only
@@ -115,7 +128,7 @@ int adasplash2_mask_from_tau(const void* q, const void* k, const void* varlen,
 int adasplash2_fwd(const void* q, const void* k, const void* v, const void* varlen,
                    const float* taus, const int32_t* bmask, void* out, void* out2,
                    const ads_attn_shape* shape, void* workspace, size_t workspace_bytes,
-                   void* stream);
+                   void* support, size_t support_bytes, void* stream);
 
 /* Backward.  Replaces `_bwd_preprocess`, `_bwd_q_kernel`, `transpose_bmask` and
  * `_bwd_kv_kernel` (adasplash/adasplash_v2.py:1441-1564).  `delta` (B,Hq,N fp32)
@@ -126,7 +139,7 @@ int adasplash2_bwd(const void* q, const void* k, const void* v, const void* dout
                    const void* out2, const void* varlen, const float* taus,
                    const int32_t* bmask, int32_t* bmask_t, float* delta, void* dq, void* dk,
                    void* dv, const ads_attn_shape* shape, void* workspace,
-                   size_t workspace_bytes, void* stream);
+                   size_t workspace_bytes, void* support, size_t support_bytes, void* stream);
 
 /* Backward for callers that cannot allocate.  It has no counterpart in the
  * reference (whose host code allocates freely through torch).  It exists for

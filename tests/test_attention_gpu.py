@@ -328,8 +328,8 @@ def test_c_abi_error_codes_on_device():
     q = torch.zeros(1, 2, 64, 64, device="cuda", dtype=torch.bfloat16)
     sh = _lib.AttnShape(B=1, Hq=2, Hkv=2, N=64, D=64, dtype=_lib.BF16, niter=1, varlen_is_i64=0,
                         path=_lib.PATH_SIMT)
-    rc = lib.adasplash2_solve(q.data_ptr(), None, None, None, None, ctypes.byref(sh), None, 0, None)
+    rc = lib.adasplash2_solve(q.data_ptr(), None, None, None, None, ctypes.byref(sh), None, 0, None, 0, None)
     assert rc == 1 and b"null pointer" in lib.adasplash_last_error_string()
     sh.path = 9
-    rc = lib.adasplash2_fwd(*([q.data_ptr()] * 8), ctypes.byref(sh), None, 0, None)
+    rc = lib.adasplash2_fwd(*([q.data_ptr()] * 8), ctypes.byref(sh), None, 0, None, 0, None)
     assert rc == 1 and b"unknown path" in lib.adasplash_last_error_string()

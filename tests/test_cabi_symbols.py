@@ -49,7 +49,7 @@ def test_backward_rejects_misaligned_rows_without_gpu():
     sh = _lib.AttnShape(B=1, Hq=2, Hkv=2, N=64, D=64, dtype=2, niter=1, varlen_is_i64=0, path=0)
     a = 0x1000  # stands for a device address; never dereferenced by the argument checks
     args = [a, a, a, a + 8, a, None, a, a, a, a, a, a, a]   # dout = a + 8
-    rc = lib.adasplash2_bwd(*args, ctypes.byref(sh), a, 256, None)
+    rc = lib.adasplash2_bwd(*args, ctypes.byref(sh), a, 256, None, 0, None)
     assert rc == 1
     assert b"16-byte aligned" in lib.adasplash_last_error_string()
     assert lib.adasplash_launch_count() == before

@@ -48,15 +48,15 @@ def test_wait_gives_up_and_the_gpu_stays_usable(short_waits, kernel):
         assert lib.adasplash2_debug_waits(1 << 16, 1) == 0
         if kernel == "solve":
             t2, m2 = torch.empty_like(taus), torch.empty_like(bmask)
-            rc = lib.adasplash2_solve(P(q), P(k), None, P(t2), P(m2), sp, P(ws), 256, st)
+            rc = lib.adasplash2_solve(P(q), P(k), None, P(t2), P(m2), sp, P(ws), 256, None, 0, st)
         elif kernel == "fwd":
             o, o2 = torch.empty_like(q), torch.empty_like(q)
-            rc = lib.adasplash2_fwd(P(q), P(k), P(v), None, P(taus), P(bmask), P(o), P(o2), sp, P(ws), 256, st)
+            rc = lib.adasplash2_fwd(P(q), P(k), P(v), None, P(taus), P(bmask), P(o), P(o2), sp, P(ws), 256, None, 0, st)
         else:
             dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
             delta, bmt = torch.empty_like(taus), torch.empty_like(bmask)
             rc = lib.adasplash2_bwd(P(q), P(k), P(v), P(do), P(out2), None, P(taus), P(bmask), P(bmt), P(delta),
-                                    P(dq), P(dk), P(dv), sp, P(ws), 256, st)
+                                    P(dq), P(dk), P(dv), sp, P(ws), 256, None, 0, st)
         assert rc == 0, lib.adasplash_last_error_string()   # the launch itself succeeds
         rc = lib.adasplash2_check_status(P(ws), st)
         msg = lib.adasplash_last_error_string().decode()
