@@ -273,11 +273,16 @@ extern "C" int adasplash2_bwd(const void* q, const void* k, const void* v, const
   p.q = q; p.k = k; p.v = v; p.varlen = varlen; p.dout = dout; p.out2_in = out2;
   p.taus = const_cast<float*>(taus); p.bmask = const_cast<int32_t*>(bmask);
   p.bmask_t = bmask_t; p.delta = delta; p.dq = dq; p.dk = dk; p.dv = dv;
+  if (int rc = resolve_support(s, path, support, support_bytes, who, &p.support)) return rc;
+  if (s->bwd_stages != 0) p.support = nullptr;  // single kernels of the tile route (timing aid)
   if (int rc = clear_status(ws, ws_bytes, st, who)) return rc;
   if (path == ADS_PATH_TCGEN05) {
     if (ws == nullptr || ws_bytes < sm100::min_workspace_bytes()) {
       set_error("%s: workspace too small (%zu < %zu)", who, ws_bytes, sm100::min_workspace_bytes());
       return ADS_ERR_WORKSPACE;
+    }
+    if (p.support != nullptr) {
+      if (int rc = sparse::bwd(p, s->dtype, st)) return rc;
     }
     return is_v2(s) ? sm100::bwd(p, s->dtype, ws, st) : sm100::v1::bwd(p, s->dtype, ws, st);
   }

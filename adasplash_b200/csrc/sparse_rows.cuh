@@ -13,6 +13,8 @@ size_t support_bytes(const ads_attn_shape* s);
 int clear_header(const simt::Params& p, cudaStream_t st);
 // out / out2 of every head whose supports were exported; other heads are left alone.
 int fwd(const simt::Params& p, int dtype, cudaStream_t st);
+// dq, dk, dv of the same heads (dk / dv of a kv head: all its query heads).
+int bwd(const simt::Params& p, int dtype, cudaStream_t st);
 
 }  // namespace sparse
 }  // namespace ads

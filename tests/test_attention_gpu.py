@@ -18,7 +18,9 @@ from oracle import entmax_oracle as O
 
 pytestmark = pytest.mark.gpu
 GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
-PATHS = ["simt", "tcgen05"]
+# "tcgen05": the tensor-core solver with row supports (sparse heads run as gathers, the others on
+# the tile kernels); "tiles": the tile kernels for every head; "simt": the CUDA-core kernels
+PATHS = ["simt", "tcgen05", "tiles"]
 
 
 def _randn(shape, seed, scale=1.0, dtype=torch.float32):
@@ -31,11 +33,15 @@ def _reset_path():
     att.DEBUG_STATUS = True   # every call also checks the kernels' bounded-wait status word
     yield
     att.DEBUG_STATUS = False
+    att.ROW_SUPPORTS = True
     _lib.set_kernel_path(None)
 
 
 def _use(path, q):
     """Select a kernel family; skip if it does not cover this dtype / head dim."""
+    att.ROW_SUPPORTS = path != "tiles"
+    if path == "tiles":
+        path = "tcgen05"
     _lib.set_kernel_path(path)
     if path == "tcgen05":
         import ctypes
@@ -293,6 +299,55 @@ def test_tensor_core_path_matches_cuda_core_path(path, shape):
     for key in ("out", "out2", "dq", "dk", "dv"):
         scale = max(1.0, b[key].abs().max().item())
         assert (a[key] - b[key]).abs().max() < 2e-2 * scale, key
+
+
+@pytest.mark.parametrize("case", [
+    # B, Hq, Hkv, N, D, varlen, scales of (q, k), dtype, kv heads expected on the gather kernels
+    (1, 2, 2, 256, 64, None, (1.0, 1.0), torch.bfloat16, 2),
+    (2, 4, 2, 1024, 128, [1024, 700], (1.5, 1.5), torch.bfloat16, 4),
+    (1, 4, 1, 2048, 64, None, (1.5, 1.5), torch.float16, 1),
+    (1, 2, 1, 1000, 128, [1000], (1.5, 1.5), torch.bfloat16, 1),      # N not a multiple of 32
+    (1, 2, 2, 2048, 128, None, (0.05, 1.0), torch.bfloat16, 0),       # flat rows: the pool overflows
+    (1, 2, 2, 512, 32, None, (1.5, 1.5), torch.bfloat16, 0),          # head dim without a gather route
+])
+def test_row_supports_match_tile_kernels(case):
+    # Heads whose supports the solver could export run as gathers over K / V / Q / dO rows; the
+    # result must be what the tile kernels give for the same thresholds (same rounding points,
+    # another summation order), head by head, and two runs must agree bit for bit.
+    B, Hq, Hkv, N, D, vl, (sq, sk), dtype, n_sparse = case
+    q, k, v, do = (_randn(s, 80 + i, sc, dtype).cuda() for i, (s, sc) in
+                   enumerate([((B, Hq, N, D), sq), ((B, Hkv, N, D), sk), ((B, Hkv, N, D), 1.5), ((B, Hq, N, D), 1.0)]))
+    varlen = None if vl is None else torch.tensor(vl, dtype=torch.int32).cuda()
+    _lib.set_kernel_path("tcgen05")
+    shape = att.make_shape(q, k, 1, varlen)
+    sup = att.support_buffer(shape, q.device)
+    if n_sparse == 0 and D < 64:
+        assert sup is None
+        return
+    sup.fill_(0x5A)   # whatever an allocator may hand out
+    taus, bm = att.solve(q, k, 1, varlen, support=sup)
+    taus0, bm0 = att.solve(q, k, 1, varlen)
+    L = [N] * B if vl is None else vl
+    for b in range(B):
+        assert torch.equal(taus[b, :, :L[b]], taus0[b, :, :L[b]])
+    assert torch.equal(bm, bm0)
+    dense = sup[256:256 + 4 * B * Hkv].view(torch.int32)
+    assert int((dense == 0).sum()) == n_sparse
+    out, out2 = att.forward_raw(q, k, v, taus, bm, varlen, support=sup)
+    ref, ref2 = att.forward_raw(q, k, v, taus, bm, varlen)
+    a = att.backward_raw(q, k, v, do, out2, taus, bm, varlen, 1, support=sup)
+    a2 = att.backward_raw(q, k, v, do, out2, taus, bm, varlen, 1, support=sup)
+    r = att.backward_raw(q, k, v, do, ref2, taus, bm, varlen, 1)
+    for name, x, y in (("out", out, ref), ("out2", out2, ref2), ("dq", a[0], r[0]), ("dk", a[1], r[1]), ("dv", a[2], r[2])):
+        scale = max(1.0, y.float().abs().max().item())
+        assert (x.float() - y.float()).abs().max().item() < 1e-2 * scale, name
+    for x, y in zip(a[:3], a2[:3]):
+        assert torch.equal(x, y)
+    if vl is not None:
+        for b in range(B):
+            if vl[b] < N:
+                assert out[b, :, vl[b]:].abs().max() == 0 and a[0][b, :, vl[b]:].abs().max() == 0
+                assert a[1][b, :, vl[b]:].abs().max() == 0 and a[2][b, :, vl[b]:].abs().max() == 0
 
 
 @pytest.mark.parametrize("scale, niter", [(0.05, 1), (0.05, 3), (0.4, 0), (1.5, 10), (1.5, 0)])
