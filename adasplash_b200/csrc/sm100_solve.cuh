@@ -675,19 +675,18 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
       }
       if (half == 0 && lane == 31) extra[grp * 4 + wq] = incl;
       ptx::bar_sync(3, kSolveRowThreads);
-      int before = 0, total = 0, biggest = 0;
+      int before = 0, total = 0;
 #pragma unroll
       for (int w = 0; w < 8; ++w) {
         const int t = extra[w];
         before += (w < grp * 4 + wq) ? t : 0;
         total += t;
-        biggest = max(biggest, t);
       }
       if (threadIdx.x == 0) {
         // one reservation per CTA; a CTA that cannot export (or whose rows are too dense for the
-        // backward's 32-row chunks) hands its kv head to the tile kernels
+        // backward's sort) hands its kv head to the tile kernels
         uint32_t base = 0xffffffffu;
-        if (can && biggest <= sup::kChunkCap) {
+        if (can && total <= sup::kBlockCap) {
           base = atomicAdd(p.sup.cursor, (uint32_t)total);
           if (base > p.sup.cap || (uint32_t)total > p.sup.cap - base) base = 0xffffffffu;
         }

@@ -25,21 +25,34 @@ struct RowsParams {
   sup::View sv;
 };
 
-// eight 16-bit elements <-> fp32
-template <typename T>
-__device__ __forceinline__ void unpack8(const uint4& raw, float (&f)[8]) {
-  const T* e = reinterpret_cast<const T*>(&raw);
-#pragma unroll
-  for (int i = 0; i < 8; ++i) f[i] = DT<T>::to_f(e[i]);
+// Two 16-bit elements <-> two fp32 values.  The accumulations below run on pairs: Blackwell's
+// packed fp32 multiply-add (`__ffma2_rn`) does two lanes of fp32 per instruction, which halves
+// the instruction count of these issue-bound kernels.
+template <typename T> __device__ __forceinline__ float2 unpack2(uint32_t x);
+template <> __device__ __forceinline__ float2 unpack2<__nv_bfloat16>(uint32_t x) {
+  return make_float2(__uint_as_float(x << 16), __uint_as_float(x & 0xffff0000u));
+}
+template <> __device__ __forceinline__ float2 unpack2<__half>(uint32_t x) {
+  return __half22float2(*reinterpret_cast<const __half2*>(&x));
+}
+template <typename T> __device__ __forceinline__ uint32_t pack2f(float2 v);
+template <> __device__ __forceinline__ uint32_t pack2f<__nv_bfloat16>(float2 v) {
+  const __nv_bfloat162 r = __float22bfloat162_rn(v);
+  return *reinterpret_cast<const uint32_t*>(&r);
+}
+template <> __device__ __forceinline__ uint32_t pack2f<__half>(float2 v) {
+  const __half2 r = __float22half2_rn(v);
+  return *reinterpret_cast<const uint32_t*>(&r);
 }
 template <typename T>
-__device__ __forceinline__ uint4 pack8(const float* f) {
-  uint4 raw;
-  T* e = reinterpret_cast<T*>(&raw);
-#pragma unroll
-  for (int i = 0; i < 8; ++i) e[i] = DT<T>::from_f(f[i]);
-  return raw;
+__device__ __forceinline__ void unpack8(const uint4& raw, float2 (&f)[4]) {
+  f[0] = unpack2<T>(raw.x); f[1] = unpack2<T>(raw.y); f[2] = unpack2<T>(raw.z); f[3] = unpack2<T>(raw.w);
 }
+template <typename T>
+__device__ __forceinline__ uint4 pack8(const float2* f) {
+  return make_uint4(pack2f<T>(f[0]), pack2f<T>(f[1]), pack2f<T>(f[2]), pack2f<T>(f[3]));
+}
+__device__ __forceinline__ float2 splat(float x) { return make_float2(x, x); }
 
 // One warp per 32 consecutive query rows of a head, eight lanes per row: lane gl of a group owns
 // the 16-byte chunks gl and (CH = 2, head dim 128) 8 + gl of the head dimension, so a V row is
@@ -70,9 +83,9 @@ __global__ void __launch_bounds__(kRowThreads) fwd_rows_kernel(RowsParams p) {
     const int rr = grp * 8 + i;  // this group's row inside the chunk
     const uint32_t first = __shfl_sync(0xffffffffu, rw.x, rr), cnt = __shfl_sync(0xffffffffu, rw.y, rr);
     const uint32_t cnt_max = __reduce_max_sync(0xffffffffu, cnt);
-    float ao[CH * 8], ao2[CH * 8];
+    float2 ao[CH * 4], ao2[CH * 4];
 #pragma unroll
-    for (int e = 0; e < CH * 8; ++e) { ao[e] = 0.f; ao2[e] = 0.f; }
+    for (int e = 0; e < CH * 4; ++e) { ao[e] = splat(0.f); ao2[e] = splat(0.f); }
     float supp = 0.f;
     for (uint32_t k0 = 0; k0 < cnt_max; k0 += 8) {
       const uint2 ent = (k0 + gl < cnt) ? p.sv.entries[first + k0 + gl] : make_uint2(0u, 0u);
@@ -93,31 +106,31 @@ __global__ void __launch_bounds__(kRowThreads) fwd_rows_kernel(RowsParams p) {
         }
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          const float pw = round_to<T>(u[j] * u[j]), uw = round_to<T>(u[j]);
+          const float2 pw = splat(round_to<T>(u[j] * u[j])), uw = splat(round_to<T>(u[j]));
           supp += u[j];
 #pragma unroll
           for (int c = 0; c < CH; ++c) {
-            float vf[8];
+            float2 vf[4];
             unpack8<T>(raw[j][c], vf);
 #pragma unroll
-            for (int e = 0; e < 8; ++e) {
-              ao[c * 8 + e] = fmaf(pw, vf[e], ao[c * 8 + e]);
-              ao2[c * 8 + e] = fmaf(uw, vf[e], ao2[c * 8 + e]);
+            for (int e = 0; e < 4; ++e) {
+              ao[c * 4 + e] = __ffma2_rn(pw, vf[e], ao[c * 4 + e]);
+              ao2[c * 4 + e] = __ffma2_rn(uw, vf[e], ao2[c * 4 + e]);
             }
           }
         }
       }
     }
-    const float inv = supp > 0.f ? 1.0f / supp : 0.f;
+    const float2 inv = splat(supp > 0.f ? 1.0f / supp : 0.f);
 #pragma unroll
-    for (int e = 0; e < CH * 8; ++e) ao2[e] *= inv;
+    for (int e = 0; e < CH * 4; ++e) ao2[e] = __fmul2_rn(ao2[e], inv);
     if (lane_on && r0 + rr < p.N) {
       T* o = (T*)p.out + (row_base + r0 + rr) * p.Dg + gl * 8;
       T* o2 = (T*)p.out2 + (row_base + r0 + rr) * p.Dg + gl * 8;
 #pragma unroll
       for (int c = 0; c < CH; ++c) {
-        *reinterpret_cast<uint4*>(o + c * 64) = pack8<T>(ao + c * 8);
-        *reinterpret_cast<uint4*>(o2 + c * 64) = pack8<T>(ao2 + c * 8);
+        *reinterpret_cast<uint4*>(o + c * 64) = pack8<T>(ao + c * 4);
+        *reinterpret_cast<uint4*>(o2 + c * 64) = pack8<T>(ao2 + c * 4);
       }
     }
   }
@@ -158,41 +171,37 @@ __device__ __forceinline__ float group_sum8(float x) {  // over the eight lanes 
   return x;
 }
 
-template <typename T>
-__device__ __forceinline__ uint32_t bits16(float x) {
-  const T t = DT<T>::from_f(x);
-  return (uint32_t)*reinterpret_cast<const uint16_t*>(&t);
-}
-
 // The arithmetic of the tile kernels (adasplash_v2.py:943-1234), pair by pair:
 //   dP = dO_i . V_j;  delta_i = out2_i . dO_i;
 //   query side:  dS = rn(u (dP - delta)) with the solver's u;  dQ_i = sm_scale * sum_j dS K_j;
 //   key side, which the reference computes from K~ = rn(k * 0.5/sqrt(D)) and the raw q:
 //     u' = K~_j . q_i - tau_i;  P^T = rn(u'^2), dS^T = rn(u' (dP - delta)) where u' > 0.
-// Same warp layout as the forward gather: 32 rows per warp, eight lanes per row.  The key-side
-// values go to shared memory at the entry's slot, are sorted there by (key, row) once the 32
-// rows are done, and leave as the chunk's run of `by_key`.
+// Same warp layout as the forward gather: 32 rows per warp, eight lanes per row; the eight warps
+// of a CTA take the 256 rows of one solver CTA, whose entries form one contiguous run.  The
+// key-side values go to shared memory at the entry's slot, are sorted there by (key, row) once
+// the 256 rows are done, and leave as the block's run of `by_key`.
 template <typename T, int CH>
 __global__ void __launch_bounds__(kRowThreads) bwd_rows_kernel(BwdParams p) {
-  extern __shared__ uint2 sort_buf[];  // [warps][kChunkCap]
+  extern __shared__ uint2 sort_buf[];  // [kBlockCap]
+  __shared__ uint32_t s_tot[kRowThreads / 32];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int grp = lane >> 3, gl = lane & 7;
-  const int chunks = (p.N + kRowsPerWarp - 1) / kRowsPerWarp;  // per head
-  const long long wg = (long long)blockIdx.x * (kRowThreads / 32) + warp;
-  if (wg >= (long long)p.B * p.Hq * chunks) return;
-  const int bh = (int)(wg / chunks), chunk = (int)(wg % chunks), r0 = chunk * kRowsPerWarp;
+  const int blocks = (p.N + sup::kBlockRows - 1) / sup::kBlockRows;  // per head
+  const int bh = (int)(blockIdx.x / blocks), blk = (int)(blockIdx.x % blocks);
+  const int r0 = blk * sup::kBlockRows + warp * kRowsPerWarp;  // this warp's first row
   const int b = bh / p.Hq, h = bh % p.Hq;
   const int kvh = h / (p.Hq / p.Hkv);
-  if (p.sv.dense[b * p.Hkv + kvh] != 0) return;  // the tile kernels own this head
+  if (p.sv.dense[b * p.Hkv + kvh] != 0) return;  // the tile kernels own this head (the whole CTA leaves)
   const int len = load_len(p.varlen, p.varlen_is_i64, b, p.N);
   const size_t row_base = (size_t)bh * p.N;
   const uint2 rw = (r0 + lane < len) ? p.sv.rows[row_base + r0 + lane] : make_uint2(0u, 0u);
-  const uint32_t run0 = __shfl_sync(0xffffffffu, rw.x, 0);
-  uint32_t total = rw.y;
+  // the block's run starts at its first row's first entry
+  const uint32_t run0 = (blk * sup::kBlockRows < len) ? p.sv.rows[row_base + blk * sup::kBlockRows].x : 0u;
+  uint32_t wtot = rw.y;
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
-  total = min(total, (uint32_t)sup::kChunkCap);  // the solver exports no denser chunk
-  uint2* sb = sort_buf + warp * sup::kChunkCap;
+  for (int o = 16; o > 0; o >>= 1) wtot += __shfl_xor_sync(0xffffffffu, wtot, o);
+  if (lane == 0) s_tot[warp] = wtot;
+  uint2* sb = sort_buf;
   const size_t kv_base = (size_t)(b * p.Hkv + kvh) * p.N * p.Dg + gl * 8;
   const T* kb_ = (const T*)p.k + kv_base;
   const T* vb = (const T*)p.v + kv_base;
@@ -202,8 +211,8 @@ __global__ void __launch_bounds__(kRowThreads) bwd_rows_kernel(BwdParams p) {
     const uint32_t first = __shfl_sync(0xffffffffu, rw.x, rr), cnt = __shfl_sync(0xffffffffu, rw.y, rr);
     const uint32_t cnt_max = __reduce_max_sync(0xffffffffu, cnt);
     const bool row_ok = row < len;
-    float qf[CH * 8], gf[CH * 8], dq[CH * 8];
-    float delta = 0.f;
+    float2 qf[CH * 4], gf[CH * 4], dq[CH * 4];
+    float2 dl2 = splat(0.f);
 #pragma unroll
     for (int c = 0; c < CH; ++c) {
       uint4 rq = make_uint4(0u, 0u, 0u, 0u), rg = rq, ro = rq;
@@ -213,16 +222,19 @@ __global__ void __launch_bounds__(kRowThreads) bwd_rows_kernel(BwdParams p) {
         rg = *reinterpret_cast<const uint4*>((const T*)p.dout + off);
         ro = *reinterpret_cast<const uint4*>((const T*)p.out2 + off);
       }
-      float q8[8], g8[8], o8[8];
-      unpack8<T>(rq, q8); unpack8<T>(rg, g8); unpack8<T>(ro, o8);
+      float2 o8[4];
+      unpack8<T>(rq, *reinterpret_cast<float2(*)[4]>(qf + c * 4));
+      unpack8<T>(rg, *reinterpret_cast<float2(*)[4]>(gf + c * 4));
+      unpack8<T>(ro, o8);
 #pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        qf[c * 8 + e] = q8[e]; gf[c * 8 + e] = g8[e]; dq[c * 8 + e] = 0.f;
-        delta = fmaf(o8[e], g8[e], delta);
+      for (int e = 0; e < 4; ++e) {
+        dq[c * 4 + e] = splat(0.f);
+        dl2 = __ffma2_rn(o8[e], gf[c * 4 + e], dl2);
       }
     }
-    delta = group_sum8(delta);
+    const float delta = group_sum8(dl2.x + dl2.y);
     const float tau = row_ok ? p.taus[row_base + row] : 0.f;
+    const float2 zs2 = splat(p.zscale);
     for (uint32_t k0 = 0; k0 < cnt_max; k0 += 8) {
       const uint2 ent = (k0 + gl < cnt) ? p.sv.entries[first + k0 + gl] : make_uint2(0u, 0u);
 #pragma unroll
@@ -247,108 +259,129 @@ __global__ void __launch_bounds__(kRowThreads) bwd_rows_kernel(BwdParams p) {
         }
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
-          float kf[CH * 8];
-          float dp = 0.f, zk = 0.f;
+          float2 kf[CH * 4];
+          float2 dp2 = splat(0.f), zk2 = splat(0.f);
 #pragma unroll
           for (int c = 0; c < CH; ++c) {
-            float v8[8], k8[8];
+            float2 v8[4];
             unpack8<T>(rv[j][c], v8);
-            unpack8<T>(rk[j][c], k8);
+            unpack8<T>(rk[j][c], *reinterpret_cast<float2(*)[4]>(kf + c * 4));
 #pragma unroll
-            for (int e = 0; e < 8; ++e) {
-              kf[c * 8 + e] = k8[e];
-              dp = fmaf(gf[c * 8 + e], v8[e], dp);
-              zk = fmaf(qf[c * 8 + e], round_to<T>(k8[e] * p.zscale), zk);
+            for (int e = 0; e < 4; ++e) {
+              dp2 = __ffma2_rn(gf[c * 4 + e], v8[e], dp2);
+              // K~ = rn(k * fp32(0.5/sqrt(D))), two elements per conversion
+              const float2 kt = unpack2<T>(pack2f<T>(__fmul2_rn(kf[c * 4 + e], zs2)));
+              zk2 = __ffma2_rn(qf[c * 4 + e], kt, zk2);
             }
           }
-          dp = group_sum8(dp);
-          zk = group_sum8(zk);
+          const float dp = group_sum8(dp2.x + dp2.y);
+          const float zk = group_sum8(zk2.x + zk2.y);
           const float dd = dp - delta;
-          const float dsq = round_to<T>(u[j] * dd);
+          const float2 dsq = splat(round_to<T>(u[j] * dd));
 #pragma unroll
-          for (int e = 0; e < CH * 8; ++e) dq[e] = fmaf(dsq, kf[e], dq[e]);
+          for (int e = 0; e < CH * 4; ++e) dq[e] = __ffma2_rn(dsq, kf[e], dq[e]);
           const float uk = zk - tau;
           if (gl == 0 && k0 + hb + j < cnt) {
             const uint32_t slot = first - run0 + k0 + hb + j;
-            const uint32_t vals = uk > 0.f ? (bits16<T>(uk * uk) | (bits16<T>(uk * dd) << 16)) : 0u;
-            if (slot < (uint32_t)sup::kChunkCap) sb[slot] = make_uint2((key[j] << 8) | (uint32_t)rr, vals);
+            const uint32_t vals = uk > 0.f ? pack2f<T>(make_float2(uk * uk, uk * dd)) : 0u;
+            if (slot < (uint32_t)sup::kBlockCap) sb[slot] = make_uint2((key[j] << 8) | (uint32_t)(warp * kRowsPerWarp + rr), vals);
           }
         }
       }
     }
     if (row < p.N) {
       T* o = (T*)p.dq + (row_base + row) * p.Dg + gl * 8;
+      const float2 sc2 = splat(p.sm_scale);
 #pragma unroll
       for (int c = 0; c < CH; ++c) {
-        float s8[8];
+        float2 s8[4];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) s8[e] = dq[c * 8 + e] * p.sm_scale;
+        for (int e = 0; e < 4; ++e) s8[e] = __fmul2_rn(dq[c * 4 + e], sc2);
         *reinterpret_cast<uint4*>(o + c * 64) = pack8<T>(s8);
       }
     }
   }
-  // sort the chunk's entries by (key, row): bitonic network over the next power of two
-  uint32_t n2 = 32;
+  // sort the block's entries by (key, row): bitonic network over the next power of two
+  __syncthreads();
+  uint32_t total = 0;
+#pragma unroll
+  for (int w = 0; w < kRowThreads / 32; ++w) total += s_tot[w];
+  total = min(total, (uint32_t)sup::kBlockCap);  // the solver exports no denser block
+  uint32_t n2 = 64;
   while (n2 < total) n2 <<= 1;
-  for (uint32_t t = total + lane; t < n2; t += 32) sb[t] = make_uint2(0xffffffffu, 0u);
-  __syncwarp();
+  for (uint32_t t = total + threadIdx.x; t < n2; t += kRowThreads) sb[t] = make_uint2(0xffffffffu, 0u);
+  __syncthreads();
   for (uint32_t k = 2; k <= n2; k <<= 1) {
     for (uint32_t j = k >> 1; j > 0; j >>= 1) {
-      for (uint32_t t = lane; t < n2; t += 32) {
-        const uint32_t x = t ^ j;
-        if (x > t) {
-          const uint2 a = sb[t], c = sb[x];
-          const bool up = (t & k) == 0;
-          if (up ? a.x > c.x : a.x < c.x) { sb[t] = c; sb[x] = a; }
-        }
+      for (uint32_t pi = threadIdx.x; pi < n2 / 2; pi += kRowThreads) {  // the pi-th pair (t, t | j) of this stage
+        const uint32_t t = ((pi & ~(j - 1)) << 1) | (pi & (j - 1)), x = t | j;
+        const uint2 a = sb[t], c = sb[x];
+        const bool up = (t & k) == 0;
+        if (up ? a.x > c.x : a.x < c.x) { sb[t] = c; sb[x] = a; }
       }
-      __syncwarp();
+      // With distances up to 32 a warp's pairs lie in 64-element windows that no other warp
+      // touches, so stages at those distances only need the warp in step.
+      const uint32_t jn = j > 1 ? (j >> 1) : k;  // the distance of the stage that follows
+      if (j > 32 || jn > 32) __syncthreads(); else __syncwarp();
     }
   }
-  for (uint32_t t = lane; t < total; t += 32) p.sv.by_key[run0 + t] = sb[t];
-  if (lane == 0) p.sv.chunks[(size_t)bh * chunks + chunk] = make_uint2(run0, total);
+  __syncthreads();
+  for (uint32_t t = threadIdx.x; t < total; t += kRowThreads) p.sv.by_key[run0 + t] = sb[t];
+  if (threadIdx.x == 0) p.sv.blocks[(size_t)bh * blocks + blk] = make_uint2(run0, total);
+  // where each 64-key block starts in the sorted run: the key kernel reads its bounds from this
+  // table instead of searching the run in global memory
+  const int nkb1 = (p.N + 63) / 64 + 1;
+  uint16_t* tab = p.sv.kb_off + ((size_t)bh * blocks + blk) * nkb1;
+  for (int kbi = threadIdx.x; kbi < nkb1; kbi += kRowThreads) {
+    const uint32_t key = (uint32_t)(kbi * 64) << 8;
+    uint32_t a = 0, z = total;
+    while (a < z) { const uint32_t m = (a + z) >> 1; if (sb[m].x < key) a = m + 1; else z = m; }
+    tab[kbi] = (uint16_t)a;
+  }
 }
 
 // ---------------------------------------------------------------------------
 // Backward, by keys: dK, dV of 64 keys per CTA.
 // ---------------------------------------------------------------------------
-// Warp w owns keys 8w .. 8w+7 of the block; a lane holds D/32 elements of dK and of dV of each of
-// the eight keys in registers.  For each query head of the group and each 32-row chunk from the
-// diagonal on, a thread finds the chunk's entries of these 64 keys by binary search in the
-// chunk's sorted run and copies them to shared memory at the offset a block-wide scan gives it --
-// the order (head, chunk, key, row) is fixed; every warp then walks the staged entries, picks
-// those of its keys and adds P^T dO_i and dS^T Q_i, the Q / dO rows of four entries in flight.
-// No atomics: every sum has a fixed order.
-constexpr int kKeyThreads = 256;
+// Sixteen warps; warp w owns keys 4w .. 4w+3 of the block, eight lanes per key, each lane D/8
+// elements of that key's dK and dV in registers.  For each query head of the group and each
+// 256-row block from the diagonal on, a thread reads where the block's entries of these 64 keys
+// lie in the block's sorted run (the row kernel left a table); the warps copy those segments to
+// shared memory at the offsets a
+// block-wide scan gives them -- the order (head, row block, key, row) is fixed -- and the staged
+// entries are regrouped by key with a stable counting sort.  The eight lanes of a key then run
+// through the key's range four entries at a time (the Q / dO rows of all four requested before
+// the first is used) and add P^T dO_i and dS^T Q_i.  No atomics: every sum has a fixed order.
+constexpr int kKeyThreads = 512;
+constexpr int kKeyWarps = kKeyThreads / 32;
 constexpr int kKeysPerCta = 64;
 constexpr int kStage = 2048;  // entries staged per round
 
-template <typename T, int EL> struct LaneVec;
-template <typename T> struct LaneVec<T, 4> { using type = uint2; };
-template <typename T> struct LaneVec<T, 2> { using type = uint32_t; };
-
 template <typename T, int D>
-__global__ void __launch_bounds__(kKeyThreads) bwd_keys_kernel(BwdParams p) {
-  constexpr int EL = D / 32;  // elements per lane
-  using LV = typename LaneVec<T, EL>::type;
+__global__ void __launch_bounds__(kKeyThreads, 1) bwd_keys_kernel(BwdParams p) {
+  constexpr int CH = D / 64;  // 16-byte loads per lane and row
   __shared__ uint2 s_ent[kStage];       // ((absolute row << 6) | key inside the block, P^T | dS^T << 16)
-  __shared__ uint32_t s_wsum[kKeyThreads / 32];
+  __shared__ uint2 s_srt[kStage];       // the same, regrouped by key
+  __shared__ uint32_t s_wsum[kKeyWarps];
+  __shared__ uint32_t s_src[kKeyThreads], s_cnt[kKeyThreads], s_off[kKeyThreads];  // one segment per row block
+  __shared__ uint32_t s_kcnt[kKeysPerCta], s_kpos[kKeysPerCta + 1];
+  __shared__ uint16_t s_ccnt[(kStage / 32) * kKeysPerCta];  // [chunk of 32 staged entries][key]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int grp = lane >> 3, gl = lane & 7;
   const int nkb = (p.N + kKeysPerCta - 1) / kKeysPerCta;
   const int bkv = blockIdx.x / nkb, kb = blockIdx.x % nkb;
   if (p.sv.dense[bkv] != 0) return;  // the tile kernels own this head
   const int b = bkv / p.Hkv, kvh = bkv % p.Hkv;
   const int G = p.Hq / p.Hkv;
   const int len = load_len(p.varlen, p.varlen_is_i64, b, p.N);
-  const int chunks = (p.N + sup::kChunkRows - 1) / sup::kChunkRows;
-  const int chunks_used = (len + sup::kChunkRows - 1) / sup::kChunkRows;  // chunks with a valid row
-  float ak[8][EL], av[8][EL];
+  const int blocks = (p.N + sup::kBlockRows - 1) / sup::kBlockRows;
+  const int blocks_used = (len + sup::kBlockRows - 1) / sup::kBlockRows;  // row blocks with a valid row
+  const int nkb1 = nkb + 1;
+  float2 ak[CH * 4], av[CH * 4];
 #pragma unroll
-  for (int kk = 0; kk < 8; ++kk)
-#pragma unroll
-    for (int e = 0; e < EL; ++e) { ak[kk][e] = 0.f; av[kk][e] = 0.f; }
+  for (int e = 0; e < CH * 4; ++e) { ak[e] = splat(0.f); av[e] = splat(0.f); }
+  const uint32_t my_local = (uint32_t)(warp * 4 + grp);  // this lane's key inside the block
   const uint32_t key0 = (uint32_t)(kb * kKeysPerCta);
-  const uint32_t key_lo = key0 << 8, key_hi = (key0 + kKeysPerCta) << 8;
   auto to_f = [](uint32_t bits16v) -> float {
     if (std::is_same<T, __nv_bfloat16>::value) return __uint_as_float(bits16v << 16);
     const uint16_t hv = (uint16_t)bits16v;
@@ -356,22 +389,18 @@ __global__ void __launch_bounds__(kKeyThreads) bwd_keys_kernel(BwdParams p) {
   };
   for (int g = 0; g < G; ++g) {
     const int bh = b * p.Hq + kvh * G + g;
-    const T* qh = (const T*)p.q + (size_t)bh * p.N * D + lane * EL;
-    const T* gh = (const T*)p.dout + (size_t)bh * p.N * D + lane * EL;
-    // causal: rows >= key, so the first chunk that can hold these keys is the one of key0
-    for (int c0 = (int)key0 / sup::kChunkRows; c0 < chunks_used; c0 += kKeyThreads) {
+    // the eight lanes of a key read 128 contiguous bytes of a row per load
+    const T* qh = (const T*)p.q + (size_t)bh * p.N * D + gl * 8;
+    const T* gh = (const T*)p.dout + (size_t)bh * p.N * D + gl * 8;
+    // causal: rows >= key, so the first row block that can hold these keys is the one of key0
+    for (int c0 = (int)key0 / sup::kBlockRows; c0 < blocks_used; c0 += kKeyThreads) {
       const int c = c0 + (int)threadIdx.x;
-      uint32_t lo = 0, hi = 0;
-      const uint2* run = p.sv.by_key;
-      if (c < chunks_used) {
-        const uint2 tab = p.sv.chunks[(size_t)bh * chunks + c];
-        run += tab.x;
-        // lower bounds of key_lo and key_hi in the sorted run
-        uint32_t a = 0, z = tab.y;
-        while (a < z) { const uint32_t m = (a + z) >> 1; if (run[m].x < key_lo) a = m + 1; else z = m; }
-        lo = a; z = tab.y;
-        while (a < z) { const uint32_t m = (a + z) >> 1; if (run[m].x < key_hi) a = m + 1; else z = m; }
-        hi = a;
+      uint32_t lo = 0, hi = 0, src0 = 0;
+      if (c < blocks_used) {
+        const size_t bi = (size_t)bh * blocks + c;
+        const uint16_t* tab = p.sv.kb_off + bi * nkb1 + kb;
+        lo = tab[0]; hi = tab[1];
+        src0 = p.sv.blocks[bi].x + lo;
       }
       // block-wide exclusive scan of the counts: where each thread's entries go
       const uint32_t n_mine = hi - lo;
@@ -383,80 +412,147 @@ __global__ void __launch_bounds__(kKeyThreads) bwd_keys_kernel(BwdParams p) {
       }
       __syncthreads();  // the previous batch has been walked
       if (lane == 31) s_wsum[warp] = incl;
+      s_src[threadIdx.x] = src0;
+      s_cnt[threadIdx.x] = n_mine;
       __syncthreads();
       uint32_t off = incl - n_mine, total = 0;
 #pragma unroll
-      for (int w = 0; w < kKeyThreads / 32; ++w) {
+      for (int w = 0; w < kKeyWarps; ++w) {
         const uint32_t t = s_wsum[w];
         off += (w < warp) ? t : 0u;
         total += t;
       }
+      s_off[threadIdx.x] = off;
+      const int n_here = min(kKeyThreads, blocks_used - c0);
       for (uint32_t r0 = 0; r0 < total; r0 += kStage) {
-        if (r0 > 0) __syncthreads();  // the previous round has been walked
-        for (uint32_t e = 0; e < n_mine; ++e) {
-          const uint32_t pos = off + e - r0;  // wraps for entries of earlier rounds
-          if (pos < (uint32_t)kStage) {
-            const uint2 ent = run[lo + e];
-            const uint32_t row = (uint32_t)c * sup::kChunkRows + (ent.x & 31u);
-            s_ent[pos] = make_uint2((row << 6) | ((ent.x >> 8) - key0), ent.y);
+        __syncthreads();  // the segment table is written / the previous round has been walked
+        // a warp copies a segment, 32 entries per trip (segments of the first row blocks are long:
+        // their rows see few keys)
+        for (int t = warp; t < n_here; t += kKeyWarps) {
+          const uint32_t n = s_cnt[t], o = s_off[t];
+          const uint2* src = p.sv.by_key + s_src[t];
+          for (uint32_t e = lane; e < n; e += 32) {
+            const uint32_t pos = o + e - r0;  // wraps for entries of earlier rounds
+            if (pos < (uint32_t)kStage) {
+              const uint2 ent = src[e];
+              const uint32_t row = (uint32_t)(c0 + t) * sup::kBlockRows + (ent.x & 255u);
+              s_ent[pos] = make_uint2((row << 6) | ((ent.x >> 8) - key0), ent.y);
+            }
           }
         }
         __syncthreads();
         const uint32_t m = min((uint32_t)kStage, total - r0);
-        for (uint32_t e0 = 0; e0 < m; e0 += 32) {
-          const uint2 ent = (e0 + lane < m) ? s_ent[e0 + lane] : make_uint2(0u, 0u);
-          // entries of this warp's eight keys with a non-zero weight
-          uint32_t pick = __ballot_sync(0xffffffffu, ent.y != 0u && ((ent.x >> 3) & 7u) == (uint32_t)warp);
-          while (pick) {
-            LV rq[4], rg[4];
-            uint32_t xs[4], ys[4];
+        // Regroup the staged entries by key, keeping their order inside a key (a stable counting
+        // sort over the 64 keys; entries with zero weights drop out): each key's entries then
+        // lie in one range of s_srt.  Per 32-entry chunk the lanes with the same key rank
+        // themselves with a match; a thread per key turns the chunks' counts into offsets.
+        const uint32_t n_chunks = (m + 31) >> 5;
+        uint2 held[kStage / 32 / kKeyWarps];
+        uint32_t ranks[kStage / 32 / kKeyWarps];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {  // the rows of four entries in flight
-              const int src = pick ? __ffs(pick) - 1 : 0;
-              xs[j] = __shfl_sync(0xffffffffu, ent.x, src);
-              ys[j] = pick ? __shfl_sync(0xffffffffu, ent.y, src) : 0u;
-              if (!pick) ys[j] = 0u;
-              pick &= pick - 1;
-              const size_t roff = (size_t)(xs[j] >> 6) * D;
-              rq[j] = LV(); rg[j] = LV();
-              if (ys[j] != 0u) {
-                rq[j] = *reinterpret_cast<const LV*>(qh + roff);
-                rg[j] = *reinterpret_cast<const LV*>(gh + roff);
+        for (int i = 0; i < kStage / 32 / kKeyWarps; ++i) {
+          const uint32_t c = (uint32_t)(warp + i * kKeyWarps);
+          held[i] = make_uint2(0u, 0u);
+          ranks[i] = 0u;
+          if (c < n_chunks) {
+            const uint32_t e = c * 32 + lane;
+            if (e < m) held[i] = s_ent[e];
+            const bool live = held[i].y != 0u;
+            const uint32_t ek = live ? (held[i].x & 63u) : (64u + (uint32_t)lane);  // dead lanes match nobody
+            const uint32_t same = __match_any_sync(0xffffffffu, ek);
+            ranks[i] = __popc(same & ((1u << lane) - 1u));
+            s_ccnt[c * kKeysPerCta + lane] = 0;
+            s_ccnt[c * kKeysPerCta + 32 + lane] = 0;
+            __syncwarp();
+            if (live && ranks[i] == 0u) s_ccnt[c * kKeysPerCta + ek] = (uint16_t)__popc(same);
+          }
+        }
+        __syncthreads();
+        if (threadIdx.x < kKeysPerCta) {
+          uint32_t running = 0;
+          for (uint32_t c = 0; c < n_chunks; ++c) {
+            const uint32_t t = s_ccnt[c * kKeysPerCta + threadIdx.x];
+            s_ccnt[c * kKeysPerCta + threadIdx.x] = (uint16_t)running;
+            running += t;
+          }
+          s_kcnt[threadIdx.x] = running;
+        }
+        __syncthreads();
+        if (warp == 0) {
+          const uint32_t c0_ = s_kcnt[2 * lane], c1_ = s_kcnt[2 * lane + 1];
+          uint32_t incl2 = c0_ + c1_;
+#pragma unroll
+          for (int o = 1; o < 32; o <<= 1) {
+            const uint32_t up = __shfl_up_sync(0xffffffffu, incl2, o);
+            if (lane >= o) incl2 += up;
+          }
+          const uint32_t ex = incl2 - c0_ - c1_;
+          s_kpos[2 * lane] = ex; s_kpos[2 * lane + 1] = ex + c0_;
+          if (lane == 31) s_kpos[kKeysPerCta] = incl2;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < kStage / 32 / kKeyWarps; ++i) {
+          const uint32_t c = (uint32_t)(warp + i * kKeyWarps);
+          if (c < n_chunks && held[i].y != 0u) {
+            const uint32_t ek = held[i].x & 63u;
+            s_srt[s_kpos[ek] + s_ccnt[c * kKeysPerCta + ek] + ranks[i]] = held[i];
+          }
+        }
+        __syncthreads();
+        uint32_t e = s_kpos[my_local];
+        const uint32_t e_end = s_kpos[my_local + 1];
+        while (__any_sync(0xffffffffu, e < e_end)) {
+          uint4 rq[4][CH], rg[4][CH];
+          uint32_t ys[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {  // the rows of four entries of each key in flight
+            ys[j] = 0u;
+            if (e + j < e_end) {
+              const uint2 ent = s_srt[e + j];
+              ys[j] = ent.y;
+              const size_t roff = (size_t)(ent.x >> 6) * D;
+#pragma unroll
+              for (int c = 0; c < CH; ++c) {
+                rq[j][c] = *reinterpret_cast<const uint4*>(qh + roff + c * 64);
+                rg[j][c] = *reinterpret_cast<const uint4*>(gh + roff + c * 64);
               }
             }
+          }
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              if (ys[j] == 0u) continue;  // the same for every lane
-              const float pT = to_f(ys[j] & 0xffffu), dsT = to_f(ys[j] >> 16);
-              float qv[EL], gv[EL];
-              const T* eq = reinterpret_cast<const T*>(&rq[j]);
-              const T* eg = reinterpret_cast<const T*>(&rg[j]);
+          for (int j = 0; j < 4; ++j) {
+            if (ys[j] != 0u) {   // staged entries all have non-zero weights
+              const float2 pT = splat(to_f(ys[j] & 0xffffu)), dsT = splat(to_f(ys[j] >> 16));
 #pragma unroll
-              for (int x = 0; x < EL; ++x) { qv[x] = DT<T>::to_f(eq[x]); gv[x] = DT<T>::to_f(eg[x]); }
-              const uint32_t kk = xs[j] & 7u;
+              for (int c = 0; c < CH; ++c) {
+                float2 q8[4], g8[4];
+                unpack8<T>(rq[j][c], q8);
+                unpack8<T>(rg[j][c], g8);
 #pragma unroll
-              for (int t = 0; t < 8; ++t) {
-                if (kk == (uint32_t)t) {
-#pragma unroll
-                  for (int x = 0; x < EL; ++x) { ak[t][x] = fmaf(dsT, qv[x], ak[t][x]); av[t][x] = fmaf(pT, gv[x], av[t][x]); }
+                for (int x = 0; x < 4; ++x) {
+                  ak[c * 4 + x] = __ffma2_rn(dsT, q8[x], ak[c * 4 + x]);
+                  av[c * 4 + x] = __ffma2_rn(pT, g8[x], av[c * 4 + x]);
                 }
               }
             }
           }
+          e += 4;
         }
       }
     }
   }
+  const int key = (int)key0 + (int)my_local;
+  if (key < p.N) {
+    T* dk = (T*)p.dk + ((size_t)bkv * p.N + key) * D + gl * 8;
+    T* dv = (T*)p.dv + ((size_t)bkv * p.N + key) * D + gl * 8;
+    const float2 sc2 = splat(p.sm_scale);
 #pragma unroll
-  for (int kk = 0; kk < 8; ++kk) {
-    const int key = (int)key0 + warp * 8 + kk;
-    if (key < p.N) {
-      __align__(8) T outk[EL];
-      __align__(8) T outv[EL];
+    for (int c = 0; c < CH; ++c) {
+      float2 s8[4];
 #pragma unroll
-      for (int x = 0; x < EL; ++x) { outk[x] = DT<T>::from_f(ak[kk][x] * p.sm_scale); outv[x] = DT<T>::from_f(av[kk][x]); }
-      *reinterpret_cast<LV*>((T*)p.dk + ((size_t)bkv * p.N + key) * D + lane * EL) = *reinterpret_cast<const LV*>(outk);
-      *reinterpret_cast<LV*>((T*)p.dv + ((size_t)bkv * p.N + key) * D + lane * EL) = *reinterpret_cast<const LV*>(outv);
+      for (int x = 0; x < 4; ++x) s8[x] = __fmul2_rn(ak[c * 4 + x], sc2);
+      *reinterpret_cast<uint4*>(dk + c * 64) = pack8<T>(s8);
+      *reinterpret_cast<uint4*>(dv + c * 64) = pack8<T>(av + c * 4);
     }
   }
 }
@@ -470,9 +566,9 @@ int bwd_t(const simt::Params& p, cudaStream_t st) {
   bp.B = p.B; bp.Hq = p.Hq; bp.Hkv = p.Hkv; bp.N = p.N; bp.Dg = p.D;
   bp.sm_scale = p.sm_scale; bp.zscale = 0.5f * p.sm_scale;
   bp.sv = sup::view(p.support, p.B, p.Hq, p.Hkv, p.N);
-  const long long warps = (long long)p.B * p.Hq * ((p.N + kRowsPerWarp - 1) / kRowsPerWarp);
-  const unsigned grid = (unsigned)((warps + kRowThreads / 32 - 1) / (kRowThreads / 32));
-  const size_t sm = (size_t)(kRowThreads / 32) * sup::kChunkCap * sizeof(uint2);
+  static_assert(sup::kBlockRows == (kRowThreads / 32) * kRowsPerWarp, "one CTA per row block");
+  const unsigned grid = (unsigned)((long long)p.B * p.Hq * ((p.N + sup::kBlockRows - 1) / sup::kBlockRows));
+  const size_t sm = (size_t)sup::kBlockCap * sizeof(uint2);
   auto rows_kernel = p.D > 64 ? bwd_rows_kernel<T, 2> : bwd_rows_kernel<T, 1>;
   {
     static std::mutex mu;

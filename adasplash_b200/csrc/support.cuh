@@ -15,18 +15,21 @@
 // counter is zero, the gather kernels while it is not.
 //
 // The backward needs the same pairs by key as well (dK_j and dV_j sum over the rows that
-// attend to key j).  Its row kernel leaves, for every 32-row chunk, the chunk's entries sorted by
-// (key, row) -- in the same slots of a second array -- and the key kernel finds the entries of
-// its 64 keys in each chunk by binary search: no atomics, and a fixed summation order.
+// attend to key j).  Its row kernel leaves, for every 256-row block (the rows of one solver CTA),
+// the block's entries sorted by (key, row) -- in the same slots of a second array -- and the key
+// kernel finds the entries of its 64 keys in each block by binary search: no atomics, and a
+// fixed summation order.
 //
 // Layout of the buffer (all offsets multiples of 256 bytes):
 //   [0]      uint32 cursor: entries handed out so far (one atomicAdd per solver CTA)
 //   [256]    int32 dense[B*Hkv]
 //   rows     uint2 [B*Hq*N]: (index of the row's first entry, number of entries)
 //   entries  uint2 [cap]: (key index, fp32 bits of u = z - tau_final > 0)
-//   by_key   uint2 [cap]: (key << 8 | row inside its 32-row chunk, P^T | dS^T << 16 as 16-bit
-//            values), each chunk's run sorted ascending; written by the backward
-//   chunks   uint2 [B*Hq*ceil(N/32)]: (first entry of the chunk's run, its length)
+//   by_key   uint2 [cap]: (key << 8 | row inside its 256-row block, P^T | dS^T << 16 as 16-bit
+//            values), each block's run sorted ascending; written by the backward
+//   blocks   uint2 [B*Hq*ceil(N/256)]: (first entry of the block's run, its length)
+//   kb_off   uint16 [B*Hq*ceil(N/256)][ceil(N/64)+1]: where the entries of each 64-key block
+//            start inside a row block's sorted run (the last one: the run's length)
 #pragma once
 #include <cstddef>
 #include <cstdint>
@@ -37,8 +40,8 @@ namespace ads {
 namespace sup {
 
 constexpr int kEntriesPerRow = 16;  // capacity of the entry array, per query row of the problem
-constexpr int kChunkRows = 32;      // rows whose entries the backward sorts together
-constexpr int kChunkCap = 1024;     // most entries such a chunk may hold (the solver checks)
+constexpr int kBlockRows = 256;     // rows whose entries the backward sorts together: one solver CTA
+constexpr int kBlockCap = 8192;     // most entries such a block may hold (the solver checks)
 
 struct View {
   uint32_t* cursor;
@@ -46,7 +49,8 @@ struct View {
   uint2* rows;
   uint2* entries;
   uint2* by_key;
-  uint2* chunks;
+  uint2* blocks;
+  uint16_t* kb_off;
   uint32_t cap;
 };
 
@@ -54,9 +58,10 @@ __host__ __device__ inline size_t align256(size_t x) { return (x + 255) & ~(size
 
 inline size_t bytes(int B, int Hq, int Hkv, int N) {
   const size_t rows = (size_t)B * Hq * N;
-  const size_t chunks = (size_t)B * Hq * ((N + kChunkRows - 1) / kChunkRows);
+  const size_t blocks = (size_t)B * Hq * ((N + kBlockRows - 1) / kBlockRows);
+  const size_t nkb1 = (size_t)(N + 63) / 64 + 1;
   return 256 + align256((size_t)B * Hkv * 4) + align256(rows * 8) + 2 * align256(rows * kEntriesPerRow * 8) +
-         align256(chunks * 8);
+         align256(blocks * 8) + align256(blocks * nkb1 * 2);
 }
 
 // Bytes at the start of the buffer that the solver's launcher clears (cursor and counters).
@@ -71,7 +76,9 @@ inline View view(void* base, int B, int Hq, int Hkv, int N) {
   v.rows = (uint2*)(p + 256 + align256((size_t)B * Hkv * 4));
   v.entries = (uint2*)((uint8_t*)v.rows + align256(rows * 8));
   v.by_key = (uint2*)((uint8_t*)v.entries + align256(rows * kEntriesPerRow * 8));
-  v.chunks = (uint2*)((uint8_t*)v.by_key + align256(rows * kEntriesPerRow * 8));
+  v.blocks = (uint2*)((uint8_t*)v.by_key + align256(rows * kEntriesPerRow * 8));
+  const size_t blocks = (size_t)B * Hq * ((N + kBlockRows - 1) / kBlockRows);
+  v.kb_off = (uint16_t*)((uint8_t*)v.blocks + align256(blocks * 8));
   const size_t cap = rows * kEntriesPerRow;
   v.cap = cap > 0xffffffffull ? 0xffffffffu : (uint32_t)cap;
   return v;
