@@ -475,7 +475,8 @@ __host__ __device__ constexpr int delta_rows_per_warp(int D) {
 template <typename T>
 __global__ void __launch_bounds__(kDeltaThreads)
 bwd_delta_kernel(const T* __restrict__ o2, const T* __restrict__ dout, float* __restrict__ delta,
-                 const void* varlen, int is_i64, int B, int H, int N, int D) {
+                 const void* varlen, int is_i64, int B, int H, int N, int D,
+                 const int32_t* __restrict__ skip = nullptr, int Hkv = 1) {
   constexpr int VEC = 16 / (int)sizeof(T);
   const int chunks = D / VEC;                     // 16-byte chunks per row
   const int lpr = chunks < 32 ? chunks : 32;      // lanes per row
@@ -493,7 +494,9 @@ bwd_delta_kernel(const T* __restrict__ o2, const T* __restrict__ dout, float* __
     if (row < total) {
       const int b = (int)(row / ((long long)H * N));
       const int r = (int)(row % N);
-      if (r < load_len(varlen, is_i64, b, N)) {
+      // heads of a kv head whose counter is zero belong to the gather kernels (support.cuh)
+      const bool mine = skip == nullptr || skip[b * Hkv + (int)((row / N) % H) / (H / Hkv)] != 0;
+      if (mine && r < load_len(varlen, is_i64, b, N)) {
         const uint4* a = reinterpret_cast<const uint4*>(o2 + row * D);
         const uint4* g = reinterpret_cast<const uint4*>(dout + row * D);
         for (int c = li; c < chunks; c += lpr) {
@@ -517,11 +520,14 @@ bwd_delta_kernel(const T* __restrict__ o2, const T* __restrict__ dout, float* __
 
 // out[n][w] bit j = in[32w+j][n/32] bit (n%32)   (adasplash_v2.py:901-940)
 static __global__ void transpose_bitmap_kernel(const int32_t* __restrict__ in, int32_t* __restrict__ out,
-                                        int heads, int rows_padded, int n_words) {
+                                        int heads, int rows_padded, int n_words,
+                                        const int32_t* __restrict__ skip = nullptr, int Hq = 1, int Hkv = 1) {
   long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   long long per_head = (long long)rows_padded * n_words;
   if (idx >= per_head * heads) return;
   long long hd = idx / per_head;
+  // heads of a kv head whose counter is zero belong to the gather kernels (support.cuh)
+  if (skip != nullptr && skip[(hd / Hq) * Hkv + (hd % Hq) / (Hq / Hkv)] == 0) return;
   int rem = (int)(idx % per_head);
   int n = rem / n_words, w = rem % n_words;
   const uint32_t* src = (const uint32_t*)in + hd * per_head;

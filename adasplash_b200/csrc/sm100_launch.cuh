@@ -96,18 +96,21 @@ int fwd_t(const simt::Params& p, void* ws, cudaStream_t st) {
 template <typename T, int D, int AM = 0, bool CAUSAL = true>
 int bwd_t(const simt::Params& p, void* ws, cudaStream_t st) {
   const int stages = p.bwd_stages ? p.bwd_stages : 0xF;
+  // with a row-support buffer, heads the gather kernels own are skipped by every kernel here
+  const int32_t* skip = p.support != nullptr ? sup::view(p.support, p.B, p.Hq, p.Hkv, p.N).dense : nullptr;
   if (stages & ADS_BWD_DELTA) {
     long long rows = (long long)p.B * p.Hq * p.N;
     const long long per_block = (long long)(simt::kDeltaThreads / 32) * simt::delta_rows_per_warp<T>(p.D);
     unsigned grid = (unsigned)((rows + per_block - 1) / per_block);
     simt::bwd_delta_kernel<T><<<grid, simt::kDeltaThreads, 0, st>>>((const T*)p.out2_in, (const T*)p.dout, p.delta,
-                                                    p.varlen, p.varlen_is_i64, p.B, p.Hq, p.N, p.D);
+                                                    p.varlen, p.varlen_is_i64, p.B, p.Hq, p.N, p.D, skip, p.Hkv);
     if (int rc = check_launch("sm100::bwd_delta")) return rc;
   }
   if (stages & ADS_BWD_TRANSPOSE) {
     long long words = (long long)p.B * p.Hq * p.rows_padded * p.n_words;
     unsigned grid = (unsigned)((words + 255) / 256);
-    simt::transpose_bitmap_kernel<<<grid, 256, 0, st>>>(p.bmask, p.bmask_t, p.B * p.Hq, p.rows_padded, p.n_words);
+    simt::transpose_bitmap_kernel<<<grid, 256, 0, st>>>(p.bmask, p.bmask_t, p.B * p.Hq, p.rows_padded, p.n_words, skip,
+                                                        p.Hq, p.Hkv);
     if (int rc = check_launch("sm100::transpose_bitmap")) return rc;
   }
   CUtensorMap tmQ, tmDO, tmK, tmV, tmQ64, tmDO64;
