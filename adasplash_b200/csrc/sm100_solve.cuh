@@ -58,7 +58,11 @@ constexpr uint32_t kSolveQCol = 384;
 constexpr int kSolveBufs = 3;
 constexpr int kSolveRows = 2 * kBlockM;  // query rows per CTA
 
-enum SweepMode : int { kModeMax = 0, kModeHist = 1, kModeHalley = 2, kModeFinal = 3, kModeCollect = 4 };
+enum SweepMode : int { kModeMax = 0, kModeHist = 1, kModeHalley = 2, kModeFinal = 3, kModeCollect = 4, kModeFinalCollect = 5 };
+
+// A final sweep that also gathers the rows' supports takes scores from at most this far below the
+// tau entering it (see there).
+constexpr float kFinalCollectMargin = 1.0f / 32.0f;
 
 // One entry of the candidate pool: a score >= tau0 of some row, its key index (sequences of more
 // than 65536 keys: only the 64-key block it sits in), and the previous entry of the same
@@ -118,6 +122,7 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
   int* start_status = (int*)(smem + L::misc_off + 8);
   int* pool_used = (int*)(smem + L::misc_off + 32);   // [16]: entries used in each row warp's region
   volatile int* pool_ovf = (volatile int*)(smem + L::misc_off + 16);
+  volatile int* fin_bad = (volatile int*)(smem + L::misc_off + 20);  // the final sweep could not gather the supports
   float* xchg = (float*)(smem + L::xchg_off);
   uint32_t* s_bits = (uint32_t*)(smem + L::bits_off);
   Cand* pool = (Cand*)sQ;  // the Q tiles are dead once Q~ is in TMEM (before the first append)
@@ -156,6 +161,7 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
     *cta_abort = 0;
     for (int w = 0; w < 16; ++w) pool_used[w] = 0;
     *pool_ovf = 0;
+    *fin_bad = 0;
   }
   if (warp == 17) {
     if (lane == 0) {
@@ -415,6 +421,40 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
                 }
               }
             }
+          } else if (mode == kModeFinalCollect) {
+            // The final sweep of a CTA whose candidate pool overflowed, when the rows' supports
+            // are wanted: the pool is free again, and the few scores above (a hair below) the tau
+            // entering this sweep go into it.  The step that follows cannot take tau below the
+            // lower end of its bracket (less the step's own tolerance), so scores above that are
+            // gathered, but from no further than kFinalCollectMargin below tau (a wide bracket
+            // would bring in too many): the support after the step is among them unless the step
+            // falls further, which the CTA checks afterwards.
+            const float thr_c = fmaxf(fminf(thr, hs.lo) - 2e-5f, thr - kFinalCollectMargin);
+#pragma unroll
+            for (int g4 = 0; g4 < 8; ++g4) {
+              const float cm = fmaxf(ptx::fmax3(v[g4 * 4], v[g4 * 4 + 1], v[g4 * 4 + 2]), v[g4 * 4 + 3]);
+              if (cm > thr_c) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                  const float z = v[g4 * 4 + c];
+                  const float d = z - thr;
+                  if (d > 0.f) { a0 = fmaf(d, d, a0); a1 += d; a2 += 1.f; }
+                  if (z > thr_c && row_ok) {
+                    const int idx = atomicAdd(pool_used + warp, 1);
+                    if (idx < warp_pool) {
+                      const int slot = warp * warp_pool + idx;
+                      Cand e;
+                      e.z = z; e.next = head;
+                      e.key = (uint16_t)(keybase + ((g4 * 4 + c) & kmask));
+                      pool[slot] = e;
+                      head = (uint16_t)slot;
+                    } else {
+                      *fin_bad = 1;
+                    }
+                  }
+                }
+              }
+            }
           } else {
             // the scores above the threshold are a tiny part of a row: look at
             // four at a time and only open a group that contains one
@@ -443,7 +483,7 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
 #pragma unroll
           for (int bb = 0; bb < 8; ++bb) cnt[bb] += (int)((packed >> (8 * bb)) & 0xffull);
         }
-        if (mode == kModeFinal) {
+        if (mode == kModeFinal || mode == kModeFinalCollect) {
           // this warp covers 32 rows x 64 keys of the 64x64 sub-tile (row block rb, key block 2kt+half)
           const bool any = __any_sync(0xffffffffu, (a2 > a2_mark) && row_ok);
           if (lane == 0 && any) {
@@ -504,6 +544,7 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
     };
 
     bool full_sweeps = false;  // the candidate pool overflowed: every step sweeps S
+    bool fin_collect = false;  // ... and the final sweep gathers the rows' supports into the pool
     if (p.tau_given) {
       // bitmap for a given tau: one sweep over S
       if (grp_on) {
@@ -547,6 +588,13 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
       ptx::bar_sync(3, kSolveRowThreads);
       full_sweeps = *pool_ovf != 0;
       ptx::mbar_arrive_warp(decide);
+      // supports wanted and the lists gone: the final sweep gathers them into the pool afresh
+      fin_collect = !V1 && full_sweeps && p.sup_on && !wide;
+      if (fin_collect) {
+        if (threadIdx.x < 16) pool_used[threadIdx.x] = 0;
+        head = kCandNil;
+        ptx::bar_sync(3, kSolveRowThreads);
+      }
       if (grp_on && !full_sweeps) {
         // ---- Halley steps and the final step on this thread's list ----
         // If the warp's share of the pool has room behind the entries in use, every thread
@@ -617,8 +665,12 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
         for (int sw = 2; sw < nsweeps; ++sw) {
           reset_stats();
           if (sw == nsweeps - 1) {
-            sweep_tiles(std::integral_constant<int, kModeFinal>{});
+            const float gathered_from = fmaxf(fminf(hs.t, hs.lo) - 2e-5f, hs.t - kFinalCollectMargin);
+            if (fin_collect) sweep_tiles(std::integral_constant<int, kModeFinalCollect>{});
+            else sweep_tiles(std::integral_constant<int, kModeFinal>{});
             exchange(kModeFinal);
+            // the last step went below what was gathered: no export for this CTA
+            if (fin_collect && row_ok && hs.t <= gathered_from) *fin_bad = 2;
           } else {
             sweep_tiles(std::integral_constant<int, kModeHalley>{});
             exchange(kModeHalley);
@@ -641,7 +693,8 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
       // Entry = (key, u = z - tau > 0) for every listed score above the final tau whose 64x64
       // tile is in the block mask just built (what the tile kernels would visit); one run per
       // row: the keys of the row's first thread (low halves of the key tiles), then the second's.
-      const bool can = !full_sweeps && !wide && !*cta_abort;  // the same for every thread of the CTA
+      // the same for every thread of the CTA: the lists held (or the final sweep gathered anew)
+      const bool can = (!full_sweeps || (!V1 && !*fin_bad)) && !wide && !*cta_abort;
       int* cnts = reinterpret_cast<int*>(xchg) + grp * (2 * 8 * 128);
       int* extra = reinterpret_cast<int*>(xchg) + 128;        // [0..7] entries of each 32-row quarter, [8] base (beside the counts)
       const uint32_t* my_bits = s_bits + (grp * 2 + rb) * p.n_words;
@@ -686,11 +739,19 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
         // one reservation per CTA; a CTA that cannot export (or whose rows are too dense for the
         // backward's sort) hands its kv head to the tile kernels
         uint32_t base = 0xffffffffu;
+        int why = sup::kWhyPool;
         if (can && total <= sup::kBlockCap) {
           base = atomicAdd(p.sup.cursor, (uint32_t)total);
-          if (base > p.sup.cap || (uint32_t)total > p.sup.cap - base) base = 0xffffffffu;
+          if (base > p.sup.cap || (uint32_t)total > p.sup.cap - base) { base = 0xffffffffu; why = sup::kWhyFull; }
+        } else if (can) {
+          why = sup::kWhyBlock;
+        } else if (full_sweeps && *fin_bad == 2) {
+          why = sup::kWhyTau;
         }
-        if (base == 0xffffffffu) atomicAdd(p.sup.dense + b * p.Hkv + kvh, 1);
+        if (base == 0xffffffffu) {
+          atomicAdd(p.sup.dense + b * p.Hkv + kvh, 1);
+          atomicAdd(p.sup.cursor + 4 + why, 1u);  // diagnostics: CTAs that could not export, by reason
+        }
         extra[8] = (int)base;
       }
       ptx::bar_sync(3, kSolveRowThreads);

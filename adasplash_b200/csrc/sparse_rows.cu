@@ -16,7 +16,8 @@ namespace ads {
 namespace sparse {
 namespace {
 
-constexpr int kRowThreads = 256;
+constexpr int kRowThreads = 256;     // forward gather: eight warps of 32 rows
+constexpr int kBwdRowThreads = 256;  // backward by rows: the eight warps of one 256-row block
 
 struct RowsParams {
   const void* v; void* out; void* out2;
@@ -181,9 +182,9 @@ __device__ __forceinline__ float group_sum8(float x) {  // over the eight lanes 
 // key-side values go to shared memory at the entry's slot, are sorted there by (key, row) once
 // the 256 rows are done, and leave as the block's run of `by_key`.
 template <typename T, int CH>
-__global__ void __launch_bounds__(kRowThreads) bwd_rows_kernel(BwdParams p) {
+__global__ void __launch_bounds__(kBwdRowThreads) bwd_rows_kernel(BwdParams p) {
   extern __shared__ uint2 sort_buf[];  // [kBlockCap]
-  __shared__ uint32_t s_tot[kRowThreads / 32];
+  __shared__ uint32_t s_tot[kBwdRowThreads / 32];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int grp = lane >> 3, gl = lane & 7;
   const int blocks = (p.N + sup::kBlockRows - 1) / sup::kBlockRows;  // per head
@@ -305,15 +306,15 @@ __global__ void __launch_bounds__(kRowThreads) bwd_rows_kernel(BwdParams p) {
   __syncthreads();
   uint32_t total = 0;
 #pragma unroll
-  for (int w = 0; w < kRowThreads / 32; ++w) total += s_tot[w];
+  for (int w = 0; w < kBwdRowThreads / 32; ++w) total += s_tot[w];
   total = min(total, (uint32_t)sup::kBlockCap);  // the solver exports no denser block
   uint32_t n2 = 64;
   while (n2 < total) n2 <<= 1;
-  for (uint32_t t = total + threadIdx.x; t < n2; t += kRowThreads) sb[t] = make_uint2(0xffffffffu, 0u);
+  for (uint32_t t = total + threadIdx.x; t < n2; t += kBwdRowThreads) sb[t] = make_uint2(0xffffffffu, 0u);
   __syncthreads();
   for (uint32_t k = 2; k <= n2; k <<= 1) {
     for (uint32_t j = k >> 1; j > 0; j >>= 1) {
-      for (uint32_t pi = threadIdx.x; pi < n2 / 2; pi += kRowThreads) {  // the pi-th pair (t, t | j) of this stage
+      for (uint32_t pi = threadIdx.x; pi < n2 / 2; pi += kBwdRowThreads) {  // the pi-th pair (t, t | j) of this stage
         const uint32_t t = ((pi & ~(j - 1)) << 1) | (pi & (j - 1)), x = t | j;
         const uint2 a = sb[t], c = sb[x];
         const bool up = (t & k) == 0;
@@ -326,13 +327,13 @@ __global__ void __launch_bounds__(kRowThreads) bwd_rows_kernel(BwdParams p) {
     }
   }
   __syncthreads();
-  for (uint32_t t = threadIdx.x; t < total; t += kRowThreads) p.sv.by_key[run0 + t] = sb[t];
+  for (uint32_t t = threadIdx.x; t < total; t += kBwdRowThreads) p.sv.by_key[run0 + t] = sb[t];
   if (threadIdx.x == 0) p.sv.blocks[(size_t)bh * blocks + blk] = make_uint2(run0, total);
   // where each 64-key block starts in the sorted run: the key kernel reads its bounds from this
   // table instead of searching the run in global memory
   const int nkb1 = (p.N + 63) / 64 + 1;
   uint16_t* tab = p.sv.kb_off + ((size_t)bh * blocks + blk) * nkb1;
-  for (int kbi = threadIdx.x; kbi < nkb1; kbi += kRowThreads) {
+  for (int kbi = threadIdx.x; kbi < nkb1; kbi += kBwdRowThreads) {
     const uint32_t key = (uint32_t)(kbi * 64) << 8;
     uint32_t a = 0, z = total;
     while (a < z) { const uint32_t m = (a + z) >> 1; if (sb[m].x < key) a = m + 1; else z = m; }
@@ -566,7 +567,7 @@ int bwd_t(const simt::Params& p, cudaStream_t st) {
   bp.B = p.B; bp.Hq = p.Hq; bp.Hkv = p.Hkv; bp.N = p.N; bp.Dg = p.D;
   bp.sm_scale = p.sm_scale; bp.zscale = 0.5f * p.sm_scale;
   bp.sv = sup::view(p.support, p.B, p.Hq, p.Hkv, p.N);
-  static_assert(sup::kBlockRows == (kRowThreads / 32) * kRowsPerWarp, "one CTA per row block");
+  static_assert(sup::kBlockRows == (kBwdRowThreads / 32) * kRowsPerWarp, "one CTA per row block");
   const unsigned grid = (unsigned)((long long)p.B * p.Hq * ((p.N + sup::kBlockRows - 1) / sup::kBlockRows));
   const size_t sm = (size_t)sup::kBlockCap * sizeof(uint2);
   auto rows_kernel = p.D > 64 ? bwd_rows_kernel<T, 2> : bwd_rows_kernel<T, 1>;
@@ -582,7 +583,7 @@ int bwd_t(const simt::Params& p, cudaStream_t st) {
       if (dev >= 0 && dev < 128) done[p.D > 64][dev] = true;
     }
   }
-  rows_kernel<<<grid, kRowThreads, sm, st>>>(bp);
+  rows_kernel<<<grid, kBwdRowThreads, sm, st>>>(bp);
   if (int rc = check_launch("sparse::bwd_rows")) return rc;
   const unsigned kgrid = (unsigned)((long long)p.B * p.Hkv * ((p.N + kKeysPerCta - 1) / kKeysPerCta));
   if (p.D > 64) bwd_keys_kernel<T, 128><<<kgrid, kKeyThreads, 0, st>>>(bp);

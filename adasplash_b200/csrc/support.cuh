@@ -21,7 +21,8 @@
 // fixed summation order.
 //
 // Layout of the buffer (all offsets multiples of 256 bytes):
-//   [0]      uint32 cursor: entries handed out so far (one atomicAdd per solver CTA)
+//   [0]      uint32 cursor: entries handed out so far (one atomicAdd per solver CTA);
+//            words 4..7: solver CTAs that could not export, by reason (kWhy*)
 //   [256]    int32 dense[B*Hkv]
 //   rows     uint2 [B*Hq*N]: (index of the row's first entry, number of entries)
 //   entries  uint2 [cap]: (key index, fp32 bits of u = z - tau_final > 0)
@@ -39,9 +40,17 @@
 namespace ads {
 namespace sup {
 
-constexpr int kEntriesPerRow = 16;  // capacity of the entry array, per query row of the problem
+constexpr int kEntriesPerRow = 32;  // capacity of the entry arrays, per query row of the problem
 constexpr int kBlockRows = 256;     // rows whose entries the backward sorts together: one solver CTA
 constexpr int kBlockCap = 8192;     // most entries such a block may hold (the solver checks)
+
+// why a solver CTA did not export (counters in words 4..7 of the buffer)
+enum : int {
+  kWhyPool = 0,   // its candidate pool overflowed, in the final sweep as well (or a wait gave up)
+  kWhyTau = 1,    // the last step took tau below the scores the final sweep had gathered
+  kWhyBlock = 2,  // more than kBlockCap entries in its 256 rows
+  kWhyFull = 3,   // the entry array is full
+};
 
 struct View {
   uint32_t* cursor;

@@ -393,6 +393,7 @@ def route_record(att, q, k, v, do, varlen, niter, reps):
     taus, bmask = att.solve(q, k, niter, varlen, support=sup)
     torch.cuda.synchronize()
     entries = int(sup[:4].view(torch.int32).item())
+    why = sup[16:32].view(torch.int32).tolist()
     dense = sup[256:256 + 4 * B * Hkv].view(torch.int32)
     sparse_heads = int((dense == 0).sum().item())
     ms["fwd"] = ev(lambda: att.forward_raw(q, k, v, taus, bmask, varlen, support=sup))
@@ -401,6 +402,9 @@ def route_record(att, q, k, v, do, varlen, niter, reps):
     rows = sum(int(x) for x in (varlen.tolist() if varlen is not None else [N] * B)) * Hq
     return {"kv_heads": B * Hkv, "kv_heads_on_gather_kernels": sparse_heads,
             "support_entries_per_row": round(entries / max(1, rows), 2),
+            # solver CTAs (256 rows each) that could not export, by reason
+            "ctas_without_export": {"pool_overflow": why[0], "tau_fell_below_gathered": why[1],
+                                    "rows_too_dense": why[2], "entry_array_full": why[3]},
             "call_ms": {n: round(x, 3) for n, x in ms.items()}}
 
 

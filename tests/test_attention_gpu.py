@@ -308,6 +308,8 @@ def test_tensor_core_path_matches_cuda_core_path(path, shape):
     (1, 4, 1, 2048, 64, None, (1.5, 1.5), torch.float16, 1),
     (1, 2, 1, 1000, 128, [1000], (1.5, 1.5), torch.bfloat16, 1),      # N not a multiple of 32
     (1, 2, 2, 2048, 128, None, (0.05, 1.0), torch.bfloat16, 0),       # flat rows: the pool overflows
+    # unit-variance scores: the candidate pool overflows, the supports come from the final sweep
+    (2, 4, 1, 16384, 128, [16384, 5000], (1.0, 1.0), torch.bfloat16, 2),
     (1, 2, 2, 512, 32, None, (1.5, 1.5), torch.bfloat16, 0),          # head dim without a gather route
 ])
 def test_row_supports_match_tile_kernels(case):
