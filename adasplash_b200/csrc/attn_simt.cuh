@@ -486,6 +486,13 @@ bwd_delta_kernel(const T* __restrict__ o2, const T* __restrict__ dout, float* __
   const long long total = (long long)B * H * N;
   const long long warp_id = (long long)blockIdx.x * (kDeltaThreads / 32) + threadIdx.x / 32;
   const long long row0 = warp_id * (rows_pass * kDeltaUnroll);
+  if (skip != nullptr && row0 < total) {
+    // the warp's rows lie in one head or two neighbours: leave if the gather kernels own both
+    const long long last = min(total, row0 + rows_pass * kDeltaUnroll) - 1;
+    const long long h0 = row0 / N, h1 = last / N;
+    const int G = H / Hkv;
+    if (h1 - h0 <= 1 && skip[(h0 / H) * Hkv + (h0 % H) / G] == 0 && skip[(h1 / H) * Hkv + (h1 % H) / G] == 0) return;
+  }
   float acc[kDeltaUnroll];
 #pragma unroll
   for (int u = 0; u < kDeltaUnroll; ++u) {

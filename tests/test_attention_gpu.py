@@ -307,6 +307,7 @@ def test_tensor_core_path_matches_cuda_core_path(path, shape):
     (2, 4, 2, 1024, 128, [1024, 700], (1.5, 1.5), torch.bfloat16, 4),
     (1, 4, 1, 2048, 64, None, (1.5, 1.5), torch.float16, 1),
     (1, 2, 1, 1000, 128, [1000], (1.5, 1.5), torch.bfloat16, 1),      # N not a multiple of 32
+    (3, 2, 2, 320, 64, [1, 70, 257], (1.5, 1.5), torch.bfloat16, 6),  # sequences of one row, of a tile and a bit
     (1, 2, 2, 2048, 128, None, (0.05, 1.0), torch.bfloat16, 0),       # flat rows: the pool overflows
     # unit-variance scores: the candidate pool overflows, the supports come from the final sweep
     (2, 4, 1, 16384, 128, [16384, 5000], (1.0, 1.0), torch.bfloat16, 2),
