@@ -71,6 +71,8 @@ NCU_DRAM_BYTES_PER_LAUNCH = {
     # headline workload: captured on the 32-head "mid" case (profiles/*_bf16_d128_mid.txt) and
     # scaled by 4 to the 128 heads of C3 (traffic is per head: every head streams its own q/k/v)
     ("c3", "solve"): 4 * (225.10e6 + 10.92e6),
+    ("c3", "solve_with_export"): 4 * (230.24e6 + 20.61e6),   # profiles/solve_export_bf16_d128_mid.txt
+    ("mid", "solve_with_export"): 230.24e6 + 20.61e6,
     ("c3", "fwd"): 4 * (202.50e6 + 103.72e6),
     ("c3", "bwd_dq"): 4 * (270.74e6 + 52.86e6),
     ("c3", "bwd_dkv"): 4 * (270.71e6 + 108.38e6),
@@ -753,7 +755,7 @@ def run_ours(args):
                 "unit": "TFLOP/s", "frac": round(achieved / peak, 4),
                 "frac_sustained": round(achieved / pk["bf16_tflops_sustained"], 4),
                 "frac_nominal": round(achieved / NOMINAL_BF16_TFLOPS, 4),
-                "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get((args.workload, dom)),
+                "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get((args.workload, "solve_with_export" if all_gather else dom)),
                 "peak_source": pk["source"] + " (burst cuBLAS bf16: the kernel is timed alone, 10 launches back to back; "
                 "frac_sustained = against the seconds-long cuBLAS loop, frac_nominal = against 2250 TFLOP/s)",
                 "algorithmic_flops_per_launch": kernel_flops[dom],
