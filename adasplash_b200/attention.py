@@ -72,6 +72,8 @@ def _workspace(shape, device):
 
 
 ROW_SUPPORTS = True   # let the solver export the rows' supports, so that sparse heads run as gathers
+ROW_SUPPORTS_MIN_N = 1024  # the autograd Function asks for supports from this sequence length on:
+#                            below it a step is a few tiles per head and the extra launches cost more
 
 
 def support_buffer(shape, device):
@@ -145,7 +147,7 @@ class _SparseAttention(torch.autograd.Function):
         out2 = torch.empty_like(q)
         with torch.cuda.device(dev):
             ws, nbytes = _workspace(shape, dev)
-            support = support_buffer(shape, dev)
+            support = support_buffer(shape, dev) if N >= ROW_SUPPORTS_MIN_N else None
             st = torch.cuda.current_stream().cuda_stream
             sp = ctypes.byref(shape)
             _lib.check(lib.adasplash2_solve(_ptr(q), _ptr(k), _ptr(varlen), _ptr(taus),
