@@ -64,10 +64,14 @@ def bitmap_extent(shape):
     return rows.value, words.value
 
 
-def _workspace(shape, device):
+def _workspace(shape, device, full=False):
+    """Scratch of one call: the 256-byte status word; `full` (a backward with a support buffer)
+    adds the room for its key-sorted copy of the supports."""
     nbytes = int(_lib.load().adasplash2_workspace_bytes(ctypes.byref(shape)))
     if nbytes == 0:
         _lib.check(_lib.load().adasplash2_resolved_path(ctypes.byref(shape)) < 0)
+    if not full:
+        nbytes = min(nbytes, 256)
     return torch.empty(max(nbytes, 256), device=device, dtype=torch.uint8), nbytes
 
 
@@ -205,7 +209,7 @@ def backward_raw(q, k, v, do, out2, taus, bmask, varlen=None, niter=1, stages=0,
                    torch.empty(taus.shape, device=dev, dtype=torch.float32), torch.empty_like(bmask))
     dq, dk, dv, delta, bmask_t = buffers
     with torch.cuda.device(dev):
-        ws, nbytes = _workspace(shape, dev)
+        ws, nbytes = _workspace(shape, dev, full=support is not None)
         st = torch.cuda.current_stream().cuda_stream
         _lib.check(lib.adasplash2_bwd(_ptr(q), _ptr(k), _ptr(v), _ptr(do), _ptr(out2),
                                       _ptr(varlen), _ptr(taus), _ptr(bmask), _ptr(bmask_t),

@@ -168,7 +168,10 @@ extern "C" size_t adasplash2_workspace_bytes(const ads_attn_shape* shape) {
   if (check_shape(shape, "workspace_bytes")) return 0;
   int path;
   if (resolve_path(shape, "workspace_bytes", &path)) return 0;
-  if (path == ADS_PATH_TCGEN05) return sm100::workspace_bytes(shape);
+  if (path == ADS_PATH_TCGEN05) {
+    // the status word, and for shapes with a gather route the backward's scratch behind it
+    return sm100::workspace_bytes(shape) + (sparse::supported(shape) ? sparse::bwd_scratch_bytes(shape) : 0);
+  }
   return 256;  // the CUDA-core kernels need no scratch; keep the pointer non-null
 }
 
@@ -282,6 +285,12 @@ extern "C" int adasplash2_bwd(const void* q, const void* k, const void* v, const
       return ADS_ERR_WORKSPACE;
     }
     if (p.support != nullptr) {
+      const size_t need = sm100::min_workspace_bytes() + sparse::bwd_scratch_bytes(s);
+      if (ws_bytes < need) {
+        set_error("%s: with a support buffer the backward needs %zu bytes of workspace (got %zu)", who, need, ws_bytes);
+        return ADS_ERR_WORKSPACE;
+      }
+      p.bwd_scratch = (uint8_t*)ws + sm100::min_workspace_bytes();
       if (int rc = sparse::bwd(p, s->dtype, st)) return rc;
     }
     return is_v2(s) ? sm100::bwd(p, s->dtype, ws, st) : sm100::v1::bwd(p, s->dtype, ws, st);

@@ -201,6 +201,7 @@ struct Params {
   int causal;       // 1 = causal mask
   float zscale;     // fp32((alpha-1) * sm_scale): scores are z = zscale * q.k
   void* support;    // row-support buffer of the tensor-core path (support.cuh), or null
+  void* bwd_scratch;  // with it, in the backward: room for the entries sorted by key (workspace + 256)
 };
 
 // ---------------------------------------------------------------------------

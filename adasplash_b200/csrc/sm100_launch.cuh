@@ -61,7 +61,7 @@ TcParams to_tc(const simt::Params& p, void* ws) {
   t.tau_given = p.tau_given;
   t.status = (int*)ws;
   t.sup_on = p.support != nullptr;
-  if (t.sup_on) t.sup = sup::view(p.support, p.B, p.Hq, p.Hkv, p.N);
+  if (t.sup_on) t.sup = sup::view(p.support, nullptr, p.B, p.Hq, p.Hkv, p.N);
   return t;
 }
 
@@ -97,7 +97,7 @@ template <typename T, int D, int AM = 0, bool CAUSAL = true>
 int bwd_t(const simt::Params& p, void* ws, cudaStream_t st) {
   const int stages = p.bwd_stages ? p.bwd_stages : 0xF;
   // with a row-support buffer, heads the gather kernels own are skipped by every kernel here
-  const int32_t* skip = p.support != nullptr ? sup::view(p.support, p.B, p.Hq, p.Hkv, p.N).dense : nullptr;
+  const int32_t* skip = p.support != nullptr ? sup::view(p.support, nullptr, p.B, p.Hq, p.Hkv, p.N).dense : nullptr;
   if (stages & ADS_BWD_DELTA) {
     long long rows = (long long)p.B * p.Hq * p.N;
     const long long per_block = (long long)(simt::kDeltaThreads / 32) * simt::delta_rows_per_warp<T>(p.D);

@@ -143,7 +143,7 @@ int fwd_t(const simt::Params& p, cudaStream_t st) {
   rp.v = p.v; rp.out = p.out; rp.out2 = p.out2;
   rp.varlen = p.varlen; rp.varlen_is_i64 = p.varlen_is_i64;
   rp.B = p.B; rp.Hq = p.Hq; rp.Hkv = p.Hkv; rp.N = p.N; rp.Dg = p.D;
-  rp.sv = sup::view(p.support, p.B, p.Hq, p.Hkv, p.N);
+  rp.sv = sup::view(p.support, nullptr, p.B, p.Hq, p.Hkv, p.N);
   const long long warps = (long long)p.B * p.Hq * ((p.N + kRowsPerWarp - 1) / kRowsPerWarp);
   const unsigned grid = (unsigned)((warps + kRowThreads / 32 - 1) / (kRowThreads / 32));
   if (p.D > 64) fwd_rows_kernel<T, 2><<<grid, kRowThreads, 0, st>>>(rp);
@@ -566,7 +566,7 @@ int bwd_t(const simt::Params& p, cudaStream_t st) {
   bp.varlen = p.varlen; bp.varlen_is_i64 = p.varlen_is_i64;
   bp.B = p.B; bp.Hq = p.Hq; bp.Hkv = p.Hkv; bp.N = p.N; bp.Dg = p.D;
   bp.sm_scale = p.sm_scale; bp.zscale = 0.5f * p.sm_scale;
-  bp.sv = sup::view(p.support, p.B, p.Hq, p.Hkv, p.N);
+  bp.sv = sup::view(p.support, p.bwd_scratch, p.B, p.Hq, p.Hkv, p.N);
   static_assert(sup::kBlockRows == (kBwdRowThreads / 32) * kRowsPerWarp, "one CTA per row block");
   const unsigned grid = (unsigned)((long long)p.B * p.Hq * ((p.N + sup::kBlockRows - 1) / sup::kBlockRows));
   const size_t sm = (size_t)sup::kBlockCap * sizeof(uint2);
@@ -603,6 +603,7 @@ bool supported(const ads_attn_shape* s) {
 }
 
 size_t support_bytes(const ads_attn_shape* s) { return sup::bytes(s->B, s->Hq, s->Hkv, s->N); }
+size_t bwd_scratch_bytes(const ads_attn_shape* s) { return sup::scratch_bytes(s->B, s->Hq, s->Hkv, s->N); }
 
 int clear_header(const simt::Params& p, cudaStream_t st) {
   cudaError_t e = cudaMemsetAsync(p.support, 0, sup::header_bytes(p.B, p.Hkv), st);

@@ -9,6 +9,8 @@ namespace sparse {
 // Shapes for which the solver exports supports: what its candidate lists can express.
 bool supported(const ads_attn_shape* s);
 size_t support_bytes(const ads_attn_shape* s);
+// Scratch the backward needs beside the status word when it is given a support buffer.
+size_t bwd_scratch_bytes(const ads_attn_shape* s);
 // Cursor and per-head counters -> 0 (before the solver runs).
 int clear_header(const simt::Params& p, cudaStream_t st);
 // out / out2 of every head whose supports were exported; other heads are left alone.

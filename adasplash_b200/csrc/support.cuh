@@ -20,12 +20,17 @@
 // kernel finds the entries of its 64 keys in each block by binary search: no atomics, and a
 // fixed summation order.
 //
-// Layout of the buffer (all offsets multiples of 256 bytes):
+// The support buffer lives from the solve to the backward (it is saved with the forward's
+// tensors), so it holds only what the solver writes; the backward's own arrays are scratch in
+// that call's workspace.
+//
+// Layout of the support buffer (all offsets multiples of 256 bytes):
 //   [0]      uint32 cursor: entries handed out so far (one atomicAdd per solver CTA);
 //            words 4..7: solver CTAs that could not export, by reason (kWhy*)
 //   [256]    int32 dense[B*Hkv]
 //   rows     uint2 [B*Hq*N]: (index of the row's first entry, number of entries)
 //   entries  uint2 [cap]: (key index, fp32 bits of u = z - tau_final > 0)
+// and of the backward's scratch (workspace + 256):
 //   by_key   uint2 [cap]: (key << 8 | row inside its 256-row block, P^T | dS^T << 16 as 16-bit
 //            values), each block's run sorted ascending; written by the backward
 //   blocks   uint2 [B*Hq*ceil(N/256)]: (first entry of the block's run, its length)
@@ -67,16 +72,22 @@ __host__ __device__ inline size_t align256(size_t x) { return (x + 255) & ~(size
 
 inline size_t bytes(int B, int Hq, int Hkv, int N) {
   const size_t rows = (size_t)B * Hq * N;
+  return 256 + align256((size_t)B * Hkv * 4) + align256(rows * 8) + align256(rows * kEntriesPerRow * 8);
+}
+
+// Scratch of the backward on the gather route (by_key, blocks, kb_off).
+inline size_t scratch_bytes(int B, int Hq, int Hkv, int N) {
+  const size_t rows = (size_t)B * Hq * N;
   const size_t blocks = (size_t)B * Hq * ((N + kBlockRows - 1) / kBlockRows);
   const size_t nkb1 = (size_t)(N + 63) / 64 + 1;
-  return 256 + align256((size_t)B * Hkv * 4) + align256(rows * 8) + 2 * align256(rows * kEntriesPerRow * 8) +
-         align256(blocks * 8) + align256(blocks * nkb1 * 2);
+  return align256(rows * kEntriesPerRow * 8) + align256(blocks * 8) + align256(blocks * nkb1 * 2);
 }
 
 // Bytes at the start of the buffer that the solver's launcher clears (cursor and counters).
 inline size_t header_bytes(int B, int Hkv) { return 256 + align256((size_t)B * Hkv * 4); }
 
-inline View view(void* base, int B, int Hq, int Hkv, int N) {
+// `scratch` may be null outside the backward (the three arrays it holds are then unset).
+inline View view(void* base, void* scratch, int B, int Hq, int Hkv, int N) {
   View v;
   uint8_t* p = (uint8_t*)base;
   const size_t rows = (size_t)B * Hq * N;
@@ -84,10 +95,13 @@ inline View view(void* base, int B, int Hq, int Hkv, int N) {
   v.dense = (int32_t*)(p + 256);
   v.rows = (uint2*)(p + 256 + align256((size_t)B * Hkv * 4));
   v.entries = (uint2*)((uint8_t*)v.rows + align256(rows * 8));
-  v.by_key = (uint2*)((uint8_t*)v.entries + align256(rows * kEntriesPerRow * 8));
-  v.blocks = (uint2*)((uint8_t*)v.by_key + align256(rows * kEntriesPerRow * 8));
-  const size_t blocks = (size_t)B * Hq * ((N + kBlockRows - 1) / kBlockRows);
-  v.kb_off = (uint16_t*)((uint8_t*)v.blocks + align256(blocks * 8));
+  v.by_key = nullptr; v.blocks = nullptr; v.kb_off = nullptr;
+  if (scratch != nullptr) {
+    const size_t blocks = (size_t)B * Hq * ((N + kBlockRows - 1) / kBlockRows);
+    v.by_key = (uint2*)scratch;
+    v.blocks = (uint2*)((uint8_t*)v.by_key + align256(rows * kEntriesPerRow * 8));
+    v.kb_off = (uint16_t*)((uint8_t*)v.blocks + align256(blocks * 8));
+  }
   const size_t cap = rows * kEntriesPerRow;
   v.cap = cap > 0xffffffffull ? 0xffffffffu : (uint32_t)cap;
   return v;

@@ -81,8 +81,11 @@ int adasplash_entmax_fwd(const void* x, void* y, float* tau_out, int64_t rows, i
 int adasplash_entmax_bwd(const void* y, const void* dy, void* dx, int64_t rows, int64_t cols,
                          float alpha, int32_t fast_math, int32_t dtype, void* stream);
 
-/* Bytes of scratch the attention entry points need for `shape` (forward and
- * backward use the same buffer; 256-byte aligned base expected). */
+/* Bytes of scratch the attention entry points need for `shape` (256-byte aligned base
+ * expected).  The first 256 bytes (the status word of the bounded device waits) are all that
+ * adasplash2_solve, _mask_from_tau and _fwd use, and all that adasplash2_bwd uses without a
+ * support buffer; with one, the backward keeps its key-sorted copy of the supports behind
+ * them.  A workspace is only live during the call it is passed to. */
 size_t adasplash2_workspace_bytes(const ads_attn_shape* shape);
 
 /* Row supports (optional; no counterpart in the reference, whose kernels are block-sparse only).
