@@ -278,6 +278,14 @@ extern "C" int adasplash2_bwd(const void* q, const void* k, const void* v, const
   p.bmask_t = bmask_t; p.delta = delta; p.dq = dq; p.dk = dk; p.dv = dv;
   if (int rc = resolve_support(s, path, support, support_bytes, who, &p.support)) return rc;
   if (s->bwd_stages != 0) p.support = nullptr;  // single kernels of the tile route (timing aid)
+  if (p.support != nullptr) {
+    const size_t need = sm100::min_workspace_bytes() + sparse::bwd_scratch_bytes(s);
+    if (ws == nullptr || ws_bytes < need) {
+      set_error("%s: with a support buffer the backward needs %zu bytes of workspace (got %zu)", who, need, ws_bytes);
+      return ADS_ERR_WORKSPACE;
+    }
+    p.bwd_scratch = (uint8_t*)ws + sm100::min_workspace_bytes();
+  }
   if (int rc = clear_status(ws, ws_bytes, st, who)) return rc;
   if (path == ADS_PATH_TCGEN05) {
     if (ws == nullptr || ws_bytes < sm100::min_workspace_bytes()) {
@@ -285,12 +293,6 @@ extern "C" int adasplash2_bwd(const void* q, const void* k, const void* v, const
       return ADS_ERR_WORKSPACE;
     }
     if (p.support != nullptr) {
-      const size_t need = sm100::min_workspace_bytes() + sparse::bwd_scratch_bytes(s);
-      if (ws_bytes < need) {
-        set_error("%s: with a support buffer the backward needs %zu bytes of workspace (got %zu)", who, need, ws_bytes);
-        return ADS_ERR_WORKSPACE;
-      }
-      p.bwd_scratch = (uint8_t*)ws + sm100::min_workspace_bytes();
       if (int rc = sparse::bwd(p, s->dtype, st)) return rc;
     }
     return is_v2(s) ? sm100::bwd(p, s->dtype, ws, st) : sm100::v1::bwd(p, s->dtype, ws, st);

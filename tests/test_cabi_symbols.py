@@ -63,3 +63,39 @@ def test_bitmap_extent_matches_reference_layout():
         r, w = ctypes.c_int32(), ctypes.c_int32()
         total = lib.adasplash2_bitmap_words(ctypes.byref(sh), ctypes.byref(r), ctypes.byref(w))
         assert (r.value, w.value, total) == (rows, words, 6 * rows * words)
+
+
+def test_support_and_workspace_sizes_without_gpu():
+    # The gather route exists for 16-bit inputs, head dim 64 / 128, causal alpha = 1.5 and up to
+    # 65536 keys; elsewhere no support buffer is asked for and the workspace is the status word.
+    lib = _lib.load()
+
+    def sizes(**kw):
+        base = dict(B=2, Hq=4, Hkv=2, N=4096, D=128, dtype=2, niter=1, varlen_is_i64=0, path=0)
+        base.update(kw)
+        sh = _lib.AttnShape(**base)
+        return lib.adasplash2_support_bytes(ctypes.byref(sh)), lib.adasplash2_workspace_bytes(ctypes.byref(sh))
+
+    rows = 2 * 4 * 4096
+    sup, ws = sizes()
+    # cursor + route counters, (first, count) per row, 32 entries of 8 bytes per row
+    assert sup == 256 + 256 + rows * 8 + rows * 32 * 8
+    # status word + the backward's sorted copy, run table (16 blocks of 256 rows per head) and key-block table
+    blocks = 2 * 4 * 16
+    assert ws == 256 + rows * 32 * 8 + blocks * 8 + ((blocks * 65 * 2 + 255) // 256) * 256
+    assert sizes(dtype=0) == (0, 256)            # fp32: CUDA-core kernels
+    assert sizes(D=32) == (0, 256)               # head dim without a gather route
+    assert sizes(N=131072) == (0, 256)           # key indices would not fit 16 bits
+    assert sizes(alpha=2.0) == (0, 256)          # first-generation semantics
+    assert sizes(non_causal=1) == (0, 256)
+    assert sizes(path=1) == (0, 256)             # CUDA-core kernels asked for explicitly
+    # a support buffer that is too small is refused before any launch
+    sh = _lib.AttnShape(B=2, Hq=4, Hkv=2, N=4096, D=128, dtype=2, niter=1, varlen_is_i64=0, path=0)
+    a = 0x1000
+    before = lib.adasplash_launch_count()
+    rc = lib.adasplash2_solve(a, a, None, a, a, ctypes.byref(sh), a, 256, a, 1024, None)
+    assert rc == 3 and b"support buffer too small" in lib.adasplash_last_error_string()
+    args = [a] * 5 + [None] + [a] * 7
+    rc = lib.adasplash2_bwd(*args, ctypes.byref(sh), a, 256, a, sup, None)
+    assert rc == 3 and b"workspace" in lib.adasplash_last_error_string()
+    assert lib.adasplash_launch_count() == before
