@@ -55,6 +55,24 @@ __device__ __forceinline__ uint4 pack8(const float2* f) {
 }
 __device__ __forceinline__ float2 splat(float x) { return make_float2(x, x); }
 
+// The four row groups of a warp work in lockstep on one row each, as long as the longest of the
+// four supports; so each group takes its eight rows in the order of their entry counts, and rows
+// of similar length meet.  Returns this lane's row's rank inside its group (0 = most entries).
+__device__ __forceinline__ int rank_in_group(uint32_t cnt, int lane) {
+  int rank = 0;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const uint32_t cj = __shfl_sync(0xffffffffu, cnt, (lane & ~7) + j);
+    rank += (cj > cnt || (cj == cnt && j < (lane & 7))) ? 1 : 0;
+  }
+  return rank;
+}
+// The row (0..31) of group `grp` whose rank is `i`.
+__device__ __forceinline__ int row_of_rank(int my_rank, int i, int grp) {
+  const uint32_t sel = __ballot_sync(0xffffffffu, my_rank == i);
+  return grp * 8 + __ffs((sel >> (grp * 8)) & 0xffu) - 1;
+}
+
 // One warp per 32 consecutive query rows of a head, eight lanes per row: lane gl of a group owns
 // the 16-byte chunks gl and (CH = 2, head dim 128) 8 + gl of the head dimension, so a V row is
 // one or two coalesced 128-byte requests per group and every instruction of the accumulation
@@ -79,9 +97,10 @@ __global__ void __launch_bounds__(kRowThreads) fwd_rows_kernel(RowsParams p) {
   // rows at or beyond the sequence length have no entries (the solver wrote nothing for them)
   const uint2 rw = (r0 + lane < len) ? p.sv.rows[row_base + r0 + lane] : make_uint2(0u, 0u);
   const T* vb = (const T*)p.v + (size_t)(b * p.Hkv + kvh) * p.N * p.Dg + gl * 8;
+  const int my_rank = rank_in_group(rw.y, lane);
 #pragma unroll 1
   for (int i = 0; i < 8; ++i) {
-    const int rr = grp * 8 + i;  // this group's row inside the chunk
+    const int rr = row_of_rank(my_rank, i, grp);  // this group's row inside the chunk
     const uint32_t first = __shfl_sync(0xffffffffu, rw.x, rr), cnt = __shfl_sync(0xffffffffu, rw.y, rr);
     const uint32_t cnt_max = __reduce_max_sync(0xffffffffu, cnt);
     float2 ao[CH * 4], ao2[CH * 4];
@@ -206,6 +225,8 @@ __global__ void __launch_bounds__(kBwdRowThreads) bwd_rows_kernel(BwdParams p) {
   const size_t kv_base = (size_t)(b * p.Hkv + kvh) * p.N * p.Dg + gl * 8;
   const T* kb_ = (const T*)p.k + kv_base;
   const T* vb = (const T*)p.v + kv_base;
+  // (taking the rows in the order of their entry counts, as the forward gather does, made this
+  // kernel slower: 1.39 against 1.28 ms on the headline workload)
 #pragma unroll 1
   for (int i = 0; i < 8; ++i) {
     const int rr = grp * 8 + i, row = r0 + rr;
@@ -329,12 +350,12 @@ __global__ void __launch_bounds__(kBwdRowThreads) bwd_rows_kernel(BwdParams p) {
   __syncthreads();
   for (uint32_t t = threadIdx.x; t < total; t += kBwdRowThreads) p.sv.by_key[run0 + t] = sb[t];
   if (threadIdx.x == 0) p.sv.blocks[(size_t)bh * blocks + blk] = make_uint2(run0, total);
-  // where each 64-key block starts in the sorted run: the key kernel reads its bounds from this
+  // where each 32-key block starts in the sorted run: the key kernel reads its bounds from this
   // table instead of searching the run in global memory
-  const int nkb1 = (p.N + 63) / 64 + 1;
+  const int nkb1 = (p.N + sup::kTableKeys - 1) / sup::kTableKeys + 1;
   uint16_t* tab = p.sv.kb_off + ((size_t)bh * blocks + blk) * nkb1;
   for (int kbi = threadIdx.x; kbi < nkb1; kbi += kBwdRowThreads) {
-    const uint32_t key = (uint32_t)(kbi * 64) << 8;
+    const uint32_t key = (uint32_t)(kbi * sup::kTableKeys) << 8;
     uint32_t a = 0, z = total;
     while (a < z) { const uint32_t m = (a + z) >> 1; if (sb[m].x < key) a = m + 1; else z = m; }
     tab[kbi] = (uint16_t)a;
@@ -344,22 +365,22 @@ __global__ void __launch_bounds__(kBwdRowThreads) bwd_rows_kernel(BwdParams p) {
 // ---------------------------------------------------------------------------
 // Backward, by keys: dK, dV of 64 keys per CTA.
 // ---------------------------------------------------------------------------
-// Sixteen warps; warp w owns keys 4w .. 4w+3 of the block, eight lanes per key, each lane D/8
+// Eight warps; warp w owns keys 4w .. 4w+3 of the CTA's 32, eight lanes per key, each lane D/8
 // elements of that key's dK and dV in registers.  For each query head of the group and each
-// 256-row block from the diagonal on, a thread reads where the block's entries of these 64 keys
+// 256-row block from the diagonal on, a thread reads where the block's entries of these 32 keys
 // lie in the block's sorted run (the row kernel left a table); the warps copy those segments to
 // shared memory at the offsets a
 // block-wide scan gives them -- the order (head, row block, key, row) is fixed -- and the staged
 // entries are regrouped by key with a stable counting sort.  The eight lanes of a key then run
 // through the key's range four entries at a time (the Q / dO rows of all four requested before
 // the first is used) and add P^T dO_i and dS^T Q_i.  No atomics: every sum has a fixed order.
-constexpr int kKeyThreads = 512;
+constexpr int kKeyThreads = 256;
 constexpr int kKeyWarps = kKeyThreads / 32;
-constexpr int kKeysPerCta = 64;
-constexpr int kStage = 2048;  // entries staged per round
+constexpr int kKeysPerCta = sup::kTableKeys;  // 32: two CTAs fit an SM, and one's serial phases overlap the other's walk
+constexpr int kStage = 1024;  // entries staged per round
 
 template <typename T, int D>
-__global__ void __launch_bounds__(kKeyThreads, 1) bwd_keys_kernel(BwdParams p) {
+__global__ void __launch_bounds__(kKeyThreads, 2) bwd_keys_kernel(BwdParams p) {
   constexpr int CH = D / 64;  // 16-byte loads per lane and row
   __shared__ uint2 s_ent[kStage];       // ((absolute row << 6) | key inside the block, P^T | dS^T << 16)
   __shared__ uint2 s_srt[kStage];       // the same, regrouped by key
@@ -459,11 +480,10 @@ __global__ void __launch_bounds__(kKeyThreads, 1) bwd_keys_kernel(BwdParams p) {
             const uint32_t e = c * 32 + lane;
             if (e < m) held[i] = s_ent[e];
             const bool live = held[i].y != 0u;
-            const uint32_t ek = live ? (held[i].x & 63u) : (64u + (uint32_t)lane);  // dead lanes match nobody
+            const uint32_t ek = live ? (held[i].x & 63u) : (64u + (uint32_t)lane);  // dead lanes match nobody (keys are < 32)
             const uint32_t same = __match_any_sync(0xffffffffu, ek);
             ranks[i] = __popc(same & ((1u << lane) - 1u));
             s_ccnt[c * kKeysPerCta + lane] = 0;
-            s_ccnt[c * kKeysPerCta + 32 + lane] = 0;
             __syncwarp();
             if (live && ranks[i] == 0u) s_ccnt[c * kKeysPerCta + ek] = (uint16_t)__popc(same);
           }
@@ -480,15 +500,15 @@ __global__ void __launch_bounds__(kKeyThreads, 1) bwd_keys_kernel(BwdParams p) {
         }
         __syncthreads();
         if (warp == 0) {
-          const uint32_t c0_ = s_kcnt[2 * lane], c1_ = s_kcnt[2 * lane + 1];
-          uint32_t incl2 = c0_ + c1_;
+          static_assert(kKeysPerCta == 32, "one key counter per lane");
+          const uint32_t cmine = s_kcnt[lane];
+          uint32_t incl2 = cmine;
 #pragma unroll
           for (int o = 1; o < 32; o <<= 1) {
             const uint32_t up = __shfl_up_sync(0xffffffffu, incl2, o);
             if (lane >= o) incl2 += up;
           }
-          const uint32_t ex = incl2 - c0_ - c1_;
-          s_kpos[2 * lane] = ex; s_kpos[2 * lane + 1] = ex + c0_;
+          s_kpos[lane] = incl2 - cmine;
           if (lane == 31) s_kpos[kKeysPerCta] = incl2;
         }
         __syncthreads();

@@ -17,7 +17,7 @@
 // The backward needs the same pairs by key as well (dK_j and dV_j sum over the rows that
 // attend to key j).  Its row kernel leaves, for every 256-row block (the rows of one solver CTA),
 // the block's entries sorted by (key, row) -- in the same slots of a second array -- and the key
-// kernel finds the entries of its 64 keys in each block by binary search: no atomics, and a
+// kernel finds the entries of its keys in each block through a table the row kernel leaves beside the run: no atomics, and a
 // fixed summation order.
 //
 // The support buffer lives from the solve to the backward (it is saved with the forward's
@@ -34,8 +34,9 @@
 //   by_key   uint2 [cap]: (key << 8 | row inside its 256-row block, P^T | dS^T << 16 as 16-bit
 //            values), each block's run sorted ascending; written by the backward
 //   blocks   uint2 [B*Hq*ceil(N/256)]: (first entry of the block's run, its length)
-//   kb_off   uint16 [B*Hq*ceil(N/256)][ceil(N/64)+1]: where the entries of each 64-key block
-//            start inside a row block's sorted run (the last one: the run's length)
+//   kb_off   uint16 [B*Hq*ceil(N/256)][ceil(N/32)+1]: where the entries of each 32-key block
+//            (the keys of one CTA of the key kernel) start inside a row block's sorted run (the
+//            last one: the run's length)
 #pragma once
 #include <cstddef>
 #include <cstdint>
@@ -48,6 +49,7 @@ namespace sup {
 constexpr int kEntriesPerRow = 32;  // capacity of the entry arrays, per query row of the problem
 constexpr int kBlockRows = 256;     // rows whose entries the backward sorts together: one solver CTA
 constexpr int kBlockCap = 8192;     // most entries such a block may hold (the solver checks)
+constexpr int kTableKeys = 32;      // keys per entry of the key-block table = keys per CTA of the key kernel
 
 // why a solver CTA did not export (counters in words 4..7 of the buffer)
 enum : int {
@@ -79,7 +81,7 @@ inline size_t bytes(int B, int Hq, int Hkv, int N) {
 inline size_t scratch_bytes(int B, int Hq, int Hkv, int N) {
   const size_t rows = (size_t)B * Hq * N;
   const size_t blocks = (size_t)B * Hq * ((N + kBlockRows - 1) / kBlockRows);
-  const size_t nkb1 = (size_t)(N + 63) / 64 + 1;
+  const size_t nkb1 = (size_t)(N + kTableKeys - 1) / kTableKeys + 1;
   return align256(rows * kEntriesPerRow * 8) + align256(blocks * 8) + align256(blocks * nkb1 * 2);
 }
 

@@ -82,7 +82,7 @@ def test_support_and_workspace_sizes_without_gpu():
     assert sup == 256 + 256 + rows * 8 + rows * 32 * 8
     # status word + the backward's sorted copy, run table (16 blocks of 256 rows per head) and key-block table
     blocks = 2 * 4 * 16
-    assert ws == 256 + rows * 32 * 8 + blocks * 8 + ((blocks * 65 * 2 + 255) // 256) * 256
+    assert ws == 256 + rows * 32 * 8 + blocks * 8 + ((blocks * 129 * 2 + 255) // 256) * 256   # 4096 / 32 + 1 table entries per block
     assert sizes(dtype=0) == (0, 256)            # fp32: CUDA-core kernels
     assert sizes(D=32) == (0, 256)               # head dim without a gather route
     assert sizes(N=131072) == (0, 256)           # key indices would not fit 16 bits
