@@ -58,11 +58,7 @@ constexpr uint32_t kSolveQCol = 384;
 constexpr int kSolveBufs = 3;
 constexpr int kSolveRows = 2 * kBlockM;  // query rows per CTA
 
-enum SweepMode : int { kModeMax = 0, kModeHist = 1, kModeHalley = 2, kModeFinal = 3, kModeCollect = 4, kModeFinalCollect = 5 };
-
-// A final sweep that also gathers the rows' supports takes scores from at most this far below the
-// tau entering it (see there).
-constexpr float kFinalCollectMargin = 1.0f / 32.0f;
+enum SweepMode : int { kModeMax = 0, kModeHist = 1, kModeHalley = 2, kModeFinal = 3, kModeCollect = 4, kModeRecollect = 5 };
 
 // One entry of the candidate pool: a score >= tau0 of some row, its key index (sequences of more
 // than 65536 keys: only the 64-key block it sits in), and the previous entry of the same
@@ -122,7 +118,8 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
   int* start_status = (int*)(smem + L::misc_off + 8);
   int* pool_used = (int*)(smem + L::misc_off + 32);   // [16]: entries used in each row warp's region
   volatile int* pool_ovf = (volatile int*)(smem + L::misc_off + 16);
-  volatile int* fin_bad = (volatile int*)(smem + L::misc_off + 20);  // the final sweep could not gather the supports
+  volatile int* pool_ovf2 = (volatile int*)(smem + L::misc_off + 20);  // ... and so did the lists of the third sweep
+  int* pool_common = (int*)(smem + L::misc_off + 24);  // third sweep: entries used (one counter for the CTA)
   float* xchg = (float*)(smem + L::xchg_off);
   uint32_t* s_bits = (uint32_t*)(smem + L::bits_off);
   Cand* pool = (Cand*)sQ;  // the Q tiles are dead once Q~ is in TMEM (before the first append)
@@ -149,6 +146,11 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
   // all if the candidate pool overflows (then the Halley .. final steps sweep S as well)
   const int total_first = p.tau_given ? T_k : 2 * T_k;
   const int total_full = nsweeps * T_k;
+  // AdaSplash-2 solver: a CTA whose pool overflowed in sweep 2 sweeps once more for the scores
+  // above the histogram's lower bound (see the row warps) before it resorts to full sweeps
+  // -- when the rows' supports are wanted: the lists are what they are exported from.  (Without
+  // that the third sweep is no gain: its appends cost what the sweep it saves would have.)
+  const bool third_sweep = !V1 && !p.tau_given && p.sup_on && p.N <= 65536;
   // Products are numbered in issue order (per K tile: A if it has one, then B); product n uses
   // S buffer n % 3 for the (n / 3)-th time.
   const int prods_per_sweep = b_on ? T_a + T_k : T_a;   // causal: T_k = T_a + 1
@@ -161,7 +163,7 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
     *cta_abort = 0;
     for (int w = 0; w < 16; ++w) pool_used[w] = 0;
     *pool_ovf = 0;
-    *fin_bad = 0;
+    *pool_ovf2 = 0;
   }
   if (warp == 17) {
     if (lane == 0) {
@@ -204,10 +206,11 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
       for (int i = 0; !ptx::c_withhold_loads; ++i) {
         if (i == total) {
           // the first sweeps are through: stream S again only if the row warps ask for it
-          if (total == total_full) break;
-          if (!ptx::mbar_wait(decide, 0)) { raise_abort(cta_abort, p.status, kStTimeoutProducer); break; }
-          if (!*pool_ovf) break;
-          total = total_full;
+          if (total == total_full + (third_sweep ? T_k : 0)) break;
+          const bool second = total > total_first;  // the decision after the third sweep
+          if (!ptx::mbar_wait(decide, second ? 1 : 0)) { raise_abort(cta_abort, p.status, kStTimeoutProducer); break; }
+          if (!(second ? *pool_ovf2 : *pool_ovf)) break;
+          total = (third_sweep && !second) ? total_first + T_k : total_full + (third_sweep ? T_k : 0);
         }
         if (*cta_abort) break;
         if (!ptx::mbar_wait(k_empty + st, use_par ^ 1)) {
@@ -237,10 +240,11 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
       uint32_t k_par = 0, buf_par = 0;
       for (int i = 0; ok; ++i) {
         if (i == total) {
-          if (total == total_full) break;
-          if (!ptx::mbar_wait(decide, 0)) { raise_abort(cta_abort, p.status, kStTimeoutMma); break; }
-          if (!*pool_ovf) break;
-          total = total_full;
+          if (total == total_full + (third_sweep ? T_k : 0)) break;
+          const bool second = total > total_first;
+          if (!ptx::mbar_wait(decide, second ? 1 : 0)) { raise_abort(cta_abort, p.status, kStTimeoutMma); break; }
+          if (!(second ? *pool_ovf2 : *pool_ovf)) break;
+          total = (third_sweep && !second) ? total_first + T_k : total_full + (third_sweep ? T_k : 0);
         }
         if (*cta_abort) break;
         if (!ptx::mbar_wait(k_full + st, k_par)) { raise_abort(cta_abort, p.status, kStTimeoutMma); break; }
@@ -421,35 +425,32 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
                 }
               }
             }
-          } else if (mode == kModeFinalCollect) {
-            // The final sweep of a CTA whose candidate pool overflowed, when the rows' supports
-            // are wanted: the pool is free again, and the few scores above (a hair below) the tau
-            // entering this sweep go into it.  The step that follows cannot take tau below the
-            // lower end of its bracket (less the step's own tolerance), so scores above that are
-            // gathered, but from no further than kFinalCollectMargin below tau (a wide bracket
-            // would bring in too many): the support after the step is among them unless the step
-            // falls further, which the CTA checks afterwards.
-            const float thr_c = fmaxf(fminf(thr, hs.lo) - 2e-5f, thr - kFinalCollectMargin);
+          } else if (mode == kModeRecollect) {
+            // Third sweep of a CTA whose pool overflowed in the second: the histogram has given
+            // every row the lower end of its bracket, which no later tau undercuts (by more than
+            // the step's tolerance), and the scores above that are few -- the support and a
+            // little more -- where the scores within 1 of the maximum were too many.
+            const float thr_c = hs.lo - 2e-5f;
 #pragma unroll
             for (int g4 = 0; g4 < 8; ++g4) {
               const float cm = fmaxf(ptx::fmax3(v[g4 * 4], v[g4 * 4 + 1], v[g4 * 4 + 2]), v[g4 * 4 + 3]);
-              if (cm > thr_c) {
+              if (cm >= thr_c) {
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
                   const float z = v[g4 * 4 + c];
-                  const float d = z - thr;
-                  if (d > 0.f) { a0 = fmaf(d, d, a0); a1 += d; a2 += 1.f; }
-                  if (z > thr_c && row_ok) {
-                    const int idx = atomicAdd(pool_used + warp, 1);
-                    if (idx < warp_pool) {
-                      const int slot = warp * warp_pool + idx;
+                  if (z >= thr_c && row_ok) {
+                    // one counter for the CTA: the whole pool is open to whichever rows need it
+                    // (per-warp shares with a common overflow area measured no faster)
+                    const int j = atomicAdd(pool_common, 1);
+                    const int slot = j < 16 * warp_pool ? j : -1;
+                    if (slot >= 0) {
                       Cand e;
                       e.z = z; e.next = head;
                       e.key = (uint16_t)(keybase + ((g4 * 4 + c) & kmask));
                       pool[slot] = e;
                       head = (uint16_t)slot;
                     } else {
-                      *fin_bad = 1;
+                      *pool_ovf2 = 1;
                     }
                   }
                 }
@@ -483,7 +484,7 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
 #pragma unroll
           for (int bb = 0; bb < 8; ++bb) cnt[bb] += (int)((packed >> (8 * bb)) & 0xffull);
         }
-        if (mode == kModeFinal || mode == kModeFinalCollect) {
+        if (mode == kModeFinal) {
           // this warp covers 32 rows x 64 keys of the 64x64 sub-tile (row block rb, key block 2kt+half)
           const bool any = __any_sync(0xffffffffu, (a2 > a2_mark) && row_ok);
           if (lane == 0 && any) {
@@ -544,7 +545,7 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
     };
 
     bool full_sweeps = false;  // the candidate pool overflowed: every step sweeps S
-    bool fin_collect = false;  // ... and the final sweep gathers the rows' supports into the pool
+    bool recollected = false;  // the lists are those of the third sweep: anywhere in the pool, not compacted
     if (p.tau_given) {
       // bitmap for a given tau: one sweep over S
       if (grp_on) {
@@ -588,12 +589,18 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
       ptx::bar_sync(3, kSolveRowThreads);
       full_sweeps = *pool_ovf != 0;
       ptx::mbar_arrive_warp(decide);
-      // supports wanted and the lists gone: the final sweep gathers them into the pool afresh
-      fin_collect = !V1 && full_sweeps && p.sup_on && !wide;
-      if (fin_collect) {
-        if (threadIdx.x < 16) pool_used[threadIdx.x] = 0;
+      if (third_sweep && full_sweeps) {
+        // ---- the lists of scores within 1 of the maximum did not fit: lists of the scores above
+        // the histogram's lower bound, from one more sweep ----
+        if (threadIdx.x == 0) *pool_common = 0;
         head = kCandNil;
+        ncand = 0;
         ptx::bar_sync(3, kSolveRowThreads);
+        if (grp_on) sweep_tiles(std::integral_constant<int, kModeRecollect>{});
+        ptx::bar_sync(3, kSolveRowThreads);
+        full_sweeps = *pool_ovf2 != 0;
+        ptx::mbar_arrive_warp(decide);
+        recollected = true;
       }
       if (grp_on && !full_sweeps) {
         // ---- Halley steps and the final step on this thread's list ----
@@ -607,7 +614,7 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
           if (lane >= o) incl += up;
         }
         const int used = min(pool_used[warp], warp_pool);
-        compact = used + __shfl_sync(0xffffffffu, incl, 31) <= warp_pool;
+        compact = !recollected && used + __shfl_sync(0xffffffffu, incl, 31) <= warp_pool;
         run0 = warp * warp_pool + used + incl - ncand;
         if (compact) {
           int dst = run0;
@@ -652,7 +659,7 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
           if (compact) {
             for (int k = 0; k < ncand; ++k) visit(pool[run0 + k]);
           } else {
-            for (int e = head, left = warp_pool; e != kCandNil && left > 0; --left) {
+            for (int e = head, left = recollected ? 16 * warp_pool : warp_pool; e != kCandNil && left > 0; --left) {
               const Cand c = pool[e];
               visit(c);
               e = c.next;
@@ -665,12 +672,8 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
         for (int sw = 2; sw < nsweeps; ++sw) {
           reset_stats();
           if (sw == nsweeps - 1) {
-            const float gathered_from = fmaxf(fminf(hs.t, hs.lo) - 2e-5f, hs.t - kFinalCollectMargin);
-            if (fin_collect) sweep_tiles(std::integral_constant<int, kModeFinalCollect>{});
-            else sweep_tiles(std::integral_constant<int, kModeFinal>{});
+            sweep_tiles(std::integral_constant<int, kModeFinal>{});
             exchange(kModeFinal);
-            // the last step went below what was gathered: no export for this CTA
-            if (fin_collect && row_ok && hs.t <= gathered_from) *fin_bad = 2;
           } else {
             sweep_tiles(std::integral_constant<int, kModeHalley>{});
             exchange(kModeHalley);
@@ -693,8 +696,8 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
       // Entry = (key, u = z - tau > 0) for every listed score above the final tau whose 64x64
       // tile is in the block mask just built (what the tile kernels would visit); one run per
       // row: the keys of the row's first thread (low halves of the key tiles), then the second's.
-      // the same for every thread of the CTA: the lists held (or the final sweep gathered anew)
-      const bool can = (!full_sweeps || (!V1 && !*fin_bad)) && !wide && !*cta_abort;
+      // the same for every thread of the CTA: its lists held (those of the second or of the third sweep)
+      const bool can = !full_sweeps && !wide && !*cta_abort;
       int* cnts = reinterpret_cast<int*>(xchg) + grp * (2 * 8 * 128);
       int* extra = reinterpret_cast<int*>(xchg) + 128;        // [0..7] entries of each 32-row quarter, [8] base (beside the counts)
       const uint32_t* my_bits = s_bits + (grp * 2 + rb) * p.n_words;
@@ -707,7 +710,7 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
         if (compact) {
           for (int k = 0; k < ncand; ++k) f(pool[run0 + k]);
         } else {
-          for (int e = head, left = warp_pool; e != kCandNil && left > 0; --left) {
+          for (int e = head, left = recollected ? 16 * warp_pool : warp_pool; e != kCandNil && left > 0; --left) {
             const Cand c = pool[e];
             f(c);
             e = c.next;
@@ -745,8 +748,6 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
           if (base > p.sup.cap || (uint32_t)total > p.sup.cap - base) { base = 0xffffffffu; why = sup::kWhyFull; }
         } else if (can) {
           why = sup::kWhyBlock;
-        } else if (full_sweeps && *fin_bad == 2) {
-          why = sup::kWhyTau;
         }
         if (base == 0xffffffffu) {
           atomicAdd(p.sup.dense + b * p.Hkv + kvh, 1);

@@ -10,8 +10,8 @@
 // query instead of dense tiles (csrc/sparse_rows.cu).
 //
 // The choice between the two routes is made per (batch, kv head): a solver CTA that cannot
-// export (its candidate pool overflowed and it fell back to sweeping S, or the entry array is
-// full) bumps the head's `dense` counter; the tile kernels of a head return at once while the
+// export (its candidate pool overflowed twice and it fell back to sweeping S, or the entry array
+// is full) bumps the head's `dense` counter; the tile kernels of a head return at once while the
 // counter is zero, the gather kernels while it is not.
 //
 // The backward needs the same pairs by key as well (dK_j and dV_j sum over the rows that
@@ -53,8 +53,8 @@ constexpr int kTableKeys = 32;      // keys per entry of the key-block table = k
 
 // why a solver CTA did not export (counters in words 4..7 of the buffer)
 enum : int {
-  kWhyPool = 0,   // its candidate pool overflowed, in the final sweep as well (or a wait gave up)
-  kWhyTau = 1,    // the last step took tau below the scores the final sweep had gathered
+  kWhyPool = 0,   // its candidate pool overflowed, in the third sweep as well (or a wait gave up)
+  kWhyUnused = 1,
   kWhyBlock = 2,  // more than kBlockCap entries in its 256 rows
   kWhyFull = 3,   // the entry array is full
 };

@@ -405,8 +405,7 @@ def route_record(att, q, k, v, do, varlen, niter, reps):
     return {"kv_heads": B * Hkv, "kv_heads_on_gather_kernels": sparse_heads,
             "support_entries_per_row": round(entries / max(1, rows), 2),
             # solver CTAs (256 rows each) that could not export, by reason
-            "ctas_without_export": {"pool_overflow": why[0], "tau_fell_below_gathered": why[1],
-                                    "rows_too_dense": why[2], "entry_array_full": why[3]},
+            "ctas_without_export": {"pool_overflow": why[0], "rows_too_dense": why[2], "entry_array_full": why[3]},
             "call_ms": {n: round(x, 3) for n, x in ms.items()}}
 
 
