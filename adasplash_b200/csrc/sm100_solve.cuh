@@ -31,13 +31,17 @@
 // histogram covers [tau0, tau0 + 1], and tau never falls below tau0 (the largest
 // probability (z_max - tau)^2 is at most 1).  Those scores are a tiny part of a
 // row, so the kernel computes S twice, not (3 + niter) times: sweep 1 finds the
-// row maxima; sweep 2 appends every score >= tau0 (value and 64-key block index)
+// row maxima; sweep 2 appends every score >= tau0 (value and key index)
 // to a per-thread list in a shared-memory pool; the histogram, the Halley steps
 // and the final bitmap + step run on the lists.  The counts and bitmap bits are
 // the same integers either way; the Halley sums add the same terms in list order.
 // If the pool fills up (rows whose scores are nearly flat), sweep 2 goes on as a
 // plain histogram sweep for the scores that find no room, and the CTA sweeps S
-// for the remaining steps as well -- what the solve cost without lists.
+// for the remaining steps as well -- what the solve cost without lists.  When the
+// caller wants the rows' supports (support.cuh), such a CTA first tries a third
+// sweep that lists the scores above the histogram's lower bound -- far fewer --
+// and runs its steps on those lists; the tail of the kernel exports the supports
+// from whichever lists it ended up with.
 // (One sweep with a running maximum does not work: the maximum of a row grows so
 // slowly that three times as many scores pass "within 1 of the maximum so far"
 // as are within 1 of the final one.)
