@@ -152,9 +152,10 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
   const int total_full = nsweeps * T_k;
   // AdaSplash-2 solver: a CTA whose pool overflowed in sweep 2 sweeps once more for the scores
   // above the histogram's lower bound (see the row warps) before it resorts to full sweeps
-  // -- when the rows' supports are wanted: the lists are what they are exported from.  (Without
-  // that the third sweep is no gain: its appends cost what the sweep it saves would have.)
-  const bool third_sweep = !V1 && !p.tau_given && p.sup_on && p.N <= 65536;
+  // -- when the rows' supports are wanted (the lists are what they are exported from) or when
+  // it saves at least two sweeps.  (With niter = 1 and no export it is no gain: its appends cost
+  // what the one sweep it saves would have.)
+  const bool third_sweep = !V1 && !p.tau_given && (p.sup_on || p.niter >= 2);
   // Products are numbered in issue order (per K tile: A if it has one, then B); product n uses
   // S buffer n % 3 for the (n / 3)-th time.
   const int prods_per_sweep = b_on ? T_a + T_k : T_a;   // causal: T_k = T_a + 1
