@@ -23,9 +23,15 @@ class _SparseAttentionV1(torch.autograd.Function):
         att._check_inputs(q, k, v, varlen, require_pow2=False, min_len=1)   # the v1 kernels take any length
         assert k.shape[1] == q.shape[1], "adasplash_v1 does not support grouped-query attention"
         assert 1.0 < alpha <= 2.0, f"alpha must be in (1, 2]; got {alpha}"
-        taus, bmask = att.solve(q, k, niter, varlen, None, alpha, is_causal)
-        out, out2 = att.forward_raw(q, k, v, taus, bmask, varlen, None, alpha, is_causal)
+        support = None
+        if q.shape[2] >= att.ROW_SUPPORTS_MIN_N:
+            # rows' supports from the solver: sparse heads run as gathers (see attention.py)
+            with torch.cuda.device(q.device):
+                support = att.support_buffer(att.make_shape(q, k, niter, varlen, None, alpha, is_causal), q.device)
+        taus, bmask = att.solve(q, k, niter, varlen, None, alpha, is_causal, support=support)
+        out, out2 = att.forward_raw(q, k, v, taus, bmask, varlen, None, alpha, is_causal, support=support)
         ctx.save_for_backward(q, k, v, out2, taus, bmask)
+        ctx.support = support
         ctx.args = (alpha, is_causal, varlen, niter)
         return out
 
@@ -37,7 +43,7 @@ class _SparseAttentionV1(torch.autograd.Function):
         if do.dtype != q.dtype:
             do = do.to(q.dtype)
         dq, dk, dv, _, _ = att.backward_raw(q, k, v, do, out2, taus, bmask, varlen, niter,
-                                            alpha=alpha, is_causal=is_causal)
+                                            alpha=alpha, is_causal=is_causal, support=ctx.support)
         return dq, dk, dv, None, None, None, None
 
 

@@ -23,6 +23,7 @@ struct RowsParams {
   const void* v; void* out; void* out2;
   const void* varlen; int varlen_is_i64;
   int B, Hq, Hkv, N, Dg;
+  float alpha;   // 1.5 (AdaSplash-2 and first-generation calls), 2 or any value in (1, 2)
   sup::View sv;
 };
 
@@ -97,6 +98,7 @@ __global__ void __launch_bounds__(kRowThreads) fwd_rows_kernel(RowsParams p) {
   // rows at or beyond the sequence length have no entries (the solver wrote nothing for them)
   const uint2 rw = (r0 + lane < len) ? p.sv.rows[row_base + r0 + lane] : make_uint2(0u, 0u);
   const T* vb = (const T*)p.v + (size_t)(b * p.Hkv + kvh) * p.N * p.Dg + gl * 8;
+  const simt::Powers powers(p.alpha);
   const int my_rank = rank_in_group(rw.y, lane);
 #pragma unroll 1
   for (int i = 0; i < 8; ++i) {
@@ -126,8 +128,10 @@ __global__ void __launch_bounds__(kRowThreads) fwd_rows_kernel(RowsParams p) {
         }
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          const float2 pw = splat(round_to<T>(u[j] * u[j])), uw = splat(round_to<T>(u[j]));
-          supp += u[j];
+          // p = u^(1/(alpha-1)) and the Jacobian weight g = u^(1/(alpha-1)-1): u^2 and u for alpha = 1.5
+          const float gj = powers.g(u[j]);
+          const float2 pw = splat(round_to<T>(powers.p(u[j]))), uw = splat(round_to<T>(gj));
+          supp += gj;
 #pragma unroll
           for (int c = 0; c < CH; ++c) {
             float2 vf[4];
@@ -162,6 +166,7 @@ int fwd_t(const simt::Params& p, cudaStream_t st) {
   rp.v = p.v; rp.out = p.out; rp.out2 = p.out2;
   rp.varlen = p.varlen; rp.varlen_is_i64 = p.varlen_is_i64;
   rp.B = p.B; rp.Hq = p.Hq; rp.Hkv = p.Hkv; rp.N = p.N; rp.Dg = p.D;
+  rp.alpha = p.alpha;
   rp.sv = sup::view(p.support, nullptr, p.B, p.Hq, p.Hkv, p.N);
   const long long warps = (long long)p.B * p.Hq * ((p.N + kRowsPerWarp - 1) / kRowsPerWarp);
   const unsigned grid = (unsigned)((warps + kRowThreads / 32 - 1) / (kRowThreads / 32));
@@ -180,7 +185,9 @@ struct BwdParams {
   const void* varlen; int varlen_is_i64;
   int B, Hq, Hkv, N, Dg;
   float sm_scale;   // fp32(1/sqrt(D))
-  float zscale;     // fp32(0.5 * sm_scale): z = zscale * q.k
+  float zscale;     // fp32((alpha-1) * sm_scale): z = zscale * q.k
+  float alpha;
+  int causal;       // 0 = full attention (first-generation semantics only)
   sup::View sv;
 };
 
@@ -193,9 +200,10 @@ __device__ __forceinline__ float group_sum8(float x) {  // over the eight lanes 
 
 // The arithmetic of the tile kernels (adasplash_v2.py:943-1234), pair by pair:
 //   dP = dO_i . V_j;  delta_i = out2_i . dO_i;
-//   query side:  dS = rn(u (dP - delta)) with the solver's u;  dQ_i = sm_scale * sum_j dS K_j;
-//   key side, which the reference computes from K~ = rn(k * 0.5/sqrt(D)) and the raw q:
-//     u' = K~_j . q_i - tau_i;  P^T = rn(u'^2), dS^T = rn(u' (dP - delta)) where u' > 0.
+//   query side:  dS = rn(g(u) (dP - delta)) with the solver's u;  dQ_i = sm_scale * sum_j dS K_j;
+//   key side, which the reference computes from K~ = rn(k * (alpha-1)/sqrt(D)) and the raw q:
+//     u' = K~_j . q_i - tau_i;  P^T = rn(p(u')), dS^T = rn(g(u') (dP - delta)) where u' > 0;
+//   p(u) = u^(1/(alpha-1)), g(u) = u^(1/(alpha-1) - 1): u^2 and u for alpha = 1.5.
 // Same warp layout as the forward gather: 32 rows per warp, eight lanes per row; the eight warps
 // of a CTA take the 256 rows of one solver CTA, whose entries form one contiguous run.  The
 // key-side values go to shared memory at the entry's slot, are sorted there by (key, row) once
@@ -225,6 +233,7 @@ __global__ void __launch_bounds__(kBwdRowThreads) bwd_rows_kernel(BwdParams p) {
   const size_t kv_base = (size_t)(b * p.Hkv + kvh) * p.N * p.Dg + gl * 8;
   const T* kb_ = (const T*)p.k + kv_base;
   const T* vb = (const T*)p.v + kv_base;
+  const simt::Powers powers(p.alpha);
   // (taking the rows in the order of their entry counts, as the forward gather does, made this
   // kernel slower: 1.39 against 1.28 ms on the headline workload)
 #pragma unroll 1
@@ -299,13 +308,13 @@ __global__ void __launch_bounds__(kBwdRowThreads) bwd_rows_kernel(BwdParams p) {
           const float dp = group_sum8(dp2.x + dp2.y);
           const float zk = group_sum8(zk2.x + zk2.y);
           const float dd = dp - delta;
-          const float2 dsq = splat(round_to<T>(u[j] * dd));
+          const float2 dsq = splat(round_to<T>(powers.g(u[j]) * dd));
 #pragma unroll
           for (int e = 0; e < CH * 4; ++e) dq[e] = __ffma2_rn(dsq, kf[e], dq[e]);
           const float uk = zk - tau;
           if (gl == 0 && k0 + hb + j < cnt) {
             const uint32_t slot = first - run0 + k0 + hb + j;
-            const uint32_t vals = uk > 0.f ? pack2f<T>(make_float2(uk * uk, uk * dd)) : 0u;
+            const uint32_t vals = uk > 0.f ? pack2f<T>(make_float2(powers.p(uk), powers.g(uk) * dd)) : 0u;
             if (slot < (uint32_t)sup::kBlockCap) sb[slot] = make_uint2((key[j] << 8) | (uint32_t)(warp * kRowsPerWarp + rr), vals);
           }
         }
@@ -415,7 +424,7 @@ __global__ void __launch_bounds__(kKeyThreads, 2) bwd_keys_kernel(BwdParams p) {
     const T* qh = (const T*)p.q + (size_t)bh * p.N * D + gl * 8;
     const T* gh = (const T*)p.dout + (size_t)bh * p.N * D + gl * 8;
     // causal: rows >= key, so the first row block that can hold these keys is the one of key0
-    for (int c0 = (int)key0 / sup::kBlockRows; c0 < blocks_used; c0 += kKeyThreads) {
+    for (int c0 = p.causal ? (int)key0 / sup::kBlockRows : 0; c0 < blocks_used; c0 += kKeyThreads) {
       const int c = c0 + (int)threadIdx.x;
       uint32_t lo = 0, hi = 0, src0 = 0;
       if (c < blocks_used) {
@@ -585,7 +594,8 @@ int bwd_t(const simt::Params& p, cudaStream_t st) {
   bp.taus = p.taus; bp.dq = p.dq; bp.dk = p.dk; bp.dv = p.dv;
   bp.varlen = p.varlen; bp.varlen_is_i64 = p.varlen_is_i64;
   bp.B = p.B; bp.Hq = p.Hq; bp.Hkv = p.Hkv; bp.N = p.N; bp.Dg = p.D;
-  bp.sm_scale = p.sm_scale; bp.zscale = 0.5f * p.sm_scale;
+  bp.sm_scale = p.sm_scale; bp.zscale = p.zscale;
+  bp.alpha = p.alpha; bp.causal = p.causal;
   bp.sv = sup::view(p.support, p.bwd_scratch, p.B, p.Hq, p.Hkv, p.N);
   static_assert(sup::kBlockRows == (kBwdRowThreads / 32) * kRowsPerWarp, "one CTA per row block");
   const unsigned grid = (unsigned)((long long)p.B * p.Hq * ((p.N + sup::kBlockRows - 1) / sup::kBlockRows));
@@ -614,11 +624,16 @@ int bwd_t(const simt::Params& p, cudaStream_t st) {
 }  // namespace
 
 bool supported(const ads_attn_shape* s) {
-  // 16-bit inputs on the tensor-core solver, causal alpha = 1.5, key indices that fit 16 bits
+  // 16-bit inputs on the tensor-core solver, causal or full attention, head dim 64 or 128, key
+  // indices that fit 16 bits, alpha <= 1.5.  Above 1.5 the Jacobian weight u^(1/(alpha-1) - 1) is
+  // steep or discontinuous at u = 0 (alpha = 2: a step), and the reference's key side decides
+  // "u > 0" from its own product K~ q, which differs from the solver's Q~ k by a rounding of the
+  // operand: pairs within that rounding of the threshold would have to be exported as well.
+  // Such calls stay on the tile kernels, which form both products.
   if (s->dtype != ADS_F16 && s->dtype != ADS_BF16) return false;
   if (s->D != 64 && s->D != 128) return false;
   if (s->N > 65536) return false;
-  if (!((s->alpha == 0.f || s->alpha == 1.5f) && s->non_causal == 0)) return false;
+  if (s->alpha > 1.5f) return false;
   return true;
 }
 
