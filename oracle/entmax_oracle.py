@@ -504,7 +504,7 @@ def transpose_bitmap(words: torch.Tensor) -> torch.Tensor:
 
 
 def v2_attention(q, k, v, niter=1, varlen=None, dout=None, tau_override=None,
-                 bits_override=None):
+                 bits_override=None, key_side_pairs="own"):
     """Operation-level restatement of `adasplash_v2` forward (+ backward).
 
     Forward: `_sparse_attention.forward` (adasplash_v2.py:1243-1438) =
@@ -517,6 +517,12 @@ def v2_attention(q, k, v, niter=1, varlen=None, dout=None, tau_override=None,
     (:943-1079) and `_bwd_kv_kernel` (:1082-1234; K is the pre-scaled, rounded
     operand there, Q is unscaled), dS and P rounded to the input dtype before
     their products, dq/dk scaled by fp32(1/sqrt(D)) and rounded on store.
+
+    `key_side_pairs`: "own" = the reference's `_bwd_kv_kernel`, whose pairs are those with a
+    positive score minus tau under ITS product (K scaled and rounded); "query" = only pairs that
+    are also in the forward's support (Q scaled and rounded) -- what a backward that works from
+    the forward's list of pairs computes.  The two differ in pairs within an operand rounding of
+    the threshold, whose weights are of the size of that rounding.
 
     Returns dict(out, out2, tau, tau_pen, tau0, tau1, bmask[, delta, dq, dk, dv]).
     """
@@ -575,6 +581,8 @@ def v2_attention(q, k, v, niter=1, varlen=None, dout=None, tau_override=None,
                 dq[b, h] = _rn((ds @ kf) * sm, dtype) * rv
                 zt = v2_scaled_scores(q[b, h], k[b, kvh], L, dtype, "k")
                 ut = torch.clamp(zt - t[:, None], min=0.0) * el * rv
+                if key_side_pairs == "query":
+                    ut = ut * (u > 0)
                 qf = q[b, h].to(F32) * rv
                 dv[b, kvh] += _rn(ut * ut, dtype).T @ do
                 dst = _rn(ut * (dp - delta[:, None]), dtype)
