@@ -197,6 +197,9 @@ static int solve_common(const void* q, const void* k, const void* varlen, float*
     }
     if (p.support != nullptr) {
       if (int rc = sparse::clear_header(p, st)) return rc;
+      if (p.alpha > 1.5f) {
+        if (int rc = sparse::key_norms(p, s->dtype, st)) return rc;
+      }
     }
     return is_v2(s) ? sm100::solve(p, s->dtype, ws, ws_bytes, st) : sm100::v1::solve(p, s->dtype, ws, ws_bytes, st);
   }

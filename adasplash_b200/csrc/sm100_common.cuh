@@ -38,6 +38,7 @@ struct TcParams {
   int causal;        // 0 = full attention (first-generation semantics only)
   int tau_given;
   int* status;       // device status word (0 = ok)
+  const void* q_raw; // q in global memory (the kernels read it through TMA; the solver's export reads rows)
   int sup_on;        // the caller gave a row-support buffer (support.cuh)
   sup::View sup;
 };

@@ -60,6 +60,7 @@ TcParams to_tc(const simt::Params& p, void* ws) {
   t.causal = p.causal;
   t.tau_given = p.tau_given;
   t.status = (int*)ws;
+  t.q_raw = p.q;
   t.sup_on = p.support != nullptr;
   if (t.sup_on) t.sup = sup::view(p.support, nullptr, p.B, p.Hq, p.Hkv, p.N);
   return t;

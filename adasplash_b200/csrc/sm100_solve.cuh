@@ -312,6 +312,27 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
     }
     ptx::mbar_arrive_warp(q_ready);
 
+    // Above alpha = 1.5, when the rows' supports are wanted: the backward's key side decides
+    // "score above tau" from its own product (K scaled and rounded, q raw), and the Jacobian
+    // weight does not vanish at the threshold, so pairs within the two products' largest
+    // possible difference below tau are listed and exported as well (with u <= 0: no weight on
+    // the query side).  |Q~ k - q K~| <= 2^-8 zscale |q| |k| for 16-bit operands (unit roundoff
+    // 2^-9 each); the largest key norm of the head comes from a small kernel run before this one.
+    float margin = 0.f;
+    if constexpr (V1) {
+      if (p.sup_on && p.alpha > 1.5f && row_ok && !dead) {
+        const T* qrow = (const T*)p.q_raw + ((size_t)bh * p.N + row) * p.d_true;
+        float qn2 = 0.f;
+        for (int d0 = 0; d0 < p.d_true; d0 += 8) {
+          const uint4 raw8 = *reinterpret_cast<const uint4*>(qrow + d0);
+          const T* e8 = reinterpret_cast<const T*>(&raw8);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) { const float x = DT<T>::to_f(e8[j]); qn2 = fmaf(x, x, qn2); }
+        }
+        margin = 0.00390625f * p.zscale * sqrtf(qn2 * p.sup.kmax2[b * p.Hkv + kvh]) + 1e-5f;
+      }
+    }
+
     float mx = -1.0e3f, tau0 = 0.f;
     int cnt[8];
     HalleyState hs;
@@ -356,7 +377,7 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
         // Collecting takes scores from a hair below tau0: a Halley step may land up to 1e-5
         // below its bracket, and a sweep over S would then see those scores too.  The
         // histogram over the list tests each score against tau0 itself.
-        const float thr = mode == kModeCollect ? tau0 - 2e-5f : ((V1 && mode == kModeFinal) ? hs.lo : hs.t);
+        const float thr = mode == kModeCollect ? tau0 - 2e-5f - margin : ((V1 && mode == kModeFinal) ? hs.lo : hs.t);
         // (Register budget: the kernel keeps nearly all of the SM's shared memory, which leaves
         // almost no L1 for local memory -- a spill in this loop costs an L2 round trip.)
 #pragma unroll 1
@@ -698,9 +719,14 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
     }
     if (p.sup_on && !p.tau_given) {
       // ---- the rows' supports, for the gather kernels ----
-      // Entry = (key, u = z - tau > 0) for every listed score above the final tau whose 64x64
+      // Entry = (key, u = z - tau) for every listed score above the final tau whose 64x64
       // tile is in the block mask just built (what the tile kernels would visit); one run per
       // row: the keys of the row's first thread (low halves of the key tiles), then the second's.
+      // Above alpha = 1.5 the backward's key side decides "score above tau" from its own product
+      // (K scaled and rounded, q raw), and the Jacobian weight does not vanish at the threshold:
+      // pairs within the two products' largest possible difference below tau are exported as well
+      // (with u <= 0: no weight on the query side).  |Q~ k - q K~| <= 2^-8 zscale |q| |k| for 16-bit
+      // operands (unit roundoff 2^-9 each).
       // the same for every thread of the CTA: its lists held (those of the second or of the third sweep)
       const bool can = !full_sweeps && !wide && !*cta_abort;
       int* cnts = reinterpret_cast<int*>(xchg) + grp * (2 * 8 * 128);
@@ -708,7 +734,7 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
       const uint32_t* my_bits = s_bits + (grp * 2 + rb) * p.n_words;
       auto in_support = [&](const Cand c) -> bool {
         const int kb = c.key >> 6;
-        return c.z > hs.t && ((my_bits[kb >> 5] >> (kb & 31)) & 1u);
+        return c.z > hs.t - margin && ((my_bits[kb >> 5] >> (kb & 31)) & 1u);
       };
       auto for_each = [&](auto&& f) {
         if (!(grp_on && row_ok)) return;

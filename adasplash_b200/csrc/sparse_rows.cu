@@ -129,8 +129,9 @@ __global__ void __launch_bounds__(kRowThreads) fwd_rows_kernel(RowsParams p) {
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           // p = u^(1/(alpha-1)) and the Jacobian weight g = u^(1/(alpha-1)-1): u^2 and u for alpha = 1.5
-          const float gj = powers.g(u[j]);
-          const float2 pw = splat(round_to<T>(powers.p(u[j]))), uw = splat(round_to<T>(gj));
+          const float uj = fmaxf(u[j], 0.f);  // alpha > 1.5: entries a rounding below tau are listed too
+          const float gj = powers.g(uj);
+          const float2 pw = splat(round_to<T>(powers.p(uj))), uw = splat(round_to<T>(gj));
           supp += gj;
 #pragma unroll
           for (int c = 0; c < CH; ++c) {
@@ -158,6 +159,32 @@ __global__ void __launch_bounds__(kRowThreads) fwd_rows_kernel(RowsParams p) {
       }
     }
   }
+}
+
+// Largest squared norm of a key row per kv head (the solver's export needs it above alpha = 1.5
+// to bound the difference between the two roundings of a score).  One warp per key row.
+template <typename T>
+__global__ void __launch_bounds__(256) key_norm_max_kernel(const T* __restrict__ k, float* __restrict__ kmax2,
+                                                           const void* varlen, int is_i64, int B, int Hkv, int N, int D) {
+  const long long row_g = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row_g >= (long long)B * Hkv * N) return;
+  const int lane = threadIdx.x & 31;
+  const int bkv = (int)(row_g / N), r = (int)(row_g % N);
+  if (r >= load_len(varlen, is_i64, bkv / Hkv, N)) return;
+  float s = 0.f;
+  for (int d = lane; d < D; d += 32) { const float x = DT<T>::to_f(k[row_g * D + d]); s = fmaf(x, x, s); }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  if (lane == 0) atomicMax(reinterpret_cast<int*>(kmax2) + bkv, __float_as_int(s));  // non-negative floats order as ints
+}
+
+template <typename T>
+int key_norms_t(const simt::Params& p, cudaStream_t st) {
+  const sup::View sv = sup::view(p.support, nullptr, p.B, p.Hq, p.Hkv, p.N);
+  const long long rows = (long long)p.B * p.Hkv * p.N;
+  key_norm_max_kernel<T><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>((const T*)p.k, sv.kmax2, p.varlen, p.varlen_is_i64,
+                                                                   p.B, p.Hkv, p.N, p.D);
+  return check_launch("sparse::key_norm_max");
 }
 
 template <typename T>
@@ -308,7 +335,7 @@ __global__ void __launch_bounds__(kBwdRowThreads) bwd_rows_kernel(BwdParams p) {
           const float dp = group_sum8(dp2.x + dp2.y);
           const float zk = group_sum8(zk2.x + zk2.y);
           const float dd = dp - delta;
-          const float2 dsq = splat(round_to<T>(powers.g(u[j]) * dd));
+          const float2 dsq = splat(round_to<T>(powers.g(fmaxf(u[j], 0.f)) * dd));
 #pragma unroll
           for (int e = 0; e < CH * 4; ++e) dq[e] = __ffma2_rn(dsq, kf[e], dq[e]);
           const float uk = zk - tau;
@@ -624,16 +651,11 @@ int bwd_t(const simt::Params& p, cudaStream_t st) {
 }  // namespace
 
 bool supported(const ads_attn_shape* s) {
-  // 16-bit inputs on the tensor-core solver, causal or full attention, head dim 64 or 128, key
-  // indices that fit 16 bits, alpha <= 1.5.  Above 1.5 the Jacobian weight u^(1/(alpha-1) - 1) is
-  // steep or discontinuous at u = 0 (alpha = 2: a step), and the reference's key side decides
-  // "u > 0" from its own product K~ q, which differs from the solver's Q~ k by a rounding of the
-  // operand: pairs within that rounding of the threshold would have to be exported as well.
-  // Such calls stay on the tile kernels, which form both products.
+  // 16-bit inputs on the tensor-core solver, any alpha, causal or full attention, head dim 64 or
+  // 128, key indices that fit 16 bits
   if (s->dtype != ADS_F16 && s->dtype != ADS_BF16) return false;
   if (s->D != 64 && s->D != 128) return false;
   if (s->N > 65536) return false;
-  if (s->alpha > 1.5f) return false;
   return true;
 }
 
@@ -644,6 +666,11 @@ int clear_header(const simt::Params& p, cudaStream_t st) {
   cudaError_t e = cudaMemsetAsync(p.support, 0, sup::header_bytes(p.B, p.Hkv), st);
   if (e != cudaSuccess) { set_error("support header memset: %s", cudaGetErrorString(e)); return ADS_ERR_CUDA; }
   return ADS_OK;
+}
+
+int key_norms(const simt::Params& p, int dtype, cudaStream_t st) {
+  if (dtype == ADS_F16) return key_norms_t<__half>(p, st);
+  return key_norms_t<__nv_bfloat16>(p, st);
 }
 
 int fwd(const simt::Params& p, int dtype, cudaStream_t st) {

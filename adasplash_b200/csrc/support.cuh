@@ -28,6 +28,7 @@
 //   [0]      uint32 cursor: entries handed out so far (one atomicAdd per solver CTA);
 //            words 4..7: solver CTAs that could not export, by reason (kWhy*)
 //   [256]    int32 dense[B*Hkv]
+//   kmax2    float [B*Hkv]: largest squared norm of a key row of the head (alpha > 1.5 only)
 //   rows     uint2 [B*Hq*N]: (index of the row's first entry, number of entries)
 //   entries  uint2 [cap]: (key index, fp32 bits of u = z - tau_final > 0)
 // and of the backward's scratch (workspace + 256):
@@ -62,6 +63,7 @@ enum : int {
 struct View {
   uint32_t* cursor;
   int32_t* dense;
+  float* kmax2;
   uint2* rows;
   uint2* entries;
   uint2* by_key;
@@ -74,7 +76,7 @@ __host__ __device__ inline size_t align256(size_t x) { return (x + 255) & ~(size
 
 inline size_t bytes(int B, int Hq, int Hkv, int N) {
   const size_t rows = (size_t)B * Hq * N;
-  return 256 + align256((size_t)B * Hkv * 4) + align256(rows * 8) + align256(rows * kEntriesPerRow * 8);
+  return 256 + 2 * align256((size_t)B * Hkv * 4) + align256(rows * 8) + align256(rows * kEntriesPerRow * 8);
 }
 
 // Scratch of the backward on the gather route (by_key, blocks, kb_off).
@@ -86,7 +88,7 @@ inline size_t scratch_bytes(int B, int Hq, int Hkv, int N) {
 }
 
 // Bytes at the start of the buffer that the solver's launcher clears (cursor and counters).
-inline size_t header_bytes(int B, int Hkv) { return 256 + align256((size_t)B * Hkv * 4); }
+inline size_t header_bytes(int B, int Hkv) { return 256 + 2 * align256((size_t)B * Hkv * 4); }
 
 // `scratch` may be null outside the backward (the three arrays it holds are then unset).
 inline View view(void* base, void* scratch, int B, int Hq, int Hkv, int N) {
@@ -95,7 +97,8 @@ inline View view(void* base, void* scratch, int B, int Hq, int Hkv, int N) {
   const size_t rows = (size_t)B * Hq * N;
   v.cursor = (uint32_t*)p;
   v.dense = (int32_t*)(p + 256);
-  v.rows = (uint2*)(p + 256 + align256((size_t)B * Hkv * 4));
+  v.kmax2 = (float*)(p + 256 + align256((size_t)B * Hkv * 4));
+  v.rows = (uint2*)(p + 256 + 2 * align256((size_t)B * Hkv * 4));
   v.entries = (uint2*)((uint8_t*)v.rows + align256(rows * 8));
   v.by_key = nullptr; v.blocks = nullptr; v.kb_off = nullptr;
   if (scratch != nullptr) {

@@ -97,7 +97,7 @@ size_t adasplash2_workspace_bytes(const ads_attn_shape* shape);
  * The route is chosen per (batch, kv head) on the device: heads whose rows are too dense for the
  * solver's lists, or that find the buffer full, take the tile kernels as if no buffer had been
  * given.  Returns 0 for shapes without this route (CUDA-core path, head dims other than 64 / 128,
- * alpha > 1.5, more than 65536 keys); NULL / 0 may always be passed instead of a buffer.  The buffer belongs
+ * more than 65536 keys); NULL / 0 may always be passed instead of a buffer.  The buffer belongs
  * to one solve: pass it to the forward and backward of the same problem, unchanged. */
 size_t adasplash2_support_bytes(const ads_attn_shape* shape);
 

@@ -229,22 +229,19 @@ def test_sequences_shorter_than_a_tile(dtype, alpha, causal, case):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
-@pytest.mark.parametrize("alpha,causal,n_sparse", [(1.5, False, 4), (1.333, True, 1), (1.333, False, 0), (2.0, False, None)])
+@pytest.mark.parametrize("alpha,causal,n_sparse", [(1.5, False, 4), (1.333, True, 1), (1.333, False, 0), (2.0, False, 4),
+                                                   (2.0, True, 4), (1.75, False, 4)])
 @pytest.mark.parametrize("case", [(2, 2, 1024, 64, [1024, 700]), (1, 4, 2048, 128, None)])
 def test_row_supports_on_first_generation_semantics(dtype, alpha, causal, n_sparse, case):
-    # alpha <= 1.5, causal or full attention: heads whose supports the solver exported (at least
+    # Any alpha, causal or full attention: heads whose supports the solver exported (at least
     # `n_sparse` of the four; with alpha = 1.333 more scores lie within 1 of the maximum and some
     # heads overflow the solver's pool: those stay on the tile kernels) run as gathers and must
-    # give what the tile kernels give (same rounding points, another summation order).  Above 1.5 the library offers no support buffer (the Jacobian weight is not
-    # continuous at the threshold, see csrc/sparse_rows.cu).
+    # give what the tile kernels give (same rounding points, another summation order).
     B, H, N, D, vl = case
     q, k, v, do = (_randn((B, H, N, D), 90 + i, 1.5 if i < 3 else 1.0, dtype).cuda() for i in range(4))
     varlen = None if vl is None else torch.tensor(vl, dtype=torch.int32).cuda()
     shape = att.make_shape(q, k, 10, varlen, None, alpha, causal)
     sup = att.support_buffer(shape, q.device)
-    if n_sparse is None:
-        assert sup is None
-        return
     sup.fill_(0x5A)
     taus, bm = att.solve(q, k, 10, varlen, None, alpha, causal, support=sup)
     dense = sup[256:256 + 4 * B * H].view(torch.int32)
@@ -263,4 +260,10 @@ def test_row_supports_on_first_generation_semantics(dtype, alpha, causal, n_spar
                                   None if vl is None else torch.tensor(vl, dtype=torch.int32), do.cpu().float())
     for key in ("out", "dq", "dk", "dv"):
         scale = max(1.0, ex[key].abs().max().item())
-        assert (got[key].double() - ex[key]).abs().max() < 3e-2 * scale, key
+        err = (got[key].double() - ex[key]).abs()
+        if alpha > 1.5 and key != "out":
+            # the Jacobian weight is not Lipschitz at the threshold (see the test above): all but
+            # a few entries within tolerance
+            assert (err < 3e-2 * scale).double().mean() > 0.98, key
+        else:
+            assert err.max() < 3e-2 * scale, key

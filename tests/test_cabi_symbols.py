@@ -66,8 +66,7 @@ def test_bitmap_extent_matches_reference_layout():
 
 
 def test_support_and_workspace_sizes_without_gpu():
-    # The gather route exists for 16-bit inputs, head dim 64 / 128, alpha <= 1.5 and up to
-    # 65536 keys; elsewhere no support buffer is asked for and the workspace is the status word.
+    # The gather route exists for 16-bit inputs, head dim 64 / 128 and up to 65536 keys; elsewhere no support buffer is asked for and the workspace is the status word.
     lib = _lib.load()
 
     def sizes(**kw):
@@ -78,16 +77,15 @@ def test_support_and_workspace_sizes_without_gpu():
 
     rows = 2 * 4 * 4096
     sup, ws = sizes()
-    # cursor + route counters, (first, count) per row, 32 entries of 8 bytes per row
-    assert sup == 256 + 256 + rows * 8 + rows * 32 * 8
+    # cursor + route counters + key norms, (first, count) per row, 32 entries of 8 bytes per row
+    assert sup == 256 + 256 + 256 + rows * 8 + rows * 32 * 8
     # status word + the backward's sorted copy, run table (16 blocks of 256 rows per head) and key-block table
     blocks = 2 * 4 * 16
     assert ws == 256 + rows * 32 * 8 + blocks * 8 + ((blocks * 129 * 2 + 255) // 256) * 256   # 4096 / 32 + 1 table entries per block
     assert sizes(dtype=0) == (0, 256)            # fp32: CUDA-core kernels
     assert sizes(D=32) == (0, 256)               # head dim without a gather route
     assert sizes(N=131072) == (0, 256)           # key indices would not fit 16 bits
-    assert sizes(alpha=2.0) == (0, 256)          # Jacobian weight discontinuous at the threshold
-    assert sizes(alpha=1.333, non_causal=1)[0] == sup   # first-generation semantics with alpha <= 1.5
+    assert sizes(alpha=2.0, non_causal=1)[0] == sup     # first-generation semantics: any alpha, causal or full
     assert sizes(path=1) == (0, 256)             # CUDA-core kernels asked for explicitly
     # a support buffer that is too small is refused before any launch
     sh = _lib.AttnShape(B=2, Hq=4, Hkv=2, N=4096, D=128, dtype=2, niter=1, varlen_is_i64=0, path=0)
