@@ -357,6 +357,43 @@ def test_row_supports_match_tile_kernels(case):
                 assert a[1][b, :, vl[b]:].abs().max() == 0 and a[2][b, :, vl[b]:].abs().max() == 0
 
 
+@pytest.mark.parametrize("seed", range(12))
+def test_row_supports_on_random_shapes(seed):
+    # Seeded random problems (grouped heads, ragged lengths, odd sequence lengths, both head dims
+    # and 16-bit dtypes, scales from flat to peaked, several refinement counts): whatever route
+    # the device picks per kv head, the result with a support buffer must be what the tile
+    # kernels alone give.
+    import random
+    rnd = random.Random(1000 + seed)
+    D = rnd.choice([64, 128])
+    Hkv = rnd.choice([1, 2, 3])
+    Hq = Hkv * rnd.choice([1, 2, 4])
+    B = rnd.choice([1, 2, 3])
+    N = rnd.choice([64, 200, 333, 1024, 1500, 2048, 4097])
+    vl = [rnd.randint(1, N) for _ in range(B)] if rnd.random() < 0.7 else None
+    scale = rnd.choice([0.3, 1.0, 1.5, 2.0])
+    niter = rnd.choice([0, 1, 3])
+    dtype = rnd.choice([torch.bfloat16, torch.float16])
+    q, k, v, do = (_randn(s, 7000 + 10 * seed + i, scale if i < 2 else 1.0, dtype).cuda() for i, s in
+                   enumerate([(B, Hq, N, D), (B, Hkv, N, D), (B, Hkv, N, D), (B, Hq, N, D)]))
+    varlen = None if vl is None else torch.tensor(vl, dtype=torch.int32).cuda()
+    _lib.set_kernel_path("tcgen05")
+    shape = att.make_shape(q, k, niter, varlen)
+    sup = att.support_buffer(shape, q.device)
+    assert sup is not None
+    sup.fill_(0xC3)
+    taus, bm = att.solve(q, k, niter, varlen, support=sup)
+    out, out2 = att.forward_raw(q, k, v, taus, bm, varlen, support=sup)
+    ref, ref2 = att.forward_raw(q, k, v, taus, bm, varlen)
+    a = att.backward_raw(q, k, v, do, out2, taus, bm, varlen, niter, support=sup)
+    r = att.backward_raw(q, k, v, do, ref2, taus, bm, varlen, niter)
+    what = f"B={B} Hq={Hq} Hkv={Hkv} N={N} D={D} lens={vl} scale={scale} niter={niter} {dtype}"
+    for name, x, y in (("out", out, ref), ("out2", out2, ref2), ("dq", a[0], r[0]), ("dk", a[1], r[1]), ("dv", a[2], r[2])):
+        assert torch.isfinite(x.float()).all(), (name, what)
+        tol = 1e-2 * max(1.0, y.float().abs().max().item())
+        assert (x.float() - y.float()).abs().max().item() < tol, (name, what)
+
+
 @pytest.mark.parametrize("scale, niter", [(0.05, 1), (0.05, 3), (0.4, 0), (1.5, 10), (1.5, 0)])
 def test_solver_with_nearly_flat_rows(scale, niter):
     # Scores that are nearly flat put most of a row within 1 of its maximum: the solver's
