@@ -53,7 +53,8 @@
 namespace ads {
 namespace sm100 {
 
-constexpr int kSolveStages = 3;  // each K tile feeds two products, three tiles in flight cover the TMA latency
+constexpr int kSolveStages = 2;  // each K tile feeds two products (1024 tensor cycles): two tiles in flight cover the
+                                 // TMA latency as well as three did, and the third tile's 32 KB serve the candidate pool
 constexpr int kSolveThreads = 576;   // 2 row groups x 8 warps + TMA warp + MMA warp
 constexpr int kSolveRowThreads = 512;
 constexpr int kSolveGroupThreads = 256;
@@ -72,8 +73,8 @@ constexpr uint16_t kCandNil = 0xffff;
 
 // Shared memory: K stages, barriers, exchange buffers, bitmap staging, then the two Q tiles and
 // whatever is left of the budget.  The Q tiles are dead once Q~ sits in TMEM (before the first
-// append), so the candidate pool is their space plus that remainder (D = 128: ~110 KB, 14000
-// entries, 27 per thread on average).  Each row warp appends to its own sixteenth, so warps
+// append), so the candidate pool is their space plus that remainder (D = 128: ~142 KB, 18000
+// entries, 35 per thread on average).  Each row warp appends to its own sixteenth, so warps
 // do not contend for a counter.
 constexpr int kSolveSmemBudget = 225 * 1024;
 
