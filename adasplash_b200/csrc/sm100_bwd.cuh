@@ -141,7 +141,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   const uint32_t tmem_base = *tmem_holder;
 
   if (warp == 8) {
-    if (lane == 0) {
+    if (ptx::elect_one()) {
       ptx::prefetch_tmap(&tmQ); ptx::prefetch_tmap(&tmDO); ptx::prefetch_tmap(&tmK); ptx::prefetch_tmap(&tmV);
       ptx::mbar_arrive_expect_tx(q_full, 2 * L::tile_bytes);
       for (int pn = 0; pn < PANELS; ++pn) {
@@ -172,14 +172,14 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     constexpr uint32_t idesc_s = ptx::make_idesc(FMT, kBlockM, kBlockN, 0, 0);
     bool ok = true;
     if (lane == 0) ok = ptx::mbar_wait(q_ready, 0);
-    ok = __shfl_sync(0xffffffffu, ok, 0);
+    ok = __all_sync(0xffffffffu, ok);
     TileScan scan(bm_head, qt, T_tiles, p.rows_padded, p.n_words);
     int kt;
     uint32_t flags;
     for (int j = 0; ok && scan.next(kt, flags); ++j) {
       const int ks = j % kDqKStages, buf = j & 1;
       if (*cta_abort) { ok = false; break; }
-      if (lane == 0) {
+      if (ptx::elect_one()) {
         ok = ptx::mbar_wait(k_full + ks, (j / kDqKStages) & 1) && ptx::mbar_wait(s_free + buf, ((j >> 1) & 1) ^ 1);
         if (ok) {
           ptx::tc_fence_after_sync();
@@ -193,7 +193,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
           ptx::mma_commit(s_full + buf);
         }
       }
-      ok = __shfl_sync(0xffffffffu, ok, 0);
+      ok = __all_sync(0xffffffffu, ok);
     }
     if (!ok && lane == 0 && !*cta_abort) raise_abort(cta_abort, p.status, kStTimeoutMma);
   } else if (warp == 10) {
@@ -201,14 +201,14 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     constexpr uint32_t idesc_s = ptx::make_idesc(FMT, kBlockM, kBlockN, 0, 0);
     bool ok = true;
     if (lane == 0) ok = ptx::mbar_wait(q_ready, 0);
-    ok = __shfl_sync(0xffffffffu, ok, 0);
+    ok = __all_sync(0xffffffffu, ok);
     TileScan scan(bm_head, qt, T_tiles, p.rows_padded, p.n_words);
     int kt;
     uint32_t flags;
     for (int j = 0; ok && scan.next(kt, flags); ++j) {
       const int vs = j % kDqVStages;
       if (*cta_abort) { ok = false; break; }
-      if (lane == 0) {
+      if (ptx::elect_one()) {
         ok = ptx::mbar_wait(v_full + vs, (j / kDqVStages) & 1);
         // the row warps have dP_{j-1} in registers (they say so before their row work)
         if (ok && j > 0) ok = ptx::mbar_wait(dp_free, (j - 1) & 1);
@@ -225,7 +225,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
           ptx::mma_commit(dp_full);
         }
       }
-      ok = __shfl_sync(0xffffffffu, ok, 0);
+      ok = __all_sync(0xffffffffu, ok);
     }
     if (!ok && lane == 0 && !*cta_abort) raise_abort(cta_abort, p.status, kStTimeoutMma);
   } else if (warp == 11) {
@@ -245,10 +245,10 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       // tile, has completed: its commit precedes p_full in program order of the row warps)
       const bool fix_k = (kt + 1) * kBlockN > len;
       if (lane == 0) ok = ptx::mbar_wait(p_full + buf, (j >> 1) & 1);
-      ok = __shfl_sync(0xffffffffu, ok, 0);
+      ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       if (fix_k) zero_tile_rows(ktile, PANELS, len - kt * kBlockN, lane);
-      if (lane == 0) {
+      if (ptx::elect_one()) {
         ptx::tc_fence_after_sync();
         const uint32_t k0 = ptx::smem_u32(ktile);
         const uint32_t pbase = tmem_base + buf * kBlockN;
@@ -564,7 +564,7 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
     // ---------------- producer: K / V tile, then per step the Q and dO blocks (TMA, lane 0) and
     // the tau / delta of the block's 64 query rows (plain loads by the 32 lanes, fetched one
     // step ahead into registers so that their latency is off the path) ----------------
-    if (lane == 0) {
+    if (ptx::elect_one()) {
       ptx::prefetch_tmap(&tmK); ptx::prefetch_tmap(&tmV); ptx::prefetch_tmap(&tmQ64); ptx::prefetch_tmap(&tmDO64);
       ptx::mbar_arrive_expect_tx(kv_full, 2 * L::tile_bytes);
       for (int pn = 0; pn < PANELS; ++pn) {
@@ -594,13 +594,13 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
       const bool have_next = scan.next(g_next, m_next, flags);
       if (*cta_abort) break;
       if (lane == 0) ok = ptx::mbar_wait(x_empty + st, ((j / kDkvStages) & 1) ^ 1);
-      ok = __shfl_sync(0xffffffffu, ok, 0);
+      ok = __all_sync(0xffffffffu, ok);
       if (!ok) { if (lane == 0) raise_abort(cta_abort, p.status, kStTimeoutProducer); break; }
       float* dst = s_td + st * 128;
       *reinterpret_cast<float2*>(dst + 2 * lane) = make_float2(td[0], td[1]);
       *reinterpret_cast<float2*>(dst + 64 + 2 * lane) = make_float2(td[2], td[3]);
       __syncwarp();
-      if (lane == 0) {
+      if (ptx::elect_one()) {
         ptx::mbar_arrive_expect_tx(x_full + st, 2 * L::qblk_bytes);  // releases the stores above to the waiters
         for (int pn = 0; pn < PANELS; ++pn) {
           ptx::tma_load_3d(sQ + st * L::qblk_bytes + pn * kQPanelBytes, &tmQ64, x_full + st, pn * 64, m * kQBlock, qh);
@@ -619,14 +619,14 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
     const bool is_s = warp == 17;
     bool ok = true;
     if (lane == 0) ok = ptx::mbar_wait(k_ready, 0);
-    ok = __shfl_sync(0xffffffffu, ok, 0);
+    ok = __all_sync(0xffffffffu, ok);
     QBlockScan<CAUSAL> scan(p.bmask_t, b, p.Hq, G, kvh, nt, n_qblocks, p.rows_padded, p.n_words);
     int g, m;
     uint32_t flags;
     for (int j = 0; ok && scan.next(g, m, flags); ++j) {
       const int st = j % kDkvStages, buf = j & 1;
       if (*cta_abort) { ok = false; break; }
-      if (lane == 0) {
+      if (ptx::elect_one()) {
         // the S^T buffer holds P^T and dS^T until the dV / dK products are done; the dP^T buffer
         // is free as soon as the row warps have copied it to registers
         ok = ptx::mbar_wait(x_full + st, (j / kDkvStages) & 1) &&
@@ -646,7 +646,7 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
           ptx::mma_commit(s_full + buf);
         }
       }
-      ok = __shfl_sync(0xffffffffu, ok, 0);
+      ok = __all_sync(0xffffffffu, ok);
     }
     if (!ok && lane == 0 && !*cta_abort) raise_abort(cta_abort, p.status, kStTimeoutMma);
   } else if (warp == 19 || warp == 20) {
@@ -663,7 +663,7 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
       const bool have_next = scan.next(g_next, m_next, flags);
       if (*cta_abort) { ok = false; break; }
       if (lane == 0) ok = ptx::mbar_wait(p_full + buf, (j >> 1) & 1);
-      ok = __shfl_sync(0xffffffffu, ok, 0);
+      ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       uint8_t* bt = (is_dv ? sDO : sQ) + st * L::qblk_bytes;  // B operand: dO for dV, Q for dK
       if ((m + 1) * kQBlock > len) {
@@ -677,7 +677,7 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
         ptx::fence_proxy_async_smem();
         __syncwarp();
       }
-      if (lane == 0) {
+      if (ptx::elect_one()) {
         ptx::tc_fence_after_sync();
         const uint32_t b0 = ptx::smem_u32(bt);
         // P^T / dS^T: 16 queries = 8 packed columns per k-step, at the start of each 16-column group

@@ -163,7 +163,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
 
   if (warp == 16) {
     // ---------------- TMA producer ----------------
-    if (lane == 0) {
+    if (ptx::elect_one()) {
       ptx::prefetch_tmap(&tmQ);
       ptx::prefetch_tmap(&tmK);
       ptx::prefetch_tmap(&tmV);
@@ -194,14 +194,14 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     constexpr uint32_t idesc_s = ptx::make_idesc(FMT, kBlockM, kBlockN, 0, 0);
     bool ok = true;
     if (lane == 0) ok = ptx::mbar_wait(q_ready, 0);
-    ok = __shfl_sync(0xffffffffu, ok, 0);
+    ok = __all_sync(0xffffffffu, ok);
     TileScan scan(bm_head, qt, T_tiles, p.rows_padded, p.n_words);
     int kt;
     uint32_t flags;
     for (int j = 0; ok && scan.next(kt, flags); ++j) {
       const int ks = j % kFwdKStages, buf = j & 1;
       if (*cta_abort) { ok = false; break; }
-      if (lane == 0) {
+      if (ptx::elect_one()) {
         ok = ptx::mbar_wait(k_full + ks, (j / kFwdKStages) & 1) && ptx::mbar_wait(s_free + buf, ((j >> 1) & 1) ^ 1);
         if (ok) {
           ptx::tc_fence_after_sync();
@@ -217,7 +217,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
           ptx::mma_commit(s_full + buf);
         }
       }
-      ok = __shfl_sync(0xffffffffu, ok, 0);
+      ok = __all_sync(0xffffffffu, ok);
     }
     if (!ok && lane == 0 && !*cta_abort) raise_abort(cta_abort, p.status, kStTimeoutMma);
   } else if (warp == 18 || warp == 19) {
@@ -235,12 +235,12 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       const bool have_next = scan.next(kt_next, flags);
       if (*cta_abort) { ok = false; break; }
       if (lane == 0) ok = ptx::mbar_wait(v_full + vs, (j / kFwdVStages) & 1);
-      ok = __shfl_sync(0xffffffffu, ok, 0);
+      ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       uint8_t* vt = sV + vs * L::tile_bytes;
       // padded keys: V = 0 (both issuers write the same zeros before their own products)
       if ((kt + 1) * kBlockN > len) zero_tile_rows(vt, PANELS, len - kt * kBlockN, lane);
-      if (lane == 0) {
+      if (ptx::elect_one()) {
         ok = ptx::mbar_wait(p_full + buf, (j >> 1) & 1);
         if (ok) {
           ptx::tc_fence_after_sync();
@@ -256,7 +256,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
           if (!have_next) ptx::mma_commit(o_full);
         }
       }
-      ok = __shfl_sync(0xffffffffu, ok, 0);
+      ok = __all_sync(0xffffffffu, ok);
       kt = kt_next;
       have = have_next;
     }

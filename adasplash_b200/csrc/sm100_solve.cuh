@@ -14,9 +14,10 @@
 //   * S_A = Q~_A K^T and S_B = Q~_B K^T rotate through three 128-column fp32 TMEM
 //     buffers (product n goes to buffer n % 3): one is read by row group A, one by
 //     row group B, one is being written, so the product of a group's next tile
-//     overlaps its row work.  One thread issues all products in order, so that it
-//     sees every phase of the three "buffer free" barriers; each row group has its
-//     own "product done" barriers per buffer for the same reason;
+//     overlaps its row work.  Each row tile has its own issuing warp (issuing an MMA
+//     costs the thread as long as the product costs the pipe) with its own "buffer
+//     free" barriers, and each row group its own "product done" barriers per buffer,
+//     so that every waiter sees every phase of the barriers it waits on;
 //   * inside a group, TMEM lane = score row, and the two warps that own the same
 //     32 lanes split the 128 keys of a tile in halves (the row work of a tile is
 //     a chain of TMEM round trips; two threads per row halve it).  The two
@@ -55,7 +56,7 @@ namespace sm100 {
 
 constexpr int kSolveStages = 2;  // each K tile feeds two products (1024 tensor cycles): two tiles in flight cover the
                                  // TMA latency as well as three did, and the third tile's 32 KB serve the candidate pool
-constexpr int kSolveThreads = 576;   // 2 row groups x 8 warps + TMA warp + MMA warp
+constexpr int kSolveThreads = 608;   // 2 row groups x 8 warps + TMA warp + one MMA warp per row tile
 constexpr int kSolveRowThreads = 512;
 constexpr int kSolveGroupThreads = 256;
 constexpr int kSolveTmemCols = 512;  // three S buffers at columns 0 / 128 / 256, Q~_A, Q~_B from column 384
@@ -83,7 +84,7 @@ struct SolveSmem {
   static constexpr int tile_bytes = (D / 64) * kPanelBytes;
   static constexpr int k_off = 0;
   static constexpr int bar_off = k_off + kSolveStages * tile_bytes;
-  static constexpr int n_bars = 2 + 2 * kSolveStages + 3 * kSolveBufs + 1;
+  static constexpr int n_bars = 2 + 2 * kSolveStages + 4 * kSolveBufs + 1;
   static constexpr int misc_off = bar_off + n_bars * 8;            // tmem base, abort flag, status, pool counters
   static constexpr int xchg_off = misc_off + 128;                  // [2 groups][2 halves][8][128] floats
   static constexpr int bits_off = xchg_off + 2 * 2 * 8 * 128 * 4;  // [4][n_words] words
@@ -116,8 +117,8 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
   uint64_t* k_full = bars + 2;
   uint64_t* k_empty = k_full + kSolveStages;
   uint64_t* s_full = k_empty + kSolveStages;  // [2 row tiles][3 S buffers]: each row group sees only its own products
-  uint64_t* s_free = s_full + 2 * kSolveBufs;  // [3 S buffers]
-  uint64_t* decide = s_free + kSolveBufs;              // the row warps have settled lists vs. full sweeps
+  uint64_t* s_free = s_full + 2 * kSolveBufs;  // [row tile of the buffer's next product][3 S buffers]
+  uint64_t* decide = s_free + 2 * kSolveBufs;              // the row warps have settled lists vs. full sweeps
   uint32_t* tmem_holder = (uint32_t*)(smem + L::misc_off);
   volatile int* cta_abort = (volatile int*)(smem + L::misc_off + 4);
   int* start_status = (int*)(smem + L::misc_off + 8);
@@ -157,11 +158,11 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
   // it saves at least two sweeps.  (With niter = 1 and no export it is no gain: its appends cost
   // what the one sweep it saves would have.)
   const bool third_sweep = !V1 && !p.tau_given && (p.sup_on || p.niter >= 2);
-  // Products are numbered in issue order (per K tile: A if it has one, then B); product n uses
+  // Products are numbered in K-tile order (per K tile: A if it has one, then B); product n uses
   // S buffer n % 3 for the (n / 3)-th time.
   const int prods_per_sweep = b_on ? T_a + T_k : T_a;   // causal: T_k = T_a + 1
-  auto product_index = [&](int sweep, int kt, int g) -> int {
-    return sweep * prods_per_sweep + (b_on ? (kt < T_a ? 2 * kt + g : T_a + kt) : kt);
+  auto product_in_sweep = [&](int kt, int g) -> int {
+    return b_on ? (kt < T_a ? 2 * kt + g : T_a + kt) : kt;
   };
 
   if (threadIdx.x == 0) {
@@ -176,9 +177,10 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
       ptx::mbar_init(q_full, 1);
       ptx::mbar_init(q_ready, kSolveRowThreads / 32);
       ptx::mbar_init(decide, kSolveRowThreads / 32);
-      for (int s = 0; s < kSolveStages; ++s) { ptx::mbar_init(k_full + s, 1); ptx::mbar_init(k_empty + s, 1); }
+      // a K stage is empty again when the issuers of both row tiles are through with it
+      for (int s = 0; s < kSolveStages; ++s) { ptx::mbar_init(k_full + s, 1); ptx::mbar_init(k_empty + s, b_on ? 2 : 1); }
       for (int s = 0; s < 2 * kSolveBufs; ++s) ptx::mbar_init(s_full + s, 1);
-      for (int s = 0; s < kSolveBufs; ++s) ptx::mbar_init(s_free + s, kSolveGroupThreads / 32);
+      for (int s = 0; s < 2 * kSolveBufs; ++s) ptx::mbar_init(s_free + s, kSolveGroupThreads / 32);
       ptx::fence_mbar_init();
     }
     __syncwarp();
@@ -197,7 +199,7 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
 
   if (warp == 16) {
     // ---------------- TMA producer ----------------
-    if (lane == 0) {
+    if (ptx::elect_one()) {
       ptx::prefetch_tmap(&tmQ);
       ptx::prefetch_tmap(&tmK);
       ptx::mbar_arrive_expect_tx(q_full, 2 * L::tile_bytes);
@@ -231,19 +233,26 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
         if (++kt == T_k) kt = 0;
       }
     }
-  } else if (warp == 17) {
-    // ---------------- MMA issuer ----------------
-    // One thread issues every product in order n = 0, 1, 2, ...: it is then the only waiter of
-    // the three "buffer free" barriers and sees each of their phases in turn (a thread that
+  } else if (warp == 17 || warp == 18) {
+    // ---------------- MMA issuers: warp 17 for row tile A, warp 18 for row tile B ----------------
+    // Issuing one tcgen05.mma keeps the issuing thread busy for about as long as the 128x128x16
+    // product keeps the tensor pipe (70 - 80 clocks measured, whatever the product's size), so a
+    // single thread issuing for both row tiles fed the pipe at half its rate.  Products keep
+    // their numbering in K-tile order (per K tile: A if it has one, then B) and product n its
+    // buffer n % 3.  A buffer's "free" barrier is chosen by the row tile of the product that takes
+    // the buffer next (the row warps know it when they let go of the buffer): each issuer is then
+    // the only waiter of its three barriers and sees each of their phases in turn (a thread that
     // skips a phase of an mbarrier cannot tell the phase after it from the one before).
-    if (lane == 0) {
+    const int g = warp - 17;
+    if ((g == 0 || b_on) && ptx::elect_one()) {
       constexpr uint32_t idesc = ptx::make_idesc(FMT, kBlockM, kBlockN, 0, 0);
       bool ok = ptx::mbar_wait(q_ready, 0);
       if (!ok) raise_abort(cta_abort, p.status, kStTimeoutMma);
       int total = total_first;
-      // stage / key tile / S buffer and their use parities are carried along (no divisions)
-      int st = 0, kt = 0, bf = 0;
-      uint32_t k_par = 0, buf_par = 0;
+      // stage / key tile / number of the K tile's first product (and its buffer) are carried along
+      int st = 0, kt = 0, n0p = 0, bf0 = 0;
+      uint32_t k_par = 0, free_par = 0;  // bit b of free_par: parity of this issuer's next wait for buffer b
+      const uint32_t a_tmem = tmem_base + kSolveQCol + g * (D / 2);
       for (int i = 0; ok; ++i) {
         if (i == total) {
           if (total == total_full + (third_sweep ? T_k : 0)) break;
@@ -254,22 +263,35 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
         }
         if (*cta_abort) break;
         if (!ptx::mbar_wait(k_full + st, k_par)) { raise_abort(cta_abort, p.status, kStTimeoutMma); break; }
-        const uint32_t b0 = ptx::smem_u32(sK + st * L::tile_bytes);
-        for (int t = 0; t < 2 && ok; ++t) {
-          if (t == 0 ? kt >= T_a : !b_on) continue;  // the diagonal key tile of B has nothing for A
-          if (!ptx::mbar_wait(s_free + bf, buf_par ^ 1)) { raise_abort(cta_abort, p.status, kStTimeoutMma); ok = false; break; }
+        const int has_a = kt < T_a ? 1 : 0;  // the diagonal key tile of B has nothing for A
+        if (g == 1 || has_a) {
+          const int skip = g == 1 ? has_a : 0;  // B's product follows A's
+          int bf = bf0 + skip;
+          if (bf >= kSolveBufs) bf -= kSolveBufs;
+          if (n0p + skip >= kSolveBufs) {  // the buffer held a product before: the row warps must be through with it
+            if (!ptx::mbar_wait(s_free + g * kSolveBufs + bf, (free_par >> bf) & 1u)) {
+              raise_abort(cta_abort, p.status, kStTimeoutMma);
+              break;
+            }
+            free_par ^= 1u << bf;
+          }
           ptx::tc_fence_after_sync();
-          const uint32_t a_tmem = tmem_base + kSolveQCol + t * (D / 2);
+          const uint32_t b0 = ptx::smem_u32(sK + st * L::tile_bytes);
           const uint32_t d = tmem_base + bf * kBlockN;
 #pragma unroll
           for (int kk = 0; kk < KSTEPS; ++kk) {
             const uint32_t off = (kk >> 2) * kPanelBytes + (kk & 3) * 32;
             ptx::mma_ts(d, a_tmem + kk * 8, ptx::make_smem_desc(b0 + off, 16, 1024), idesc, kk > 0);
           }
-          ptx::mma_commit(s_full + t * kSolveBufs + bf);
-          if (++bf == kSolveBufs) { bf = 0; buf_par ^= 1; }
+          ptx::mma_commit(s_full + g * kSolveBufs + bf);
+          ptx::mma_commit(k_empty + st);
+        } else {
+          ptx::mbar_arrive(k_empty + st);
         }
-        ptx::mma_commit(k_empty + st);
+        const int adv = has_a + (b_on ? 1 : 0);
+        n0p += adv;
+        bf0 += adv;
+        if (bf0 >= kSolveBufs) bf0 -= kSolveBufs;
         if (++st == kSolveStages) { st = 0; k_par ^= 1; }
         if (++kt == T_k) kt = 0;
       }
@@ -358,8 +380,13 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
       const int sweep = sweep_no++;
       for (int kt = 0; kt < T_g; ++kt) {
         if (dead || *cta_abort) { dead = true; continue; }
-        const int n = product_index(sweep, kt, grp);
+        const int idx = product_in_sweep(kt, grp);
+        const int n = sweep * prods_per_sweep + idx;
         const int bf = n % kSolveBufs;
+        // the row tile of product n + 3, the next one in this buffer: its issuer waits for this release
+        int idx3 = idx + kSolveBufs;
+        while (idx3 >= prods_per_sweep) idx3 -= prods_per_sweep;
+        const int g_next = b_on ? (idx3 < 2 * T_a ? (idx3 & 1) : 1) : 0;
         const uint32_t par = (full_par >> bf) & 1u;
         full_par ^= 1u << bf;
         if (!ptx::mbar_wait_warp(s_full + grp * kSolveBufs + bf, par)) {
@@ -389,7 +416,7 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
           ptx::tmem_ld_wait();
           if (q32 == 1) {  // the last of this buffer is in registers: hand it back before the row work
             ptx::tc_fence_before_sync();
-            ptx::mbar_arrive_warp(s_free + bf);
+            ptx::mbar_arrive_warp(s_free + g_next * kSolveBufs + bf);
           }
           float* v = reinterpret_cast<float*>(raw);
           const int keybase = wide ? 2 * kt + half : n0 + c0;
