@@ -141,7 +141,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   const uint32_t tmem_base = *tmem_holder;
 
   if (warp == 8) {
-    if (ptx::elect_one()) {
+    if (lane == 0) {
       ptx::prefetch_tmap(&tmQ); ptx::prefetch_tmap(&tmDO); ptx::prefetch_tmap(&tmK); ptx::prefetch_tmap(&tmV);
       ptx::mbar_arrive_expect_tx(q_full, 2 * L::tile_bytes);
       for (int pn = 0; pn < PANELS; ++pn) {
@@ -179,7 +179,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     for (int j = 0; ok && scan.next(kt, flags); ++j) {
       const int ks = j % kDqKStages, buf = j & 1;
       if (*cta_abort) { ok = false; break; }
-      if (ptx::elect_one()) {
+      if (lane == 0) {
         ok = ptx::mbar_wait(k_full + ks, (j / kDqKStages) & 1) && ptx::mbar_wait(s_free + buf, ((j >> 1) & 1) ^ 1);
         if (ok) {
           ptx::tc_fence_after_sync();
@@ -208,7 +208,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     for (int j = 0; ok && scan.next(kt, flags); ++j) {
       const int vs = j % kDqVStages;
       if (*cta_abort) { ok = false; break; }
-      if (ptx::elect_one()) {
+      if (lane == 0) {
         ok = ptx::mbar_wait(v_full + vs, (j / kDqVStages) & 1);
         // the row warps have dP_{j-1} in registers (they say so before their row work)
         if (ok && j > 0) ok = ptx::mbar_wait(dp_free, (j - 1) & 1);
@@ -248,7 +248,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       if (fix_k) zero_tile_rows(ktile, PANELS, len - kt * kBlockN, lane);
-      if (ptx::elect_one()) {
+      if (lane == 0) {
         ptx::tc_fence_after_sync();
         const uint32_t k0 = ptx::smem_u32(ktile);
         const uint32_t pbase = tmem_base + buf * kBlockN;

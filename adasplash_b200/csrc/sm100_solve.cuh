@@ -370,6 +370,7 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
     const bool wide = p.N > 65536;  // key indices do not fit the 16 bits of a list entry
     const int kb_shift = wide ? 0 : 6;
     bool compact = false;      // the list was copied to one contiguous run starting at run0
+    int my_used = 0;           // entries of this warp's share of the pool handed out so far (the same in all lanes)
     int run0 = 0;
 
     // One pass over the S tiles of this group's causal range.  Instantiated once per sweep
@@ -440,41 +441,69 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
             // The histogram sweep: every score within 1 of the row maximum goes to this
             // thread's list while the pool has room (and is binned from there after the
             // sweep), else straight into the histogram.  Those scores are a small part of a
-            // row: look at four at a time and only open a group that contains one.
+            // row (a thread has one in every sixth tile on the headline workload), but some lane
+            // of the warp has one in a third of all groups of four, and a warp that opens each
+            // such group in turn spends its time in sparsely occupied branches.  So: mark the
+            // groups without branching, then let the warp work through the marked groups in
+            // rounds -- in a round every lane that has one moves it to the same four registers
+            // and appends one score, all lanes in one pass through one copy of the code.
+            uint32_t mg = 0u;
 #pragma unroll
             for (int g4 = 0; g4 < 8; ++g4) {
               const float cm = fmaxf(ptx::fmax3(v[g4 * 4], v[g4 * 4 + 1], v[g4 * 4 + 2]), v[g4 * 4 + 3]);
-              if (cm >= thr) {
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                  const float z = v[g4 * 4 + c];
-                  if (z >= thr) {
-                    // to the list while there is room, else straight into the histogram
-                    bool listed = false;
-                    if (collecting) {
-                      const int idx = atomicAdd(pool_used + warp, 1);
-                      if (idx < warp_pool) {
-                        const int slot = warp * warp_pool + idx;
-                        Cand e;
-                        e.z = z; e.next = head;
-                        e.key = (uint16_t)(keybase + ((g4 * 4 + c) & kmask));
-                        pool[slot] = e;
-                        head = (uint16_t)slot;
-                        listed = true;
-                      } else {
-                        *pool_ovf = 1;
-                      }
-                    }
-                    if (!listed) {
-                      // bin = floor((z - tau0) * BINS) clamped to 7; one add of a byte pattern
-                      // bumps the cumulative counters N_0..N_bin (<= 64 hits per tile: no overflow)
-                      const float prj = (z - tau0) * fbins;
-                      if (prj >= 0.f) {
-                        const int bsel = min(__float2int_rd(prj), 7);
-                        packed += 0x0101010101010101ull >> ((7 - bsel) * 8);
-                      }
-                    }
-                  }
+              mg |= (cm >= thr) ? (1u << g4) : 0u;
+            }
+            float z0 = 0.f, z1 = 0.f, z2 = 0.f, z3 = 0.f;
+            uint32_t pend = 0u;  // positions of the open group that are still to be taken
+            int gbase = 0;
+            while (__any_sync(0xffffffffu, (mg | pend) != 0u)) {
+              if (pend == 0u && mg != 0u) {
+                const int gsel = __ffs(mg) - 1;
+                mg &= mg - 1u;
+                switch (gsel) {
+                  case 0: z0 = v[0]; z1 = v[1]; z2 = v[2]; z3 = v[3]; break;
+                  case 1: z0 = v[4]; z1 = v[5]; z2 = v[6]; z3 = v[7]; break;
+                  case 2: z0 = v[8]; z1 = v[9]; z2 = v[10]; z3 = v[11]; break;
+                  case 3: z0 = v[12]; z1 = v[13]; z2 = v[14]; z3 = v[15]; break;
+                  case 4: z0 = v[16]; z1 = v[17]; z2 = v[18]; z3 = v[19]; break;
+                  case 5: z0 = v[20]; z1 = v[21]; z2 = v[22]; z3 = v[23]; break;
+                  case 6: z0 = v[24]; z1 = v[25]; z2 = v[26]; z3 = v[27]; break;
+                  default: z0 = v[28]; z1 = v[29]; z2 = v[30]; z3 = v[31]; break;
+                }
+                gbase = gsel * 4;
+                pend = (z0 >= thr ? 1u : 0u) | (z1 >= thr ? 2u : 0u) | (z2 >= thr ? 4u : 0u) | (z3 >= thr ? 8u : 0u);
+              }
+              const bool has = pend != 0u;
+              const int c = has ? __ffs(pend) - 1 : 0;
+              pend &= pend - 1u;
+              const float z = c == 0 ? z0 : (c == 1 ? z1 : (c == 2 ? z2 : z3));
+              // to the list while there is room, else straight into the histogram; the warp's
+              // share of the pool is its own, so the slots come from a vote, not from an atomic
+              const bool want = has && collecting;
+              const uint32_t votes = __ballot_sync(0xffffffffu, want);
+              bool listed = false;
+              if (want) {
+                const int idx = my_used + __popc(votes & ((1u << lane) - 1u));
+                if (idx < warp_pool) {
+                  const int slot = warp * warp_pool + idx;
+                  Cand e;
+                  e.z = z; e.next = head;
+                  e.key = (uint16_t)(keybase + ((gbase + c) & kmask));
+                  pool[slot] = e;
+                  head = (uint16_t)slot;
+                  listed = true;
+                } else {
+                  *pool_ovf = 1;
+                }
+              }
+              my_used += __popc(votes);
+              if (has && !listed) {
+                // bin = floor((z - tau0) * BINS) clamped to 7; one add of a byte pattern
+                // bumps the cumulative counters N_0..N_bin (<= 64 hits per tile: no overflow)
+                const float prj = (z - tau0) * fbins;
+                if (prj >= 0.f) {
+                  const int bsel = min(__float2int_rd(prj), 7);
+                  packed += 0x0101010101010101ull >> ((7 - bsel) * 8);
                 }
               }
             }
@@ -482,29 +511,56 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
             // Third sweep of a CTA whose pool overflowed in the second: the histogram has given
             // every row the lower end of its bracket, which no later tau undercuts (by more than
             // the step's tolerance), and the scores above that are few -- the support and a
-            // little more -- where the scores within 1 of the maximum were too many.
+            // little more -- where the scores within 1 of the maximum were too many.  Same
+            // rounds as above; one counter for the CTA, so that the whole pool is open to
+            // whichever rows need it (per-warp shares with a common overflow area measured no
+            // faster), bumped once per round and warp.
             const float thr_c = hs.lo - 2e-5f;
+            uint32_t mg = 0u;
 #pragma unroll
             for (int g4 = 0; g4 < 8; ++g4) {
               const float cm = fmaxf(ptx::fmax3(v[g4 * 4], v[g4 * 4 + 1], v[g4 * 4 + 2]), v[g4 * 4 + 3]);
-              if (cm >= thr_c) {
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                  const float z = v[g4 * 4 + c];
-                  if (z >= thr_c && row_ok) {
-                    // one counter for the CTA: the whole pool is open to whichever rows need it
-                    // (per-warp shares with a common overflow area measured no faster)
-                    const int j = atomicAdd(pool_common, 1);
-                    const int slot = j < 16 * warp_pool ? j : -1;
-                    if (slot >= 0) {
-                      Cand e;
-                      e.z = z; e.next = head;
-                      e.key = (uint16_t)(keybase + ((g4 * 4 + c) & kmask));
-                      pool[slot] = e;
-                      head = (uint16_t)slot;
-                    } else {
-                      *pool_ovf2 = 1;
-                    }
+              mg |= (cm >= thr_c) ? (1u << g4) : 0u;
+            }
+            float z0 = 0.f, z1 = 0.f, z2 = 0.f, z3 = 0.f;
+            uint32_t pend = 0u;
+            int gbase = 0;
+            while (__any_sync(0xffffffffu, (mg | pend) != 0u)) {
+              if (pend == 0u && mg != 0u) {
+                const int gsel = __ffs(mg) - 1;
+                mg &= mg - 1u;
+                switch (gsel) {
+                  case 0: z0 = v[0]; z1 = v[1]; z2 = v[2]; z3 = v[3]; break;
+                  case 1: z0 = v[4]; z1 = v[5]; z2 = v[6]; z3 = v[7]; break;
+                  case 2: z0 = v[8]; z1 = v[9]; z2 = v[10]; z3 = v[11]; break;
+                  case 3: z0 = v[12]; z1 = v[13]; z2 = v[14]; z3 = v[15]; break;
+                  case 4: z0 = v[16]; z1 = v[17]; z2 = v[18]; z3 = v[19]; break;
+                  case 5: z0 = v[20]; z1 = v[21]; z2 = v[22]; z3 = v[23]; break;
+                  case 6: z0 = v[24]; z1 = v[25]; z2 = v[26]; z3 = v[27]; break;
+                  default: z0 = v[28]; z1 = v[29]; z2 = v[30]; z3 = v[31]; break;
+                }
+                gbase = gsel * 4;
+                pend = (z0 >= thr_c ? 1u : 0u) | (z1 >= thr_c ? 2u : 0u) | (z2 >= thr_c ? 4u : 0u) | (z3 >= thr_c ? 8u : 0u);
+              }
+              const bool want = pend != 0u && row_ok;
+              const int c = pend != 0u ? __ffs(pend) - 1 : 0;
+              pend &= pend - 1u;
+              const float z = c == 0 ? z0 : (c == 1 ? z1 : (c == 2 ? z2 : z3));
+              const uint32_t votes = __ballot_sync(0xffffffffu, want);
+              if (votes != 0u) {
+                int base = 0;
+                if (lane == 0) base = atomicAdd(pool_common, __popc(votes));
+                base = __shfl_sync(0xffffffffu, base, 0);
+                if (want) {
+                  const int j = base + __popc(votes & ((1u << lane) - 1u));
+                  if (j < 16 * warp_pool) {
+                    Cand e;
+                    e.z = z; e.next = head;
+                    e.key = (uint16_t)(keybase + ((gbase + c) & kmask));
+                    pool[j] = e;
+                    head = (uint16_t)j;
+                  } else {
+                    *pool_ovf2 = 1;
                   }
                 }
               }
@@ -611,6 +667,8 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
         sweep_tiles(std::integral_constant<int, kModeMax>{});
         exchange(kModeMax);
         sweep_tiles(std::integral_constant<int, kModeCollect>{});
+        if (lane == 0) pool_used[warp] = my_used;
+        __syncwarp();
         // the listed scores join the histogram
         // (a thread's list is no longer than its warp's share of the pool: the walks are bounded)
         for (int e = head, left = warp_pool; e != kCandNil && left > 0; --left) {
