@@ -73,9 +73,9 @@ constexpr uint16_t kCandNil = 0xffff;
 
 // Shared memory: K stages, barriers, exchange buffers, bitmap staging, then the two Q tiles and
 // whatever is left of the budget.  The Q tiles are dead once Q~ sits in TMEM (before the first
-// append), so the candidate pool is their space plus that remainder (D = 128: ~142 KB, 18000
-// entries, 35 per thread on average).  Each row warp appends to its own sixteenth, so warps
-// do not contend for a counter.
+// append), so the candidate pool is their space plus that remainder (D = 128: ~110 KB, 14000
+// entries, 27 per thread on average).  Each row warp appends to its own sixteenth and hands
+// out its slots by a warp vote.
 constexpr int kSolveSmemBudget = 225 * 1024;
 
 template <int D>
