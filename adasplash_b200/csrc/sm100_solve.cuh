@@ -375,6 +375,14 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
 
     // One pass over the S tiles of this group's causal range.  Instantiated once per sweep
     // kind, so that the per-group code carries no mode tests and each sweep runs a compact loop.
+    // score j of group g (four consecutive scores) of a thread's 32: seven selects
+    auto pick_group = [](const float* v, int g, int j) -> float {
+      const bool b0 = (g & 1) != 0, b1 = (g & 2) != 0, b2 = (g & 4) != 0;
+      const float t0 = b0 ? v[4 + j] : v[j], t1 = b0 ? v[12 + j] : v[8 + j];
+      const float t2 = b0 ? v[20 + j] : v[16 + j], t3 = b0 ? v[28 + j] : v[24 + j];
+      const float u0 = b1 ? t1 : t0, u1 = b1 ? t3 : t2;
+      return b2 ? u1 : u0;
+    };
     auto sweep_tiles = [&](auto mode_c) {
       constexpr int mode = decltype(mode_c)::value;
       const int sweep = sweep_no++;
@@ -460,16 +468,10 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
               if (pend == 0u && mg != 0u) {
                 const int gsel = __ffs(mg) - 1;
                 mg &= mg - 1u;
-                switch (gsel) {
-                  case 0: z0 = v[0]; z1 = v[1]; z2 = v[2]; z3 = v[3]; break;
-                  case 1: z0 = v[4]; z1 = v[5]; z2 = v[6]; z3 = v[7]; break;
-                  case 2: z0 = v[8]; z1 = v[9]; z2 = v[10]; z3 = v[11]; break;
-                  case 3: z0 = v[12]; z1 = v[13]; z2 = v[14]; z3 = v[15]; break;
-                  case 4: z0 = v[16]; z1 = v[17]; z2 = v[18]; z3 = v[19]; break;
-                  case 5: z0 = v[20]; z1 = v[21]; z2 = v[22]; z3 = v[23]; break;
-                  case 6: z0 = v[24]; z1 = v[25]; z2 = v[26]; z3 = v[27]; break;
-                  default: z0 = v[28]; z1 = v[29]; z2 = v[30]; z3 = v[31]; break;
-                }
+                // (a select tree, not a switch: the lanes' groups differ, and a switch would run
+                // through up to eight cases one after the other)
+                z0 = pick_group(v, gsel, 0); z1 = pick_group(v, gsel, 1);
+                z2 = pick_group(v, gsel, 2); z3 = pick_group(v, gsel, 3);
                 gbase = gsel * 4;
                 pend = (z0 >= thr ? 1u : 0u) | (z1 >= thr ? 2u : 0u) | (z2 >= thr ? 4u : 0u) | (z3 >= thr ? 8u : 0u);
               }
@@ -529,16 +531,10 @@ solve_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
               if (pend == 0u && mg != 0u) {
                 const int gsel = __ffs(mg) - 1;
                 mg &= mg - 1u;
-                switch (gsel) {
-                  case 0: z0 = v[0]; z1 = v[1]; z2 = v[2]; z3 = v[3]; break;
-                  case 1: z0 = v[4]; z1 = v[5]; z2 = v[6]; z3 = v[7]; break;
-                  case 2: z0 = v[8]; z1 = v[9]; z2 = v[10]; z3 = v[11]; break;
-                  case 3: z0 = v[12]; z1 = v[13]; z2 = v[14]; z3 = v[15]; break;
-                  case 4: z0 = v[16]; z1 = v[17]; z2 = v[18]; z3 = v[19]; break;
-                  case 5: z0 = v[20]; z1 = v[21]; z2 = v[22]; z3 = v[23]; break;
-                  case 6: z0 = v[24]; z1 = v[25]; z2 = v[26]; z3 = v[27]; break;
-                  default: z0 = v[28]; z1 = v[29]; z2 = v[30]; z3 = v[31]; break;
-                }
+                // (a select tree, not a switch: the lanes' groups differ, and a switch would run
+                // through up to eight cases one after the other)
+                z0 = pick_group(v, gsel, 0); z1 = pick_group(v, gsel, 1);
+                z2 = pick_group(v, gsel, 2); z3 = pick_group(v, gsel, 3);
                 gbase = gsel * 4;
                 pend = (z0 >= thr_c ? 1u : 0u) | (z1 >= thr_c ? 2u : 0u) | (z2 >= thr_c ? 4u : 0u) | (z3 >= thr_c ? 8u : 0u);
               }
