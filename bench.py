@@ -71,8 +71,8 @@ NCU_DRAM_BYTES_PER_LAUNCH = {
     # headline workload: captured on the 32-head "mid" case (profiles/*_bf16_d128_mid.txt) and
     # scaled by 4 to the 128 heads of C3 (traffic is per head: every head streams its own q/k/v)
     ("c3", "solve"): 4 * (225.10e6 + 10.92e6),
-    ("c3", "solve_with_export"): 4 * (225.04e6 + 19.29e6),   # profiles/solve_export_bf16_d128_mid.txt
-    ("mid", "solve_with_export"): 225.04e6 + 19.29e6,
+    ("c3", "solve_with_export"): 4 * (226.04e6 + 18.88e6),   # profiles/solve_export_bf16_d128_mid.txt
+    ("mid", "solve_with_export"): 226.04e6 + 18.88e6,
     ("c3", "fwd"): 4 * (202.50e6 + 103.72e6),
     ("c3", "bwd_dq"): 4 * (270.74e6 + 52.86e6),
     ("c3", "bwd_dkv"): 4 * (270.71e6 + 108.38e6),
